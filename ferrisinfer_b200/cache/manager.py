@@ -1,0 +1,253 @@
+"""The cache manager: pages and block tables per request and page group, and fixed-size state slots.
+
+What the reference has: one cache per session, per-layer pages ``[page, kv heads, head dim]``
+with a per-layer table from logical block (position / page size) to page
+(crates/ferrisinfer-runtime/src/paged_kv.rs:131-172, 469-527, 605-613); everything is returned
+when the session is reset or dropped (crates/ferrisinfer-runtime/src/paged_kv.rs:529-549;
+crates/ferrisinfer-runtime/src/scheduler.rs:590-599); the per-request state of fixed size (position,
+last sample, RNG state) lives in the session (crates/ferrisinfer-runtime/src/session.rs:92-102).
+
+Here ONE manager serves all requests:
+
+* Mixers that keep keys and values declare a ``PagedKV`` need.  Run-order entries with the same
+  need (kv heads, head size, window) form a **page group**: the group has one pool of page ids and
+  one block table per request, and each entry of the group has key and value tensors of its own
+  ``[pages, kv heads, page size, head dim]`` addressed by the group's page ids.  Groups with
+  different needs (all keys / a window of them) have pools and tables of their own.
+* A request's pages are allocated before a step for every token the step brings (``extend``),
+  counted as held after it (``commit``), and given back when the request ends (``release``) or, in a
+  window group, as soon as the window has passed them (in ``commit``); a page that is given back is
+  the next one handed out.
+* Mixers with a ``FixedState`` need, and the engine itself (sampler state), get a tensor
+  ``[slots, *shape]``; a request holds one slot id from admission to release, and the slot's rows
+  are zeroed at admission.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+import torch
+
+from ..errors import CacheError, OutOfPages
+from ..parts.base import FixedState, LayerCache, PagedKV
+from .pages import PagePool
+
+NO_PAGE = -1
+
+
+@dataclass
+class PageGroup:
+    gid: int
+    need: PagedKV
+    members: list  # run-order entries whose k/v tensors this group's page ids address
+    page_size: int
+    pool: PagePool
+
+    @property
+    def window(self) -> Optional[int]:
+        return self.need.window
+
+
+@dataclass
+class RequestCache:
+    request_id: Any
+    slot: int
+    num_tokens: int = 0  # tokens whose keys/values (or state) are in the cache
+    tables: dict = field(default_factory=dict)  # gid -> list of page ids (NO_PAGE = hole)
+
+
+class CacheManager:
+    def __init__(self, needs: list, page_size: int, num_pages, max_requests: int,
+                 dtype: torch.dtype = torch.float32, device=None, extra_states: Optional[dict] = None):
+        """``needs[i]``: the cache need of run-order entry i (PagedKV, FixedState or None).
+        ``num_pages``: pages per group (an int for all groups, or a dict gid -> int).
+        ``device`` None: bookkeeping only (no tensors), as the CPU tests use it."""
+        if page_size <= 0:
+            raise CacheError(f"page size must be positive, not {page_size}")
+        if max_requests <= 0:
+            raise CacheError(f"at least one request slot is needed, not {max_requests}")
+        self.page_size = int(page_size)
+        self.max_requests = int(max_requests)
+        self.dtype, self.device = dtype, device
+        self.groups: list = []
+        self.layer_caches: list = [None] * len(needs)
+        self.state_tensors: dict = {}
+        by_need: dict = {}
+        for i, need in enumerate(needs):
+            if isinstance(need, PagedKV):
+                if need not in by_need:
+                    gid = len(self.groups)
+                    n = num_pages[gid] if isinstance(num_pages, dict) else num_pages
+                    self.groups.append(PageGroup(gid, need, [], self.page_size, PagePool(n)))
+                    by_need[need] = gid
+                g = self.groups[by_need[need]]
+                g.members.append(i)
+                cache = LayerCache(need=need, group=g.gid)
+                if device is not None:
+                    shape = (g.pool.num_pages, need.num_kv_heads, self.page_size, need.head_dim)
+                    cache.k = torch.zeros(shape, dtype=dtype, device=device)
+                    cache.v = torch.zeros(shape, dtype=dtype, device=device)
+                self.layer_caches[i] = cache
+            elif isinstance(need, FixedState):
+                cache = LayerCache(need=need)
+                if device is not None:
+                    cache.state = torch.zeros((self.max_requests, *need.shape), dtype=need.dtype, device=device)
+                self.layer_caches[i] = cache
+            elif need is not None:
+                raise CacheError(f"run-order entry {i} has an unknown cache need {need!r}")
+        for name, need in (extra_states or {}).items():
+            if device is not None:
+                self.state_tensors[name] = torch.zeros((self.max_requests, *need.shape), dtype=need.dtype,
+                                                       device=device)
+        self._free_slots = list(range(self.max_requests - 1, -1, -1))
+        self.requests: dict = {}
+
+    # ------------------------------------------------------------------ requests
+    def has(self, request_id) -> bool:
+        return request_id in self.requests
+
+    @property
+    def num_free_slots(self) -> int:
+        return len(self._free_slots)
+
+    def admit(self, request_id) -> RequestCache:
+        """Give ``request_id`` a state slot (zeroed) and empty block tables."""
+        if request_id in self.requests:
+            raise CacheError(f"request {request_id!r} is already admitted")
+        if not self._free_slots:
+            raise CacheError(f"all {self.max_requests} request slots are taken")
+        slot = self._free_slots.pop()
+        rc = RequestCache(request_id, slot, 0, {g.gid: [] for g in self.groups})
+        self.requests[request_id] = rc
+        for cache in self.layer_caches:
+            if cache is not None and cache.state is not None:
+                cache.state[slot].zero_()
+        for t in self.state_tensors.values():
+            t[slot].zero_()
+        return rc
+
+    def get(self, request_id) -> RequestCache:
+        try:
+            return self.requests[request_id]
+        except KeyError:
+            raise CacheError(f"request {request_id!r} is not admitted") from None
+
+    # --------------------------------------------------------------------- pages
+    def _first_needed_block(self, g: PageGroup, num_tokens: int) -> int:
+        """Lowest block that a query at position >= num_tokens can still read."""
+        if g.window is None:
+            return 0
+        return max(0, num_tokens - g.window + 1) // self.page_size
+
+    def pages_needed(self, request_id, new_total: int) -> dict:
+        """gid -> pages that ``extend(request_id, new_total)`` would take from the pool."""
+        rc = self.get(request_id)
+        out = {}
+        for g in self.groups:
+            blocks = -(-new_total // self.page_size)
+            table = rc.tables[g.gid]
+            first = self._first_needed_block(g, rc.num_tokens)
+            need = 0
+            for b in range(first, blocks):
+                if b >= len(table) or table[b] == NO_PAGE:
+                    need += 1
+            out[g.gid] = need
+        return out
+
+    def free_pages(self) -> dict:
+        return {g.gid: g.pool.num_free for g in self.groups}
+
+    def can_extend(self, request_id, new_total: int, reserve: Optional[dict] = None) -> bool:
+        """Whether the pools can cover ``new_total`` tokens of the request, leaving ``reserve``
+        (gid -> pages) for others."""
+        need = self.pages_needed(request_id, new_total)
+        return all(need[g.gid] + (reserve or {}).get(g.gid, 0) <= g.pool.num_free for g in self.groups)
+
+    def extend(self, request_id, new_total: int) -> None:
+        """Make every position below ``new_total`` that the next step can read or write addressable.
+        All groups or none: raises OutOfPages without taking a page if any pool is short."""
+        rc = self.get(request_id)
+        if new_total < rc.num_tokens:
+            raise CacheError(f"request {request_id!r} holds {rc.num_tokens} tokens; cannot extend to {new_total}")
+        need = self.pages_needed(request_id, new_total)
+        for g in self.groups:
+            if need[g.gid] > g.pool.num_free:
+                raise OutOfPages(
+                    f"request {request_id!r} needs {need[g.gid]} more pages in group {g.gid} "
+                    f"({g.pool.num_free} of {g.pool.num_pages} free)"
+                )
+        blocks = -(-new_total // self.page_size)
+        for g in self.groups:
+            table = rc.tables[g.gid]
+            first = self._first_needed_block(g, rc.num_tokens)
+            while len(table) < blocks:
+                table.append(NO_PAGE)
+            missing = [b for b in range(first, blocks) if table[b] == NO_PAGE]
+            for b, page in zip(missing, g.pool.alloc(len(missing))):
+                table[b] = page
+
+    def commit(self, request_id, new_total: int) -> int:
+        """The step that brought the request to ``new_total`` tokens is done: count them, and give
+        back the pages of window groups that no later query can read.  Returns pages freed."""
+        rc = self.get(request_id)
+        if new_total < rc.num_tokens:
+            raise CacheError(f"request {request_id!r} cannot shrink from {rc.num_tokens} to {new_total} tokens")
+        rc.num_tokens = new_total
+        freed = 0
+        for g in self.groups:
+            if g.window is None:
+                continue
+            table = rc.tables[g.gid]
+            for b in range(min(self._first_needed_block(g, new_total), len(table))):
+                if table[b] != NO_PAGE:
+                    g.pool.release(table[b])
+                    table[b] = NO_PAGE
+                    freed += 1
+        return freed
+
+    def release(self, request_id) -> int:
+        """The request is over (finished, cancelled or preempted): pages and slot go back."""
+        rc = self.requests.pop(request_id, None)
+        if rc is None:
+            raise CacheError(f"request {request_id!r} is released twice (or was never admitted)")
+        freed = 0
+        for g in self.groups:
+            for page in rc.tables[g.gid]:
+                if page != NO_PAGE and g.pool.release(page):
+                    freed += 1
+        self._free_slots.append(rc.slot)
+        return freed
+
+    # ----------------------------------------------------------------- addressing
+    def block_table(self, request_id, gid: int) -> list:
+        return self.get(request_id).tables[gid]
+
+    def slots_for(self, request_id, gid: int, start: int, count: int) -> list:
+        """Cache slot (page * page_size + offset) of positions start .. start + count - 1."""
+        table = self.get(request_id).tables[gid]
+        ps = self.page_size
+        out = []
+        for pos in range(start, start + count):
+            page = table[pos // ps]
+            if page == NO_PAGE:
+                raise CacheError(f"request {request_id!r}: position {pos} has no page in group {gid}")
+            out.append(page * ps + pos % ps)
+        return out
+
+    # ----------------------------------------------------------------- invariants
+    def check_invariants(self) -> None:
+        """No page lost, held twice without a count, or freed twice; no slot lost or held twice."""
+        for g in self.groups:
+            holders: dict = {}
+            for rc in self.requests.values():
+                for page in rc.tables[g.gid]:
+                    if page != NO_PAGE:
+                        holders[page] = holders.get(page, 0) + 1
+            g.pool.check(holders)
+        held = [rc.slot for rc in self.requests.values()]
+        if len(set(held)) != len(held):
+            raise CacheError("a state slot is held by two requests")
+        if set(held) & set(self._free_slots) or len(held) + len(self._free_slots) != self.max_requests:
+            raise CacheError("a state slot is lost or both free and held")

@@ -1,0 +1,82 @@
+// Shared helpers of the sm_100a kernels: element conversion, reductions, the C ABI's error reporting.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define FERRIS_API extern "C" __attribute__((visibility("default")))
+
+// Error codes of the C ABI. 0 = ok; > 0 = a cudaError_t; < 0 = the launcher refused its arguments
+// (ferris_last_error() gives the text).
+#define FERRIS_OK 0
+#define FERRIS_BAD_ARGUMENT (-1)
+#define FERRIS_TIMEOUT (-2)
+
+// Data types of the C ABI.
+#define FERRIS_F32 0
+#define FERRIS_BF16 1
+
+void ferris_set_error(const char* fmt, ...);
+
+#define FERRIS_REFUSE(...)            \
+    do {                              \
+        ferris_set_error(__VA_ARGS__); \
+        return FERRIS_BAD_ARGUMENT;   \
+    } while (0)
+
+#define FERRIS_LAUNCH_CHECK()                          \
+    do {                                               \
+        cudaError_t e_ = cudaGetLastError();           \
+        if (e_ != cudaSuccess) {                       \
+            ferris_set_error("%s", cudaGetErrorString(e_)); \
+            return (int)e_;                            \
+        }                                              \
+        return FERRIS_OK;                              \
+    } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) {
+    return v;
+}
+template <>
+__device__ __forceinline__ bf16 from_float<bf16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result. `scratch` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const int nwarps = (blockDim.x + 31) >> 5;
+    if (warp == 0) {
+        float w = lane < nwarps ? scratch[lane] : 0.0f;
+        w = warp_sum(w);
+        if (lane == 0) scratch[32] = w;
+    }
+    __syncthreads();
+    float r = scratch[32];
+    __syncthreads();
+    return r;
+}

@@ -1,0 +1,217 @@
+"""Python face of the CUDA kernels: one function per kernel, taking torch CUDA tensors.
+
+Every function checks dtypes, contiguity and sizes, then launches on the current
+CUDA stream through the C ABI of the compiled library.  Nothing here computes on
+the CPU or falls back to a library: a tensor that is not on a CUDA device, or a
+library that cannot be built or loaded, raises ``KernelError``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..errors import KernelError
+from . import build
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+_c_int = ctypes.c_int
+_c_float = ctypes.c_float
+_c_void_p = ctypes.c_void_p
+
+
+def _lib():
+    return build.load_library()
+
+
+def _dt(t: torch.Tensor, what: str) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"{what}: dtype {t.dtype} is not supported (float32 or bfloat16)") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> _c_void_p:
+    return _c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> _c_void_p:
+    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t: torch.Tensor, what: str, dtype=None, contiguous: bool = True) -> None:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{what} must be a CUDA tensor (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what} must be {dtype}, found {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{what} must be contiguous")
+
+
+def _rows(t: torch.Tensor, what: str) -> tuple[int, int, int]:
+    """(rows, cols, row stride) of a 2-D tensor whose rows are contiguous."""
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{what} must be a CUDA tensor (there is no CPU path)")
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise KernelError(f"{what} must be 2-D with contiguous rows, found shape {tuple(t.shape)} strides {t.stride()}")
+    return t.shape[0], t.shape[1], t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        msg = _lib().ferris_last_error().decode("utf-8", "replace")
+        kind = "refused its arguments" if code < 0 else f"failed (CUDA error {code})"
+        raise KernelError(f"{what} {kind}: {msg}")
+
+
+def require_device() -> None:
+    """Raise unless a CUDA device of compute capability 10.x is current and the library loads."""
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device is available; this engine has no CPU path")
+    arch = _lib().ferris_device_arch()
+    if arch < 0:
+        raise KernelError("cannot query the CUDA device: " + _lib().ferris_last_error().decode())
+    if arch // 10 != 10:
+        raise KernelError(f"the kernels are built for sm_100a; the current device is sm_{arch}")
+
+
+# ------------------------------------------------------------------------------------------
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: Optional[torch.Tensor] = None):
+    """out[t, :] = table[ids[t], :] as fp32.  ids int32 [T]; out fp32 [T, H]."""
+    _need(table, "embedding table")
+    _need(ids, "token ids", torch.int32)
+    _need(out, "embedding output", torch.float32)
+    T, H = out.shape
+    if table.dim() != 2 or table.shape[1] != H or ids.numel() != T:
+        raise KernelError(f"embed_gather: table {tuple(table.shape)}, ids {tuple(ids.shape)}, out {tuple(out.shape)}")
+    _check(
+        _lib().ferris_embed_gather(_ptr(table), _dt(table, "embedding table"), _ptr(ids), _ptr(out), _c_int(T),
+                                   _c_int(H), _c_int(table.shape[0]), _ptr(status), _stream()),
+        "embed_gather",
+    )
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            row_index: Optional[torch.Tensor] = None):
+    """out[i] = rmsnorm(x[row_index[i]] or x[i]) * weight.  x fp32 [T, H]; weight fp32 [H]."""
+    _need(x, "rmsnorm input", torch.float32)
+    _need(weight, "rmsnorm weight", torch.float32)
+    _need(out, "rmsnorm output")
+    rows, H = out.shape
+    if x.shape[1] != H or weight.numel() != H:
+        raise KernelError(f"rmsnorm: x {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    if row_index is not None:
+        _need(row_index, "rmsnorm row index", torch.int32)
+        if row_index.numel() != rows:
+            raise KernelError("rmsnorm: one row index per output row is needed")
+    elif x.shape[0] != rows:
+        raise KernelError("rmsnorm: input and output row counts differ")
+    _check(
+        _lib().ferris_rmsnorm(_ptr(x), _ptr(weight), _ptr(row_index), _ptr(out), _dt(out, "rmsnorm output"),
+                              _c_int(rows), _c_int(H), _c_float(eps), _stream()),
+        "rmsnorm",
+    )
+
+
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+              accumulate: bool = False):
+    """out[t, n] (+)= sum_k x[t, k] w[n, k] + bias[n] with fp32 FMAs on the CUDA cores."""
+    M, K, ldx = _rows(x, "gemm input")
+    N, K2, ldw = _rows(w, "gemm weight")
+    M2, N2, ldo = _rows(out, "gemm output")
+    if K != K2 or M != M2 or N != N2 or x.dtype != w.dtype:
+        raise KernelError(f"gemm: x {tuple(x.shape)} {x.dtype}, w {tuple(w.shape)} {w.dtype}, out {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, "gemm bias", torch.float32)
+        if bias.numel() != N:
+            raise KernelError("gemm: bias length differs from the output width")
+    _check(
+        _lib().ferris_gemm_simt(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _dt(x, "gemm input"), _dt(out, "gemm output"),
+                                _c_int(M), _c_int(N), _c_int(K), _c_int(ldx), _c_int(ldw), _c_int(ldo),
+                                _c_int(1 if accumulate else 0), _stream()),
+        "gemm",
+    )
+
+
+def gemm(x, w, bias, out, accumulate: bool = False):
+    """The matrix product of the model: picks the tensor-core kernel for bf16 shapes it takes,
+    the CUDA-core kernel for everything else (all of the 32-bit path)."""
+    gemm_simt(x, w, bias, out, accumulate)
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor):
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    _need(gate_up, "swiglu input")
+    _need(out, "swiglu output", gate_up.dtype)
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I):
+        raise KernelError(f"swiglu: input {tuple(gate_up.shape)}, output {tuple(out.shape)}")
+    _check(_lib().ferris_swiglu(_ptr(gate_up), _ptr(out), _dt(out, "swiglu"), _c_int(T), _c_int(I), _stream()), "swiglu")
+
+
+def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                     slot_mapping: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                     v_cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
+                     rotary_dim: int, page_size: int, write_kv: bool = True):
+    """Rotate q and k of ``qkv`` [T, (nh + 2 nkv) d] by position; store k and v into the paged cache."""
+    _need(qkv, "qkv")
+    _need(positions, "positions", torch.int32)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim or positions.numel() != T:
+        raise KernelError(f"rope_cache_write: qkv {tuple(qkv.shape)} for {num_heads}+2x{num_kv_heads} heads of {head_dim}")
+    if rotary_dim > 0:
+        _need(inv_freq, "rotary frequencies", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("rope_cache_write: one frequency per rotated pair is needed")
+    if write_kv:
+        _need(slot_mapping, "slot mapping", torch.int32)
+        _need(k_cache, "key cache", qkv.dtype)
+        _need(v_cache, "value cache", qkv.dtype)
+        if slot_mapping.numel() != T or k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) \
+                or v_cache.shape != k_cache.shape:
+            raise KernelError(f"rope_cache_write: cache {tuple(k_cache.shape)} does not fit "
+                              f"[pages, {num_kv_heads}, {page_size}, {head_dim}]")
+    _check(
+        _lib().ferris_rope_cache_write(_ptr(qkv), _dt(qkv, "qkv"), _ptr(positions), _ptr(inv_freq),
+                                       _ptr(slot_mapping if write_kv else None), _ptr(k_cache if write_kv else None),
+                                       _ptr(v_cache if write_kv else None), _c_int(T), _c_int(num_heads),
+                                       _c_int(num_kv_heads), _c_int(head_dim), _c_int(rotary_dim), _c_int(page_size),
+                                       _c_int(1 if write_kv else 0), _stream()),
+        "rope_cache_write",
+    )
+
+
+def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                         block_tables: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
+                         num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float):
+    """General attention over the paged cache; q is read from the first nh*d columns of ``qkv``."""
+    T, _, ldq = _rows(qkv, "attention queries")
+    T2, width, ldo = _rows(out, "attention output")
+    _need(k_cache, "key cache", qkv.dtype)
+    _need(v_cache, "value cache", qkv.dtype)
+    _need(block_tables, "block tables", torch.int32)
+    _need(token_seq, "token-to-request map", torch.int32)
+    _need(positions, "positions", torch.int32)
+    if T != T2 or width != num_heads * head_dim or out.dtype != qkv.dtype or qkv.shape[1] < num_heads * head_dim:
+        raise KernelError(f"attention: q {tuple(qkv.shape)}, out {tuple(out.shape)}")
+    if k_cache.dim() != 4 or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim or block_tables.dim() != 2:
+        raise KernelError(f"attention: cache {tuple(k_cache.shape)}, tables {tuple(block_tables.shape)}")
+    _check(
+        _lib().ferris_paged_attention_simt(_ptr(qkv), _c_int(ldq), _ptr(out), _c_int(ldo), _ptr(k_cache), _ptr(v_cache),
+                                           _dt(qkv, "attention"), _ptr(block_tables), _c_int(block_tables.shape[1]),
+                                           _ptr(token_seq), _ptr(positions), _c_int(T), _c_int(num_heads),
+                                           _c_int(num_kv_heads), _c_int(head_dim), _c_int(k_cache.shape[2]),
+                                           _c_int(window or 0), _c_float(scale), _stream()),
+        "paged attention",
+    )
+
+
+def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale):
+    """Attention of the step's tokens over the paged cache (their own keys are in it already).
+    ``ctx`` is the step context (token-to-request map, positions, request lengths)."""
+    paged_attention_simt(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
+                         num_kv_heads, head_dim, window, scale)

@@ -1,0 +1,346 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, random-weight Qwen2.5-0.5B sizes, bfloat16.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8 and context 4,096, K decode steps
+timed on the device with CUDA events (step function + sampling kernel; token ids preset on the host).
+``e2e``: the same through ``Engine.step()``: host token ids in (pinned metadata, one copy per step) and
+sampled tokens out (one read per step).  ``prefill``: one 2,048-token prompt.  ``roofline``: bytes a
+decode step must read (every weight once, the cache of the live requests) over its time, against the
+measured copy bandwidth.  ``points``: decode at batch 1 and 64.  Peaks come from MEASURED_PEAKS.json
+when present, else the fallback figures of this pool.
+
+The weights (1 GB) and the cache are far larger than the 126 MB L2, so every step reads them from
+HBM; no explicit L2 flush is needed between timed steps.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# layer sizes of BASELINE.json configs[2] (Qwen2.5-0.5B)
+QWEN25_05B = {
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 151936, "hidden_size": 896, "intermediate_size": 4864, "num_hidden_layers": 24,
+    "num_attention_heads": 14, "num_key_value_heads": 2, "max_position_embeddings": 32768,
+    "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "hidden_act": "silu", "tie_word_embeddings": True,
+    "use_sliding_window": False, "sliding_window": None, "max_window_layers": 24,
+}
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        out = dict(FALLBACK_PEAKS)
+        for k in out:
+            if isinstance(d.get(k), (int, float)) and d[k] > 0:
+                out[k] = float(d[k])
+        return out, "measured"
+    except (OSError, ValueError):
+        return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while the timed regions run."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200", "-i", "0"],
+                stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        try:
+            os.unlink(self.file.name)
+        except OSError:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons)}
+
+
+def model_numbers(cfg: dict) -> dict:
+    H, I, L, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"], cfg["vocab_size"]
+    nh, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    d = cfg.get("head_dim") or H // nh
+    Q, KV = nh * d, nkv * d
+    layer_matrix = H * (Q + 2 * KV) + Q * H + 3 * H * I
+    layer_vectors = (Q + 2 * KV) + 2 * H
+    head = V * H
+    untied = 0 if cfg.get("tie_word_embeddings") else V * H
+    return {"layer_matrix": layer_matrix, "layer_vectors": layer_vectors, "head": head, "untied_embedding": untied,
+            "kv_bytes_per_token": L * 2 * KV * 2, "d": d, "nh": nh, "L": L, "H": H, "V": V}
+
+
+def decode_bytes(cfg, batch, context) -> float:
+    n = model_numbers(cfg)
+    weights = (n["L"] * (n["layer_matrix"] * 2 + n["layer_vectors"] * 4) + n["head"] * 2 + n["H"] * 4)
+    return float(weights + batch * context * n["kv_bytes_per_token"])
+
+
+def prefill_flops(cfg, T) -> float:
+    n = model_numbers(cfg)
+    linear = 2.0 * T * n["L"] * n["layer_matrix"] + 2.0 * n["head"]
+    attention = n["L"] * 2.0 * T * T * n["d"] * n["nh"]
+    return linear + attention
+
+
+def build_engine(cfg, batch, context, extra_tokens=0):
+    from ferrisinfer_b200 import SchedulerConfig
+    from ferrisinfer_b200.engine.engine import Engine
+
+    page = 16
+    per_request = -(-(context + 8) // page)
+    sched = SchedulerConfig(max_batch_size=batch, max_prefill_chunk_tokens=2048,
+                            max_prefill_batch_tokens=max(2048, batch), max_sequence_length=context + 8,
+                            max_generated_tokens=context)
+    return Engine(config=cfg, seed=0, dtype="bfloat16", page_size=page, init_device="cuda",
+                  num_pages=batch * per_request + -(-extra_tokens // page) + 4, scheduler=sched)
+
+
+def fill_cache(engine, batch, context):
+    """Give ``batch`` requests ``context`` tokens of cache without running the model: pages are taken
+    from the pool as a real prompt would take them and filled with small random keys and values."""
+    import torch
+
+    cache = engine.runner.cache
+    for lc in cache.layer_caches:
+        if lc is not None and lc.k is not None:
+            lc.k.normal_(0.0, 0.5)
+            lc.v.normal_(0.0, 0.5)
+    ids = []
+    for b in range(batch):
+        rid = f"bench{b}"
+        cache.admit(rid)
+        cache.extend(rid, context)
+        cache.commit(rid, context)
+        ids.append(rid)
+    return ids
+
+
+def time_decode(engine, batch, context, steps, warmup):
+    """K decode steps (step function + greedy sampling kernel) timed with CUDA events."""
+    import torch
+
+    from ferrisinfer_b200.engine.runner import StepEntry
+    from ferrisinfer_b200.kernels import ops
+
+    start_ctx = context - steps - warmup - 1
+    ids = fill_cache(engine, batch, start_ctx)
+    vocab = engine.model.vocab_size
+    gen = torch.Generator().manual_seed(1)
+    tokens = torch.randint(0, vocab, (steps + warmup, batch), generator=gen).tolist()
+    out_tok = torch.empty(batch, dtype=torch.int32, device=engine.device)
+
+    def one(i):
+        logits = engine.runner.step([StepEntry(rid, [tokens[i][b]], [0]) for b, rid in enumerate(ids)])
+        ops.sample(logits, out_tok)
+
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    launches0 = ops.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    launches = ops.launch_count() - launches0
+    for rid in ids:
+        engine.runner.free_request(rid)
+    return ms, launches
+
+
+def time_prefill(engine, tokens, warmup=2, iters=3):
+    import torch
+
+    from ferrisinfer_b200.engine.runner import StepEntry
+
+    vocab = engine.model.vocab_size
+    gen = torch.Generator().manual_seed(2)
+    times = []
+    for i in range(warmup + iters):
+        prompt = torch.randint(0, vocab, (tokens,), generator=gen).tolist()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        engine.runner.step([StepEntry("prefill", prompt, [tokens - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        engine.runner.free_request("prefill")
+        if i >= warmup:
+            times.append(e0.elapsed_time(e1))
+    return statistics.median(times)
+
+
+def time_e2e(engine, batch, context, steps, warmup):
+    """The same decode through Engine.step(): token ids come from and return to the host every step."""
+    import torch
+
+    from ferrisinfer_b200 import SamplingParams
+    from ferrisinfer_b200.engine.scheduler import Phase
+
+    start_ctx = context - steps - warmup - 2
+    ids = fill_cache(engine, batch, start_ctx - 1)
+    sched = engine.scheduler
+    # hand the pre-filled requests to the scheduler as running, decoding sequences
+    for b, rid in enumerate(ids):
+        seq = sched.submit(rid, [(b * 7 + j) % engine.model.vocab_size for j in range(start_ctx)],
+                           SamplingParams.greedy(max_new_tokens=steps + warmup + 1))
+        sched.waiting.remove(seq)
+        seq.phase, seq.num_computed, seq.slot = Phase.PREFILL, start_ctx - 1, engine.runner.cache.get(rid).slot
+        sched.running.append(seq)
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    n = 0
+    for _ in range(steps):
+        n += sum(1 for o in engine.step() if o.token is not None)
+    e1.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    ms = max(e0.elapsed_time(e1), wall * 1e3) / steps
+    for rid in ids:
+        sched.cancel(rid)
+    return ms, n, engine.runner.last_h2d_bytes, 16 * batch
+
+
+def reference_arm(args) -> int:
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "the reference is a Rust workspace (no Python package, no GPU kernel); this image has no "
+                       "cargo or rustc, so it can be neither installed with pip nor built",
+    }))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (nothing here spans GPUs)")
+        return 2
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+
+    cfg = dict(QWEN25_05B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+        cfg["max_window_layers"] = args.layers
+    peaks, peak_source = load_peaks()
+    clocks = ClockSampler()
+
+    engine = build_engine(cfg, args.batch, CONTEXT, extra_tokens=PREFILL_TOKENS)
+    clocks.start()
+    ms, launches = time_decode(engine, args.batch, CONTEXT, args.steps, args.warmup)
+    prefill_ms = time_prefill(engine, PREFILL_TOKENS)
+    e2e_ms, e2e_tokens, h2d, d2h = time_e2e(engine, args.batch, CONTEXT, args.steps, args.warmup)
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            del engine
+            torch.cuda.empty_cache()
+            engine = build_engine(cfg, b, CONTEXT)
+            pms, _ = time_decode(engine, b, CONTEXT, max(8, args.steps // 2), args.warmup)
+            points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+    clock_record = clocks.stop()
+
+    value = args.batch / ms * 1e3
+    bytes_step = decode_bytes(cfg, args.batch, CONTEXT)
+    achieved = bytes_step / (ms * 1e-3) / 1e9
+    flops = prefill_flops(cfg, PREFILL_TOKENS)
+    n = model_numbers(cfg)
+    line = {
+        "metric": "decode tok/s at batch 8, context 4096 (Qwen2.5-0.5B sizes, random weights)",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random-init weights)", "impl": "ours",
+        "config": {
+            "model": "Qwen2.5-0.5B sizes", "layers": cfg["num_hidden_layers"], "layers_of_model": full_layers,
+            "hidden": n["H"], "heads": n["nh"], "kv_heads": cfg["num_key_value_heads"], "head_dim": n["d"],
+            "intermediate": cfg["intermediate_size"], "vocab": n["V"], "tied": True, "global_batch": args.batch,
+            "seq_len": CONTEXT, "kv_page": 16, "parallelism": "single GPU",
+            "l2": "weights and cache exceed L2; no flush", "peaks": peak_source,
+        },
+        "e2e": {"value": round(e2e_tokens / args.steps / e2e_ms * 1e3, 1), "unit": "tok/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4)},
+        "gpu_launches": launches,
+        "prefill": {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
+                    "ms": round(prefill_ms, 3),
+                    "frac": round(flops / (prefill_ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clock_record,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,343 @@
+// Sampling from fp32 logits: greedy, and temperature with top-k / top-p, one block per row.
+//
+// The reference's sampler (crates/ferrisinfer-runtime/src/sampler.rs:77-241):
+//   greedy if temperature <= 0, top_k == 1 or top_p <= 0: argmax, probability 1 / sum exp(l - max);
+//   else keep the top_k largest logits, sort them descending, w = exp(l/T - max/T) with
+//   T = max(T, f32 epsilon), keep the shortest prefix whose mass reaches top_p * total, draw
+//   u in [0,1) from xorshift64*, threshold = u * retained_total, walk the prefix subtracting
+//   weights until the threshold is <= 0; probability = w / retained_total.
+//
+// A walk over sorted candidates is a weighted quantile: the chosen token is the one at which the
+// mass of everything before it (in descending order) first reaches the threshold.  This kernel
+// finds such quantiles without sorting, by descending a radix tree over 64-bit keys
+// (order-preserving logit bits, then the inverted index, so that keys are unique and ties go to
+// the lower index).  Masses are 2^-40 fixed-point integers: sums are exact and independent of the
+// order of the atomic additions, so the result is deterministic.  top-k (a count quantile), top-p
+// and the final draw (mass quantiles) share the first level of the tree.
+//
+// RNG: one xorshift64* state per request slot, advanced once per sampled (non-greedy) token
+// (crates/ferrisinfer-runtime/src/sampler.rs:50-75), so a request's draws do not depend on what
+// else is in the batch.
+#include <float.h>
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 1024;
+constexpr int BINS = 2048;
+constexpr int NUM_DIGITS = 6;
+__device__ __constant__ int kShift[NUM_DIGITS] = {53, 42, 31, 20, 9, 0};
+__device__ __constant__ int kWidth[NUM_DIGITS] = {11, 11, 11, 11, 11, 9};
+
+typedef unsigned long long u64;
+typedef unsigned int u32;
+
+__device__ __forceinline__ u64 make_key(float logit, int index) {
+    u32 u = __float_as_uint(logit);
+    u32 k = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+    if (logit != logit) k = 0;  // NaN sorts last
+    return ((u64)k << 32) | (u64)(0xFFFFFFFFu - (u32)index);
+}
+
+struct Shared {
+    u32 count[BINS];
+    u64 mass[BINS];
+    u64 warp_count[32];
+    u64 warp_mass[32];
+    u64 red[32];
+    // results of a scan / find
+    int chosen_bin;
+    u32 chosen_count;
+    u64 excl_count, excl_mass;
+    u64 found_key, found_mass;
+    // level-0 histogram kept for the later descents
+    u32 count0[BINS];
+    u64 mass0[BINS];
+};
+
+struct RowArgs {
+    const float* row;
+    int V;
+    float inv_t_max;  // max / T
+    float T;
+};
+
+__device__ __forceinline__ u64 weight_fixed(const RowArgs& a, float logit) {
+    const float w = expf(logit / a.T - a.inv_t_max);
+    return (u64)((double)w * 1099511627776.0);  // 2^40; w <= 1
+}
+
+// Histogram of digit d over the elements whose higher digits equal those of `prefix`.
+__device__ void hist_pass(Shared& s, const RowArgs& a, u64 prefix, int d) {
+    for (int b = threadIdx.x; b < BINS; b += THREADS) {
+        s.count[b] = 0;
+        s.mass[b] = 0;
+    }
+    __syncthreads();
+    const int shift = kShift[d];
+    const u32 mask = (1u << kWidth[d]) - 1u;
+    const int up = d > 0 ? kShift[d - 1] : 64;
+    // a small per-thread cache of buckets, so that clustered logits do not serialise on one counter
+    int cb0 = -1, cb1 = -1, cb2 = -1, cb3 = -1;
+    u32 cc0 = 0, cc1 = 0, cc2 = 0, cc3 = 0;
+    u64 cm0 = 0, cm1 = 0, cm2 = 0, cm3 = 0;
+    int victim = 0;
+    for (int i = threadIdx.x; i < a.V; i += THREADS) {
+        const float l = a.row[i];
+        const u64 key = make_key(l, i);
+        if (d > 0 && (key >> up) != (prefix >> up)) continue;
+        const int b = (int)((key >> shift) & mask);
+        const u64 m = weight_fixed(a, l);
+        if (b == cb0) { cc0++; cm0 += m; }
+        else if (b == cb1) { cc1++; cm1 += m; }
+        else if (b == cb2) { cc2++; cm2 += m; }
+        else if (b == cb3) { cc3++; cm3 += m; }
+        else {
+            int ob; u32 oc; u64 om;
+            if (victim == 0) { ob = cb0; oc = cc0; om = cm0; cb0 = b; cc0 = 1; cm0 = m; }
+            else if (victim == 1) { ob = cb1; oc = cc1; om = cm1; cb1 = b; cc1 = 1; cm1 = m; }
+            else if (victim == 2) { ob = cb2; oc = cc2; om = cm2; cb2 = b; cc2 = 1; cm2 = m; }
+            else { ob = cb3; oc = cc3; om = cm3; cb3 = b; cc3 = 1; cm3 = m; }
+            victim = (victim + 1) & 3;
+            if (ob >= 0) {
+                atomicAdd(&s.count[ob], oc);
+                atomicAdd(&s.mass[ob], om);
+            }
+        }
+    }
+    if (cb0 >= 0) { atomicAdd(&s.count[cb0], cc0); atomicAdd(&s.mass[cb0], cm0); }
+    if (cb1 >= 0) { atomicAdd(&s.count[cb1], cc1); atomicAdd(&s.mass[cb1], cm1); }
+    if (cb2 >= 0) { atomicAdd(&s.count[cb2], cc2); atomicAdd(&s.mass[cb2], cm2); }
+    if (cb3 >= 0) { atomicAdd(&s.count[cb3], cc3); atomicAdd(&s.mass[cb3], cm3); }
+    __syncthreads();
+}
+
+// Scan the histogram from the highest bin down; pick the bin in which the running total
+// (of counts if by_count, else of masses) first reaches `target`.
+__device__ void scan_pick(Shared& s, const u32* count, const u64* mass, bool by_count, u64 target) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // thread t owns descending bins 2t, 2t+1 -> actual bins BINS-1-2t, BINS-2-2t
+    const int b0 = BINS - 1 - 2 * threadIdx.x, b1 = b0 - 1;
+    const u64 c0 = count[b0], c1 = count[b1];
+    const u64 m0 = mass[b0], m1 = mass[b1];
+    u64 pc = c0 + c1, pm = m0 + m1;  // inclusive scan within the warp
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const u64 tc = __shfl_up_sync(0xffffffffu, pc, o);
+        const u64 tm = __shfl_up_sync(0xffffffffu, pm, o);
+        if (lane >= o) { pc += tc; pm += tm; }
+    }
+    if (lane == 31) { s.warp_count[warp] = pc; s.warp_mass[warp] = pm; }
+    if (threadIdx.x == 0) { s.chosen_bin = -1; }
+    __syncthreads();
+    u64 oc = 0, om = 0;
+    for (int w = 0; w < warp; ++w) { oc += s.warp_count[w]; om += s.warp_mass[w]; }
+    const u64 incl_c = oc + pc, incl_m = om + pm;
+    const u64 excl_c = incl_c - (c0 + c1), excl_m = incl_m - (m0 + m1);
+    // first bin of the pair
+    {
+        const u64 before = by_count ? excl_c : excl_m;
+        const u64 after = by_count ? excl_c + c0 : excl_m + m0;
+        if (c0 > 0 && before < target && target <= after) {
+            s.chosen_bin = b0; s.chosen_count = (u32)c0; s.excl_count = excl_c; s.excl_mass = excl_m;
+        }
+    }
+    {
+        const u64 before = by_count ? excl_c + c0 : excl_m + m0;
+        const u64 after = by_count ? incl_c : incl_m;
+        if (c1 > 0 && before < target && target <= after) {
+            s.chosen_bin = b1; s.chosen_count = (u32)c1; s.excl_count = excl_c + c0; s.excl_mass = excl_m + m0;
+        }
+    }
+    __syncthreads();
+    if (s.chosen_bin < 0) {
+        // the target lies beyond the total (only possible through the caller's rounding): take the
+        // lowest bin that holds anything
+        if (threadIdx.x == 0) {
+            u64 ec = 0, em = 0;
+            int last = -1;
+            for (int b = BINS - 1; b >= 0; --b)
+                if (count[b]) last = b;
+            for (int b = BINS - 1; b > last; --b) { ec += count[b]; em += mass[b]; }
+            s.chosen_bin = last; s.chosen_count = count[last]; s.excl_count = ec; s.excl_mass = em;
+        }
+        __syncthreads();
+    }
+}
+
+// The only element whose digits 0..d equal those of `prefix`.
+__device__ void find_unique(Shared& s, const RowArgs& a, u64 prefix, int d) {
+    const int shift = kShift[d];
+    for (int i = threadIdx.x; i < a.V; i += THREADS) {
+        const float l = a.row[i];
+        const u64 key = make_key(l, i);
+        if ((key >> shift) == (prefix >> shift)) {
+            s.found_key = key;
+            s.found_mass = weight_fixed(a, l);
+        }
+    }
+    __syncthreads();
+}
+
+struct Quantile {
+    u64 key;       // the element at which the running total first reaches the target
+    u64 mass_ge;   // mass of all elements with key >= key
+    u64 mass_self; // its own mass
+};
+
+// Descend the tree.  Level 0 reads the kept histogram (count0 / mass0).
+__device__ Quantile descend(Shared& s, const RowArgs& a, bool by_count, u64 target) {
+    u64 prefix = 0, cum_count = 0, cum_mass = 0;
+    Quantile q;
+    for (int d = 0; d < NUM_DIGITS; ++d) {
+        if (d == 0) {
+            scan_pick(s, s.count0, s.mass0, by_count, target);
+        } else {
+            hist_pass(s, a, prefix, d);
+            scan_pick(s, s.count, s.mass, by_count, target);
+        }
+        const int bin = s.chosen_bin;
+        const u32 cnt = s.chosen_count;
+        const u64 ec = s.excl_count, em = s.excl_mass;
+        __syncthreads();
+        cum_count += ec;
+        cum_mass += em;
+        target -= by_count ? ec : em;
+        prefix |= (u64)bin << kShift[d];
+        if (cnt == 1 || d == NUM_DIGITS - 1) {
+            find_unique(s, a, prefix, d);
+            q.key = s.found_key;
+            q.mass_self = s.found_mass;
+            q.mass_ge = cum_mass + s.found_mass;
+            __syncthreads();
+            return q;
+        }
+    }
+    return q;  // not reached
+}
+
+__device__ __forceinline__ u64 block_max_u64(u64 v, u64* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const u64 t = __shfl_xor_sync(0xffffffffu, v, o);
+        v = t > v ? t : v;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    u64 r = red[0];
+    for (int w = 1; w < THREADS / 32; ++w) r = red[w] > r ? red[w] : r;
+    __syncthreads();
+    return r;
+}
+
+__global__ void __launch_bounds__(THREADS)
+    sample_kernel(const float* __restrict__ logits, int ldl, int V, const float* __restrict__ temperature,
+                  const int* __restrict__ top_k, const float* __restrict__ top_p, const int* __restrict__ slots,
+                  u64* __restrict__ rng_states, int* __restrict__ out_token, float* __restrict__ out_prob) {
+    extern __shared__ __align__(16) unsigned char raw[];
+    Shared& s = *reinterpret_cast<Shared*>(raw);
+    __shared__ float fscratch[33];
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * ldl;
+    const float T = temperature ? temperature[r] : 0.0f;
+    const int k = top_k ? top_k[r] : 0;
+    const float p = top_p ? top_p[r] : 1.0f;
+    const bool greedy = !(T > 0.0f) || k == 1 || !(p > 0.0f);
+
+    // argmax (lowest index among equal maxima) through the key order
+    u64 best = 0;
+    for (int i = threadIdx.x; i < V; i += THREADS) {
+        const u64 key = make_key(row[i], i);
+        best = key > best ? key : best;
+    }
+    best = block_max_u64(best, s.red);
+    const int best_index = (int)(0xFFFFFFFFu - (u32)(best & 0xFFFFFFFFu));
+    const float max_logit = row[best_index];
+
+    if (greedy) {
+        float denom = 0.0f;
+        for (int i = threadIdx.x; i < V; i += THREADS) denom += expf(row[i] - max_logit);
+        denom = block_sum(denom, fscratch);
+        if (threadIdx.x == 0) {
+            out_token[r] = best_index;
+            if (out_prob) out_prob[r] = 1.0f / denom;
+        }
+        return;
+    }
+
+    RowArgs a;
+    a.row = row;
+    a.V = V;
+    a.T = fmaxf(T, FLT_EPSILON);
+    a.inv_t_max = max_logit / a.T;
+
+    hist_pass(s, a, 0, 0);
+    for (int b = threadIdx.x; b < BINS; b += THREADS) {
+        s.count0[b] = s.count[b];
+        s.mass0[b] = s.mass[b];
+    }
+    __syncthreads();
+
+    const int k_eff = (k <= 0 || k > V) ? V : k;
+    // mass of the top-k set: the count quantile at k
+    Quantile qk = descend(s, a, true, (u64)k_eff);
+    const u64 total_k = qk.mass_ge;
+    u64 retained = total_k;
+    if (p < 1.0f) {
+        u64 cutoff = (u64)((double)total_k * (double)p);
+        if (cutoff < 1) cutoff = 1;
+        if (cutoff > total_k) cutoff = total_k;
+        Quantile qp = descend(s, a, false, cutoff);
+        retained = qp.mass_ge;
+    }
+    // one uniform draw from the request's own generator
+    __shared__ float u_shared;
+    if (threadIdx.x == 0) {
+        u64* st = rng_states + slots[r];
+        u64 x = *st;
+        if (x == 0) x = 0x9e3779b97f4a7c15ull;
+        x ^= x >> 12;
+        x ^= x << 25;
+        x ^= x >> 27;
+        *st = x;
+        const u64 value = x * 0x2545F4914F6CDD1Dull;
+        u_shared = (float)(u32)(value >> 40) / 16777216.0f;
+    }
+    __syncthreads();
+    u64 threshold = (u64)((double)u_shared * (double)retained);
+    if (threshold < 1) threshold = 1;
+    if (threshold > retained) threshold = retained;
+    Quantile qs = descend(s, a, false, threshold);
+    if (threadIdx.x == 0) {
+        out_token[r] = (int)(0xFFFFFFFFu - (u32)(qs.key & 0xFFFFFFFFu));
+        if (out_prob) out_prob[r] = (float)((double)qs.mass_self / (double)retained);
+    }
+}
+
+}  // namespace
+
+// logits fp32 [rows, V] (row stride ldl).  temperature / top_k / top_p: per row, or null for greedy.
+// slots[r] indexes rng_states (one u64 per request slot; 0 stands for the reference's default seed).
+FERRIS_API int ferris_sample(const float* logits, int ldl, int rows, int V, const float* temperature, const int* top_k,
+                             const float* top_p, const int* slots, unsigned long long* rng_states, int* out_token,
+                             float* out_prob, void* stream) {
+    if (rows <= 0) return FERRIS_OK;
+    if (V <= 0 || ldl < V) FERRIS_REFUSE("sample: vocabulary %d, row stride %d", V, ldl);
+    if (temperature && (!slots || !rng_states)) FERRIS_REFUSE("sample: sampling with a temperature needs generator states");
+    static bool configured = false;
+    const size_t smem = sizeof(Shared);
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            ferris_set_error("sample: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        configured = true;
+    }
+    sample_kernel<<<rows, THREADS, smem, (cudaStream_t)stream>>>(logits, ldl, V, temperature, top_k, top_p, slots,
+                                                              rng_states, out_token, out_prob);
+    FERRIS_LAUNCH_CHECK();
+}

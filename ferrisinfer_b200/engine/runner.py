@@ -53,6 +53,8 @@ class ModelRunner:
                                   device=self.device, extra_states=extra_states)
         self.workspace = Workspace(self.device)
         self.steps_run = 0
+        self.last_h2d_bytes = 0
+        self._pinned = None
 
     # ------------------------------------------------------------------ requests
     def add_request(self, request_id) -> int:
@@ -85,6 +87,25 @@ class ModelRunner:
             self.cache.commit(e.request_id, s.start_pos + s.q_len)
         self.steps_run += 1
         return logits
+
+    def _upload(self, pieces) -> torch.Tensor:
+        """One copy of the step's int32 metadata, host (pinned) to device."""
+        total = sum(p.size for p in pieces)
+        if self.device.type != "cuda":
+            return torch.from_numpy(np.concatenate(pieces)).to(self.device)
+        if self._pinned is None or self._pinned.numel() < total:
+            self._pinned = torch.empty(max(total, 4096) * 2, dtype=torch.int32).pin_memory()
+        host = self._pinned.numpy()
+        off = 0
+        for p in pieces:
+            host[off:off + p.size] = p.reshape(-1)
+            off += p.size
+        dev = torch.empty(total, dtype=torch.int32, device=self.device)
+        dev.copy_(self._pinned[:total], non_blocking=True)
+        # the pinned buffer is rewritten by the next step: the copy must have left it by then
+        torch.cuda.current_stream(self.device).synchronize()
+        self.last_h2d_bytes = total * 4
+        return dev
 
     # ----------------------------------------------------------- step preparation
     def _prepare(self, entries):
@@ -167,8 +188,7 @@ class ModelRunner:
         pieces = [token_ids, positions, token_seq, q_start, start_pos, state_slot, want]
         for slot_mapping, tables in group_arrays:
             pieces += [slot_mapping, tables.reshape(-1)]
-        packed = np.concatenate(pieces)
-        dev = torch.from_numpy(packed).to(self.device, non_blocking=False)
+        dev = self._upload(pieces)
         views = []
         off = 0
         for p in pieces:

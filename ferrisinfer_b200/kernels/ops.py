@@ -61,7 +61,17 @@ def _rows(t: torch.Tensor, what: str) -> tuple[int, int, int]:
     return t.shape[0], t.shape[1], t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel launches this process has made through this module."""
+    return _launches
+
+
 def _check(code: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if code != 0:
         msg = _lib().ferris_last_error().decode("utf-8", "replace")
         kind = "refused its arguments" if code < 0 else f"failed (CUDA error {code})"
@@ -215,3 +225,33 @@ def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, nu
     ``ctx`` is the step context (token-to-request map, positions, request lengths)."""
     paged_attention_simt(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
                          num_kv_heads, head_dim, window, scale)
+
+
+def sample(logits: torch.Tensor, out_token: torch.Tensor, out_prob: Optional[torch.Tensor] = None,
+           temperature: Optional[torch.Tensor] = None, top_k: Optional[torch.Tensor] = None,
+           top_p: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
+           rng_states: Optional[torch.Tensor] = None):
+    """One token per row of fp32 ``logits`` [n, V].  Without ``temperature``: argmax (lowest index on
+    ties).  With it: per-row temperature, top_k (<= 0: whole vocabulary), top_p, and one draw from
+    ``rng_states[slots[row]]`` (int64 xorshift64* states, advanced in place)."""
+    n, V, ld = _rows(logits, "logits")
+    if logits.dtype != torch.float32:
+        raise KernelError("sample: logits must be float32")
+    _need(out_token, "sampled tokens", torch.int32)
+    if out_token.numel() != n:
+        raise KernelError("sample: one output token per row is needed")
+    if out_prob is not None:
+        _need(out_prob, "sample probabilities", torch.float32)
+    if temperature is not None:
+        _need(temperature, "temperatures", torch.float32)
+        _need(top_k, "top_k", torch.int32)
+        _need(top_p, "top_p", torch.float32)
+        _need(slots, "generator slots", torch.int32)
+        _need(rng_states, "generator states", torch.int64)
+        if not (temperature.numel() == top_k.numel() == top_p.numel() == slots.numel() == n):
+            raise KernelError("sample: one temperature, top_k, top_p and slot per row is needed")
+    _check(
+        _lib().ferris_sample(_ptr(logits), _c_int(ld), _c_int(n), _c_int(V), _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                             _ptr(slots), _ptr(rng_states), _ptr(out_token), _ptr(out_prob), _stream()),
+        "sample",
+    )

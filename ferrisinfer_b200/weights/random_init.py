@@ -24,33 +24,34 @@ from .safetensors_io import write_safetensors
 INIT_STD = 0.02
 
 
-def _generator(seed: int, name: str) -> torch.Generator:
+def _generator(seed: int, name: str, device="cpu") -> torch.Generator:
     digest = hashlib.sha256(f"{seed}:{name}".encode()).digest()
-    g = torch.Generator(device="cpu")
+    g = torch.Generator(device=device)
     g.manual_seed(int.from_bytes(digest[:8], "little") & 0x7FFFFFFFFFFFFFFF)
     return g
 
 
-def random_tensor(spec, seed: int, store_dtype: torch.dtype, optional_too: bool = True):
+def random_tensor(spec, seed: int, store_dtype: torch.dtype, device="cpu"):
     if spec.role == "int_table":
-        return torch.zeros(spec.shape, dtype=torch.int32)
-    g = _generator(seed, spec.name)
-    t = torch.randn(spec.shape, generator=g, dtype=torch.float32) * INIT_STD
+        return torch.zeros(spec.shape, dtype=torch.int32, device=device)
+    g = _generator(seed, spec.name, device)
+    t = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device) * INIT_STD
     if spec.role == "norm":
         t = t + 1.0
     return t.to(store_dtype)
 
 
-def random_tensors(config, seed: int, store_dtype="bfloat16", optional: bool = True) -> dict:
-    """name -> CPU tensor for every tensor the architecture's parts ask for (optional ones,
-    such as the q/k/v biases, included unless ``optional`` is False)."""
+def random_tensors(config, seed: int, store_dtype="bfloat16", optional: bool = True, device="cpu") -> dict:
+    """name -> tensor for every tensor the architecture's parts ask for (optional ones, such as the
+    q/k/v biases, included unless ``optional`` is False).  Drawn on ``device``: the CPU stream is the
+    one that model folders are written from; a CUDA device draws other values, faster."""
     arch, cfg = resolve_config(config)
     store = parse_dtype(store_dtype)
     model = build_model(arch.plan(cfg))
     out = {}
     for spec in model.tensor_specs():
         if spec.required or optional:
-            out[spec.name] = random_tensor(spec, seed, store)
+            out[spec.name] = random_tensor(spec, seed, store, device)
     return out
 
 

@@ -1,0 +1,177 @@
+"""Generation through the Python entry point: greedy against the plain implementation, sampling with seeds,
+preemption when pages run out, the command line."""
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import helpers
+import plain_qwen2 as plain
+from helpers import TINY
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PROMPTS = {"A": (5, 9, 17), "B": (3, 11, 23, 40)}
+SLACK = {"float32": 1e-4, "bfloat16": 3e-2}  # how far below the plain maximum a chosen logit may lie
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("gen")
+    return {name: helpers.make_folder(root, TINY[name], seed=31 + i) for i, name in enumerate(("A", "B"))}
+
+
+def _engine(folder, dtype, device=None, **kw):
+    from ferrisinfer_b200 import SchedulerConfig
+    from ferrisinfer_b200.engine.engine import Engine
+
+    sched = SchedulerConfig(max_batch_size=4, max_prefill_chunk_tokens=8, max_prefill_batch_tokens=24,
+                            max_sequence_length=256, max_generated_tokens=64)
+    return Engine(folder, dtype=dtype, device=device, scheduler=kw.pop("scheduler", sched), **kw)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_follows_the_plain_implementation(name, dtype, device, folders):
+    from ferrisinfer_b200 import FinishReason, SamplingParams
+
+    config, weights = helpers.read_folder(folders[name])
+    prompts = [helpers.random_ids(config["vocab_size"], n, n) for n in PROMPTS[name]]
+    engine = _engine(folders[name], dtype, device, page_size=4 if name == "A" else 8, num_pages=64)
+    outs = engine.generate(prompts, SamplingParams.greedy(max_new_tokens=8))
+    for prompt, out in zip(prompts, outs):
+        ids = out.generated_token_ids()
+        assert len(ids) == 8 and out.finish_reason is FinishReason.MAX_NEW_TOKENS and out.prompt_token_ids == prompt
+        logits = plain.forward(config, weights, prompt + ids, torch.float64)
+        for i, tok in enumerate(ids):
+            row = logits[len(prompt) + i - 1]
+            assert row[tok] >= row.max() - SLACK[dtype], (i, tok, int(row.argmax()))
+        if dtype == "float32":
+            assert ids == plain.generate_greedy(config, weights, prompt, 8, torch.float64)
+            p0 = plain.greedy(logits[len(prompt) - 1].float().numpy())[1]
+            assert abs(out.generated_tokens[0].probability - p0) < 1e-5
+    engine.runner.cache.check_invariants()
+    assert all(g.pool.num_used == 0 for g in engine.runner.cache.groups)
+
+
+def test_stop_token_and_length_limits(device, folders):
+    from ferrisinfer_b200 import FinishReason, SamplingParams, SchedulerConfig
+
+    config, weights = helpers.read_folder(folders["A"])
+    prompt = helpers.random_ids(256, 9, 4)
+    greedy = plain.generate_greedy(config, weights, prompt, 6, torch.float64)
+    engine = _engine(folders["A"], "float32", device, page_size=4, num_pages=64)
+    out = engine.generate(prompt, SamplingParams.greedy(max_new_tokens=6, stop_token_id=greedy[2]))
+    first_hit = greedy.index(greedy[2])
+    assert out.generated_token_ids() == greedy[:first_hit + 1] and out.finish_reason is FinishReason.STOP_TOKEN
+    out = engine.generate(prompt, SamplingParams.greedy(max_new_tokens=0))
+    assert out.generated_token_ids() == [] and out.finish_reason is FinishReason.MAX_NEW_TOKENS
+    short = SchedulerConfig(max_batch_size=2, max_sequence_length=12, max_generated_tokens=64)
+    engine = _engine(folders["A"], "float32", device, page_size=4, num_pages=16, scheduler=short)
+    out = engine.generate(prompt, SamplingParams.greedy(max_new_tokens=30))
+    assert len(out.generated_token_ids()) == 3 and out.finish_reason is FinishReason.SEQUENCE_LENGTH
+
+
+def test_sampling_is_seeded_and_does_not_depend_on_the_batch(device, folders):
+    """Config B of the baseline: temperature 0.7 with a fixed seed.  In 32-bit a row's logits do not depend on
+    what else is in the batch, and each request draws from its own generator."""
+    from ferrisinfer_b200 import SamplingParams
+
+    vocab = TINY["B"]["vocab_size"]
+    prompts = [helpers.random_ids(vocab, n, n) for n in PROMPTS["B"]]
+    params = [SamplingParams(temperature=0.7, top_k=0, top_p=1.0, seed=100 + i, max_new_tokens=12)
+              for i in range(len(prompts))]
+    engine = _engine(folders["B"], "float32", device, page_size=8, num_pages=64)
+    together = [o.generated_token_ids() for o in engine.generate(prompts, params)]
+    again = [o.generated_token_ids() for o in engine.generate(prompts, params)]
+    alone = [engine.generate(p, sp).generated_token_ids() for p, sp in zip(prompts, params)]
+    assert together == again == alone
+    other = engine.generate(prompts[0], SamplingParams(temperature=0.7, top_k=0, top_p=1.0, seed=999, max_new_tokens=12))
+    assert other.generated_token_ids() != together[0]
+    chat = engine.generate(prompts[1], SamplingParams.chat_default(max_new_tokens=12))
+    assert len(chat.generated_token_ids()) == 12 and all(0 < t.probability <= 1 for t in chat.generated_tokens)
+
+
+def test_sampled_tokens_follow_the_plain_sampler(device, folders):
+    """Teacher-forced: at each step the plain sampler, given the plain logits of the engine's prefix and the same
+    generator state, picks the engine's token."""
+    from ferrisinfer_b200 import SamplingParams
+
+    config, weights = helpers.read_folder(folders["B"])
+    prompt = helpers.random_ids(config["vocab_size"], 11, 5)
+    sp = SamplingParams(temperature=0.7, top_k=0, top_p=1.0, seed=42, max_new_tokens=10)
+    engine = _engine(folders["B"], "float32", device, page_size=8, num_pages=64)
+    out = engine.generate(prompt, sp)
+    ids = out.generated_token_ids()
+    logits = plain.forward(config, weights, prompt + ids, torch.float32)
+    rng = plain.XorShift64Star(42)
+    agree = 0
+    for i, tok in enumerate(ids):
+        want, prob = plain.sample(logits[len(prompt) + i - 1].numpy(), 0.7, 0, 1.0, rng)
+        agree += int(want == tok)
+        if want == tok:
+            assert abs(prob - out.generated_tokens[i].probability) < 1e-4
+    assert agree >= len(ids) - 1, (ids, agree)  # a draw that lands within rounding of a boundary may differ
+
+
+def test_preemption_when_pages_run_out_does_not_change_the_tokens(device, folders):
+    from ferrisinfer_b200 import SamplingParams, SchedulerConfig
+
+    vocab = TINY["A"]["vocab_size"]
+    prompts = [helpers.random_ids(vocab, n, 50 + n) for n in (14, 11, 9)]
+    params = [SamplingParams(temperature=0.8, top_k=0, top_p=1.0, seed=7 + i, max_new_tokens=20) for i in range(3)]
+    sched = SchedulerConfig(max_batch_size=4, max_prefill_chunk_tokens=8, max_prefill_batch_tokens=24,
+                            max_sequence_length=64, max_generated_tokens=32)
+    roomy = _engine(folders["A"], "float32", device, page_size=4, num_pages=64, scheduler=sched)
+    want = [o.generated_token_ids() for o in roomy.generate(prompts, params)]
+    tight = _engine(folders["A"], "float32", device, page_size=4, num_pages=15, scheduler=sched)  # 60 tokens for three requests of ~31
+    outs = tight.generate(prompts, params)
+    assert tight.scheduler.stats["preemptions"] >= 1 and sum(o.preemptions for o in outs) >= 1
+    assert [o.generated_token_ids() for o in outs] == want
+    tight.runner.cache.check_invariants()
+    assert all(g.pool.num_used == 0 for g in tight.runner.cache.groups)
+
+
+def test_abort_gives_pages_back(device, folders):
+    from ferrisinfer_b200 import FinishReason, SamplingParams
+
+    engine = _engine(folders["A"], "float32", device, page_size=4, num_pages=32)
+    a = engine.submit(helpers.random_ids(256, 20, 1), SamplingParams.greedy(max_new_tokens=30))
+    b = engine.submit(helpers.random_ids(256, 10, 2), SamplingParams.greedy(max_new_tokens=5))
+    for _ in range(3):
+        engine.step()
+    assert engine.abort(a) and not engine.abort("nobody")
+    while engine.has_unfinished():
+        engine.step()
+    assert engine.output_of(a).finish_reason is FinishReason.CANCELLED
+    assert len(engine.output_of(b).generated_tokens) == 5
+    assert all(g.pool.num_used == 0 for g in engine.runner.cache.groups)
+
+
+def test_command_line(device, folders):
+    def run(*args):
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "ferrisinfer"), *args], capture_output=True,
+                           text=True, timeout=600)
+        return r.returncode, r.stdout, r.stderr
+
+    code, out, _ = run("help")
+    assert code == 0 and "generate-hf [ids] [tokens]" in out
+    code, out, _ = run("inspect-hf", folders["B"])
+    assert code == 0 and json.loads(out)["problems"] is None
+    config, weights = helpers.read_folder(folders["B"])
+    prompt = helpers.random_ids(config["vocab_size"], 7, 8)
+    code, out, err = run("generate-hf", ",".join(map(str, prompt)), "5", "--model", folders["B"], "--dtype", "float32")
+    assert code == 0, err
+    line = [l for l in out.splitlines() if l.startswith("generated token ids:")][0]
+    assert [int(t) for t in line.split(":")[1].split()] == plain.generate_greedy(config, weights, prompt, 5, torch.float64)
+    code, out, err = run("profile-continuous-hf", "6", "--model", folders["B"])
+    assert code == 0 and "preemptions" in out, err
+    code, _, err = run("generate-hf", "1,2", "--model", os.path.join(folders["B"], "nowhere"))
+    assert code == 1 and "error" in err
+    code, _, _ = run("no-such-command")
+    assert code == 1

@@ -1,0 +1,377 @@
+"""Each kernel alone against a plain fp32 PyTorch reference of the same op, at sizes other than the engine's.
+
+Where random data would hide a fault, the inputs are made so that it shows: one far key that must dominate,
+keys just inside and just outside a window, pages in shuffled order, ragged shapes.
+"""
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+
+F32, BF16 = torch.float32, torch.bfloat16
+
+
+def tol(dtype):
+    return dict(atol=1e-5, rtol=1e-5) if dtype == F32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def rnd(shape, dtype, device, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(device)
+
+
+# ------------------------------------------------------------------------------------ embedding
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_embed_gather(dtype, device):
+    from ferrisinfer_b200.kernels import ops
+
+    table = rnd((1000, 200), dtype, device, 1)
+    ids = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32, device=device)
+    out = torch.empty(5, 200, dtype=F32, device=device)
+    ops.embed_gather(table, ids, out)
+    assert torch.equal(out, table[ids.long()].float())
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    bad = torch.tensor([3, 1000, 7], dtype=torch.int32, device=device)
+    out = torch.empty(3, 200, dtype=F32, device=device)
+    ops.embed_gather(table, bad, out, status)
+    assert status.item() == 2 and out[1].abs().sum().item() == 0 and torch.equal(out[2], table[7].float())
+
+
+# ------------------------------------------------------------------------------------- rmsnorm
+@pytest.mark.parametrize("out_dtype", [F32, BF16])
+@pytest.mark.parametrize("hidden, eps", [(1000, 1e-5), (3584, 1e-6), (48, 3e-3)])
+def test_rmsnorm(hidden, eps, out_dtype, device):
+    from ferrisinfer_b200.kernels import ops
+
+    x = rnd((37, hidden), F32, device, 2, scale=3.0)
+    w = 1 + rnd((hidden,), F32, device, 3, scale=0.1)
+    want = plain.rms_norm(x.cpu().double(), w.cpu().double(), eps)
+    out = torch.empty(37, hidden, dtype=out_dtype, device=device)
+    ops.rmsnorm(x, w, eps, out)
+    assert torch.allclose(out.cpu().double(), want, **tol(out_dtype))
+    rows = torch.tensor([36, 0, 0, 11], dtype=torch.int32, device=device)
+    out = torch.empty(4, hidden, dtype=out_dtype, device=device)
+    ops.rmsnorm(x, w, eps, out, rows)
+    assert torch.allclose(out.cpu().double(), want[rows.cpu().long()], **tol(out_dtype))
+
+
+# ---------------------------------------------------------------------------------------- gemm
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("M, N, K", [(1, 7, 33), (5, 130, 72), (67, 300, 1000), (64, 64, 16), (130, 65, 17)])
+def test_gemm_simt(M, N, K, dtype, device):
+    from ferrisinfer_b200.kernels import ops
+
+    x, w = rnd((M, K), dtype, device, 4), rnd((N, K), dtype, device, 5, scale=0.1)
+    bias = rnd((N,), F32, device, 6)
+    want = x.cpu().double() @ w.cpu().double().t()
+    out = torch.empty(M, N, dtype=dtype, device=device)
+    ops.gemm_simt(x, w, None, out)
+    assert torch.allclose(out.cpu().double(), want, **tol(dtype))
+    out32 = torch.empty(M, N, dtype=F32, device=device)
+    ops.gemm_simt(x, w, bias, out32)
+    assert torch.allclose(out32.cpu().double(), want + bias.cpu().double(), atol=1e-4, rtol=1e-5)
+    acc = rnd((M, N), F32, device, 7)
+    before = acc.clone()
+    ops.gemm_simt(x, w, None, acc, accumulate=True)
+    assert torch.allclose(acc.cpu().double(), before.cpu().double() + want, atol=1e-4, rtol=1e-5)
+    # rows of a wider buffer (a column slice) as input
+    wide = rnd((M, K + 24), dtype, device, 8)
+    out = torch.empty(M, N, dtype=dtype, device=device)
+    ops.gemm_simt(wide[:, 8:8 + K], w, None, out)
+    assert torch.allclose(out.cpu().double(), wide[:, 8:8 + K].cpu().double() @ w.cpu().double().t(), **tol(dtype))
+
+
+def test_gemm_rows_do_not_depend_on_the_batch(device):
+    from ferrisinfer_b200.kernels import ops
+
+    x, w = rnd((70, 200), F32, device, 9), rnd((150, 200), F32, device, 10)
+    full = torch.empty(70, 150, dtype=F32, device=device)
+    ops.gemm_simt(x, w, None, full)
+    one = torch.empty(1, 150, dtype=F32, device=device)
+    ops.gemm_simt(x[41:42], w, None, one)
+    assert torch.equal(one[0], full[41])
+
+
+# -------------------------------------------------------------------------------------- swiglu
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_swiglu(dtype, device):
+    from ferrisinfer_b200.kernels import ops
+
+    gu = rnd((9, 600), dtype, device, 11, scale=2.0)
+    out = torch.empty(9, 300, dtype=dtype, device=device)
+    ops.swiglu(gu, out)
+    g, u = gu[:, :300].cpu().double(), gu[:, 300:].cpu().double()
+    assert torch.allclose(out.cpu().double(), u * plain.silu(g), **tol(dtype))
+
+
+# ------------------------------------------------------------------------- rope + cache write
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("nh, nkv, d, rotary, page", [(6, 3, 48, 24, 8), (4, 1, 16, 16, 4), (2, 2, 128, 128, 16),
+                                                      (3, 1, 32, 0, 8)])
+def test_rope_cache_write(nh, nkv, d, rotary, page, dtype, device):
+    from ferrisinfer_b200.kernels import ops
+
+    T, pages = 21, 9
+    qkv = rnd((T, (nh + 2 * nkv) * d), dtype, device, 12)
+    src = qkv.clone()
+    positions = torch.tensor([0, 1, 2, 7, 8, 9, 500, 501, 31999, 32000, 3, 3, 3, 40, 41, 42, 43, 44, 45, 46, 47],
+                             dtype=torch.int32, device=device)
+    slots = torch.randperm(pages * page, generator=torch.Generator().manual_seed(1))[:T].to(torch.int32).to(device)
+    slots[5] = -1  # nothing is written for this token
+    k_cache = torch.zeros(pages, nkv, page, d, dtype=dtype, device=device)
+    v_cache = torch.zeros_like(k_cache)
+    inv_freq = torch.tensor(plain.rotary_inverse_frequencies(d, rotary, 1e6).numpy(), device=device) if rotary else None
+    ops.rope_cache_write(qkv, positions, inv_freq, slots, k_cache, v_cache, nh, nkv, d, rotary, page)
+    s3 = src.cpu().float().view(T, nh + 2 * nkv, d)
+    pos = positions.cpu().tolist()
+    q_want = plain.rope(s3[:, :nh].double(), pos, d, rotary, 1e6)
+    k_want = plain.rope(s3[:, nh:nh + nkv].double(), pos, d, rotary, 1e6)
+    got = qkv.cpu().double().view(T, nh + 2 * nkv, d)
+    # the angle is the same fp32 product in the kernel and in the plain implementation, also at position 32000
+    t = dict(atol=2e-5, rtol=1e-5) if dtype == F32 else dict(atol=3e-2, rtol=2e-2)
+    assert torch.allclose(got[:, :nh], q_want, **t)
+    assert torch.equal(got[:, nh:], s3[:, nh:].double())  # k and v stay as they were in the buffer
+    small = [i for i, p in enumerate(pos) if p < 1000]
+    assert torch.allclose(got[small, :nh], q_want[small], **tol(dtype))
+    for i in range(T):
+        slot = slots[i].item()
+        if slot < 0:
+            continue
+        pg, off = slot // page, slot % page
+        assert torch.allclose(k_cache[pg, :, off].cpu().double(), k_want[i], **t)
+        assert torch.equal(v_cache[pg, :, off].cpu().double(), s3[i, nh + nkv:].double())
+    written = {s.item() for s in slots if s.item() >= 0}
+    for slot in range(pages * page):
+        if slot not in written:
+            assert k_cache[slot // page, :, slot % page].abs().sum().item() == 0
+    again = src.clone()
+    ops.rope_cache_write(again, positions, inv_freq, None, None, None, nh, nkv, d, rotary, page, write_kv=False)
+    assert torch.equal(again.view(T, -1, d)[:, :nh], qkv.view(T, -1, d)[:, :nh])
+
+
+# ----------------------------------------------------------------------------------- attention
+class AttentionCase:
+    """A batch of requests over a shuffled page pool; keys and values are set by position."""
+
+    def __init__(self, device, dtype, nh, nkv, d, page, seqs, seed=0, window=0):
+        # seqs: list of (kv_len, q_len): the last q_len positions of each request are the step's queries
+        self.nh, self.nkv, self.d, self.page, self.window = nh, nkv, d, page, window
+        g = torch.Generator().manual_seed(seed)
+        blocks = [-(-kv // page) for kv, _ in seqs]
+        total = sum(blocks) + 3
+        order = torch.randperm(total, generator=g).tolist()
+        self.max_blocks = max(blocks)
+        tables = torch.full((len(seqs), self.max_blocks), -1, dtype=torch.int32)
+        self.k = [torch.randn(kv, nkv, d, generator=g) for kv, _ in seqs]
+        self.v = [torch.randn(kv, nkv, d, generator=g) for kv, _ in seqs]
+        self.q = [torch.randn(ql, nh, d, generator=g) for _, ql in seqs]
+        self.seqs = seqs
+        used = 0
+        for s, nb in enumerate(blocks):
+            tables[s, :nb] = torch.tensor(order[used:used + nb], dtype=torch.int32)
+            used += nb
+        self.tables, self.total, self.dtype, self.device = tables, total, dtype, device
+
+    def device_inputs(self):
+        nh, nkv, d, page = self.nh, self.nkv, self.d, self.page
+        k_cache = torch.full((self.total, nkv, page, d), 7.0)  # stale contents of pages that nobody owns
+        v_cache = torch.full((self.total, nkv, page, d), -7.0)
+        for s, (kv, _) in enumerate(self.seqs):
+            for p in range(kv):
+                pg = self.tables[s, p // page].item()
+                k_cache[pg, :, p % page] = self.k[s][p]
+                v_cache[pg, :, p % page] = self.v[s][p]
+        T = sum(ql for _, ql in self.seqs)
+        qkv = torch.zeros(T, (nh + 2 * nkv) * d)
+        token_seq, positions = [], []
+        row = 0
+        for s, (kv, ql) in enumerate(self.seqs):
+            qkv[row:row + ql, :nh * d] = self.q[s].reshape(ql, nh * d)
+            token_seq += [s] * ql
+            positions += list(range(kv - ql, kv))
+            row += ql
+        to = lambda t, dt: t.to(dt).to(self.device)
+        from types import SimpleNamespace
+
+        ctx = SimpleNamespace(token_seq=to(torch.tensor(token_seq), torch.int32),
+                              positions=to(torch.tensor(positions), torch.int32),
+                              seqs=[SimpleNamespace(q_start=sum(q for _, q in self.seqs[:i]), q_len=ql, start_pos=kv - ql)
+                                    for i, (kv, ql) in enumerate(self.seqs)],
+                              num_tokens=T, num_seqs=len(self.seqs), max_q_len=max(ql for _, ql in self.seqs),
+                              max_kv_len=max(kv for kv, _ in self.seqs))
+        return (to(qkv, self.dtype), to(k_cache, self.dtype), to(v_cache, self.dtype),
+                self.tables.to(self.device), ctx, T)
+
+    def reference(self):
+        """Plain attention per request in float64, from the values as the storage type rounds them."""
+        outs = []
+        r = lambda t: t.to(self.dtype).double()
+        for s, (kv, ql) in enumerate(self.seqs):
+            q_all = torch.zeros(kv, self.nh, self.d, dtype=torch.float64)
+            q_all[kv - ql:] = r(self.q[s])
+            o = plain.attention(q_all, r(self.k[s]), r(self.v[s]), list(range(kv)), self.window or None)
+            outs.append(o[kv - ql:].reshape(ql, self.nh * self.d))
+        return torch.cat(outs)
+
+
+def attention_impls():
+    from ferrisinfer_b200.kernels import ops
+
+    def simt(qkv, out, k, v, tables, ctx, nh, nkv, d, window, scale):
+        ops.paged_attention_simt(qkv, out, k, v, tables, ctx.token_seq, ctx.positions, nh, nkv, d, window, scale)
+
+    return {"simt": simt, "dispatch": ops.paged_attention}
+
+
+def run_attention(case, impl):
+    qkv, k, v, tables, ctx, T = case.device_inputs()
+    out = torch.full((T, case.nh * case.d), float("nan"), dtype=case.dtype, device=case.device)
+    attention_impls()[impl](qkv, out, k, v, tables, ctx, case.nh, case.nkv, case.d, case.window,
+                            1.0 / math.sqrt(case.d))
+    torch.cuda.synchronize()
+    return out.cpu().double()
+
+
+ATT_TOL = {F32: dict(atol=2e-5, rtol=1e-4), BF16: dict(atol=2e-2, rtol=2e-2)}
+
+
+@pytest.mark.parametrize("impl", ["simt", "dispatch"])
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("nh, nkv, d, page", [(4, 2, 16, 4), (3, 1, 32, 8), (5, 5, 48, 16), (14, 2, 64, 16),
+                                              (12, 2, 128, 16), (7, 1, 64, 16), (2, 1, 256, 32), (6, 2, 80, 16)])
+def test_attention_mixed_batch(nh, nkv, d, page, dtype, impl, device):
+    """Whole prompts, portions and single decoded tokens in one batch, lengths at and around page edges."""
+    seqs = [(1, 1), (page, page), (page + 1, 1), (3 * page, 1), (3 * page - 1, 2), (77, 77), (130, 17), (200, 1), (5, 3)]
+    case = AttentionCase(device, dtype, nh, nkv, d, page, seqs, seed=nh * d)
+    got, want = run_attention(case, impl), case.reference()
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got, want, **ATT_TOL[dtype]), (got - want).abs().max()
+
+
+@pytest.mark.parametrize("impl", ["simt", "dispatch"])
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("q_len", [1, 5, 64])
+def test_attention_finds_one_far_key_among_hundreds(q_len, dtype, impl, device):
+    """Key 37 of 900 is aligned with every query and scaled up: the output must be its value."""
+    nh, nkv, d, page, kv = 8, 2, 64, 16, 900
+    case = AttentionCase(device, dtype, nh, nkv, d, page, [(kv, q_len), (300, 1)], seed=3)
+    direction = torch.randn(d, generator=torch.Generator().manual_seed(9))
+    direction = direction / direction.norm()
+    case.q[0][:] = direction * 6.0 + 0.05 * case.q[0]
+    case.k[0][37] = direction * 30.0
+    case.v[0][37] = torch.arange(d).float().repeat(nkv, 1) / d + 3.0
+    got, want = run_attention(case, impl), case.reference()
+    row = got[q_len - 1].view(nh, d)
+    assert (row - case.v[0][37][0].to(dtype).double()).abs().max() < 0.05
+    assert torch.allclose(got, want, **ATT_TOL[dtype])
+
+
+@pytest.mark.parametrize("impl", ["simt", "dispatch"])
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("window, page", [(21, 8), (16, 16), (33, 16), (5, 4)])
+def test_attention_window_edges(window, page, dtype, impl, device):
+    """The key at P - W + 1 is the last one inside the window; the key at P - W is outside.  Both carry loud
+    values, so a window that is off by one shows."""
+    nh, nkv, d = 4, 2, 32
+    seqs = [(100, 1), (100, 30), (window, 1), (window + 1, 2), (64, 64)]
+    case = AttentionCase(device, dtype, nh, nkv, d, page, seqs, seed=window, window=window)
+    P = 99
+    case.v[0][P - window + 1] += 50.0  # inside: must show
+    case.v[0][P - window] -= 5000.0  # outside: must not
+    got, want = run_attention(case, impl), case.reference()
+    assert got[0].max() > 0.5 and got[0].min() > -100.0
+    assert torch.allclose(got, want, atol=ATT_TOL[dtype]["atol"] * 10, rtol=ATT_TOL[dtype]["rtol"])
+
+
+@pytest.mark.parametrize("impl", ["simt", "dispatch"])
+def test_attention_long_context_decode_batch(impl, device):
+    """Decoding at a context of several thousand keys for a batch of requests of unequal length."""
+    nh, nkv, d, page = 14, 2, 64, 16
+    seqs = [(4096, 1), (4095, 1), (2049, 1), (17, 1), (4081, 1), (3000, 1), (1, 1), (2048, 1)]
+    case = AttentionCase(device, BF16, nh, nkv, d, page, seqs, seed=11)
+    got, want = run_attention(case, impl), case.reference()
+    assert torch.allclose(got, want, **ATT_TOL[BF16]), (got - want).abs().max()
+
+
+# ------------------------------------------------------------------------------------ sampling
+def test_argmax_takes_the_lowest_index_among_equal_maxima(device):
+    from ferrisinfer_b200.kernels import ops
+
+    logits = rnd((6, 5000), F32, device, 20)
+    logits[0, 4000] = logits[0, 17] = 9.0
+    logits[1, 4999] = 9.0
+    logits[2, 0] = 9.0
+    logits[3] = -3.0  # all equal
+    logits[4, 123] = float("inf")
+    tok = torch.empty(6, dtype=torch.int32, device=device)
+    prob = torch.empty(6, dtype=F32, device=device)
+    ops.sample(logits, tok, prob)
+    want = [plain.greedy(logits[i].cpu().numpy()) for i in range(6)]
+    assert tok.cpu().tolist()[:4] == [17, 4999, 0, 0] and tok[4].item() == 123
+    assert tok[5].item() == want[5][0]
+    for i in (0, 1, 2, 3, 5):
+        assert abs(prob[i].item() - want[i][1]) < 1e-6 * max(1.0, 1 / want[i][1]) + 1e-6
+
+
+@pytest.mark.parametrize("V", [257, 5000, 151936])
+def test_sampling_matches_the_plain_sampler(V, device):
+    """Rows with different temperatures, top_k and top_p; each row draws from its own generator state.  A draw
+    may differ from the sequential f32 walk only when the threshold lies within rounding of a boundary."""
+    from ferrisinfer_b200.kernels import ops
+
+    rows = 24 if V > 100000 else 48
+    g = torch.Generator().manual_seed(V)
+    logits = (torch.randn(rows, V, generator=g) * 2.0)
+    logits[3, 10:20] = logits[3, 5]  # ties
+    logits[4] = torch.round(logits[4])  # many ties
+    options = [(0.7, 0, 1.0), (1.0, 20, 0.9), (0.3, 0, 0.5), (1.5, 50, 1.0), (0.7, 5, 0.1), (2.0, 0, 0.95),
+               (0.0, 0, 1.0), (0.7, 1, 1.0), (1e-9, 0, 1.0), (1.0, 100000000, 0.999)]
+    temperature = torch.tensor([options[i % len(options)][0] for i in range(rows)])
+    top_k = torch.tensor([options[i % len(options)][1] for i in range(rows)], dtype=torch.int32)
+    top_p = torch.tensor([options[i % len(options)][2] for i in range(rows)])
+    slots = torch.randperm(64, generator=g)[:rows].to(torch.int32)
+    states = torch.randint(1, 2**62, (64,), generator=g)
+    states[slots[2]] = 0  # stands for the default seed
+    dev_states = states.clone().to(device)
+    tok = torch.empty(rows, dtype=torch.int32, device=device)
+    prob = torch.empty(rows, dtype=F32, device=device)
+    for draw in range(3):
+        ops.sample(logits.to(device), tok, prob, temperature.to(device), top_k.to(device), top_p.to(device),
+                   slots.to(device), dev_states)
+        differ = 0
+        for r in range(rows):
+            T, k, p = temperature[r].item(), top_k[r].item(), top_p[r].item()
+            rng = plain.XorShift64Star(int(states[slots[r]].item()))
+            want_tok, want_prob = plain.sample(logits[r].numpy(), T, k, p, rng)
+            greedy = T <= 0 or k == 1 or p <= 0
+            if not greedy:
+                states[slots[r]] = rng.state - (1 << 64) if rng.state >= 1 << 63 else rng.state
+            assert dev_states[slots[r]].item() == states[slots[r]].item(), "generator state advances once per draw"
+            if tok[r].item() != want_tok:
+                differ += 1
+                assert not greedy
+            else:
+                assert abs(prob[r].item() - want_prob) < 1e-3 * want_prob + 1e-6
+        assert differ <= 1, differ
+
+
+def test_sampling_distribution(device):
+    """Ten thousand draws at temperature 1 from a row of five tokens follow softmax."""
+    from ferrisinfer_b200.kernels import ops
+
+    row = torch.tensor([[1.0, 2.0, 0.0, -1.0, 1.5]])
+    n = 10000
+    logits = row.repeat(n, 1).to(device)
+    states = torch.arange(1, n + 1, dtype=torch.int64, device=device) * 2654435761
+    tok = torch.empty(n, dtype=torch.int32, device=device)
+    ops.sample(logits, tok, None, torch.ones(n, device=device), torch.zeros(n, dtype=torch.int32, device=device),
+               torch.ones(n, device=device), torch.arange(n, dtype=torch.int32, device=device), states)
+    freq = torch.bincount(tok.cpu().long(), minlength=5).double() / n
+    want = torch.softmax(row[0].double(), 0)
+    assert (freq - want).abs().max() < 0.02, (freq, want)

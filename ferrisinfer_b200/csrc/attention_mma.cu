@@ -1,0 +1,593 @@
+// Attention over the paged bf16 cache on the tensor cores, for head sizes 64 and 128 and pages of a
+// multiple of 16 tokens: a split-KV kernel for steps of single tokens (decode) with its merge, and a
+// kernel for portions of prompts (prefill).  Both stream 16-key tiles of K and V from the pages by
+// TMA (128-byte swizzle, boxes addressed through the request's block table), form q.k with
+// mma.sync m16n8k16 (bf16 in, fp32 out), keep the softmax (scale, running maximum, sum) in fp32,
+// and share one tile routine.
+//
+// The formulas are those of the reference's streaming attention
+// (crates/ferrisinfer-kernel/src/cpu/attention.rs:729-781, 1125-1155): query head hq reads kv head
+// hq / (nh / nkv); s = (q . k) * scale; the query at position P attends keys lo..P (lo = 0, or
+// P - window + 1); out = sum softmax(s) v.  The rows of an MMA tile are (token, head of the group)
+// pairs that share one kv head, so the keys and values of a group are loaded once for all its heads.
+//
+// Every mbarrier wait is bounded; a wait that runs out records its place in the status word and
+// the kernel runs on to its end with a wrong result instead of hanging.
+#include <limits.h>
+#include <math.h>
+
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace {
+
+constexpr int TILE_KEYS = 16;
+constexpr int WARPS = 4;
+
+// Position limits of one thread's two rows (g and g + 8 of the warp's 16-row slab).
+struct RowLimits {
+    int hi[2];  // last key a row may see (its own position); -1 for a row that does not exist
+    int lo[2];  // first key it may see
+};
+
+template <int D>
+struct WarpState {
+    uint32_t q[D / 16][4];  // A fragments of the 16 x D query slab
+    float o[D / 8][4];      // output accumulators
+    float m[2], l[2];       // running maximum and (per-thread partial) sum of rows g and g + 8
+};
+
+template <int D>
+__device__ __forceinline__ void init_state(WarpState<D>& st) {
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) st.o[n][e] = 0.0f;
+    st.m[0] = st.m[1] = -INFINITY;
+    st.l[0] = st.l[1] = 0.0f;
+}
+
+// Load the query fragments of rows g and g + 8; row pointers may be null (rows that do not exist).
+template <int D>
+__device__ __forceinline__ void load_q(WarpState<D>& st, const bf16* row0, const bf16* row1) {
+    const int t = threadIdx.x & 3;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+        const int c = ks * 16 + 2 * t;
+        st.q[ks][0] = row0 ? *reinterpret_cast<const uint32_t*>(row0 + c) : 0u;
+        st.q[ks][1] = row1 ? *reinterpret_cast<const uint32_t*>(row1 + c) : 0u;
+        st.q[ks][2] = row0 ? *reinterpret_cast<const uint32_t*>(row0 + c + 8) : 0u;
+        st.q[ks][3] = row1 ? *reinterpret_cast<const uint32_t*>(row1 + c + 8) : 0u;
+    }
+}
+
+// One tile of 16 keys starting at absolute key `key0`; K and V tiles lie in shared memory as D/64
+// swizzled boxes of 16 rows x 128 bytes each (box c = columns 64c .. 64c+63).
+template <int D>
+__device__ __forceinline__ void attend_tile(WarpState<D>& st, uint32_t k_smem, uint32_t v_smem, int key0,
+                                            const RowLimits& lim, float scale) {
+    const int lane = threadIdx.x & 31;
+    const int t = lane & 3;
+    float s[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] = 0.0f;
+
+    // scores: S[16 x 16] = Q[16 x D] K^T
+    {
+        const int mi = lane >> 3, r8 = lane & 7;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ks += 2) {
+                const int cc = 2 * ks + mi;  // 16-byte chunk of the row: k columns 8cc .. 8cc+7
+                uint32_t r[4];
+                ldmatrix_x4(r, k_smem + (cc >> 3) * 2048 + swizzle128(8 * j + r8, cc & 7));
+                mma_bf16_16816(s[j], st.q[ks], r[0], r[1]);
+                mma_bf16_16816(s[j], st.q[ks + 1], r[2], r[3]);
+            }
+        }
+    }
+    // scale, mask, running maximum
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int row = e >> 1;
+            const int key = key0 + 8 * j + 2 * t + (e & 1);
+            const bool ok = key <= lim.hi[row] && key >= lim.lo[row];
+            s[j][e] = ok ? s[j][e] * scale : -INFINITY;
+            mx[row] = fmaxf(mx[row], s[j][e]);
+        }
+    float corr[2], base[2];
+#pragma unroll
+    for (int row = 0; row < 2; ++row) {
+        mx[row] = fmaxf(mx[row], __shfl_xor_sync(0xffffffffu, mx[row], 1));
+        mx[row] = fmaxf(mx[row], __shfl_xor_sync(0xffffffffu, mx[row], 2));
+        const float m_new = fmaxf(st.m[row], mx[row]);
+        base[row] = m_new == -INFINITY ? 0.0f : m_new;  // a row that has seen no key yet
+        corr[row] = st.m[row] == -INFINITY ? 0.0f : expf(st.m[row] - base[row]);
+        st.m[row] = m_new;
+        st.l[row] *= corr[row];
+    }
+    uint32_t p[4];
+    {
+        float e00 = expf(s[0][0] - base[0]), e01 = expf(s[0][1] - base[0]);
+        float e02 = expf(s[0][2] - base[1]), e03 = expf(s[0][3] - base[1]);
+        float e10 = expf(s[1][0] - base[0]), e11 = expf(s[1][1] - base[0]);
+        float e12 = expf(s[1][2] - base[1]), e13 = expf(s[1][3] - base[1]);
+        st.l[0] += (e00 + e01) + (e10 + e11);
+        st.l[1] += (e02 + e03) + (e12 + e13);
+        p[0] = pack_bf16(e00, e01);
+        p[1] = pack_bf16(e02, e03);
+        p[2] = pack_bf16(e10, e11);
+        p[3] = pack_bf16(e12, e13);
+    }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+        st.o[n][0] *= corr[0];
+        st.o[n][1] *= corr[0];
+        st.o[n][2] *= corr[1];
+        st.o[n][3] *= corr[1];
+    }
+    // O[16 x D] += P[16 x 16] V[16 x D]
+    {
+        const int mi = lane >> 3, r8 = lane & 7;
+        const int row = (mi & 1) * 8 + r8;
+#pragma unroll
+        for (int n = 0; n < D / 8; n += 2) {
+            const int cc = n + (mi >> 1);
+            uint32_t r[4];
+            ldmatrix_x4_trans(r, v_smem + (cc >> 3) * 2048 + swizzle128(row, cc & 7));
+            mma_bf16_16816(st.o[n], p, r[0], r[1]);
+            mma_bf16_16816(st.o[n + 1], p, r[2], r[3]);
+        }
+    }
+}
+
+// Sum the per-thread partial sums of a row over the four threads that share it.
+template <int D>
+__device__ __forceinline__ void finish_rows(WarpState<D>& st) {
+#pragma unroll
+    for (int row = 0; row < 2; ++row) {
+        st.l[row] += __shfl_xor_sync(0xffffffffu, st.l[row], 1);
+        st.l[row] += __shfl_xor_sync(0xffffffffu, st.l[row], 2);
+    }
+}
+
+// The first 1024-byte boundary of the shared address space at or after p (swizzled TMA tiles need it).
+__device__ __forceinline__ uint8_t* align1024(uint8_t* p) { return p + ((1024u - (smem_u32(p) & 1023u)) & 1023u); }
+
+// Issue the TMA loads of one 16-key tile of K and of V into a stage (2 x D/64 boxes of 2 KB).
+template <int D>
+__device__ __forceinline__ void load_tile(uint8_t* stage, const CUtensorMap* mk, const CUtensorMap* mv, int cache_row,
+                                          uint64_t* bar) {
+    mbar_expect_tx(bar, 2 * TILE_KEYS * D * 2);
+#pragma unroll
+    for (int c = 0; c < D / 64; ++c) {
+        tma_load_2d(stage + c * 2048, mk, 64 * c, cache_row, bar);
+        tma_load_2d(stage + (D / 64) * 2048 + c * 2048, mv, 64 * c, cache_row, bar);
+    }
+}
+
+// Row of the cache's 2-D view [pages * kv heads * page_size, D] that holds key `key` of a request.
+__device__ __forceinline__ int cache_row_of(const int* table, int key, int page_size, int nkv, int hk) {
+    const int page = table[key / page_size];
+    return (page * nkv + hk) * page_size + key % page_size;
+}
+
+// =============================================================================================
+// Decode: one CTA per (split, kv head, token).  Its four warps take the 16-key tiles of the
+// split's key range in turn, each with a pipeline of its own; their results are merged through
+// shared memory and written either as the final output or as one partial (m, l, O) per split.
+// =============================================================================================
+template <int D, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32)
+    decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                            const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
+                            float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ block_tables,
+                            int max_blocks, const int* __restrict__ token_seq, const int* __restrict__ positions, int nh,
+                            int nkv, int page_size, int window, float scale, int splits, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full[WARPS][STAGES];
+    uint8_t* smem = align1024(smem_raw);
+    constexpr int STAGE_BYTES = 2 * TILE_KEYS * D * 2;
+
+    const int split = blockIdx.x, hk = blockIdx.y, tok = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = nh / nkv;
+    const int seq = token_seq[tok];
+    const int P = positions[tok];
+    const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
+    const int* table = block_tables + (size_t)seq * max_blocks;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&map_k);
+        tma_prefetch_descriptor(&map_v);
+    }
+    if (lane == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(&full[warp][s], 1);
+    }
+    mbar_fence_init();
+    __syncthreads();
+
+    // key tiles of this split
+    const int first_tile = lo / TILE_KEYS, last_tile = P / TILE_KEYS;
+    const int n_tiles = last_tile - first_tile + 1;
+    const int per_split = (n_tiles + splits - 1) / splits;
+    const int t_begin = first_tile + split * per_split;
+    const int t_end = min(t_begin + per_split, last_tile + 1);
+    const int my_count = t_end > t_begin + warp ? (t_end - t_begin - warp + WARPS - 1) / WARPS : 0;
+
+    WarpState<D> st;
+    init_state(st);
+    RowLimits lim;
+    {
+        const int g = lane >> 2;
+        const bf16* qrow = q + (size_t)tok * ldq + (size_t)hk * G * D;
+        load_q(st, g < G ? qrow + (size_t)g * D : nullptr, g + 8 < G ? qrow + (size_t)(g + 8) * D : nullptr);
+        lim.hi[0] = g < G ? P : -1;
+        lim.hi[1] = g + 8 < G ? P : -1;
+        lim.lo[0] = lim.lo[1] = lo;
+    }
+    uint8_t* my_stages = smem + (size_t)warp * STAGES * STAGE_BYTES;
+    auto issue = [&](int i) {
+        const int tile = t_begin + warp + i * WARPS;
+        load_tile<D>(my_stages + (i % STAGES) * STAGE_BYTES, &map_k, &map_v,
+                     cache_row_of(table, tile * TILE_KEYS, page_size, nkv, hk), &full[warp][i % STAGES]);
+    };
+    if (lane == 0)
+        for (int i = 0; i < STAGES && i < my_count; ++i) issue(i);
+    for (int i = 0; i < my_count; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(&full[warp][s], (i / STAGES) & 1, status, 1)) break;
+        const uint32_t base = smem_u32(my_stages + s * STAGE_BYTES);
+        attend_tile<D>(st, base, base + (D / 64) * 2048, (t_begin + warp + i * WARPS) * TILE_KEYS, lim, scale);
+        __syncwarp();
+        if (lane == 0 && i + STAGES < my_count) issue(i + STAGES);
+    }
+    finish_rows(st);
+
+    // merge the four warps through shared memory (the stages are no longer read)
+    __syncthreads();
+    float* merge = reinterpret_cast<float*>(smem);  // [WARPS][16][D + 2]
+    {
+        const int g = lane >> 2, t = lane & 3;
+        float* mine = merge + (size_t)warp * 16 * (D + 2);
+#pragma unroll
+        for (int row = 0; row < 2; ++row) {
+            float* r = mine + (g + 8 * row) * (D + 2);
+            if (t == 0) {
+                r[0] = st.m[row];
+                r[1] = st.l[row];
+            }
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n) {
+                r[2 + 8 * n + 2 * t] = st.o[n][2 * row];
+                r[2 + 8 * n + 2 * t + 1] = st.o[n][2 * row + 1];
+            }
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += WARPS * 32) {
+        const int r = idx / D, c = idx % D;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, merge[(size_t)(w * 16 + r) * (D + 2)]);
+        float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float* rw = merge + (size_t)(w * 16 + r) * (D + 2);
+            const float f = rw[0] == -INFINITY ? 0.0f : expf(rw[0] - mm);
+            ll += rw[1] * f;
+            oo += rw[2 + c] * f;
+        }
+        const int head = hk * G + r;
+        if (splits == 1) {
+            out[(size_t)tok * ldo + (size_t)head * D + c] = __float2bfloat16_rn(oo / ll);
+        } else {
+            const size_t slot = ((size_t)tok * nh + head) * splits + split;
+            part_o[slot * D + c] = oo;
+            if (c == 0) {
+                part_ml[slot * 2] = mm;
+                part_ml[slot * 2 + 1] = ll;
+            }
+        }
+    }
+}
+
+// Merge of the splits: out = sum_s O_s e^{m_s - M} / sum_s l_s e^{m_s - M}.  One block per (token, head).
+template <int D>
+__global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    bf16* __restrict__ out, int ldo, int nh, int splits) {
+    const int tok = blockIdx.x, head = blockIdx.y;
+    const size_t base = ((size_t)tok * nh + head) * splits;
+    float mm = -INFINITY;
+    for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float ll = 0.0f, oo = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = part_ml[(base + s) * 2];
+            const float f = ms == -INFINITY ? 0.0f : expf(ms - mm);
+            ll += part_ml[(base + s) * 2 + 1] * f;
+            oo += part_o[(base + s) * D + c] * f;
+        }
+        out[(size_t)tok * ldo + (size_t)head * D + c] = __float2bfloat16_rn(oo / ll);
+    }
+}
+
+// =============================================================================================
+// Prefill: one CTA per (row block, kv head, request).  The rows of a request's portion are
+// (token, head of the group) pairs, 64 to a CTA (16 per warp).  A fifth warp streams 64-key
+// stages of K and V for the CTA; each consumer warp skips the 16-key tiles that none of its rows
+// can see.
+// =============================================================================================
+constexpr int PF_ROWS = 64;
+constexpr int PF_STAGE_TILES = 4;  // 64 keys per stage
+
+template <int D, int STAGES>
+__global__ void __launch_bounds__((WARPS + 1) * 32)
+    prefill_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                             const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
+                             const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ seq_q_start,
+                             const int* __restrict__ seq_start_pos, int nh, int nkv, int page_size, int window,
+                             float scale, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full[STAGES], empty[STAGES];
+    uint8_t* smem = align1024(smem_raw);
+    constexpr int TILE_BYTES = 2 * TILE_KEYS * D * 2;
+    constexpr int STAGE_BYTES = PF_STAGE_TILES * TILE_BYTES;
+
+    const int G = nh / nkv;
+    const int seq = blockIdx.z, hk = blockIdx.y;
+    const int q_start = seq_q_start[seq], q_len = seq_q_start[seq + 1] - q_start;
+    const int rows_total = q_len * G;
+    // heavy row blocks (the last tokens see the most keys) first
+    const int n_blocks = (rows_total + PF_ROWS - 1) / PF_ROWS;
+    if ((int)blockIdx.x >= n_blocks) return;
+    const int block = n_blocks - 1 - blockIdx.x;
+    const int row0 = block * PF_ROWS;
+    const int start_pos = seq_start_pos[seq];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* table = block_tables + (size_t)seq * max_blocks;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&map_k);
+        tma_prefetch_descriptor(&map_v);
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], WARPS);
+        }
+    }
+    mbar_fence_init();
+    __syncthreads();
+
+    // key range of the block: from the first key its first token may see to its last token's position
+    const int tok_first = row0 / G;
+    const int tok_last = min(row0 + PF_ROWS - 1, rows_total - 1) / G;
+    const int p_first = start_pos + tok_first, p_last = start_pos + tok_last;
+    const int lo_block = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+    const int stage_keys = PF_STAGE_TILES * TILE_KEYS;
+    const int s_begin = lo_block / stage_keys, s_end = p_last / stage_keys + 1;  // stages of 64 keys
+    const int n_stages = s_end - s_begin;
+
+    if (warp == WARPS) {
+        // producer
+        if (lane == 0) {
+            for (int i = 0; i < n_stages; ++i) {
+                const int s = i % STAGES;
+                if (i >= STAGES && !mbar_wait(&empty[s], ((i / STAGES) - 1) & 1, status, 2)) break;
+                const int key_base = (s_begin + i) * stage_keys;
+                int tiles = 0;
+                for (int k = 0; k < PF_STAGE_TILES; ++k)
+                    if (key_base + k * TILE_KEYS <= p_last) ++tiles;
+                mbar_expect_tx(&full[s], tiles * TILE_BYTES);
+                for (int k = 0; k < tiles; ++k) {
+                    uint8_t* dst = smem + (size_t)s * STAGE_BYTES + k * TILE_BYTES;
+                    const int row = cache_row_of(table, key_base + k * TILE_KEYS, page_size, nkv, hk);
+#pragma unroll
+                    for (int c = 0; c < D / 64; ++c) {
+                        tma_load_2d(dst + c * 2048, &map_k, 64 * c, row, &full[s]);
+                        tma_load_2d(dst + (D / 64) * 2048 + c * 2048, &map_v, 64 * c, row, &full[s]);
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // consumers
+    WarpState<D> st;
+    init_state(st);
+    RowLimits lim;
+    int my_lo = INT_MAX, my_hi = -1;
+    const bf16* qrow[2];
+    bf16* orow[2];
+    {
+        const int g = lane >> 2;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = row0 + warp * 16 + g + 8 * r;
+            if (row < rows_total) {
+                const int tok = row / G, head = hk * G + row % G;
+                const int pos = start_pos + tok;
+                lim.hi[r] = pos;
+                lim.lo[r] = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+                qrow[r] = q + (size_t)(q_start + tok) * ldq + (size_t)head * D;
+                orow[r] = out + (size_t)(q_start + tok) * ldo + (size_t)head * D;
+            } else {
+                lim.hi[r] = -1;
+                lim.lo[r] = 0;
+                qrow[r] = nullptr;
+                orow[r] = nullptr;
+            }
+        }
+        load_q(st, qrow[0], qrow[1]);
+        // key range that any row of this warp can see
+        const int wr0 = row0 + warp * 16, wr1 = min(wr0 + 15, rows_total - 1);
+        if (wr0 < rows_total) {
+            const int pa = start_pos + wr0 / G, pb = start_pos + wr1 / G;
+            my_lo = (window > 0 && pa - window + 1 > 0) ? pa - window + 1 : 0;
+            my_hi = pb;
+        }
+    }
+    for (int i = 0; i < n_stages; ++i) {
+        const int s = i % STAGES;
+        if (!mbar_wait(&full[s], (i / STAGES) & 1, status, 3)) break;
+        const int key_base = (s_begin + i) * stage_keys;
+#pragma unroll
+        for (int k = 0; k < PF_STAGE_TILES; ++k) {
+            const int key0 = key_base + k * TILE_KEYS;
+            if (key0 > my_hi || key0 + TILE_KEYS - 1 < my_lo) continue;
+            const uint32_t base = smem_u32(smem + (size_t)s * STAGE_BYTES + k * TILE_BYTES);
+            attend_tile<D>(st, base, base + (D / 64) * 2048, key0, lim, scale);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    finish_rows(st);
+    {
+        const int t = lane & 3;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            if (!orow[r]) continue;
+            const float inv = 1.0f / st.l[r];
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n)
+                *reinterpret_cast<uint32_t*>(orow[r] + 8 * n + 2 * t) =
+                    pack_bf16(st.o[n][2 * r] * inv, st.o[n][2 * r + 1] * inv);
+        }
+    }
+}
+
+struct MapCacheEntry {
+    const void* base;
+    uint64_t rows;
+    int d;
+    CUtensorMap map;
+};
+constexpr int MAP_CACHE = 512;
+MapCacheEntry g_maps[MAP_CACHE];
+int g_map_count = 0;
+
+// Tensor maps are cached by (base address, extent): a cache tensor keeps both for its lifetime.
+int cache_map(const void* base, uint64_t rows, int d, CUtensorMap* out) {
+    for (int i = 0; i < g_map_count; ++i)
+        if (g_maps[i].base == base && g_maps[i].rows == rows && g_maps[i].d == d) {
+            *out = g_maps[i].map;
+            return FERRIS_OK;
+        }
+    CUtensorMap m;
+    int rc = ferris_make_tensor_map_2d(&m, base, rows, (uint64_t)d, (uint64_t)d, TILE_KEYS, 64);
+    if (rc != FERRIS_OK) return rc;
+    const int slot = g_map_count < MAP_CACHE ? g_map_count++ : 0;
+    g_maps[slot] = {base, rows, d, m};
+    *out = m;
+    return FERRIS_OK;
+}
+
+int check_common(int nh, int nkv, int d, int page_size, int max_blocks) {
+    if (nh <= 0 || nkv <= 0 || nh % nkv != 0) FERRIS_REFUSE("attention: %d heads over %d kv heads", nh, nkv);
+    if (nh / nkv > 16) FERRIS_REFUSE("tensor-core attention takes groups of at most 16 heads, not %d", nh / nkv);
+    if (d != 64 && d != 128) FERRIS_REFUSE("tensor-core attention takes head sizes 64 and 128, not %d", d);
+    if (page_size <= 0 || page_size % TILE_KEYS) FERRIS_REFUSE("tensor-core attention takes pages of a multiple of 16 tokens, not %d", page_size);
+    if (max_blocks <= 0) FERRIS_REFUSE("attention: max_blocks=%d", max_blocks);
+    return FERRIS_OK;
+}
+
+template <typename F>
+int set_smem(F kernel, size_t bytes) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) {
+        ferris_set_error("attention: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    return FERRIS_OK;
+}
+
+}  // namespace
+
+// Floats of scratch that decode attention with `splits` > 1 needs: partial outputs and (m, l) pairs.
+FERRIS_API long long ferris_decode_attention_scratch_floats(int tokens, int nh, int d, int splits) {
+    if (splits <= 1) return 0;
+    return (long long)tokens * nh * splits * (d + 2);
+}
+
+// Single-token steps.  scratch: fp32 [tokens * nh * splits * (d + 2)] when splits > 1.
+FERRIS_API int ferris_decode_attention(const void* q, int ldq, void* out, int ldo, const void* k_cache,
+                                       const void* v_cache, long long cache_pages, const int* block_tables,
+                                       int max_blocks, const int* token_seq, const int* positions, int tokens, int nh,
+                                       int nkv, int d, int page_size, int window, float scale, int splits, float* scratch,
+                                       void* stream) {
+    if (tokens <= 0) return FERRIS_OK;
+    int rc = check_common(nh, nkv, d, page_size, max_blocks);
+    if (rc != FERRIS_OK) return rc;
+    if (splits < 1 || splits > 65535) FERRIS_REFUSE("decode attention: %d splits", splits);
+    if (splits > 1 && !scratch) FERRIS_REFUSE("decode attention: splitting the keys needs scratch memory");
+    if (nkv > 65535 || tokens > 65535) FERRIS_REFUSE("decode attention: %d tokens x %d kv heads exceed one launch", tokens, nkv);
+    const uint64_t rows = (uint64_t)cache_pages * nkv * page_size;
+    CUtensorMap mk, mv;
+    if ((rc = cache_map(k_cache, rows, d, &mk)) != FERRIS_OK) return rc;
+    if ((rc = cache_map(v_cache, rows, d, &mv)) != FERRIS_OK) return rc;
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)tokens * nh * splits * d : nullptr;
+    dim3 grid(splits, nkv, tokens);
+    cudaStream_t s = (cudaStream_t)stream;
+    int* status = ferris_status_ptr();
+    if (d == 64) {
+        constexpr int ST = 3;
+        const size_t smem = (size_t)WARPS * ST * 2 * TILE_KEYS * 64 * 2 + 1024;
+        if ((rc = set_smem(decode_attention_kernel<64, ST>, smem)) != FERRIS_OK) return rc;
+        decode_attention_kernel<64, ST><<<grid, WARPS * 32, smem, s>>>(
+            mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
+            nh, nkv, page_size, window, scale, splits, status);
+        if (splits > 1) decode_merge_kernel<64><<<dim3(tokens, nh), 64, 0, s>>>(part_o, part_ml, (bf16*)out, ldo, nh, splits);
+    } else {
+        constexpr int ST = 2;
+        const size_t smem = (size_t)WARPS * ST * 2 * TILE_KEYS * 128 * 2 + 1024;
+        if ((rc = set_smem(decode_attention_kernel<128, ST>, smem)) != FERRIS_OK) return rc;
+        decode_attention_kernel<128, ST><<<grid, WARPS * 32, smem, s>>>(
+            mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
+            nh, nkv, page_size, window, scale, splits, status);
+        if (splits > 1) decode_merge_kernel<128><<<dim3(tokens, nh), 128, 0, s>>>(part_o, part_ml, (bf16*)out, ldo, nh, splits);
+    }
+    FERRIS_LAUNCH_CHECK();
+}
+
+// Portions of prompts (and anything else: a request with one token is a portion of one).
+FERRIS_API int ferris_prefill_attention(const void* q, int ldq, void* out, int ldo, const void* k_cache,
+                                        const void* v_cache, long long cache_pages, const int* block_tables,
+                                        int max_blocks, const int* seq_q_start, const int* seq_start_pos, int num_seqs,
+                                        int max_q_len, int nh, int nkv, int d, int page_size, int window, float scale,
+                                        void* stream) {
+    if (num_seqs <= 0 || max_q_len <= 0) return FERRIS_OK;
+    int rc = check_common(nh, nkv, d, page_size, max_blocks);
+    if (rc != FERRIS_OK) return rc;
+    if (nkv > 65535 || num_seqs > 65535) FERRIS_REFUSE("prefill attention: %d requests x %d kv heads exceed one launch", num_seqs, nkv);
+    const uint64_t rows = (uint64_t)cache_pages * nkv * page_size;
+    CUtensorMap mk, mv;
+    if ((rc = cache_map(k_cache, rows, d, &mk)) != FERRIS_OK) return rc;
+    if ((rc = cache_map(v_cache, rows, d, &mv)) != FERRIS_OK) return rc;
+    const int G = nh / nkv;
+    dim3 grid(((size_t)max_q_len * G + PF_ROWS - 1) / PF_ROWS, nkv, num_seqs);
+    cudaStream_t s = (cudaStream_t)stream;
+    int* status = ferris_status_ptr();
+    if (d == 64) {
+        constexpr int ST = 3;
+        const size_t smem = (size_t)ST * PF_STAGE_TILES * 2 * TILE_KEYS * 64 * 2 + 1024;
+        if ((rc = set_smem(prefill_attention_kernel<64, ST>, smem)) != FERRIS_OK) return rc;
+        prefill_attention_kernel<64, ST><<<grid, (WARPS + 1) * 32, smem, s>>>(
+            mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, block_tables, max_blocks, seq_q_start, seq_start_pos, nh, nkv,
+            page_size, window, scale, status);
+    } else {
+        constexpr int ST = 2;
+        const size_t smem = (size_t)ST * PF_STAGE_TILES * 2 * TILE_KEYS * 128 * 2 + 1024;
+        if ((rc = set_smem(prefill_attention_kernel<128, ST>, smem)) != FERRIS_OK) return rc;
+        prefill_attention_kernel<128, ST><<<grid, (WARPS + 1) * 32, smem, s>>>(
+            mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, block_tables, max_blocks, seq_q_start, seq_start_pos, nh, nkv,
+            page_size, window, scale, status);
+    }
+    FERRIS_LAUNCH_CHECK();
+}

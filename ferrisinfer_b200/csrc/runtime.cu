@@ -3,6 +3,7 @@
 #include <stdio.h>
 
 #include "common.cuh"
+#include "sm100.cuh"
 
 static thread_local char g_error[512] = "";
 
@@ -34,4 +35,65 @@ FERRIS_API int ferris_sm_count() {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
     return n;
 }
-// touch
+
+// ---------------------------------------------------------------------------------------------
+// The status word that kernels with bounded waits write when a wait runs out.
+// ---------------------------------------------------------------------------------------------
+static __device__ int g_status_word = 0;
+static int* g_status_ptr = nullptr;
+
+int* ferris_status_ptr() {
+    if (!g_status_ptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_word) == cudaSuccess) g_status_ptr = (int*)p;
+    }
+    return g_status_ptr;
+}
+
+// Reads and clears the status word (synchronises the device).  0 = no kernel reported a fault.
+FERRIS_API int ferris_kernel_status() {
+    int* p = ferris_status_ptr();
+    if (!p) return -1;
+    int v = 0, zero = 0;
+    if (cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Tensor maps.  cuTensorMapEncodeTiled is reached through the runtime's driver entry point, so the
+// library links against no driver stub.
+// ---------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+int ferris_make_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                              uint32_t box_rows, uint32_t box_cols) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) FERRIS_REFUSE("tensor map: the driver offers no cuTensorMapEncodeTiled");
+    if (((uintptr_t)base & 15) || ((row_stride * 2) & 15) || box_cols * 2 != 128 || box_rows == 0 || box_rows > 256)
+        FERRIS_REFUSE("tensor map: base %p, row stride %llu, box %u x %u do not meet the alignment rules", base,
+                      (unsigned long long)row_stride, box_rows, box_cols);
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {row_stride * 2};
+    cuuint32_t box[2] = {box_cols, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) FERRIS_REFUSE("tensor map: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return FERRIS_OK;
+}

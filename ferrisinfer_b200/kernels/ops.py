@@ -220,11 +220,107 @@ def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
     )
 
 
+def kernel_status() -> int:
+    """Reads and clears the device status word (synchronises).  0: no kernel gave up a bounded wait;
+    otherwise (code << 16) | place."""
+    return int(_lib().ferris_kernel_status())
+
+
+def check_kernel_status() -> None:
+    v = kernel_status()
+    if v:
+        raise KernelError(f"a kernel gave up a bounded wait (code {v >> 16}, place {v & 0xffff}); its results are wrong")
+
+
+_sm_count = None
+
+
+def sm_count() -> int:
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = max(1, _lib().ferris_sm_count())
+    return _sm_count
+
+
+def tensor_core_attention_takes(dtype, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
+    """Whether the TMA + tensor-core attention kernels take this geometry (the general kernel takes the rest)."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and page_size % 16 == 0
+            and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 16)
+
+
+def decode_splits(tokens: int, num_kv_heads: int, max_kv_len: int) -> int:
+    """Into how many key ranges a single-token step is split, so that the GPU's SMs have work:
+    about two CTAs per SM, and at least eight 16-key tiles per CTA."""
+    base = max(1, tokens * num_kv_heads)
+    want = -(-2 * sm_count() // base)
+    most = max(1, (max_kv_len // 16) // 8)
+    return max(1, min(want, most))
+
+
+def decode_attention(qkv, out, k_cache, v_cache, block_tables, token_seq, positions, num_heads, num_kv_heads,
+                     head_dim, window, scale, splits, scratch):
+    """Split-KV attention for steps of single tokens (bf16, head size 64 or 128)."""
+    T, _, ldq = _rows(qkv, "attention queries")
+    _, _, ldo = _rows(out, "attention output")
+    need = T * num_heads * splits * (head_dim + 2) if splits > 1 else 0
+    if need and (scratch is None or scratch.numel() < need or scratch.dtype != torch.float32):
+        raise KernelError(f"decode attention with {splits} splits needs {need} floats of scratch")
+    _check(
+        _lib().ferris_decode_attention(_ptr(qkv), _c_int(ldq), _ptr(out), _c_int(ldo), _ptr(k_cache), _ptr(v_cache),
+                                       ctypes.c_longlong(k_cache.shape[0]), _ptr(block_tables),
+                                       _c_int(block_tables.shape[1]), _ptr(token_seq), _ptr(positions), _c_int(T),
+                                       _c_int(num_heads), _c_int(num_kv_heads), _c_int(head_dim),
+                                       _c_int(k_cache.shape[2]), _c_int(window or 0), _c_float(scale), _c_int(splits),
+                                       _ptr(scratch if need else None), _stream()),
+        "decode attention",
+    )
+
+
+def prefill_attention(qkv, out, k_cache, v_cache, block_tables, seq_q_start, seq_start_pos, num_seqs, max_q_len,
+                      num_heads, num_kv_heads, head_dim, window, scale):
+    """Tensor-core attention for portions of prompts (bf16, head size 64 or 128)."""
+    _, _, ldq = _rows(qkv, "attention queries")
+    _, _, ldo = _rows(out, "attention output")
+    _check(
+        _lib().ferris_prefill_attention(_ptr(qkv), _c_int(ldq), _ptr(out), _c_int(ldo), _ptr(k_cache), _ptr(v_cache),
+                                        ctypes.c_longlong(k_cache.shape[0]), _ptr(block_tables),
+                                        _c_int(block_tables.shape[1]), _ptr(seq_q_start), _ptr(seq_start_pos),
+                                        _c_int(num_seqs), _c_int(max_q_len), _c_int(num_heads), _c_int(num_kv_heads),
+                                        _c_int(head_dim), _c_int(k_cache.shape[2]), _c_int(window or 0), _c_float(scale),
+                                        _stream()),
+        "prefill attention",
+    )
+
+
 def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale):
     """Attention of the step's tokens over the paged cache (their own keys are in it already).
-    ``ctx`` is the step context (token-to-request map, positions, request lengths)."""
-    paged_attention_simt(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
-                         num_kv_heads, head_dim, window, scale)
+    ``ctx`` is the step context.  bf16 with head size 64 / 128 runs on the tensor cores: the split-KV
+    kernel when every request brings one token, the prefill kernel otherwise; every other geometry, and
+    the 32-bit path, runs the general kernel."""
+    _need(k_cache, "key cache", qkv.dtype)
+    _need(v_cache, "value cache", qkv.dtype)
+    _need(block_tables, "block tables", torch.int32)
+    if k_cache.dim() != 4 or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim \
+            or v_cache.shape != k_cache.shape or block_tables.dim() != 2:
+        raise KernelError(f"attention: cache {tuple(k_cache.shape)}, tables {tuple(block_tables.shape)}")
+    if out.dtype != qkv.dtype or out.shape[1] != num_heads * head_dim or out.shape[0] != qkv.shape[0]:
+        raise KernelError(f"attention: q {tuple(qkv.shape)}, out {tuple(out.shape)}")
+    if not tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim, k_cache.shape[2]):
+        paged_attention_simt(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
+                             num_kv_heads, head_dim, window, scale)
+        return
+    T = qkv.shape[0]
+    if ctx.max_q_len == 1:
+        kv_span = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
+        splits = decode_splits(T, num_kv_heads, kv_span)
+        scratch = None
+        if splits > 1:
+            scratch = ctx.workspace.get("attn_split_scratch", (T * num_heads * splits * (head_dim + 2),), torch.float32)
+        decode_attention(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
+                         num_kv_heads, head_dim, window, scale, splits, scratch)
+    else:
+        prefill_attention(qkv, out, k_cache, v_cache, block_tables, ctx.seq_q_start, ctx.seq_start_pos, ctx.num_seqs,
+                          ctx.max_q_len, num_heads, num_kv_heads, head_dim, window, scale)
 
 
 def sample(logits: torch.Tensor, out_token: torch.Tensor, out_prob: Optional[torch.Tensor] = None,

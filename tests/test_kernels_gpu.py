@@ -199,7 +199,15 @@ class AttentionCase:
         to = lambda t, dt: t.to(dt).to(self.device)
         from types import SimpleNamespace
 
+        from ferrisinfer_b200.engine.workspace import Workspace
+
+        starts = [0]
+        for _, ql in self.seqs:
+            starts.append(starts[-1] + ql)
         ctx = SimpleNamespace(token_seq=to(torch.tensor(token_seq), torch.int32),
+                              seq_q_start=to(torch.tensor(starts), torch.int32),
+                              seq_start_pos=to(torch.tensor([kv - ql for kv, ql in self.seqs]), torch.int32),
+                              workspace=Workspace(self.device),
                               positions=to(torch.tensor(positions), torch.int32),
                               seqs=[SimpleNamespace(q_start=sum(q for _, q in self.seqs[:i]), q_len=ql, start_pos=kv - ql)
                                     for i, (kv, ql) in enumerate(self.seqs)],
@@ -235,6 +243,9 @@ def run_attention(case, impl):
     attention_impls()[impl](qkv, out, k, v, tables, ctx, case.nh, case.nkv, case.d, case.window,
                             1.0 / math.sqrt(case.d))
     torch.cuda.synchronize()
+    from ferrisinfer_b200.kernels import ops
+
+    assert ops.kernel_status() == 0, "a bounded wait ran out"
     return out.cpu().double()
 
 
@@ -274,16 +285,21 @@ def test_attention_finds_one_far_key_among_hundreds(q_len, dtype, impl, device):
 
 @pytest.mark.parametrize("impl", ["simt", "dispatch"])
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("window, page", [(21, 8), (16, 16), (33, 16), (5, 4)])
-def test_attention_window_edges(window, page, dtype, impl, device):
+@pytest.mark.parametrize("decode_only", [False, True])
+@pytest.mark.parametrize("window, page, d", [(21, 8, 32), (16, 16, 32), (33, 16, 64), (5, 4, 16), (16, 16, 64),
+                                             (47, 32, 128), (100, 16, 64)])
+def test_attention_window_edges(window, page, d, decode_only, dtype, impl, device):
     """The key at P - W + 1 is the last one inside the window; the key at P - W is outside.  Both carry loud
     values, so a window that is off by one shows."""
-    nh, nkv, d = 4, 2, 32
-    seqs = [(100, 1), (100, 30), (window, 1), (window + 1, 2), (64, 64)]
+    nh, nkv = 4, 2
+    seqs = [(100, 1), (100, 30), (window, 1), (window + 1, 2), (64, 64), (300, 1)]
+    if decode_only:
+        seqs = [(kv, 1) for kv, _ in seqs]
     case = AttentionCase(device, dtype, nh, nkv, d, page, seqs, seed=window, window=window)
     P = 99
     case.v[0][P - window + 1] += 50.0  # inside: must show
-    case.v[0][P - window] -= 5000.0  # outside: must not
+    if P - window >= 0:
+        case.v[0][P - window] -= 5000.0  # outside: must not
     got, want = run_attention(case, impl), case.reference()
     assert got[0].max() > 0.5 and got[0].min() > -100.0
     assert torch.allclose(got, want, atol=ATT_TOL[dtype]["atol"] * 10, rtol=ATT_TOL[dtype]["rtol"])
@@ -319,10 +335,34 @@ def test_argmax_takes_the_lowest_index_among_equal_maxima(device):
         assert abs(prob[i].item() - want[i][1]) < 1e-6 * max(1.0, 1 / want[i][1]) + 1e-6
 
 
+def exact_interval(row, T, k, p, token):
+    """In float64: the mass before ``token`` and through it in the reference's order (descending logit, ascending
+    index), after the top-k and top-p cuts, both as fractions of the retained mass; None if the token was cut."""
+    V = row.shape[0]
+    order = np.lexsort((np.arange(V), -row.astype(np.float64)))
+    k = V if k <= 0 else min(k, V)
+    order = order[:k]
+    Tc = max(np.float32(T), np.finfo(np.float32).eps)
+    w = np.exp((row[order] / Tc - row[order[0]] / Tc).astype(np.float64))
+    cum = np.cumsum(w)
+    kept = k
+    if p < 1.0:
+        kept = int(np.searchsorted(cum, cum[-1] * np.float64(np.float32(p)), side="left")) + 1
+        kept = min(max(kept, 1), k)
+    where = np.nonzero(order[:kept + 1] == token)[0]  # one more than kept: the cut itself may fall within rounding
+    if where.size == 0:
+        return None
+    i = int(where[0])
+    total = cum[kept - 1]
+    return (cum[i] - w[i]) / total, cum[i] / total
+
+
 @pytest.mark.parametrize("V", [257, 5000, 151936])
 def test_sampling_matches_the_plain_sampler(V, device):
-    """Rows with different temperatures, top_k and top_p; each row draws from its own generator state.  A draw
-    may differ from the sequential f32 walk only when the threshold lies within rounding of a boundary."""
+    """Rows with different temperatures, top_k and top_p; each row draws from its own generator state.
+    The chosen token must be the one whose span of the retained mass (float64, the reference's order) holds the
+    draw u.  For small vocabularies it must also be the token that the reference's sequential f32 walk picks
+    (over 150,000 tokens that walk's own f32 sums are coarser than a token's span, so it is no oracle there)."""
     from ferrisinfer_b200.kernels import ops
 
     rows = 24 if V > 100000 else 48
@@ -347,17 +387,27 @@ def test_sampling_matches_the_plain_sampler(V, device):
         differ = 0
         for r in range(rows):
             T, k, p = temperature[r].item(), top_k[r].item(), top_p[r].item()
+            row = logits[r].numpy()
             rng = plain.XorShift64Star(int(states[slots[r]].item()))
-            want_tok, want_prob = plain.sample(logits[r].numpy(), T, k, p, rng)
             greedy = T <= 0 or k == 1 or p <= 0
-            if not greedy:
-                states[slots[r]] = rng.state - (1 << 64) if rng.state >= 1 << 63 else rng.state
-            assert dev_states[slots[r]].item() == states[slots[r]].item(), "generator state advances once per draw"
-            if tok[r].item() != want_tok:
-                differ += 1
-                assert not greedy
-            else:
-                assert abs(prob[r].item() - want_prob) < 1e-3 * want_prob + 1e-6
+            if greedy:
+                assert tok[r].item() == plain.greedy(row)[0]
+                assert dev_states[slots[r]].item() == states[slots[r]].item(), "greedy rows draw nothing"
+                continue
+            if V <= 5000:
+                want_tok, want_prob = plain.sample(row, T, k, p, plain.XorShift64Star(rng.state))
+                if tok[r].item() != want_tok:
+                    differ += 1
+                else:
+                    assert abs(prob[r].item() - want_prob) < 1e-3 * want_prob + 1e-6
+            u = rng.next_f32()
+            states[slots[r]] = rng.state - (1 << 64) if rng.state >= 1 << 63 else rng.state
+            assert dev_states[slots[r]].item() == states[slots[r]].item(), "the generator advances once per draw"
+            span = exact_interval(row, T, k, p, tok[r].item())
+            assert span is not None, (r, "the chosen token lies outside the top-k / top-p set")
+            lo, hi = span
+            assert lo - 1e-5 <= u <= hi + 1e-5, (r, T, k, p, u, lo, hi)
+            assert abs(prob[r].item() - (hi - lo)) < 1e-3 * (hi - lo) + 1e-6
         assert differ <= 1, differ
 
 

@@ -591,3 +591,59 @@ FERRIS_API int ferris_prefill_attention(const void* q, int ldq, void* out, int l
     }
     FERRIS_LAUNCH_CHECK();
 }
+
+// =============================================================================================
+// The same decode attention for callers that cannot allocate: the partial results of the splits go
+// to a fixed array in the device image instead of a buffer that the caller brings (no_alloc.h).
+// =============================================================================================
+#include "no_alloc.h"
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) float g_static_scratch[FERRIS_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_ptr[MAX_DEVICES] = {};
+
+// Device address of the array on the current device; looked up once per device.
+int static_scratch(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        ferris_set_error("static scratch: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    if (dev < 0 || dev >= MAX_DEVICES) FERRIS_REFUSE("static scratch: device %d is beyond the %d this build tracks", dev, MAX_DEVICES);
+    if (!g_static_scratch_ptr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p) {
+            ferris_set_error("static scratch: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+            return e != cudaSuccess ? (int)e : FERRIS_BAD_ARGUMENT;
+        }
+        g_static_scratch_ptr[dev] = (float*)p;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return FERRIS_OK;
+}
+}  // namespace
+
+int ferris_decode_attention_static_scratch(const void* q, int ldq, void* out, int ldo, const void* k_cache,
+                                           const void* v_cache, long long cache_pages, const int* block_tables,
+                                           int max_blocks, const int* token_seq, const int* positions, int tokens,
+                                           int nh, int nkv, int d, int page_size, int window, float scale, int splits,
+                                           void* stream) {
+    if (tokens <= 0) return FERRIS_OK;
+    if (splits < 1) FERRIS_REFUSE("decode attention: %d splits", splits);
+    const long long need = ferris_decode_attention_scratch_floats(tokens, nh, d, splits);
+    if (need > (long long)FERRIS_STATIC_SCRATCH_FLOATS)
+        FERRIS_REFUSE("decode attention without allocation: %d tokens x %d heads x %d splits x (%d + 2) = %lld floats of "
+                      "partial results exceed the built-in scratch of %u floats; use fewer splits or tokens, or the "
+                      "entry point that takes a scratch buffer",
+                      tokens, nh, splits, d, need, FERRIS_STATIC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    int rc = static_scratch(&scratch);
+    if (rc != FERRIS_OK) return rc;
+    return ferris_decode_attention(q, ldq, out, ldo, k_cache, v_cache, cache_pages, block_tables, max_blocks, token_seq,
+                                   positions, tokens, nh, nkv, d, page_size, window, scale, splits, scratch, stream);
+}

@@ -1,0 +1,345 @@
+// bf16 matrix product on the 5th-generation tensor cores:  out[t, n] = sum_k x[t, k] * w[n, k]  (+ bias[n]).
+//
+// Both operands are K-major as the model folder and the activations store them, so nothing is
+// transposed.  The WEIGHT rows are the M side of the MMA (128 per tile) and the TOKENS its N side
+// (16 to 256 per tile): a decode step of a few tokens fills a whole 128-row MMA with weights, which is
+// what streams from HBM, and a prefill step uses the same kernel with wide token tiles.
+//
+// One CTA per (weight tile, token tile, K split); 6 warps:
+//   warp 0    TMA producer: 64-wide K slices of the weight tile(s) and the token tile into a ring of
+//             shared-memory stages (128-byte swizzle), completion on mbarriers;
+//   warp 1    allocates tensor memory, issues tcgen05.mma (one thread) from shared-memory descriptors
+//             into fp32 accumulators in TMEM, frees each stage with tcgen05.commit;
+//   warps 2-5 epilogue: tcgen05.ld of their lane quarter (lane = weight row), then bias / store /
+//             fp32 residual accumulation / SwiGLU, or a partial for the K split.
+// With a K split, the CTA that finishes last adds the partials in split order (a fixed order, so
+// the result does not depend on timing) and runs the epilogue.
+//
+// SwiGLU mode keeps TWO accumulators (gate rows and up rows of the same outputs, two MMAs per K
+// slice) so that silu(g) * u is formed in the epilogue and the [T, 2I] intermediate never exists.
+//
+// Formula of the product: crates/ferrisinfer-kernel/src/cpu/matmul.rs:46-118; bias:
+// crates/ferrisinfer-runtime/src/reference.rs:1132-1191; SwiGLU: crates/ferrisinfer-runtime/src/reference.rs:346-360.
+#include "common.cuh"
+#include "sm100.cuh"
+
+namespace {
+
+constexpr int BLOCK_N = 128;  // weight rows per tile (MMA M)
+constexpr int BLOCK_K = 64;   // one 128-byte swizzle row of bf16
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr int MAX_STAGES = 8;
+
+enum Mode { STORE_BF16 = 0, STORE_F32 = 1, ACCUM_F32 = 2, SWIGLU_BF16 = 3 };
+
+struct Params {
+    void* out;
+    const float* bias;
+    float* scratch;     // [splits][accumulators][T][N] fp32 partials when splits > 1
+    int* counters;      // one per (weight tile, token tile); zero between launches
+    int T, N, K, ldo;
+    int bt;             // tokens per tile
+    int stages;
+    int kblocks;        // ceil(K / 64)
+    int splits;
+    int up_row_offset;  // SwiGLU: row of the weight matrix where the up rows start
+    int* status;
+};
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return u * (g * (1.0f / (1.0f + expf(-g)))); }
+
+template <int MODE>
+__device__ __forceinline__ void write_out(const Params& p, int t, int n, float a, float b) {
+    if (MODE == STORE_BF16) {
+        reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(a + (p.bias ? p.bias[n] : 0.0f));
+    } else if (MODE == STORE_F32) {
+        reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = a + (p.bias ? p.bias[n] : 0.0f);
+    } else if (MODE == ACCUM_F32) {
+        float* o = reinterpret_cast<float*>(p.out) + (size_t)t * p.ldo + n;
+        *o = *o + (a + (p.bias ? p.bias[n] : 0.0f));
+    } else {
+        reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(silu_mul(a, b));
+    }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(THREADS)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                        const Params p) {
+    constexpr int ACCS = MODE == SWIGLU_BF16 ? 2 : 1;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full[MAX_STAGES], empty[MAX_STAGES], accum_full;
+    __shared__ uint32_t tmem_base;
+    __shared__ int is_last;
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BLOCK_N, t0 = blockIdx.y * p.bt, split = blockIdx.z;
+    const int a_bytes = BLOCK_N * BLOCK_K * 2, b_bytes = p.bt * BLOCK_K * 2;
+    const int stage_bytes = ACCS * a_bytes + b_bytes;
+    const int per_split = (p.kblocks + p.splits - 1) / p.splits;
+    const int kb0 = split * per_split, kb1 = min(kb0 + per_split, p.kblocks);
+    const int n_kb = max(kb1 - kb0, 0);
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < (uint32_t)(ACCS * p.bt)) tmem_cols <<= 1;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&map_w);
+        tma_prefetch_descriptor(&map_x);
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(&accum_full, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(&tmem_base, tmem_cols);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem = tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % p.stages;
+                if (i >= p.stages && !mbar_wait(&empty[s], ((i / p.stages) - 1) & 1, p.status, 10)) break;
+                uint8_t* st = smem + (size_t)s * stage_bytes;
+                const int k = (kb0 + i) * BLOCK_K;
+                mbar_expect_tx(&full[s], stage_bytes);
+                tma_load_2d(st, &map_w, k, n0, &full[s]);
+                if (ACCS == 2) tma_load_2d(st + a_bytes, &map_w, k, p.up_row_offset + n0, &full[s]);
+                tma_load_2d(st + ACCS * a_bytes, &map_x, k, t0, &full[s]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(BLOCK_N, p.bt);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % p.stages;
+                ok = mbar_wait(&full[s], (i / p.stages) & 1, p.status, 11);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t st = smem_u32(smem + (size_t)s * stage_bytes);
+                const uint64_t a_desc = umma_desc_k_major_sw128(st);
+                const uint64_t a2_desc = umma_desc_k_major_sw128(st + a_bytes);
+                const uint64_t b_desc = umma_desc_k_major_sw128(st + ACCS * a_bytes);
+#pragma unroll
+                for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                    const uint64_t adv = (uint64_t)((k * UMMA_K * 2) >> 4);  // 32 bytes per K step, in 16-byte units
+                    const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                    tcgen05_mma_bf16(tmem, a_desc + adv, b_desc + adv, idesc, acc);
+                    if (ACCS == 2) tcgen05_mma_bf16(tmem + p.bt, a2_desc + adv, b_desc + adv, idesc, acc);
+                }
+                tcgen05_commit(&empty[s]);  // the stage is free once these MMAs have read it
+            }
+            tcgen05_commit(&accum_full);
+        }
+    } else {
+        // epilogue: this warp's quarter of the 128 TMEM lanes
+        const int quarter = warp & 3;
+        const int n = n0 + quarter * 32 + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        const bool have = n_kb > 0 && mbar_wait(&accum_full, 0, p.status, 12);
+        tcgen05_fence_after();
+        const bool n_ok = n < p.N;
+        if (p.splits == 1) {
+            if (have) {
+                for (int c0 = 0; c0 < p.bt; c0 += 16) {
+                    uint32_t ra[16], rb[16];
+                    tmem_load_32x16(lane_addr + c0, ra);
+                    if (ACCS == 2) tmem_load_32x16(lane_addr + p.bt + c0, rb);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const int t = t0 + c0 + c;
+                        if (n_ok && t < p.T)
+                            write_out<MODE>(p, t, n, __uint_as_float(ra[c]), ACCS == 2 ? __uint_as_float(rb[c]) : 0.0f);
+                    }
+                }
+            }
+        } else {
+            // partials of this split: scratch[((split * ACCS + a) * T + t) * N + n]
+            for (int c0 = 0; c0 < p.bt; c0 += 16) {
+                uint32_t ra[16], rb[16];
+                if (have) {
+                    tmem_load_32x16(lane_addr + c0, ra);
+                    if (ACCS == 2) tmem_load_32x16(lane_addr + p.bt + c0, rb);
+                    tmem_load_wait();
+                }
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const int t = t0 + c0 + c;
+                    if (n_ok && t < p.T) {
+                        p.scratch[((size_t)(split * ACCS) * p.T + t) * p.N + n] = have ? __uint_as_float(ra[c]) : 0.0f;
+                        if (ACCS == 2)
+                            p.scratch[((size_t)(split * ACCS + 1) * p.T + t) * p.N + n] = have ? __uint_as_float(rb[c]) : 0.0f;
+                    }
+                }
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (threadIdx.x == 64) {
+                const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+                const int old = atomicAdd(&p.counters[tile], 1);
+                is_last = old == p.splits - 1;
+                if (is_last) p.counters[tile] = 0;  // ready for the next launch
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (is_last) {
+                __threadfence();
+                const int t_end = min(t0 + p.bt, p.T);
+                if (n_ok) {
+                    for (int t = t0; t < t_end; ++t) {
+                        float a = 0.0f, b = 0.0f;
+                        for (int s = 0; s < p.splits; ++s) {
+                            a += __ldcg(&p.scratch[((size_t)(s * ACCS) * p.T + t) * p.N + n]);
+                            if (ACCS == 2) b += __ldcg(&p.scratch[((size_t)(s * ACCS + 1) * p.T + t) * p.N + n]);
+                        }
+                        write_out<MODE>(p, t, n, a, b);
+                    }
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem, tmem_cols);
+    }
+}
+
+struct WeightMap {
+    const void* base;
+    uint64_t rows, cols, ld;
+    CUtensorMap map;
+};
+constexpr int WEIGHT_MAPS = 1024;
+WeightMap g_weight_maps[WEIGHT_MAPS];
+int g_weight_map_count = 0;
+
+int weight_map(const void* base, uint64_t rows, uint64_t cols, uint64_t ld, CUtensorMap* out) {
+    for (int i = 0; i < g_weight_map_count; ++i) {
+        const WeightMap& m = g_weight_maps[i];
+        if (m.base == base && m.rows == rows && m.cols == cols && m.ld == ld) {
+            *out = m.map;
+            return FERRIS_OK;
+        }
+    }
+    CUtensorMap m;
+    int rc = ferris_make_tensor_map_2d(&m, base, rows, cols, ld, BLOCK_N, BLOCK_K);
+    if (rc != FERRIS_OK) return rc;
+    const int slot = g_weight_map_count < WEIGHT_MAPS ? g_weight_map_count++ : 0;
+    g_weight_maps[slot] = {base, rows, cols, ld, m};
+    *out = m;
+    return FERRIS_OK;
+}
+
+int g_sms = 0;
+
+template <int MODE>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, size_t smem, cudaStream_t s) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+        ferris_set_error("gemm: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    gemm_tcgen05_kernel<MODE><<<grid, THREADS, smem, s>>>(mw, mx, p);
+    FERRIS_LAUNCH_CHECK();
+}
+
+}  // namespace
+
+// How the launcher would cut a product: token tile, K splits, and the fp32 scratch / counters it needs.
+// accumulators: 2 for SwiGLU, else 1.
+FERRIS_API int ferris_gemm_tcgen05_plan(int T, int N, int K, int accumulators, int* bt_out, int* splits_out,
+                                        long long* scratch_floats, int* counters) {
+    if (g_sms <= 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sms <= 0)
+            g_sms = 148;
+    }
+    int bt = 16;
+    while (bt < T && bt < 256) bt <<= 1;
+    const int n_tiles = (N + BLOCK_N - 1) / BLOCK_N, t_tiles = (T + bt - 1) / bt;
+    const int kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+    int splits = 1;
+    const int tiles = n_tiles * t_tiles;
+    if (tiles < g_sms && kblocks >= 4) {
+        splits = (g_sms + tiles - 1) / tiles;
+        if (splits > kblocks / 2) splits = kblocks / 2;
+        if (splits < 1) splits = 1;
+        // no split may be empty
+        const int per = (kblocks + splits - 1) / splits;
+        splits = (kblocks + per - 1) / per;
+    }
+    *bt_out = bt;
+    *splits_out = splits;
+    *scratch_floats = splits > 1 ? (long long)splits * accumulators * T * N : 0;
+    *counters = splits > 1 ? tiles : 0;
+    return FERRIS_OK;
+}
+
+// x: bf16 [T, K] rows ldx apart; w: bf16 [rows_w, K] rows ldw apart (rows_w = N, or for SwiGLU at
+// least up_row_offset + N); out: [T, N] rows ldo apart in the mode's type.
+// mode: 0 bf16 = acc + bias; 1 fp32 = acc + bias; 2 fp32 += acc + bias; 3 bf16 = silu(gate) * up.
+// scratch / counters: as ferris_gemm_tcgen05_plan says (counters must be zero; they are left zero).
+FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N,
+                                   int K, int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch,
+                                   int* counters, void* stream) {
+    if (T <= 0 || N <= 0) return FERRIS_OK;
+    if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ldx < K || ldw < K)
+        FERRIS_REFUSE("tensor-core gemm: K=%d and row strides %d, %d must be multiples of 8 elements", K, ldx, ldw);
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) FERRIS_REFUSE("tensor-core gemm: operands must be 16-byte aligned");
+    if (mode < 0 || mode > 3) FERRIS_REFUSE("tensor-core gemm: unknown mode %d", mode);
+    if (mode == SWIGLU_BF16 && (bias || up_row_offset + N > rows_w)) FERRIS_REFUSE("tensor-core gemm: bad SwiGLU operands");
+    if (mode != SWIGLU_BF16 && N > rows_w) FERRIS_REFUSE("tensor-core gemm: %d outputs from %d weight rows", N, rows_w);
+    if (ldo < N) FERRIS_REFUSE("tensor-core gemm: output row stride %d < %d", ldo, N);
+    const int accs = mode == SWIGLU_BF16 ? 2 : 1;
+    int bt, splits, n_counters;
+    long long scratch_floats;
+    ferris_gemm_tcgen05_plan(T, N, K, accs, &bt, &splits, &scratch_floats, &n_counters);
+    if (splits > 1 && (!scratch || !counters)) FERRIS_REFUSE("tensor-core gemm: a K split needs scratch and counters");
+
+    CUtensorMap mw, mx;
+    int rc = weight_map(w, (uint64_t)rows_w, (uint64_t)K, (uint64_t)ldw, &mw);
+    if (rc != FERRIS_OK) return rc;
+    rc = ferris_make_tensor_map_2d(&mx, x, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bt, BLOCK_K);
+    if (rc != FERRIS_OK) return rc;
+
+    Params p;
+    p.out = out;
+    p.bias = bias;
+    p.scratch = scratch;
+    p.counters = counters;
+    p.T = T;
+    p.N = N;
+    p.K = K;
+    p.ldo = ldo;
+    p.bt = bt;
+    p.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+    p.splits = splits;
+    p.up_row_offset = up_row_offset;
+    p.status = ferris_status_ptr();
+    const int stage_bytes = accs * BLOCK_N * BLOCK_K * 2 + bt * BLOCK_K * 2;
+    int stages = (227 * 1024 - 2048) / stage_bytes;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    const int per_split = (p.kblocks + splits - 1) / splits;
+    if (stages > per_split) stages = per_split;
+    if (stages < 1) stages = 1;
+    p.stages = stages;
+    const size_t smem = (size_t)stages * stage_bytes + 1024;
+    dim3 grid((N + BLOCK_N - 1) / BLOCK_N, (T + bt - 1) / bt, splits);
+    if (grid.y > 65535) FERRIS_REFUSE("tensor-core gemm: %d rows are more than one launch takes", T);
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (mode) {
+        case STORE_BF16: return launch<STORE_BF16>(mw, mx, p, grid, smem, s);
+        case STORE_F32: return launch<STORE_F32>(mw, mx, p, grid, smem, s);
+        case ACCUM_F32: return launch<ACCUM_F32>(mw, mx, p, grid, smem, s);
+        default: return launch<SWIGLU_BF16>(mw, mx, p, grid, smem, s);
+    }
+}

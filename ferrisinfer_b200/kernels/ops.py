@@ -147,10 +147,94 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     )
 
 
+# Scratch of the tensor-core GEMM's K split: fp32 partials and per-tile counters.  Buffers only ever grow, and
+# outgrown ones are kept alive, because a captured CUDA graph may still point at them.
+_gemm_buffers: dict = {}
+_gemm_retired: list = []
+_GEMM_COUNTERS = 8192
+
+
+def _gemm_scratch(device, floats: int, counters: int):
+    key = str(device)
+    entry = _gemm_buffers.get(key)
+    if entry is None or entry[0].numel() < floats or entry[1].numel() < counters:
+        if entry is not None:
+            _gemm_retired.append(entry)
+        size = max(floats, 1 << 20, 0 if entry is None else entry[0].numel())
+        entry = (torch.empty(size, dtype=torch.float32, device=device),
+                 torch.zeros(max(counters, _GEMM_COUNTERS), dtype=torch.int32, device=device))
+        _gemm_buffers[key] = entry
+    return entry
+
+
+def tensor_core_gemm_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """bf16 operands with contiguous rows, K and the row strides multiples of 8, 16-byte aligned bases."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or x.dim() != 2 or w.dim() != 2:
+        return False
+    K = x.shape[1]
+    ldx = x.stride(0) if x.shape[0] > 1 else max(x.stride(0), K)
+    ldw = w.stride(0) if w.shape[0] > 1 else max(w.stride(0), K)
+    return (K % 8 == 0 and ldx % 8 == 0 and ldw % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and (K <= 1 or (x.stride(1) == 1 and w.stride(1) == 1)))
+
+
+def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row_offset: int = 0):
+    """out = x w^T on the tcgen05 tensor cores.  mode 0: bf16 store (+bias); 1: fp32 store (+bias);
+    2: fp32 out += ; 3: bf16 silu(x w[:N]^T) * (x w[up_row_offset:up_row_offset+N]^T)."""
+    T, K, ldx = _rows(x, "gemm input")
+    rows_w, K2, ldw = _rows(w, "gemm weight")
+    T2, N, ldo = _rows(out, "gemm output")
+    if n_out is not None and n_out != N:
+        raise KernelError("gemm: output width differs from what was asked")
+    want_dtype = torch.bfloat16 if mode in (0, 3) else torch.float32
+    if K != K2 or T != T2 or out.dtype != want_dtype:
+        raise KernelError(f"gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}, mode {mode}")
+    if bias is not None:
+        _need(bias, "gemm bias", torch.float32)
+        if bias.numel() != N:
+            raise KernelError("gemm: bias length differs from the output width")
+    accs = 2 if mode == 3 else 1
+    bt, splits, floats, counters = _c_int(), _c_int(), ctypes.c_longlong(), _c_int()
+    _lib().ferris_gemm_tcgen05_plan(_c_int(T), _c_int(N), _c_int(K), _c_int(accs), ctypes.byref(bt), ctypes.byref(splits),
+                                    ctypes.byref(floats), ctypes.byref(counters))
+    scratch = cnt = None
+    if splits.value > 1:
+        scratch, cnt = _gemm_scratch(x.device, floats.value, counters.value)
+    _check(
+        _lib().ferris_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K),
+                                   _c_int(ldx), _c_int(ldw), _c_int(ldo), _c_int(rows_w), _c_int(up_row_offset),
+                                   _ptr(scratch), _ptr(cnt), _stream()),
+        "tensor-core gemm",
+    )
+
+
 def gemm(x, w, bias, out, accumulate: bool = False):
-    """The matrix product of the model: picks the tensor-core kernel for bf16 shapes it takes,
+    """The matrix product of the model, out (+)= x w^T + bias: the tcgen05 kernel for bf16 operands it takes,
     the CUDA-core kernel for everything else (all of the 32-bit path)."""
+    if tensor_core_gemm_takes(x, w) and w.shape[0] == out.shape[1]:
+        if accumulate:
+            gemm_tcgen05(x, w, bias, out, 2)
+        else:
+            gemm_tcgen05(x, w, bias, out, 0 if out.dtype == torch.bfloat16 else 1)
+        return
     gemm_simt(x, w, bias, out, accumulate)
+
+
+def gemm_swiglu(x, gate_up_weight, out, workspace=None):
+    """out [T, I] = silu(x Wg^T) * (x Wu^T) with gate_up_weight = [Wg; Wu] ([2I, K]).  bf16: one tensor-core
+    kernel with two accumulators (the [T, 2I] intermediate never exists); otherwise a product and the SwiGLU kernel."""
+    T, I = out.shape
+    if gate_up_weight.shape[0] != 2 * I:
+        raise KernelError(f"gemm_swiglu: weight {tuple(gate_up_weight.shape)} for {I} outputs")
+    if tensor_core_gemm_takes(x, gate_up_weight) and out.dtype == torch.bfloat16:
+        gemm_tcgen05(x, gate_up_weight, None, out, 3, up_row_offset=I)
+        return
+    if workspace is not None:
+        gate_up = workspace.get("ffn_gate_up", (T, 2 * I), x.dtype)
+    else:
+        gate_up = torch.empty(T, 2 * I, dtype=x.dtype, device=x.device)
+    gemm_simt(x, gate_up_weight, None, gate_up)
+    swiglu(gate_up, out)
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor):

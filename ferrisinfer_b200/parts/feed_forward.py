@@ -37,10 +37,8 @@ class SwiGLU(FeedForward):
 
     def forward(self, x, h, ctx):
         T, I = x.shape[0], self.intermediate_size
-        gate_up = ctx.workspace.get("ffn_gate_up", (T, 2 * I), x.dtype)
-        ops.gemm(x, self.gate_up, None, gate_up)
         act = ctx.workspace.get("ffn_act", (T, I), x.dtype)
-        ops.swiglu(gate_up, act)
+        ops.gemm_swiglu(x, self.gate_up, act, ctx.workspace)
         ops.gemm(act, self.down, None, h, accumulate=True)
 
 

@@ -98,6 +98,79 @@ def test_gemm_rows_do_not_depend_on_the_batch(device):
     assert torch.equal(one[0], full[41])
 
 
+# ------------------------------------------------------------------------- tensor-core gemm
+TC_SHAPES = [(1, 1152, 896), (8, 1152, 896), (64, 896, 4864), (5, 130, 72), (16, 128, 64), (17, 300, 1000),
+             (300, 256, 128), (2048, 384, 256), (33, 1000, 80), (257, 129, 200)]
+
+
+def _gemm_reference(x, w, bias=None):
+    y = x.cpu().double() @ w.cpu().double().t()
+    return y if bias is None else y + bias.cpu().double()
+
+
+def _close(got, want, K, out_dtype):
+    # fp32 accumulation of K bf16 products, then one rounding to the output type
+    scale = want.abs().max().item() + 1e-6
+    atol = scale * (2e-2 if out_dtype == BF16 else 2e-5 * math.sqrt(K) + 1e-5)
+    err = (got.cpu().double() - want).abs().max().item()
+    assert err <= atol, (err, atol)
+
+
+@pytest.mark.parametrize("T, N, K", TC_SHAPES)
+def test_gemm_tcgen05_store_and_accumulate(T, N, K, device):
+    from ferrisinfer_b200.kernels import ops
+
+    x, w = rnd((T, K), BF16, device, 21), rnd((N, K), BF16, device, 22, scale=0.1)
+    bias = rnd((N,), F32, device, 23)
+    assert ops.tensor_core_gemm_takes(x, w)
+    want = _gemm_reference(x, w)
+    out = torch.full((T, N), float("nan"), dtype=BF16, device=device)
+    ops.gemm_tcgen05(x, w, bias, out, 0)
+    _close(out, want + bias.cpu().double(), K, BF16)
+    out32 = torch.full((T, N), float("nan"), dtype=F32, device=device)
+    ops.gemm_tcgen05(x, w, None, out32, 1)
+    _close(out32, want, K, F32)
+    again = torch.empty_like(out32)
+    ops.gemm_tcgen05(x, w, None, again, 1)
+    assert torch.equal(again, out32), "the K split adds its partials in a fixed order"
+    acc = rnd((T, N), F32, device, 24)
+    before = acc.clone()
+    ops.gemm_tcgen05(x, w, bias, acc, 2)
+    _close(acc - before, want + bias.cpu().double(), K, F32)
+    assert ops.kernel_status() == 0
+
+
+@pytest.mark.parametrize("T, I, K", [(1, 4864, 896), (8, 300, 96), (64, 4864, 896), (130, 128, 64), (700, 224, 96)])
+def test_gemm_tcgen05_swiglu(T, I, K, device):
+    from ferrisinfer_b200.kernels import ops
+
+    x, w = rnd((T, K), BF16, device, 25), rnd((2 * I, K), BF16, device, 26, scale=0.2)
+    out = torch.full((T, I), float("nan"), dtype=BF16, device=device)
+    ops.gemm_swiglu(x, w, out)
+    y = _gemm_reference(x, w)
+    want = y[:, I:] * plain.silu(y[:, :I])
+    _close(out, want, K, BF16)
+    assert ops.kernel_status() == 0
+
+
+def test_gemm_dispatch_takes_strided_rows_and_refuses_nothing_silently(device):
+    from ferrisinfer_b200.kernels import ops
+
+    wide = rnd((40, 256 + 64), BF16, device, 27)
+    w = rnd((200, 256), BF16, device, 28, scale=0.1)
+    x = wide[:, 32:32 + 256]  # rows 320 apart, start 64 bytes into the row: takes the tensor-core path
+    assert ops.tensor_core_gemm_takes(x, w)
+    out = torch.empty(40, 200, dtype=BF16, device=device)
+    ops.gemm(x, w, None, out)
+    _close(out, _gemm_reference(x, w), 256, BF16)
+    odd = rnd((40, 100), BF16, device, 29)[:, :99]  # K = 99: the CUDA-core kernel runs instead
+    w2 = rnd((50, 99), BF16, device, 30)
+    assert not ops.tensor_core_gemm_takes(odd, w2)
+    out = torch.empty(40, 50, dtype=BF16, device=device)
+    ops.gemm(odd, w2, None, out)
+    _close(out, _gemm_reference(odd, w2), 99, BF16)
+
+
 # -------------------------------------------------------------------------------------- swiglu
 @pytest.mark.parametrize("dtype", [F32, BF16])
 def test_swiglu(dtype, device):

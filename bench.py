@@ -188,7 +188,7 @@ def time_decode(engine, batch, context, steps, warmup):
     for i in range(warmup):
         one(i)
     torch.cuda.synchronize()
-    launches0 = ops.launch_count()
+    launches0 = ops.launch_count() + engine.runner.graph_kernels
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(warmup, warmup + steps):
@@ -196,7 +196,7 @@ def time_decode(engine, batch, context, steps, warmup):
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
-    launches = ops.launch_count() - launches0
+    launches = ops.launch_count() + engine.runner.graph_kernels - launches0
     for rid in ids:
         engine.runner.free_request(rid)
     return ms, launches

@@ -37,11 +37,43 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
+@dataclass
+class _HostStep:
+    """A step laid out on the host: the int32 pieces that go to the device, and what the host keeps."""
+
+    pieces: list
+    T: int
+    S: int
+    max_q: int
+    max_kv: int
+    max_blocks: int
+    seqs: list
+    n_want: int
+
+
+@dataclass
+class _GraphEntry:
+    meta: torch.Tensor  # static device buffer of the step's metadata
+    ctx: StepContext
+    logits_index: torch.Tensor
+    logits: torch.Tensor
+    graph: Any = None
+    kernels: int = 0  # kernel launches that one replay stands for
+
+
 class ModelRunner:
-    """Owns the model, the cache manager and the workspace; ``step`` is the only way tokens run."""
+    """Owns the model, the cache manager and the workspace; ``step`` is the only way tokens run.
+
+    Steps in which every request brings exactly one token and wants its logits (decoding) are replayed
+    from CUDA graphs, one per (number of requests, block-table width): the ~200 kernel launches of a step
+    become one.  Their metadata lives in a static device buffer that is rewritten before each replay.
+    Every other step launches its kernels one by one."""
+
+    N_FIXED = 7  # token_ids, positions, token_seq, q_start, start_pos, state_slot, want
 
     def __init__(self, model: DecoderModel, dtype: torch.dtype, device, page_size: int, num_pages: int,
-                 max_requests: int, max_model_len: Optional[int] = None, extra_states: Optional[dict] = None):
+                 max_requests: int, max_model_len: Optional[int] = None, extra_states: Optional[dict] = None,
+                 cuda_graphs: bool = True):
         if not model.bound:
             raise FerrisError("the model has no weights bound")
         self.model = model
@@ -54,7 +86,12 @@ class ModelRunner:
         self.workspace = Workspace(self.device)
         self.steps_run = 0
         self.last_h2d_bytes = 0
-        self._pinned = None
+        self._staging = []  # ring of (pinned buffer, event of the last copy out of it)
+        self._staging_next = 0
+        self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda" and getattr(model, "graph_safe", False)
+        self._graphs: dict = {}
+        self.graph_replays = 0
+        self.graph_kernels = 0  # kernel launches made through graph replays
 
     # ------------------------------------------------------------------ requests
     def add_request(self, request_id) -> int:
@@ -73,42 +110,92 @@ class ModelRunner:
     def step(self, entries: Sequence[StepEntry], out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run the tokens of ``entries`` as one batch from the cache that earlier steps left.
         Returns fp32 logits [wanted, vocab] in the order of the entries and of their ``want``
-        (None if nothing is wanted).  Requests that are not admitted yet are admitted."""
+        (None if nothing is wanted).  Requests that are not admitted yet are admitted.
+        The returned tensor is the runner's own buffer: it is overwritten by the next step."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return None
-        ctx, logits_index = self._prepare(entries)
-        n_want = 0 if logits_index is None else logits_index.numel()
-        logits = None
-        if n_want:
-            logits = out if out is not None else self.workspace.get("logits", (n_want, self.vocab_size), torch.float32)
-        self.model.forward(ctx, self.cache.layer_caches, logits_index, logits)
-        for e, s in zip(entries, ctx.seqs):
+        host = self._layout(entries)
+        decode = host.max_q == 1 and host.n_want == host.S and all(list(e.want) == [0] for e in entries)
+        if self.cuda_graphs and decode and out is None:
+            logits = self._step_graph(host)
+        else:
+            ctx, logits_index = self._context(host, self._upload(host.pieces))
+            logits = None
+            if host.n_want:
+                logits = out if out is not None else self.workspace.get("logits", (host.n_want, self.vocab_size),
+                                                                        torch.float32)
+            self.model.forward(ctx, self.cache.layer_caches, logits_index, logits)
+        for e, s in zip(entries, host.seqs):
             self.cache.commit(e.request_id, s.start_pos + s.q_len)
         self.steps_run += 1
         return logits
 
-    def _upload(self, pieces) -> torch.Tensor:
-        """One copy of the step's int32 metadata, host (pinned) to device."""
+    def _step_graph(self, host: _HostStep) -> torch.Tensor:
+        key = (host.S, host.max_blocks)
+        entry = self._graphs.get(key)
+        if entry is None:
+            total = sum(p.size for p in host.pieces)
+            meta = torch.zeros(total, dtype=torch.int32, device=self.device)
+            self._upload(host.pieces, meta)
+            ctx, logits_index = self._context(host, meta)
+            # launch geometry that depends on the keys' length is fixed for the width of the block table
+            ctx.max_kv_len = host.max_blocks * self.cache.page_size
+            logits = torch.empty(host.S, self.vocab_size, dtype=torch.float32, device=self.device)
+            entry = _GraphEntry(meta, ctx, logits_index, logits)
+            # the first step of this shape runs eagerly (it also sizes every workspace buffer) ...
+            self.model.forward(ctx, self.cache.layer_caches, logits_index, logits)
+            # ... and is then recorded for the steps to come
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
+            with torch.cuda.graph(graph):
+                self.model.forward(ctx, self.cache.layer_caches, logits_index, logits)
+            entry.kernels = ops.launch_count() - before
+            entry.graph = graph
+            self._graphs[key] = entry
+            # the capture itself ran nothing, but the eager run before it did: the result is in ``logits``
+            return logits
+        self._upload(host.pieces, entry.meta)
+        entry.ctx.seqs = host.seqs
+        entry.graph.replay()
+        self.graph_replays += 1
+        self.graph_kernels += entry.kernels
+        return entry.logits
+
+    # ------------------------------------------------------------------- upload
+    def _upload(self, pieces, dest: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One copy of the step's int32 metadata from pinned host memory to the device."""
         total = sum(p.size for p in pieces)
         if self.device.type != "cuda":
-            return torch.from_numpy(np.concatenate(pieces)).to(self.device)
-        if self._pinned is None or self._pinned.numel() < total:
-            self._pinned = torch.empty(max(total, 4096) * 2, dtype=torch.int32).pin_memory()
-        host = self._pinned.numpy()
+            flat = torch.from_numpy(np.concatenate([p.reshape(-1) for p in pieces]))
+            if dest is None:
+                return flat.to(self.device)
+            dest[:total].copy_(flat)
+            return dest
+        if not self._staging:
+            self._staging = [[None, None] for _ in range(4)]
+        slot = self._staging[self._staging_next]
+        self._staging_next = (self._staging_next + 1) % len(self._staging)
+        if slot[1] is not None:
+            slot[1].synchronize()  # the copy that last read this buffer has finished (long ago, as a rule)
+        if slot[0] is None or slot[0].numel() < total:
+            slot[0] = torch.empty(max(total * 2, 16384), dtype=torch.int32).pin_memory()
+            slot[1] = torch.cuda.Event()
+        host = slot[0].numpy()
         off = 0
         for p in pieces:
             host[off:off + p.size] = p.reshape(-1)
             off += p.size
-        dev = torch.empty(total, dtype=torch.int32, device=self.device)
-        dev.copy_(self._pinned[:total], non_blocking=True)
-        # the pinned buffer is rewritten by the next step: the copy must have left it by then
-        torch.cuda.current_stream(self.device).synchronize()
+        if dest is None:
+            dest = torch.empty(total, dtype=torch.int32, device=self.device)
+        dest[:total].copy_(slot[0][:total], non_blocking=True)
+        slot[1].record(torch.cuda.current_stream(self.device))
         self.last_h2d_bytes = total * 4
-        return dev
+        return dest
 
     # ----------------------------------------------------------- step preparation
-    def _prepare(self, entries):
+    def _layout(self, entries) -> _HostStep:
         cache = self.cache
         seen = set()
         T = 0
@@ -121,22 +208,30 @@ class ModelRunner:
                 if not (0 <= w < n):
                     raise FerrisError(f"request {e.request_id!r}: wanted place {w} is not among its {n} tokens")
             T += n
+        admitted_here = []
         for e in entries:
             if not cache.has(e.request_id):
                 cache.admit(e.request_id)
-        # all pages of the step or none
-        short = {g.gid: 0 for g in cache.groups}
-        for e in entries:
-            rc = cache.get(e.request_id)
-            total = rc.num_tokens + len(e.tokens)
-            if total > self.max_model_len:
-                raise FerrisError(f"request {e.request_id!r} would reach {total} tokens; the limit is {self.max_model_len}")
-            for gid, n in cache.pages_needed(e.request_id, total).items():
-                short[gid] += n
-        for g in cache.groups:
-            if short[g.gid] > g.pool.num_free:
-                raise OutOfPages(f"the step needs {short[g.gid]} new pages in group {g.gid}; "
-                                 f"{g.pool.num_free} of {g.pool.num_pages} are free")
+                admitted_here.append(e.request_id)
+        try:
+            # all pages of the step or none
+            short = {g.gid: 0 for g in cache.groups}
+            for e in entries:
+                rc = cache.get(e.request_id)
+                total = rc.num_tokens + len(e.tokens)
+                if total > self.max_model_len:
+                    raise FerrisError(
+                        f"request {e.request_id!r} would reach {total} tokens; the limit is {self.max_model_len}")
+                for gid, n in cache.pages_needed(e.request_id, total).items():
+                    short[gid] += n
+            for g in cache.groups:
+                if short[g.gid] > g.pool.num_free:
+                    raise OutOfPages(f"the step needs {short[g.gid]} new pages in group {g.gid}; "
+                                     f"{g.pool.num_free} of {g.pool.num_pages} are free")
+        except FerrisError:
+            for rid in admitted_here:
+                cache.release(rid)
+            raise
         for e in entries:
             cache.extend(e.request_id, cache.get(e.request_id).num_tokens + len(e.tokens))
 
@@ -169,7 +264,13 @@ class ModelRunner:
             max_q = max(max_q, n)
             max_kv = max(max_kv, rc.num_tokens + n)
             row += n
-        max_blocks = max(1, -(-max_kv // ps))
+        # block tables are as wide as the next power of two of what the longest request needs, so that the
+        # shapes a decode graph is recorded with recur
+        need_blocks = max(1, -(-max_kv // ps))
+        max_blocks = 8
+        while max_blocks < need_blocks:
+            max_blocks *= 2
+        max_blocks = min(max_blocks, max(need_blocks, -(-self.max_model_len // ps)))
         group_arrays = []
         for g in cache.groups:
             slot_mapping = np.empty(T, dtype=np.int32)
@@ -184,23 +285,25 @@ class ModelRunner:
                 slot_mapping[s.q_start:s.q_start + s.q_len] = pages * ps + pos % ps
             group_arrays.append((slot_mapping, tables))
         want = np.asarray(want_rows, dtype=np.int32)
-
         pieces = [token_ids, positions, token_seq, q_start, start_pos, state_slot, want]
         for slot_mapping, tables in group_arrays:
             pieces += [slot_mapping, tables.reshape(-1)]
-        dev = self._upload(pieces)
+        return _HostStep(pieces, T, S, max_q, max_kv, max_blocks, seqs, int(want.size))
+
+    def _context(self, host: _HostStep, dev: torch.Tensor):
         views = []
         off = 0
-        for p in pieces:
+        for p in host.pieces:
             views.append(dev[off:off + p.size])
             off += p.size
         paged = {}
-        for k, g in enumerate(cache.groups):
-            paged[g.gid] = PagedMeta(block_tables=views[7 + 2 * k + 1].view(S, max_blocks),
-                                     slot_mapping=views[7 + 2 * k], page_size=ps)
+        for k, g in enumerate(self.cache.groups):
+            paged[g.gid] = PagedMeta(block_tables=views[self.N_FIXED + 2 * k + 1].view(host.S, host.max_blocks),
+                                     slot_mapping=views[self.N_FIXED + 2 * k], page_size=self.cache.page_size)
         ctx = StepContext(
-            num_tokens=T, num_seqs=S, token_ids=views[0], positions=views[1], token_seq=views[2],
-            seq_q_start=views[3], seq_start_pos=views[4], seq_state_slot=views[5], seqs=seqs, paged=paged,
-            max_q_len=max_q, max_kv_len=max_kv, act_dtype=self.dtype, workspace=self.workspace, device=self.device,
+            num_tokens=host.T, num_seqs=host.S, token_ids=views[0], positions=views[1], token_seq=views[2],
+            seq_q_start=views[3], seq_start_pos=views[4], seq_state_slot=views[5], seqs=host.seqs, paged=paged,
+            max_q_len=host.max_q, max_kv_len=host.max_kv, act_dtype=self.dtype, workspace=self.workspace,
+            device=self.device,
         )
-        return ctx, (views[6] if want.size else None)
+        return ctx, (views[6] if host.n_want else None)

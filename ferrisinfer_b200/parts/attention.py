@@ -28,6 +28,8 @@ from .plan import PartSpec, build_part, register_part
 
 
 class GroupedQueryAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, window: Optional[int] = None, scale: Optional[float] = None):
         if num_heads % num_kv_heads:

@@ -139,6 +139,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if forward only launches kernels on the current stream from device-resident metadata (no host
+    # loops over requests, no allocation), so that a decode step can be recorded into a CUDA graph.
+    graph_safe = False
+
     def cache_need(self):
         """PagedKV, FixedState or None."""
         return None
@@ -156,6 +160,8 @@ class FeedForward(Part):
 
 
 class Block(Part):
+    graph_safe = False
+
     def cache_need(self):
         return None
 

@@ -43,6 +43,10 @@ class PreNormResidualBlock(Block):
     def cache_need(self):
         return self.mixer.cache_need()
 
+    @property
+    def graph_safe(self):
+        return bool(getattr(self.mixer, "graph_safe", False))
+
     def forward(self, h, ctx, cache, owns_cache):
         x = ctx.workspace.get("block_normed", (h.shape[0], self.hidden_size), ctx.act_dtype)
         self.mixer_norm.forward(h, x)

@@ -41,6 +41,11 @@ class DecoderModel:
             feed_forward_norm=build_part("norm", lp.feed_forward_norm),
         )
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step of this model may be recorded into a CUDA graph."""
+        return all(getattr(b, "graph_safe", False) for b in self.blocks)
+
     # ------------------------------------------------------------------ weights
     def tensor_specs(self) -> list:
         p = self.plan

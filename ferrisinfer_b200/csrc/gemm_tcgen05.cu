@@ -5,12 +5,12 @@
 // (16 to 256 per tile): a decode step of a few tokens fills a whole 128-row MMA with weights, which is
 // what streams from HBM, and a prefill step uses the same kernel with wide token tiles.
 //
-// One CTA per (weight tile, token tile, K split); 6 warps:
+// One CTA per (weight tile, token tile, K split); 10 warps:
 //   warp 0    TMA producer: 64-wide K slices of the weight tile(s) and the token tile into a ring of
 //             shared-memory stages (128-byte swizzle), completion on mbarriers;
 //   warp 1    allocates tensor memory, issues tcgen05.mma (one thread) from shared-memory descriptors
 //             into fp32 accumulators in TMEM, frees each stage with tcgen05.commit;
-//   warps 2-5 epilogue: tcgen05.ld of their lane quarter (lane = weight row), then bias / store /
+//   warps 2-9 epilogue: tcgen05.ld of their lane quarter (lane = weight row), then bias / store /
 //             fp32 residual accumulation / SwiGLU, or a partial for the K split.
 // With a K split, the CTA that finishes last adds the partials in split order (a fixed order, so
 // the result does not depend on timing) and runs the epilogue.
@@ -28,7 +28,7 @@ namespace {
 constexpr int BLOCK_N = 128;  // weight rows per tile (MMA M)
 constexpr int BLOCK_K = 64;   // one 128-byte swizzle row of bf16
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;  // TMA warp, MMA warp, eight epilogue warps
 constexpr int MAX_STAGES = 8;
 
 enum Mode { STORE_BF16 = 0, STORE_F32 = 1, ACCUM_F32 = 2, SWIGLU_BF16 = 3 };
@@ -45,19 +45,27 @@ struct Params {
     int splits;
     int up_row_offset;  // SwiGLU: row of the weight matrix where the up rows start
     int* status;
+    unsigned long long* trace;  // optional: CTA (0,0,0) writes nanosecond timestamps of its phases here (8 slots)
 };
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return u * (g * (1.0f / (1.0f + expf(-g)))); }
 
+// a: the product (the gate's in SwiGLU mode), b: the up product, bias_v: bias[n] or 0.
 template <int MODE>
-__device__ __forceinline__ void write_out(const Params& p, int t, int n, float a, float b) {
+__device__ __forceinline__ void write_out(const Params& p, int t, int n, float a, float b, float bias_v) {
     if (MODE == STORE_BF16) {
-        reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(a + (p.bias ? p.bias[n] : 0.0f));
+        reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(a + bias_v);
     } else if (MODE == STORE_F32) {
-        reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = a + (p.bias ? p.bias[n] : 0.0f);
+        reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = a + bias_v;
     } else if (MODE == ACCUM_F32) {
         float* o = reinterpret_cast<float*>(p.out) + (size_t)t * p.ldo + n;
-        *o = *o + (a + (p.bias ? p.bias[n] : 0.0f));
+        *o = *o + (a + bias_v);
     } else {
         reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(silu_mul(a, b));
     }
@@ -75,6 +83,8 @@ __global__ void __launch_bounds__(THREADS)
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool traced = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    if (traced && threadIdx.x == 0) p.trace[0] = global_ns();
     const int n0 = blockIdx.x * BLOCK_N, t0 = blockIdx.y * p.bt, split = blockIdx.z;
     const int a_bytes = BLOCK_N * BLOCK_K * 2, b_bytes = p.bt * BLOCK_K * 2;
     const int stage_bytes = ACCS * a_bytes + b_bytes;
@@ -99,6 +109,7 @@ __global__ void __launch_bounds__(THREADS)
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem = tmem_base;
+    if (traced && threadIdx.x == 0) p.trace[1] = global_ns();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -121,6 +132,7 @@ __global__ void __launch_bounds__(THREADS)
                 const int s = i % p.stages;
                 ok = mbar_wait(&full[s], (i / p.stages) & 1, p.status, 11);
                 if (!ok) break;
+                if (traced && i == 0) p.trace[2] = global_ns();
                 tcgen05_fence_after();
                 const uint32_t st = smem_u32(smem + (size_t)s * stage_bytes);
                 const uint64_t a_desc = umma_desc_k_major_sw128(st);
@@ -136,33 +148,57 @@ __global__ void __launch_bounds__(THREADS)
                 tcgen05_commit(&empty[s]);  // the stage is free once these MMAs have read it
             }
             tcgen05_commit(&accum_full);
+            if (traced) p.trace[3] = global_ns();
         }
     } else {
-        // epilogue: this warp's quarter of the 128 TMEM lanes
-        const int quarter = warp & 3;
+        // epilogue: eight warps; warp e reads TMEM lane quarter (warp % 4) (lane = weight row) and every
+        // second 16-column chunk (column = token)
+        const int e = warp - 2;
+        const int quarter = warp & 3, half = e >> 2;
         const int n = n0 + quarter * 32 + lane;
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         const bool have = n_kb > 0 && mbar_wait(&accum_full, 0, p.status, 12);
         tcgen05_fence_after();
+        if (traced && threadIdx.x == 64) p.trace[4] = global_ns();
         const bool n_ok = n < p.N;
+        const float bias_v = (p.bias && n_ok) ? p.bias[n] : 0.0f;
         if (p.splits == 1) {
             if (have) {
-                for (int c0 = 0; c0 < p.bt; c0 += 16) {
+                for (int c0 = half * 16; c0 < p.bt; c0 += 32) {
                     uint32_t ra[16], rb[16];
                     tmem_load_32x16(lane_addr + c0, ra);
                     if (ACCS == 2) tmem_load_32x16(lane_addr + p.bt + c0, rb);
+                    float old[16];
+                    if (MODE == ACCUM_F32) {
+                        // the sixteen reads of the residual are in flight together
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const int t = t0 + c0 + c;
+                            old[c] = (n_ok && t < p.T) ? reinterpret_cast<const float*>(p.out)[(size_t)t * p.ldo + n] : 0.0f;
+                        }
+                    }
                     tmem_load_wait();
 #pragma unroll
                     for (int c = 0; c < 16; ++c) {
                         const int t = t0 + c0 + c;
-                        if (n_ok && t < p.T)
-                            write_out<MODE>(p, t, n, __uint_as_float(ra[c]), ACCS == 2 ? __uint_as_float(rb[c]) : 0.0f);
+                        if (!(n_ok && t < p.T)) continue;
+                        const float a = __uint_as_float(ra[c]);
+                        if (MODE == STORE_BF16)
+                            reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(a + bias_v);
+                        else if (MODE == STORE_F32)
+                            reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = a + bias_v;
+                        else if (MODE == ACCUM_F32)
+                            reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = old[c] + (a + bias_v);
+                        else
+                            reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] =
+                                __float2bfloat16_rn(silu_mul(a, __uint_as_float(rb[c])));
                     }
                 }
             }
         } else {
             // partials of this split: scratch[((split * ACCS + a) * T + t) * N + n]
-            for (int c0 = 0; c0 < p.bt; c0 += 16) {
+            for (int c0 = half * 16; c0 < p.bt; c0 += 32) {
+                if (t0 + c0 >= p.T) break;
                 uint32_t ra[16], rb[16];
                 if (have) {
                     tmem_load_32x16(lane_addr + c0, ra);
@@ -180,25 +216,45 @@ __global__ void __launch_bounds__(THREADS)
                 }
             }
             __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             if (threadIdx.x == 64) {
                 const int tile = blockIdx.y * gridDim.x + blockIdx.x;
                 const int old = atomicAdd(&p.counters[tile], 1);
                 is_last = old == p.splits - 1;
                 if (is_last) p.counters[tile] = 0;  // ready for the next launch
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             if (is_last) {
                 __threadfence();
+                // the last CTA adds the partials in split order; the two warps of a lane quarter take
+                // tokens in turn, four at a time, with the reads of up to eight splits of each in flight
                 const int t_end = min(t0 + p.bt, p.T);
                 if (n_ok) {
-                    for (int t = t0; t < t_end; ++t) {
-                        float a = 0.0f, b = 0.0f;
-                        for (int s = 0; s < p.splits; ++s) {
-                            a += __ldcg(&p.scratch[((size_t)(s * ACCS) * p.T + t) * p.N + n]);
-                            if (ACCS == 2) b += __ldcg(&p.scratch[((size_t)(s * ACCS + 1) * p.T + t) * p.N + n]);
+                    for (int tb = t0 + 4 * half; tb < t_end; tb += 8) {
+                        float a[4] = {0.0f, 0.0f, 0.0f, 0.0f}, b[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                        for (int s0 = 0; s0 < p.splits; s0 += 8) {
+                            float va[4][8], vb[4][8];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    const int sp = s0 + j, t = tb + q;
+                                    const bool ok = sp < p.splits && t < t_end;
+                                    va[q][j] = ok ? __ldcg(&p.scratch[((size_t)(sp * ACCS) * p.T + t) * p.N + n]) : 0.0f;
+                                    if (ACCS == 2)
+                                        vb[q][j] = ok ? __ldcg(&p.scratch[((size_t)(sp * ACCS + 1) * p.T + t) * p.N + n]) : 0.0f;
+                                }
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    a[q] += va[q][j];
+                                    if (ACCS == 2) b[q] += vb[q][j];
+                                }
                         }
-                        write_out<MODE>(p, t, n, a, b);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q)
+                            if (tb + q < t_end) write_out<MODE>(p, tb + q, n, a[q], b[q], bias_v);
                     }
                 }
             }
@@ -210,6 +266,7 @@ __global__ void __launch_bounds__(THREADS)
         tcgen05_fence_after();
         tmem_dealloc(tmem, tmem_cols);
     }
+    if (traced && threadIdx.x == 32) p.trace[6] = global_ns();
 }
 
 struct WeightMap {
@@ -263,14 +320,25 @@ FERRIS_API int ferris_gemm_tcgen05_plan(int T, int N, int K, int accumulators, i
             cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sms <= 0)
             g_sms = 148;
     }
+    // Start from the widest tile that the step fills (every weight byte is then read once) and narrow it
+    // while the SMs would lack tiles: short steps down to 16 tokens (narrow tiles rather than deep K splits:
+    // more CTAs stream the weights, L2 serves the repeats, and the last CTA of a tile has few tokens to add
+    // up), long steps down to 64.
+    const int n_tiles = (N + BLOCK_N - 1) / BLOCK_N;
     int bt = 16;
     while (bt < T && bt < 256) bt <<= 1;
-    const int n_tiles = (N + BLOCK_N - 1) / BLOCK_N, t_tiles = (T + bt - 1) / bt;
+    const int narrowest = T <= 64 ? 16 : (T <= 256 ? 32 : 64);
+    while (bt > narrowest && n_tiles * ((T + bt - 1) / bt) < g_sms) bt >>= 1;
+    const int t_tiles = (T + bt - 1) / bt;
     const int kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+    // K split: only where tiles are fewer than SMs, and the fewer splits the wider the token tile (the last
+    // CTA of a tile adds the partials of all splits for every token)
     int splits = 1;
     const int tiles = n_tiles * t_tiles;
-    if (tiles < g_sms && kblocks >= 4) {
+    const int most = bt <= 16 ? 16 : (bt == 32 ? 8 : (bt == 64 ? 4 : (bt == 128 ? 2 : 1)));
+    if (tiles < g_sms && kblocks >= 4 && most > 1) {
         splits = (g_sms + tiles - 1) / tiles;
+        if (splits > most) splits = most;
         if (splits > kblocks / 2) splits = kblocks / 2;
         if (splits < 1) splits = 1;
         // no split may be empty
@@ -288,9 +356,11 @@ FERRIS_API int ferris_gemm_tcgen05_plan(int T, int N, int K, int accumulators, i
 // least up_row_offset + N); out: [T, N] rows ldo apart in the mode's type.
 // mode: 0 bf16 = acc + bias; 1 fp32 = acc + bias; 2 fp32 += acc + bias; 3 bf16 = silu(gate) * up.
 // scratch / counters: as ferris_gemm_tcgen05_plan says (counters must be zero; they are left zero).
+// trace: null, or 8 device u64: CTA (0,0,0) records nanosecond timestamps of its phases (start, set-up done,
+// first stage landed, last MMA issued, accumulator ready, epilogue done, TMEM freed).
 FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N,
                                    int K, int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch,
-                                   int* counters, void* stream) {
+                                   int* counters, void* stream, unsigned long long* trace) {
     if (T <= 0 || N <= 0) return FERRIS_OK;
     if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ldx < K || ldw < K)
         FERRIS_REFUSE("tensor-core gemm: K=%d and row strides %d, %d must be multiples of 8 elements", K, ldx, ldw);
@@ -325,6 +395,7 @@ FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bi
     p.splits = splits;
     p.up_row_offset = up_row_offset;
     p.status = ferris_status_ptr();
+    p.trace = trace;
     const int stage_bytes = accs * BLOCK_N * BLOCK_K * 2 + bt * BLOCK_K * 2;
     int stages = (227 * 1024 - 2048) / stage_bytes;
     if (stages > MAX_STAGES) stages = MAX_STAGES;

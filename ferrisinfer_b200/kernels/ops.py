@@ -178,7 +178,8 @@ def tensor_core_gemm_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
             and (K <= 1 or (x.stride(1) == 1 and w.stride(1) == 1)))
 
 
-def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row_offset: int = 0):
+def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row_offset: int = 0,
+                 trace: Optional[torch.Tensor] = None):
     """out = x w^T on the tcgen05 tensor cores.  mode 0: bf16 store (+bias); 1: fp32 store (+bias);
     2: fp32 out += ; 3: bf16 silu(x w[:N]^T) * (x w[up_row_offset:up_row_offset+N]^T)."""
     T, K, ldx = _rows(x, "gemm input")
@@ -203,7 +204,7 @@ def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row
     _check(
         _lib().ferris_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K),
                                    _c_int(ldx), _c_int(ldw), _c_int(ldo), _c_int(rows_w), _c_int(up_row_offset),
-                                   _ptr(scratch), _ptr(cnt), _stream()),
+                                   _ptr(scratch), _ptr(cnt), _stream(), _ptr(trace)),
         "tensor-core gemm",
     )
 

@@ -147,6 +147,104 @@ __device__ __forceinline__ void attend_tile(WarpState<D>& st, uint32_t k_smem, u
     }
 }
 
+// Four consecutive 16-key tiles (64 keys from `key0`) at once: one running-maximum update and one
+// rescale of the output per 64 keys, and four independent score tiles in flight.  The tiles lie
+// `tile_bytes` apart in shared memory, each laid out as attend_tile expects.
+template <int D>
+__device__ __forceinline__ void attend_block64(WarpState<D>& st, uint32_t base, uint32_t tile_bytes, int key0,
+                                               const RowLimits& lim, float scale) {
+    const int lane = threadIdx.x & 31;
+    const int t = lane & 3;
+    const int mi = lane >> 3, r8 = lane & 7;
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const uint32_t k_smem = base + k * tile_bytes;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ks += 2) {
+                const int cc = 2 * ks + mi;
+                uint32_t r[4];
+                ldmatrix_x4(r, k_smem + (cc >> 3) * 2048 + swizzle128(8 * j + r8, cc & 7));
+                mma_bf16_16816(s[2 * k + j], st.q[ks], r[0], r[1]);
+                mma_bf16_16816(s[2 * k + j], st.q[ks + 1], r[2], r[3]);
+            }
+        }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+    const bool interior = key0 + 63 <= min(lim.hi[0], lim.hi[1]) && key0 >= max(lim.lo[0], lim.lo[1]) &&
+                          lim.hi[0] >= 0 && lim.hi[1] >= 0;
+    if (__all_sync(0xffffffffu, interior)) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                s[j][e] *= scale;
+                mx[e >> 1] = fmaxf(mx[e >> 1], s[j][e]);
+            }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int row = e >> 1;
+                const int key = key0 + 8 * j + 2 * t + (e & 1);
+                const bool ok = key <= lim.hi[row] && key >= lim.lo[row];
+                s[j][e] = ok ? s[j][e] * scale : -INFINITY;
+                mx[row] = fmaxf(mx[row], s[j][e]);
+            }
+    }
+    float corr[2], sub[2];
+#pragma unroll
+    for (int row = 0; row < 2; ++row) {
+        mx[row] = fmaxf(mx[row], __shfl_xor_sync(0xffffffffu, mx[row], 1));
+        mx[row] = fmaxf(mx[row], __shfl_xor_sync(0xffffffffu, mx[row], 2));
+        const float m_new = fmaxf(st.m[row], mx[row]);
+        sub[row] = m_new == -INFINITY ? 0.0f : m_new;
+        corr[row] = st.m[row] == -INFINITY ? 0.0f : expf(st.m[row] - sub[row]);
+        st.m[row] = m_new;
+        st.l[row] *= corr[row];
+    }
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+        st.o[n][0] *= corr[0];
+        st.o[n][1] *= corr[0];
+        st.o[n][2] *= corr[1];
+        st.o[n][3] *= corr[1];
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        uint32_t p[4];
+        {
+            const float e00 = expf(s[2 * k][0] - sub[0]), e01 = expf(s[2 * k][1] - sub[0]);
+            const float e02 = expf(s[2 * k][2] - sub[1]), e03 = expf(s[2 * k][3] - sub[1]);
+            const float e10 = expf(s[2 * k + 1][0] - sub[0]), e11 = expf(s[2 * k + 1][1] - sub[0]);
+            const float e12 = expf(s[2 * k + 1][2] - sub[1]), e13 = expf(s[2 * k + 1][3] - sub[1]);
+            st.l[0] += (e00 + e01) + (e10 + e11);
+            st.l[1] += (e02 + e03) + (e12 + e13);
+            p[0] = pack_bf16(e00, e01);
+            p[1] = pack_bf16(e02, e03);
+            p[2] = pack_bf16(e10, e11);
+            p[3] = pack_bf16(e12, e13);
+        }
+        const uint32_t v_smem = base + k * tile_bytes + (D / 64) * 2048;
+        const int row = (mi & 1) * 8 + r8;
+#pragma unroll
+        for (int n = 0; n < D / 8; n += 2) {
+            const int cc = n + (mi >> 1);
+            uint32_t r[4];
+            ldmatrix_x4_trans(r, v_smem + (cc >> 3) * 2048 + swizzle128(row, cc & 7));
+            mma_bf16_16816(st.o[n], p, r[0], r[1]);
+            mma_bf16_16816(st.o[n + 1], p, r[2], r[3]);
+        }
+    }
+}
+
 // Sum the per-thread partial sums of a row over the four threads that share it.
 template <int D>
 __device__ __forceinline__ void finish_rows(WarpState<D>& st) {
@@ -188,21 +286,17 @@ __global__ void __launch_bounds__(WARPS * 32)
     decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
                             float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ block_tables,
-                            int max_blocks, const int* __restrict__ token_seq, const int* __restrict__ positions, int nh,
-                            int nkv, int page_size, int window, float scale, int splits, int* status) {
+                            int max_blocks, const int* __restrict__ token_seq, const int* __restrict__ positions,
+                            const int* __restrict__ token_list, int nh, int nkv, int page_size, int window, float scale,
+                            int splits, int* status) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full[WARPS][STAGES];
     uint8_t* smem = align1024(smem_raw);
     constexpr int STAGE_BYTES = 2 * TILE_KEYS * D * 2;
 
-    const int split = blockIdx.x, hk = blockIdx.y, tok = blockIdx.z;
+    const int split = blockIdx.x, hk = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = nh / nkv;
-    const int seq = token_seq[tok];
-    const int P = positions[tok];
-    const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
-    const int* table = block_tables + (size_t)seq * max_blocks;
-
     if (threadIdx.x == 0) {
         tma_prefetch_descriptor(&map_k);
         tma_prefetch_descriptor(&map_v);
@@ -212,6 +306,14 @@ __global__ void __launch_bounds__(WARPS * 32)
     }
     mbar_fence_init();
     __syncthreads();
+    pdl_launch_dependents();
+    pdl_wait();
+    // with a token list, only the listed rows of the step are attended (the others belong to another kernel)
+    const int tok = token_list ? token_list[blockIdx.z] : (int)blockIdx.z;
+    const int seq = token_seq[tok];
+    const int P = positions[tok];
+    const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
+    const int* table = block_tables + (size_t)seq * max_blocks;
 
     // key tiles of this split
     const int first_tile = lo / TILE_KEYS, last_tile = P / TILE_KEYS;
@@ -301,8 +403,11 @@ __global__ void __launch_bounds__(WARPS * 32)
 // Merge of the splits: out = sum_s O_s e^{m_s - M} / sum_s l_s e^{m_s - M}.  One block per (token, head).
 template <int D>
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    bf16* __restrict__ out, int ldo, int nh, int splits) {
-    const int tok = blockIdx.x, head = blockIdx.y;
+                                    bf16* __restrict__ out, int ldo, const int* __restrict__ token_list, int nh,
+                                    int splits) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int tok = token_list ? token_list[blockIdx.x] : (int)blockIdx.x, head = blockIdx.y;
     const size_t base = ((size_t)tok * nh + head) * splits;
     float mm = -INFINITY;
     for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
@@ -333,7 +438,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32)
                              const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
                              const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ seq_q_start,
                              const int* __restrict__ seq_start_pos, int nh, int nkv, int page_size, int window,
-                             float scale, int* status) {
+                             float scale, int skip_single, int* status) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full[STAGES], empty[STAGES];
     uint8_t* smem = align1024(smem_raw);
@@ -342,7 +447,10 @@ __global__ void __launch_bounds__((WARPS + 1) * 32)
 
     const int G = nh / nkv;
     const int seq = blockIdx.z, hk = blockIdx.y;
+    pdl_wait();
+    pdl_launch_dependents();
     const int q_start = seq_q_start[seq], q_len = seq_q_start[seq + 1] - q_start;
+    if (skip_single && q_len == 1) return;  // single tokens are the decode kernel's
     const int rows_total = q_len * G;
     // heavy row blocks (the last tokens see the most keys) first
     const int n_blocks = (rows_total + PF_ROWS - 1) / PF_ROWS;
@@ -437,12 +545,17 @@ __global__ void __launch_bounds__((WARPS + 1) * 32)
         const int s = i % STAGES;
         if (!mbar_wait(&full[s], (i / STAGES) & 1, status, 3)) break;
         const int key_base = (s_begin + i) * stage_keys;
+        if (key_base + stage_keys - 1 <= my_hi && key_base >= my_lo - (TILE_KEYS - 1)) {
+            // all four tiles hold keys that rows of this warp see: one pass over the 64 keys
+            attend_block64<D>(st, smem_u32(smem + (size_t)s * STAGE_BYTES), TILE_BYTES, key_base, lim, scale);
+        } else {
 #pragma unroll
-        for (int k = 0; k < PF_STAGE_TILES; ++k) {
-            const int key0 = key_base + k * TILE_KEYS;
-            if (key0 > my_hi || key0 + TILE_KEYS - 1 < my_lo) continue;
-            const uint32_t base = smem_u32(smem + (size_t)s * STAGE_BYTES + k * TILE_BYTES);
-            attend_tile<D>(st, base, base + (D / 64) * 2048, key0, lim, scale);
+            for (int k = 0; k < PF_STAGE_TILES; ++k) {
+                const int key0 = key_base + k * TILE_KEYS;
+                if (key0 > my_hi || key0 + TILE_KEYS - 1 < my_lo) continue;
+                const uint32_t base = smem_u32(smem + (size_t)s * STAGE_BYTES + k * TILE_BYTES);
+                attend_tile<D>(st, base, base + (D / 64) * 2048, key0, lim, scale);
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
@@ -515,12 +628,10 @@ FERRIS_API long long ferris_decode_attention_scratch_floats(int tokens, int nh, 
     return (long long)tokens * nh * splits * (d + 2);
 }
 
-// Single-token steps.  scratch: fp32 [tokens * nh * splits * (d + 2)] when splits > 1.
-FERRIS_API int ferris_decode_attention(const void* q, int ldq, void* out, int ldo, const void* k_cache,
-                                       const void* v_cache, long long cache_pages, const int* block_tables,
-                                       int max_blocks, const int* token_seq, const int* positions, int tokens, int nh,
-                                       int nkv, int d, int page_size, int window, float scale, int splits, float* scratch,
-                                       void* stream) {
+static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, const void* k_cache, const void* v_cache,
+                                 long long cache_pages, const int* block_tables, int max_blocks, const int* token_seq,
+                                 const int* positions, const int* token_list, int tokens, int nh, int nkv, int d,
+                                 int page_size, int window, float scale, int splits, float* scratch, void* stream) {
     if (tokens <= 0) return FERRIS_OK;
     int rc = check_common(nh, nkv, d, page_size, max_blocks);
     if (rc != FERRIS_OK) return rc;
@@ -540,28 +651,50 @@ FERRIS_API int ferris_decode_attention(const void* q, int ldq, void* out, int ld
         constexpr int ST = 3;
         const size_t smem = (size_t)WARPS * ST * 2 * TILE_KEYS * 64 * 2 + 1024;
         if ((rc = set_smem(decode_attention_kernel<64, ST>, smem)) != FERRIS_OK) return rc;
-        decode_attention_kernel<64, ST><<<grid, WARPS * 32, smem, s>>>(
-            mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
-            nh, nkv, page_size, window, scale, splits, status);
-        if (splits > 1) decode_merge_kernel<64><<<dim3(tokens, nh), 64, 0, s>>>(part_o, part_ml, (bf16*)out, ldo, nh, splits);
+        ferris_launch(decode_attention_kernel<64, ST>, grid, dim3(WARPS * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
+            token_list, nh, nkv, page_size, window, scale, splits, status);
+        if (splits > 1) ferris_launch(decode_merge_kernel<64>, dim3(tokens, nh), dim3(64), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
     } else {
         constexpr int ST = 2;
         const size_t smem = (size_t)WARPS * ST * 2 * TILE_KEYS * 128 * 2 + 1024;
         if ((rc = set_smem(decode_attention_kernel<128, ST>, smem)) != FERRIS_OK) return rc;
-        decode_attention_kernel<128, ST><<<grid, WARPS * 32, smem, s>>>(
-            mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
-            nh, nkv, page_size, window, scale, splits, status);
-        if (splits > 1) decode_merge_kernel<128><<<dim3(tokens, nh), 128, 0, s>>>(part_o, part_ml, (bf16*)out, ldo, nh, splits);
+        ferris_launch(decode_attention_kernel<128, ST>, grid, dim3(WARPS * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
+            token_list, nh, nkv, page_size, window, scale, splits, status);
+        if (splits > 1) ferris_launch(decode_merge_kernel<128>, dim3(tokens, nh), dim3(128), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
     }
     FERRIS_LAUNCH_CHECK();
 }
 
-// Portions of prompts (and anything else: a request with one token is a portion of one).
+// Single-token steps.  scratch: fp32 [tokens * nh * splits * (d + 2)] when splits > 1.
+FERRIS_API int ferris_decode_attention(const void* q, int ldq, void* out, int ldo, const void* k_cache,
+                                       const void* v_cache, long long cache_pages, const int* block_tables,
+                                       int max_blocks, const int* token_seq, const int* positions, int tokens, int nh,
+                                       int nkv, int d, int page_size, int window, float scale, int splits, float* scratch,
+                                       void* stream) {
+    return decode_attention_impl(q, ldq, out, ldo, k_cache, v_cache, cache_pages, block_tables, max_blocks, token_seq,
+                                 positions, nullptr, tokens, nh, nkv, d, page_size, window, scale, splits, scratch, stream);
+}
+
+// The same for the rows of a step that `token_list` (int32 [tokens]) names: the single tokens of a step
+// that also carries portions of prompts.  The scratch is indexed by row of the step, so it must hold
+// step_rows * nh * splits * (d + 2) floats.
+FERRIS_API int ferris_decode_attention_listed(const void* q, int ldq, void* out, int ldo, const void* k_cache,
+                                              const void* v_cache, long long cache_pages, const int* block_tables,
+                                              int max_blocks, const int* token_seq, const int* positions,
+                                              const int* token_list, int tokens, int nh, int nkv, int d, int page_size,
+                                              int window, float scale, int splits, float* scratch, void* stream) {
+    if (!token_list) FERRIS_REFUSE("decode attention: no token list");
+    return decode_attention_impl(q, ldq, out, ldo, k_cache, v_cache, cache_pages, block_tables, max_blocks, token_seq,
+                                 positions, token_list, tokens, nh, nkv, d, page_size, window, scale, splits, scratch, stream);
+}
+
+// Portions of prompts (and anything else: a request with one token is a portion of one, unless
+// skip_single leaves those to the decode kernel).
 FERRIS_API int ferris_prefill_attention(const void* q, int ldq, void* out, int ldo, const void* k_cache,
                                         const void* v_cache, long long cache_pages, const int* block_tables,
                                         int max_blocks, const int* seq_q_start, const int* seq_start_pos, int num_seqs,
                                         int max_q_len, int nh, int nkv, int d, int page_size, int window, float scale,
-                                        void* stream) {
+                                        int skip_single, void* stream) {
     if (num_seqs <= 0 || max_q_len <= 0) return FERRIS_OK;
     int rc = check_common(nh, nkv, d, page_size, max_blocks);
     if (rc != FERRIS_OK) return rc;
@@ -578,16 +711,14 @@ FERRIS_API int ferris_prefill_attention(const void* q, int ldq, void* out, int l
         constexpr int ST = 3;
         const size_t smem = (size_t)ST * PF_STAGE_TILES * 2 * TILE_KEYS * 64 * 2 + 1024;
         if ((rc = set_smem(prefill_attention_kernel<64, ST>, smem)) != FERRIS_OK) return rc;
-        prefill_attention_kernel<64, ST><<<grid, (WARPS + 1) * 32, smem, s>>>(
-            mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, block_tables, max_blocks, seq_q_start, seq_start_pos, nh, nkv,
-            page_size, window, scale, status);
+        ferris_launch(prefill_attention_kernel<64, ST>, grid, dim3((WARPS + 1) * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, block_tables, max_blocks, seq_q_start, seq_start_pos, nh, nkv,
+            page_size, window, scale, skip_single, status);
     } else {
         constexpr int ST = 2;
         const size_t smem = (size_t)ST * PF_STAGE_TILES * 2 * TILE_KEYS * 128 * 2 + 1024;
         if ((rc = set_smem(prefill_attention_kernel<128, ST>, smem)) != FERRIS_OK) return rc;
-        prefill_attention_kernel<128, ST><<<grid, (WARPS + 1) * 32, smem, s>>>(
-            mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, block_tables, max_blocks, seq_q_start, seq_start_pos, nh, nkv,
-            page_size, window, scale, status);
+        ferris_launch(prefill_attention_kernel<128, ST>, grid, dim3((WARPS + 1) * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, block_tables, max_blocks, seq_q_start, seq_start_pos, nh, nkv,
+            page_size, window, scale, skip_single, status);
     }
     FERRIS_LAUNCH_CHECK();
 }

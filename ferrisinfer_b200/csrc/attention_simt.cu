@@ -26,6 +26,8 @@ __global__ void __launch_bounds__(ATT_THREADS)
                                 const int* __restrict__ token_seq, const int* __restrict__ positions, int nh,
                                 int nkv, int d, int page_size, int window, float scale) {
     extern __shared__ float smem[];  // per warp: m, z, acc[d]
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x, hq = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int hk = hq / (nh / nkv);
@@ -119,12 +121,10 @@ FERRIS_API int ferris_paged_attention_simt(const void* q, int ldq, void* out, in
     const size_t smem = (size_t)ATT_WARPS * (d + 2) * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == FERRIS_F32)
-        paged_attention_simt_kernel<float><<<grid, ATT_THREADS, smem, s>>>(
-            (const float*)q, ldq, (float*)out, ldo, (const float*)k_cache, (const float*)v_cache, block_tables,
+        ferris_launch(paged_attention_simt_kernel<float>, grid, dim3(ATT_THREADS), smem, s, (const float*)q, ldq, (float*)out, ldo, (const float*)k_cache, (const float*)v_cache, block_tables,
             max_blocks, token_seq, positions, nh, nkv, d, page_size, window, scale);
     else if (dtype == FERRIS_BF16)
-        paged_attention_simt_kernel<bf16><<<grid, ATT_THREADS, smem, s>>>(
-            (const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
+        ferris_launch(paged_attention_simt_kernel<bf16>, grid, dim3(ATT_THREADS), smem, s, (const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
             token_seq, positions, nh, nkv, d, page_size, window, scale);
     else
         FERRIS_REFUSE("attention: unknown dtype %d", dtype);

@@ -37,6 +37,35 @@ void ferris_set_error(const char* fmt, ...);
 
 typedef __nv_bfloat16 bf16;
 
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch: a kernel launched through ferris_launch may begin while the kernel
+// before it in the stream is still draining.  Its set-up (barriers, tensor memory, descriptor
+// prefetch) overlaps that tail; pdl_wait() then blocks until the earlier kernel has completed and its
+// writes are visible, and must come before the first access to global memory.
+// pdl_launch_dependents() lets the NEXT kernel start its own set-up early; it takes effect once every
+// CTA of this grid has called it (or exited), so CTAs that are not resident yet are never starved.
+// Launched without the attribute (FERRIS_PDL=0), both are no-ops.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool ferris_pdl_enabled();
+
+template <typename Kernel, typename... Args>
+inline cudaError_t ferris_launch(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ferris_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
 

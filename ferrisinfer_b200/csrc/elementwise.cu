@@ -10,6 +10,8 @@
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int hidden, int vocab, int* status) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * hidden;
@@ -29,9 +31,9 @@ FERRIS_API int ferris_embed_gather(const void* table, int dtype, const int* ids,
     const int threads = hidden >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == FERRIS_F32)
-        embed_gather_kernel<float><<<tokens, threads, 0, s>>>((const float*)table, ids, out, hidden, vocab, status);
+        ferris_launch(embed_gather_kernel<float>, dim3(tokens), dim3(threads), 0, s, (const float*)table, ids, out, hidden, vocab, status);
     else if (dtype == FERRIS_BF16)
-        embed_gather_kernel<bf16><<<tokens, threads, 0, s>>>((const bf16*)table, ids, out, hidden, vocab, status);
+        ferris_launch(embed_gather_kernel<bf16>, dim3(tokens), dim3(threads), 0, s, (const bf16*)table, ids, out, hidden, vocab, status);
     else
         FERRIS_REFUSE("embed_gather: unknown dtype %d", dtype);
     FERRIS_LAUNCH_CHECK();
@@ -49,6 +51,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                const int* __restrict__ row_index, TOut* __restrict__ out, int hidden,
                                float eps) {
     __shared__ float scratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const int src = row_index ? row_index[r] : r;
     const float* xr = x + (size_t)src * hidden;
@@ -70,9 +74,9 @@ FERRIS_API int ferris_rmsnorm(const float* x, const float* w, const int* row_ind
     const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == FERRIS_F32)
-        rmsnorm_kernel<float><<<rows, threads, 0, s>>>(x, w, row_index, (float*)out, hidden, eps);
+        ferris_launch(rmsnorm_kernel<float>, dim3(rows), dim3(threads), 0, s, x, w, row_index, (float*)out, hidden, eps);
     else if (out_dtype == FERRIS_BF16)
-        rmsnorm_kernel<bf16><<<rows, threads, 0, s>>>(x, w, row_index, (bf16*)out, hidden, eps);
+        ferris_launch(rmsnorm_kernel<bf16>, dim3(rows), dim3(threads), 0, s, x, w, row_index, (bf16*)out, hidden, eps);
     else
         FERRIS_REFUSE("rmsnorm: unknown dtype %d", out_dtype);
     FERRIS_LAUNCH_CHECK();
@@ -85,6 +89,8 @@ FERRIS_API int ferris_rmsnorm(const float* x, const float* w, const int* row_ind
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int tokens, int inter) {
+    pdl_wait();
+    pdl_launch_dependents();
     const size_t n = (size_t)tokens * inter;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
         const size_t t = i / inter, j = i % inter;
@@ -103,9 +109,9 @@ FERRIS_API int ferris_swiglu(const void* gate_up, void* out, int dtype, int toke
     const int blocks = (int)((n + threads - 1) / threads < 148 * 16 ? (n + threads - 1) / threads : 148 * 16);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == FERRIS_F32)
-        swiglu_kernel<float><<<blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, tokens, inter);
+        ferris_launch(swiglu_kernel<float>, dim3(blocks), dim3(threads), 0, s, (const float*)gate_up, (float*)out, tokens, inter);
     else if (dtype == FERRIS_BF16)
-        swiglu_kernel<bf16><<<blocks, threads, 0, s>>>((const bf16*)gate_up, (bf16*)out, tokens, inter);
+        ferris_launch(swiglu_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, (const bf16*)gate_up, (bf16*)out, tokens, inter);
     else
         FERRIS_REFUSE("swiglu: unknown dtype %d", dtype);
     FERRIS_LAUNCH_CHECK();
@@ -128,6 +134,8 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
                                         const float* __restrict__ inv_freq, const int* __restrict__ slot_mapping,
                                         T* __restrict__ k_cache, T* __restrict__ v_cache, int nh, int nkv, int d,
                                         int rotary, int page_size, int write_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const int half = rotary / 2;
     const float pos = (float)positions[t];
@@ -180,11 +188,11 @@ FERRIS_API int ferris_rope_cache_write(void* qkv, int dtype, const int* position
     const int threads = 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == FERRIS_F32)
-        rope_cache_write_kernel<float><<<tokens, threads, 0, s>>>((float*)qkv, positions, inv_freq, slot_mapping,
+        ferris_launch(rope_cache_write_kernel<float>, dim3(tokens), dim3(threads), 0, s, (float*)qkv, positions, inv_freq, slot_mapping,
                                                                   (float*)k_cache, (float*)v_cache, nh, nkv, d, rotary,
                                                                   page_size, write_kv);
     else if (dtype == FERRIS_BF16)
-        rope_cache_write_kernel<bf16><<<tokens, threads, 0, s>>>((bf16*)qkv, positions, inv_freq, slot_mapping,
+        ferris_launch(rope_cache_write_kernel<bf16>, dim3(tokens), dim3(threads), 0, s, (bf16*)qkv, positions, inv_freq, slot_mapping,
                                                                  (bf16*)k_cache, (bf16*)v_cache, nh, nkv, d, rotary,
                                                                  page_size, write_kv);
     else

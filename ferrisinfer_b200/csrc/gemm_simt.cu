@@ -20,6 +20,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TIn* __restrict__ 
                                                         int M, int N, int K, int ldx, int ldw, int ldo) {
     __shared__ float xs[BK][BM + 1];
     __shared__ float ws[BK][BN + 1];
+    pdl_wait();
+    pdl_launch_dependents();
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int tr = tid / 16, tc = tid % 16;  // this thread's 4x4 patch: rows tr*4.., cols tc*4..
@@ -77,10 +79,10 @@ int launch(const void* x, const void* w, const float* bias, void* out, int M, in
            int accumulate, cudaStream_t s) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (accumulate)
-        gemm_simt_kernel<TIn, TOut, 1><<<grid, 256, 0, s>>>((const TIn*)x, (const TIn*)w, bias, (TOut*)out, M, N, K,
+        ferris_launch(gemm_simt_kernel<TIn, TOut, 1>, grid, dim3(256), 0, s, (const TIn*)x, (const TIn*)w, bias, (TOut*)out, M, N, K,
                                                            ldx, ldw, ldo);
     else
-        gemm_simt_kernel<TIn, TOut, 0><<<grid, 256, 0, s>>>((const TIn*)x, (const TIn*)w, bias, (TOut*)out, M, N, K,
+        ferris_launch(gemm_simt_kernel<TIn, TOut, 0>, grid, dim3(256), 0, s, (const TIn*)x, (const TIn*)w, bias, (TOut*)out, M, N, K,
                                                            ldx, ldw, ldo);
     FERRIS_LAUNCH_CHECK();
 }

@@ -84,7 +84,6 @@ __global__ void __launch_bounds__(THREADS)
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool traced = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-    if (traced && threadIdx.x == 0) p.trace[0] = global_ns();
     const int n0 = blockIdx.x * BLOCK_N, t0 = blockIdx.y * p.bt, split = blockIdx.z;
     const int a_bytes = BLOCK_N * BLOCK_K * 2, b_bytes = p.bt * BLOCK_K * 2;
     const int stage_bytes = ACCS * a_bytes + b_bytes;
@@ -109,7 +108,10 @@ __global__ void __launch_bounds__(THREADS)
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem = tmem_base;
-    if (traced && threadIdx.x == 0) p.trace[1] = global_ns();
+    // everything above touched no global memory: it may overlap the tail of the kernel before this one
+    pdl_launch_dependents();
+    pdl_wait();
+    if (traced && threadIdx.x == 0) p.trace[0] = p.trace[1] = global_ns();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -304,7 +306,11 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
         ferris_set_error("gemm: %s", cudaGetErrorString(e));
         return (int)e;
     }
-    gemm_tcgen05_kernel<MODE><<<grid, THREADS, smem, s>>>(mw, mx, p);
+    e = ferris_launch(gemm_tcgen05_kernel<MODE>, grid, dim3(THREADS), smem, s, mw, mx, p);
+    if (e != cudaSuccess) {
+        ferris_set_error("gemm: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
     FERRIS_LAUNCH_CHECK();
 }
 

@@ -1,6 +1,7 @@
 // Error text of the C ABI and a few queries about the device.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "sm100.cuh"
@@ -15,6 +16,17 @@ void ferris_set_error(const char* fmt, ...) {
 }
 
 FERRIS_API const char* ferris_last_error() { return g_error; }
+
+// Programmatic dependent launch is on unless the environment says FERRIS_PDL=0.
+static int g_pdl = -1;
+bool ferris_pdl_enabled() {
+    if (g_pdl < 0) {
+        const char* v = getenv("FERRIS_PDL");
+        g_pdl = (v && v[0] == '0') ? 0 : 1;
+    }
+    return g_pdl != 0;
+}
+FERRIS_API void ferris_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
 // Compute capability of the current device as major * 10 + minor, or a negative cudaError_t.
 FERRIS_API int ferris_device_arch() {

@@ -240,6 +240,8 @@ __global__ void __launch_bounds__(THREADS)
     extern __shared__ __align__(16) unsigned char raw[];
     Shared& s = *reinterpret_cast<Shared*>(raw);
     __shared__ float fscratch[33];
+    pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * ldl;
     const float T = temperature ? temperature[r] : 0.0f;
@@ -337,7 +339,7 @@ FERRIS_API int ferris_sample(const float* logits, int ldl, int rows, int V, cons
         }
         configured = true;
     }
-    sample_kernel<<<rows, THREADS, smem, (cudaStream_t)stream>>>(logits, ldl, V, temperature, top_k, top_p, slots,
+    ferris_launch(sample_kernel, dim3(rows), dim3(THREADS), smem, (cudaStream_t)stream, logits, ldl, V, temperature, top_k, top_p, slots,
                                                               rng_states, out_token, out_prob);
     FERRIS_LAUNCH_CHECK();
 }

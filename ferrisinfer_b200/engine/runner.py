@@ -288,6 +288,8 @@ class ModelRunner:
         pieces = [token_ids, positions, token_seq, q_start, start_pos, state_slot, want]
         for slot_mapping, tables in group_arrays:
             pieces += [slot_mapping, tables.reshape(-1)]
+        singles = [s.q_start for s in seqs if s.q_len == 1] if max_q > 1 else []
+        pieces.append(np.asarray(singles, dtype=np.int32))
         return _HostStep(pieces, T, S, max_q, max_kv, max_blocks, seqs, int(want.size))
 
     def _context(self, host: _HostStep, dev: torch.Tensor):
@@ -304,6 +306,6 @@ class ModelRunner:
             num_tokens=host.T, num_seqs=host.S, token_ids=views[0], positions=views[1], token_seq=views[2],
             seq_q_start=views[3], seq_start_pos=views[4], seq_state_slot=views[5], seqs=host.seqs, paged=paged,
             max_q_len=host.max_q, max_kv_len=host.max_kv, act_dtype=self.dtype, workspace=self.workspace,
-            device=self.device,
+            device=self.device, single_rows=views[-1] if host.pieces[-1].size else None,
         )
         return ctx, (views[6] if host.n_want else None)

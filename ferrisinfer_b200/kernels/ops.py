@@ -343,27 +343,30 @@ def decode_splits(tokens: int, num_kv_heads: int, max_kv_len: int) -> int:
 
 
 def decode_attention(qkv, out, k_cache, v_cache, block_tables, token_seq, positions, num_heads, num_kv_heads,
-                     head_dim, window, scale, splits, scratch):
-    """Split-KV attention for steps of single tokens (bf16, head size 64 or 128)."""
+                     head_dim, window, scale, splits, scratch, rows: Optional[torch.Tensor] = None):
+    """Split-KV attention for single tokens (bf16, head size 64 or 128): every row of the step, or the rows
+    that ``rows`` (int32) names when the step also carries portions of prompts."""
     T, _, ldq = _rows(qkv, "attention queries")
     _, _, ldo = _rows(out, "attention output")
     need = T * num_heads * splits * (head_dim + 2) if splits > 1 else 0
     if need and (scratch is None or scratch.numel() < need or scratch.dtype != torch.float32):
         raise KernelError(f"decode attention with {splits} splits needs {need} floats of scratch")
-    _check(
-        _lib().ferris_decode_attention(_ptr(qkv), _c_int(ldq), _ptr(out), _c_int(ldo), _ptr(k_cache), _ptr(v_cache),
-                                       ctypes.c_longlong(k_cache.shape[0]), _ptr(block_tables),
-                                       _c_int(block_tables.shape[1]), _ptr(token_seq), _ptr(positions), _c_int(T),
-                                       _c_int(num_heads), _c_int(num_kv_heads), _c_int(head_dim),
-                                       _c_int(k_cache.shape[2]), _c_int(window or 0), _c_float(scale), _c_int(splits),
-                                       _ptr(scratch if need else None), _stream()),
-        "decode attention",
-    )
+    common = (_ptr(qkv), _c_int(ldq), _ptr(out), _c_int(ldo), _ptr(k_cache), _ptr(v_cache),
+              ctypes.c_longlong(k_cache.shape[0]), _ptr(block_tables), _c_int(block_tables.shape[1]), _ptr(token_seq),
+              _ptr(positions))
+    tail = (_c_int(num_heads), _c_int(num_kv_heads), _c_int(head_dim), _c_int(k_cache.shape[2]), _c_int(window or 0),
+            _c_float(scale), _c_int(splits), _ptr(scratch if need else None), _stream())
+    if rows is None:
+        _check(_lib().ferris_decode_attention(*common, _c_int(T), *tail), "decode attention")
+    else:
+        _need(rows, "rows of the single tokens", torch.int32)
+        _check(_lib().ferris_decode_attention_listed(*common, _ptr(rows), _c_int(rows.numel()), *tail), "decode attention")
 
 
 def prefill_attention(qkv, out, k_cache, v_cache, block_tables, seq_q_start, seq_start_pos, num_seqs, max_q_len,
-                      num_heads, num_kv_heads, head_dim, window, scale):
-    """Tensor-core attention for portions of prompts (bf16, head size 64 or 128)."""
+                      num_heads, num_kv_heads, head_dim, window, scale, skip_single: bool = False):
+    """Tensor-core attention for portions of prompts (bf16, head size 64 or 128).  ``skip_single``: requests
+    that bring one token are left out (the decode kernel takes them)."""
     _, _, ldq = _rows(qkv, "attention queries")
     _, _, ldo = _rows(out, "attention output")
     _check(
@@ -372,7 +375,7 @@ def prefill_attention(qkv, out, k_cache, v_cache, block_tables, seq_q_start, seq
                                         _c_int(block_tables.shape[1]), _ptr(seq_q_start), _ptr(seq_start_pos),
                                         _c_int(num_seqs), _c_int(max_q_len), _c_int(num_heads), _c_int(num_kv_heads),
                                         _c_int(head_dim), _c_int(k_cache.shape[2]), _c_int(window or 0), _c_float(scale),
-                                        _stream()),
+                                        _c_int(1 if skip_single else 0), _stream()),
         "prefill attention",
     )
 
@@ -395,17 +398,22 @@ def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, nu
                              num_kv_heads, head_dim, window, scale)
         return
     T = qkv.shape[0]
-    if ctx.max_q_len == 1:
+    singles = getattr(ctx, "single_rows", None)
+    if ctx.max_q_len == 1 or singles is not None:
+        # single tokens: all rows of the step, or the listed ones beside portions of prompts
+        n = T if ctx.max_q_len == 1 else singles.numel()
         kv_span = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
-        splits = decode_splits(T, num_kv_heads, kv_span)
+        splits = decode_splits(n, num_kv_heads, kv_span)
         scratch = None
         if splits > 1:
             scratch = ctx.workspace.get("attn_split_scratch", (T * num_heads * splits * (head_dim + 2),), torch.float32)
         decode_attention(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
-                         num_kv_heads, head_dim, window, scale, splits, scratch)
-    else:
+                         num_kv_heads, head_dim, window, scale, splits, scratch,
+                         rows=None if ctx.max_q_len == 1 else singles)
+    if ctx.max_q_len > 1:
         prefill_attention(qkv, out, k_cache, v_cache, block_tables, ctx.seq_q_start, ctx.seq_start_pos, ctx.num_seqs,
-                          ctx.max_q_len, num_heads, num_kv_heads, head_dim, window, scale)
+                          ctx.max_q_len, num_heads, num_kv_heads, head_dim, window, scale,
+                          skip_single=singles is not None)
 
 
 def sample(logits: torch.Tensor, out_token: torch.Tensor, out_prob: Optional[torch.Tensor] = None,

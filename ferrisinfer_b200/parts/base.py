@@ -81,6 +81,9 @@ class StepContext:
     act_dtype: torch.dtype
     workspace: Any  # engine.workspace.Workspace
     device: torch.device = None
+    # in a step that mixes portions of prompts with single tokens: the rows (int32, device) of the
+    # requests that bring exactly one token, so that kernels made for either kind can share the step
+    single_rows: Optional[torch.Tensor] = None
 
     @property
     def all_decode(self) -> bool:

@@ -281,6 +281,10 @@ class AttentionCase:
                               seq_q_start=to(torch.tensor(starts), torch.int32),
                               seq_start_pos=to(torch.tensor([kv - ql for kv, ql in self.seqs]), torch.int32),
                               workspace=Workspace(self.device),
+                              single_rows=(to(torch.tensor([starts[i] for i, (_, ql) in enumerate(self.seqs) if ql == 1]),
+                                              torch.int32)
+                                           if any(ql == 1 for _, ql in self.seqs) and any(ql > 1 for _, ql in self.seqs)
+                                           else None),
                               positions=to(torch.tensor(positions), torch.int32),
                               seqs=[SimpleNamespace(q_start=sum(q for _, q in self.seqs[:i]), q_len=ql, start_pos=kv - ql)
                                     for i, (kv, ql) in enumerate(self.seqs)],

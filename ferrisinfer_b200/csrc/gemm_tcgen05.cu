@@ -271,6 +271,213 @@ __global__ void __launch_bounds__(THREADS)
     if (traced && threadIdx.x == 32) p.trace[6] = global_ns();
 }
 
+// =============================================================================================
+// Long steps (prefill): a PERSISTENT kernel with the TOKENS on the M side of the MMA (128 per tile,
+// lane = token) and the weight rows on its N side (256 per tile; 2 x 128 gate / up in SwiGLU mode).
+// Each CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the accumulators are double-buffered
+// in tensor memory, so the epilogue of one tile (tcgen05.ld, bias / SiLU / residual, 16-byte
+// stores along the output row) runs while the MMA warp works on the next.
+// =============================================================================================
+constexpr int PT_BLOCK_M = 128;     // tokens per tile
+constexpr int PT_STAGES = 4;
+constexpr int PT_EPI_WARPS = 8;
+constexpr int PT_THREADS = (2 + PT_EPI_WARPS) * 32;
+
+struct PTParams {
+    void* out;
+    const float* bias;
+    int T, N, K, ldo;
+    int bn;             // weight rows per accumulator and tile: 256, or 128 in SwiGLU mode
+    int kblocks;
+    int m_tiles, n_tiles;
+    int up_row_offset;
+    int* status;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(PT_THREADS)
+    gemm_tokens_m_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                         const __grid_constant__ CUtensorMap map_out, const PTParams p) {
+    constexpr int ACCS = MODE == SWIGLU_BF16 ? 2 : 1;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full[PT_STAGES], empty[PT_STAGES], tmem_full[2], tmem_empty[2];
+    __shared__ uint32_t tmem_base;
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int a_bytes = PT_BLOCK_M * BLOCK_K * 2, b_bytes = p.bn * BLOCK_K * 2;
+    const int stage_bytes = a_bytes + ACCS * b_bytes;
+    const int acc_cols = ACCS * p.bn;  // columns of one accumulator buffer
+    const int tiles = p.m_tiles * p.n_tiles;
+    // fp32 outputs leave through shared memory and TMA: 4 KB (32 tokens x 32 floats, swizzled) per epilogue warp
+    uint8_t* out_stage = smem + (size_t)PT_STAGES * stage_bytes + (size_t)(warp >= 2 ? warp - 2 : 0) * 4096;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&map_x);
+        tma_prefetch_descriptor(&map_w);
+        for (int s = 0; s < PT_STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], PT_EPI_WARPS);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(&tmem_base, 512);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem = tmem_base;
+    pdl_launch_dependents();
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % p.m_tiles) * PT_BLOCK_M, n0 = (tile / p.m_tiles) * p.bn;
+                for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+                    const int s = it % PT_STAGES;
+                    if (it >= PT_STAGES && !mbar_wait(&empty[s], ((it / PT_STAGES) - 1) & 1, p.status, 20)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* st = smem + (size_t)s * stage_bytes;
+                    mbar_expect_tx(&full[s], stage_bytes);
+                    tma_load_2d(st, &map_x, kb * BLOCK_K, m0, &full[s]);
+                    tma_load_2d(st + a_bytes, &map_w, kb * BLOCK_K, n0, &full[s]);
+                    if (ACCS == 2) tma_load_2d(st + a_bytes + b_bytes, &map_w, kb * BLOCK_K, p.up_row_offset + n0, &full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_bf16(PT_BLOCK_M, p.bn);
+            int it = 0, local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                // the epilogue must have drained this accumulator buffer (two tiles ago)
+                if (local >= 2 && !mbar_wait(&tmem_empty[buf], ((local >> 1) - 1) & 1, p.status, 21)) break;
+                tcgen05_fence_after();
+                const uint32_t d0 = tmem + buf * acc_cols;
+                for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+                    const int s = it % PT_STAGES;
+                    if (!mbar_wait(&full[s], (it / PT_STAGES) & 1, p.status, 22)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t st = smem_u32(smem + (size_t)s * stage_bytes);
+                    const uint64_t a_desc = umma_desc_k_major_sw128(st);
+                    const uint64_t b_desc = umma_desc_k_major_sw128(st + a_bytes);
+                    const uint64_t b2_desc = umma_desc_k_major_sw128(st + a_bytes + b_bytes);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint64_t adv = (uint64_t)((k * UMMA_K * 2) >> 4);
+                        const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+                        tcgen05_mma_bf16(d0, a_desc + adv, b_desc + adv, idesc, acc);
+                        if (ACCS == 2) tcgen05_mma_bf16(d0 + p.bn, a_desc + adv, b2_desc + adv, idesc, acc);
+                    }
+                    tcgen05_commit(&empty[s]);
+                }
+                if (ok) tcgen05_commit(&tmem_full[buf]);
+            }
+        }
+    } else {
+        // epilogue: warp e owns TMEM lane quarter (warp % 4) = 32 tokens, and one half of the columns
+        const int e = warp - 2;
+        const int quarter = warp & 3, half = e >> 2;
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        int local = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const int m0 = (tile % p.m_tiles) * PT_BLOCK_M, n0 = (tile / p.m_tiles) * p.bn;
+            const int t = m0 + quarter * 32 + lane;
+            if (!mbar_wait(&tmem_full[buf], (local >> 1) & 1, p.status, 23)) break;
+            tcgen05_fence_after();
+            const uint32_t d0 = lane_addr + buf * acc_cols;
+            const int cols = p.bn;  // output columns of this tile
+            for (int c0 = half * 32; c0 < cols; c0 += 64) {
+                uint32_t ra[32], rb[32];
+                tmem_load_32x32(d0 + c0, ra);
+                if (ACCS == 2) tmem_load_32x32(d0 + p.bn + c0, rb);
+                tmem_load_wait();
+                const int n = n0 + c0;
+                if (MODE == STORE_F32 || MODE == ACCUM_F32) {
+                    // the warp's 32 x 32 block goes to shared memory (lane = row, 16-byte chunks swizzled as the
+                    // tensor map expects) and from there to global memory by one TMA store / add-reduction,
+                    // which also clips rows >= T and columns >= N
+                    if (n >= p.N || m0 + quarter * 32 >= p.T) continue;  // warp-uniform
+                    if (lane == 0) tma_store_wait_read();
+                    __syncwarp();
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        float4 r;
+                        r.x = __uint_as_float(ra[4 * v]) + ((p.bias && n + 4 * v < p.N) ? __ldg(p.bias + n + 4 * v) : 0.0f);
+                        r.y = __uint_as_float(ra[4 * v + 1]) + ((p.bias && n + 4 * v + 1 < p.N) ? __ldg(p.bias + n + 4 * v + 1) : 0.0f);
+                        r.z = __uint_as_float(ra[4 * v + 2]) + ((p.bias && n + 4 * v + 2 < p.N) ? __ldg(p.bias + n + 4 * v + 2) : 0.0f);
+                        r.w = __uint_as_float(ra[4 * v + 3]) + ((p.bias && n + 4 * v + 3 < p.N) ? __ldg(p.bias + n + 4 * v + 3) : 0.0f);
+                        *reinterpret_cast<float4*>(out_stage + swizzle128(lane, v)) = r;
+                    }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (MODE == ACCUM_F32)
+                            tma_reduce_add_2d(&map_out, out_stage, n, m0 + quarter * 32);
+                        else
+                            tma_store_2d(&map_out, out_stage, n, m0 + quarter * 32);
+                        tma_store_commit();
+                    }
+                    continue;
+                }
+                if (t >= p.T || n >= p.N) continue;
+                const bool whole = n + 32 <= p.N;
+                if (MODE == STORE_BF16 || MODE == SWIGLU_BF16) {
+                    bf16* o = reinterpret_cast<bf16*>(p.out) + (size_t)t * p.ldo + n;
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int c = 0; c < 32; c += 2) {
+                        float v0, v1;
+                        if (MODE == SWIGLU_BF16) {
+                            v0 = silu_mul(__uint_as_float(ra[c]), __uint_as_float(rb[c]));
+                            v1 = silu_mul(__uint_as_float(ra[c + 1]), __uint_as_float(rb[c + 1]));
+                        } else {
+                            v0 = __uint_as_float(ra[c]) + ((p.bias && n + c < p.N) ? __ldg(p.bias + n + c) : 0.0f);
+                            v1 = __uint_as_float(ra[c + 1]) + ((p.bias && n + c + 1 < p.N) ? __ldg(p.bias + n + c + 1) : 0.0f);
+                        }
+                        packed[c >> 1] = pack_bf16(v0, v1);
+                    }
+                    if (whole) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            reinterpret_cast<uint4*>(o)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            if (n + c < p.N)
+                                o[c] = __ushort_as_bfloat16(
+                                    (unsigned short)((c & 1) ? (packed[c >> 1] >> 16) : (packed[c >> 1] & 0xffffu)));
+                    }
+                }
+            }
+            // this warp has read its part of the buffer: the MMA warp may overwrite it
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+        }
+    }
+    if ((MODE == STORE_F32 || MODE == ACCUM_F32) && warp >= 2 && lane == 0) tma_store_wait_all();
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem, 512);
+    }
+}
+
 struct WeightMap {
     const void* base;
     uint64_t rows, cols, ld;
@@ -297,7 +504,43 @@ int weight_map(const void* base, uint64_t rows, uint64_t cols, uint64_t ld, CUte
     return FERRIS_OK;
 }
 
+// Weight maps of the token-major kernel: boxes of bn rows.
+WeightMap g_pt_maps[WEIGHT_MAPS];
+uint32_t g_pt_box[WEIGHT_MAPS];
+int g_pt_map_count = 0;
+
+int pt_weight_map(const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows, CUtensorMap* out) {
+    for (int i = 0; i < g_pt_map_count; ++i) {
+        const WeightMap& m = g_pt_maps[i];
+        if (m.base == base && m.rows == rows && m.cols == cols && m.ld == ld && g_pt_box[i] == box_rows) {
+            *out = m.map;
+            return FERRIS_OK;
+        }
+    }
+    CUtensorMap m;
+    int rc = ferris_make_tensor_map_2d(&m, base, rows, cols, ld, box_rows, BLOCK_K);
+    if (rc != FERRIS_OK) return rc;
+    const int slot = g_pt_map_count < WEIGHT_MAPS ? g_pt_map_count++ : 0;
+    g_pt_maps[slot] = {base, rows, cols, ld, m};
+    g_pt_box[slot] = box_rows;
+    *out = m;
+    return FERRIS_OK;
+}
+
 int g_sms = 0;
+
+template <int MODE>
+int launch_pt(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const PTParams& p, int ctas,
+              size_t smem, cudaStream_t s) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tokens_m_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+        e = ferris_launch(gemm_tokens_m_kernel<MODE>, dim3(ctas), dim3(PT_THREADS), smem, s, mx, mw, mo, p);
+    if (e != cudaSuccess) {
+        ferris_set_error("gemm: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    FERRIS_LAUNCH_CHECK();
+}
 
 template <int MODE>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, size_t smem, cudaStream_t s) {
@@ -381,6 +624,46 @@ FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bi
     ferris_gemm_tcgen05_plan(T, N, K, accs, &bt, &splits, &scratch_floats, &n_counters);
     if (splits > 1 && (!scratch || !counters)) FERRIS_REFUSE("tensor-core gemm: a K split needs scratch and counters");
 
+    cudaStream_t s = (cudaStream_t)stream;
+    // long steps: the persistent token-major kernel (its 16-byte stores need aligned output rows)
+    const int elt = (mode == STORE_BF16 || mode == SWIGLU_BF16) ? 2 : 4;
+    if (T >= PT_BLOCK_M && !trace && ((size_t)ldo * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0) {
+        PTParams q;
+        q.out = out;
+        q.bias = bias;
+        q.T = T;
+        q.N = N;
+        q.K = K;
+        q.ldo = ldo;
+        q.m_tiles = (T + PT_BLOCK_M - 1) / PT_BLOCK_M;
+        // 256 weight rows per tile where that still gives every SM a tile, else 128 (always 128 + 128 for SwiGLU)
+        q.bn = (accs == 2 || q.m_tiles * ((N + 255) / 256) < g_sms) ? 128 : 256;
+        q.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+        q.n_tiles = (N + q.bn - 1) / q.bn;
+        q.up_row_offset = up_row_offset;
+        q.status = ferris_status_ptr();
+        CUtensorMap mx, mw;
+        int rc = ferris_make_tensor_map_2d(&mx, x, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, PT_BLOCK_M, BLOCK_K);
+        if (rc != FERRIS_OK) return rc;
+        rc = pt_weight_map(w, (uint64_t)rows_w, (uint64_t)K, (uint64_t)ldw, (uint32_t)q.bn, &mw);
+        if (rc != FERRIS_OK) return rc;
+        CUtensorMap mo = mx;  // unused by the bf16 modes
+        if (elt == 4) {
+            rc = ferris_make_tensor_map_2d_f32(&mo, out, (uint64_t)T, (uint64_t)N, (uint64_t)ldo, 32);
+            if (rc != FERRIS_OK) return rc;
+        }
+        const int stage_bytes = PT_BLOCK_M * BLOCK_K * 2 + accs * q.bn * BLOCK_K * 2;
+        const size_t smem = (size_t)PT_STAGES * stage_bytes + (size_t)PT_EPI_WARPS * 4096 + 1024;
+        int ctas = q.m_tiles * q.n_tiles;
+        if (ctas > g_sms) ctas = g_sms;
+        switch (mode) {
+            case STORE_BF16: return launch_pt<STORE_BF16>(mx, mw, mo, q, ctas, smem, s);
+            case STORE_F32: return launch_pt<STORE_F32>(mx, mw, mo, q, ctas, smem, s);
+            case ACCUM_F32: return launch_pt<ACCUM_F32>(mx, mw, mo, q, ctas, smem, s);
+            default: return launch_pt<SWIGLU_BF16>(mx, mw, mo, q, ctas, smem, s);
+        }
+    }
+
     CUtensorMap mw, mx;
     int rc = weight_map(w, (uint64_t)rows_w, (uint64_t)K, (uint64_t)ldw, &mw);
     if (rc != FERRIS_OK) return rc;
@@ -412,7 +695,6 @@ FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bi
     const size_t smem = (size_t)stages * stage_bytes + 1024;
     dim3 grid((N + BLOCK_N - 1) / BLOCK_N, (T + bt - 1) / bt, splits);
     if (grid.y > 65535) FERRIS_REFUSE("tensor-core gemm: %d rows are more than one launch takes", T);
-    cudaStream_t s = (cudaStream_t)stream;
     switch (mode) {
         case STORE_BF16: return launch<STORE_BF16>(mw, mx, p, grid, smem, s);
         case STORE_F32: return launch<STORE_F32>(mw, mx, p, grid, smem, s);

@@ -109,3 +109,21 @@ int ferris_make_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t rows,
     if (r != CUDA_SUCCESS) FERRIS_REFUSE("tensor map: cuTensorMapEncodeTiled failed with %d", (int)r);
     return FERRIS_OK;
 }
+
+int ferris_make_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                                  uint64_t row_stride, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) FERRIS_REFUSE("tensor map: the driver offers no cuTensorMapEncodeTiled");
+    if (((uintptr_t)base & 15) || ((row_stride * 4) & 15) || box_rows == 0 || box_rows > 256)
+        FERRIS_REFUSE("tensor map: base %p, row stride %llu, box rows %u do not meet the alignment rules", base,
+                      (unsigned long long)row_stride, box_rows);
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {row_stride * 4};
+    cuuint32_t box[2] = {32, box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) FERRIS_REFUSE("tensor map: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return FERRIS_OK;
+}

@@ -85,6 +85,27 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+// TMA tile shared -> global: a plain store, or an element-wise add into global memory (done by the memory
+// system, so the old values are never read by the SM).  Completion is tracked per thread in bulk groups.
+// Coordinates must not be negative; rows and columns beyond the tensor's extent are dropped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+                 "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+                 "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all of this thread's bulk groups have finished READING shared memory (the source may be rewritten)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// all of this thread's bulk groups are complete (their writes are done)
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -209,3 +230,8 @@ __device__ __forceinline__ uint32_t umma_idesc_bf16(int M, int N) {
 // Returns 0 or a negative error (text in ferris_last_error()).
 int ferris_make_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
                               uint32_t box_rows, uint32_t box_cols);
+
+// The same for an fp32 tensor (boxes of box_rows x 32 floats = 128 bytes, 128-byte swizzle): the target of
+// TMA stores and TMA add-reductions of output tiles.
+int ferris_make_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                                  uint64_t row_stride, uint32_t box_rows);

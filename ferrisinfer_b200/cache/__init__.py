@@ -1,4 +1,4 @@
 """The cache manager: page pools, block tables, state slots."""
 
-from .manager import NO_PAGE, CacheManager, PageGroup, RequestCache
+from .manager import NO_PAGE, CacheManager, PageGroup, PrefixIndex, RequestCache
 from .pages import PagePool

@@ -56,11 +56,58 @@ class RequestCache:
     slot: int
     num_tokens: int = 0  # tokens whose keys/values (or state) are in the cache
     tables: dict = field(default_factory=dict)  # gid -> list of page ids (NO_PAGE = hole)
+    arrays: dict = field(default_factory=dict)  # gid -> int32 array copy of the table, dropped when it changes
+    prompt: Optional[list] = None  # the request's known tokens, when its full pages may be shared
+    registered_blocks: int = 0  # leading blocks of the prompt that are in the prefix index
+    block_keys: list = field(default_factory=list)  # chain hash of each registered or borrowed block
+    shared_tokens: int = 0  # tokens that came from other requests' pages at admission
+
+
+class PrefixIndex:
+    """Full pages of prompts that live requests hold, by the hash of all tokens up to the page's end.
+
+    The reference finds a donor by scanning live sequences for the longest common prompt prefix and
+    COPIES its pages (crates/ferrisinfer-runtime/src/prefix_index.rs:42-108;
+    crates/ferrisinfer-runtime/src/paged_kv.rs:329-389), counting references only as metadata
+    (crates/ferrisinfer-runtime/src/block_manager.rs:84-122).  Here the pages themselves are shared:
+    a chain hash key_i = H(key_{i-1}, tokens of page i) names a block; a borrower's block tables point at
+    the same page ids and the pool counts the holders.  An entry lives as long as its pages do."""
+
+    def __init__(self):
+        self.blocks: dict = {}  # key -> (page ids, one per page group; previous key; the page's tokens)
+        self.by_page: dict = {}  # (gid, page) -> key
+
+    @staticmethod
+    def chain(prev, tokens) -> int:
+        return hash((prev, tuple(tokens)))
+
+    def lookup(self, key, prev, tokens):
+        """The pages of the block, or None; a hash that collides is told apart by the tokens themselves."""
+        entry = self.blocks.get(key)
+        if entry is None or entry[1] != prev or entry[2] != tuple(tokens):
+            return None
+        return entry[0]
+
+    def insert(self, key, prev, tokens, pages: tuple) -> None:
+        if key in self.blocks:
+            return
+        self.blocks[key] = (pages, prev, tuple(tokens))
+        for gid, page in enumerate(pages):
+            self.by_page[(gid, page)] = key
+
+    def forget_page(self, gid: int, page: int) -> None:
+        key = self.by_page.pop((gid, page), None)
+        if key is not None:
+            entry = self.blocks.pop(key, None)
+            if entry is not None:
+                for g2, p2 in enumerate(entry[0]):
+                    self.by_page.pop((g2, p2), None)
 
 
 class CacheManager:
     def __init__(self, needs: list, page_size: int, num_pages, max_requests: int,
-                 dtype: torch.dtype = torch.float32, device=None, extra_states: Optional[dict] = None):
+                 dtype: torch.dtype = torch.float32, device=None, extra_states: Optional[dict] = None,
+                 prefix_sharing: bool = False, min_prefix_share_tokens: int = 0):
         """``needs[i]``: the cache need of run-order entry i (PagedKV, FixedState or None).
         ``num_pages``: pages per group (an int for all groups, or a dict gid -> int).
         ``device`` None: bookkeeping only (no tensors), as the CPU tests use it."""
@@ -103,6 +150,13 @@ class CacheManager:
                                                        device=device)
         self._free_slots = list(range(self.max_requests - 1, -1, -1))
         self.requests: dict = {}
+        # Pages of prompts are shared only where a page means the same for every layer: all page groups keep
+        # every key (no window) and no mixer keeps a state of its own.
+        shareable = bool(self.groups) and all(g.window is None for g in self.groups) and not any(
+            isinstance(n, FixedState) for n in needs)
+        self.prefix = PrefixIndex() if (prefix_sharing and shareable) else None
+        self.min_prefix_share_tokens = int(min_prefix_share_tokens)
+        self.stats = {"shared_tokens": 0, "shared_pages": 0}
 
     # ------------------------------------------------------------------ requests
     def has(self, request_id) -> bool:
@@ -112,8 +166,11 @@ class CacheManager:
     def num_free_slots(self) -> int:
         return len(self._free_slots)
 
-    def admit(self, request_id) -> RequestCache:
-        """Give ``request_id`` a state slot (zeroed) and empty block tables."""
+    def admit(self, request_id, prompt: Optional[list] = None) -> RequestCache:
+        """Give ``request_id`` a state slot (zeroed) and empty block tables.  With ``prompt`` (its known
+        tokens) and prefix sharing on, leading full pages that another live request already holds are
+        borrowed: the request then starts with ``num_tokens`` > 0.  At least one token is always left to
+        compute, and fewer than ``min_prefix_share_tokens`` are not worth sharing."""
         if request_id in self.requests:
             raise CacheError(f"request {request_id!r} is already admitted")
         if not self._free_slots:
@@ -121,6 +178,28 @@ class CacheManager:
         slot = self._free_slots.pop()
         rc = RequestCache(request_id, slot, 0, {g.gid: [] for g in self.groups})
         self.requests[request_id] = rc
+        if self.prefix is not None and prompt is not None:
+            rc.prompt = prompt
+            ps = self.page_size
+            most = (len(prompt) - 1) // ps  # never the whole prompt
+            key, found = None, []
+            for b in range(most):
+                tokens = prompt[b * ps:(b + 1) * ps]
+                prev, key = key, PrefixIndex.chain(key, tokens)
+                pages = self.prefix.lookup(key, prev, tokens)
+                if pages is None:
+                    break
+                found.append((key, pages))
+            if found and len(found) * ps >= self.min_prefix_share_tokens:
+                for key, pages in found:
+                    for g, page in zip(self.groups, pages):
+                        g.pool.retain(page)
+                        rc.tables[g.gid].append(page)
+                    rc.block_keys.append(key)
+                rc.registered_blocks = len(found)
+                rc.num_tokens = rc.shared_tokens = len(found) * ps
+                self.stats["shared_tokens"] += rc.shared_tokens
+                self.stats["shared_pages"] += len(found) * len(self.groups)
         for cache in self.layer_caches:
             if cache is not None and cache.state is not None:
                 cache.state[slot].zero_()
@@ -145,15 +224,13 @@ class CacheManager:
         """gid -> pages that ``extend(request_id, new_total)`` would take from the pool."""
         rc = self.get(request_id)
         out = {}
+        blocks = -(-new_total // self.page_size)
         for g in self.groups:
-            blocks = -(-new_total // self.page_size)
             table = rc.tables[g.gid]
             first = self._first_needed_block(g, rc.num_tokens)
-            need = 0
-            for b in range(first, blocks):
-                if b >= len(table) or table[b] == NO_PAGE:
-                    need += 1
-            out[g.gid] = need
+            # every block from `first` up to the table's end has a page (extend fills them, commit frees
+            # only below `first`), so what is missing lies beyond the table's end
+            out[g.gid] = max(0, blocks - max(len(table), first))
         return out
 
     def free_pages(self) -> dict:
@@ -181,12 +258,15 @@ class CacheManager:
         blocks = -(-new_total // self.page_size)
         for g in self.groups:
             table = rc.tables[g.gid]
+            if blocks <= len(table):
+                continue
             first = self._first_needed_block(g, rc.num_tokens)
-            while len(table) < blocks:
-                table.append(NO_PAGE)
-            missing = [b for b in range(first, blocks) if table[b] == NO_PAGE]
-            for b, page in zip(missing, g.pool.alloc(len(missing))):
-                table[b] = page
+            start = len(table)
+            if first > start:  # blocks that the window has passed before they were ever needed
+                table.extend([NO_PAGE] * (first - start))
+                start = first
+            table.extend(g.pool.alloc(blocks - start))
+            rc.arrays.pop(g.gid, None)
 
     def commit(self, request_id, new_total: int) -> int:
         """The step that brought the request to ``new_total`` tokens is done: count them, and give
@@ -195,16 +275,32 @@ class CacheManager:
         if new_total < rc.num_tokens:
             raise CacheError(f"request {request_id!r} cannot shrink from {rc.num_tokens} to {new_total} tokens")
         rc.num_tokens = new_total
+        if self.prefix is not None and rc.prompt is not None:
+            # full pages of the prompt that are now in the cache can be borrowed by later requests
+            ps = self.page_size
+            upto = min(new_total, len(rc.prompt)) // ps
+            while rc.registered_blocks < upto:
+                b = rc.registered_blocks
+                prev = rc.block_keys[-1] if rc.block_keys else None
+                tokens = rc.prompt[b * ps:(b + 1) * ps]
+                key = PrefixIndex.chain(prev, tokens)
+                rc.block_keys.append(key)
+                self.prefix.insert(key, prev, tokens, tuple(rc.tables[g.gid][b] for g in self.groups))
+                rc.registered_blocks += 1
         freed = 0
         for g in self.groups:
             if g.window is None:
                 continue
             table = rc.tables[g.gid]
-            for b in range(min(self._first_needed_block(g, new_total), len(table))):
-                if table[b] != NO_PAGE:
-                    g.pool.release(table[b])
-                    table[b] = NO_PAGE
-                    freed += 1
+            upto = min(self._first_needed_block(g, new_total), len(table))
+            b = upto - 1
+            while b >= 0 and table[b] != NO_PAGE:  # everything below an earlier hole went back before
+                g.pool.release(table[b])
+                table[b] = NO_PAGE
+                freed += 1
+                b -= 1
+            if freed:
+                rc.arrays.pop(g.gid, None)
         return freed
 
     def release(self, request_id) -> int:
@@ -217,12 +313,25 @@ class CacheManager:
             for page in rc.tables[g.gid]:
                 if page != NO_PAGE and g.pool.release(page):
                     freed += 1
+                    if self.prefix is not None:
+                        self.prefix.forget_page(g.gid, page)
         self._free_slots.append(rc.slot)
         return freed
 
     # ----------------------------------------------------------------- addressing
     def block_table(self, request_id, gid: int) -> list:
         return self.get(request_id).tables[gid]
+
+    def block_table_array(self, request_id, gid: int):
+        """The block table as an int32 array (cached until the table changes)."""
+        import numpy as np
+
+        rc = self.get(request_id)
+        arr = rc.arrays.get(gid)
+        if arr is None:
+            arr = np.asarray(rc.tables[gid], dtype=np.int32)
+            rc.arrays[gid] = arr
+        return arr
 
     def slots_for(self, request_id, gid: int, start: int, count: int) -> list:
         """Cache slot (page * page_size + offset) of positions start .. start + count - 1."""
@@ -246,6 +355,11 @@ class CacheManager:
                     if page != NO_PAGE:
                         holders[page] = holders.get(page, 0) + 1
             g.pool.check(holders)
+        if self.prefix is not None:
+            for key, entry in self.prefix.blocks.items():
+                for g, page in zip(self.groups, entry[0]):
+                    if g.pool.refcount(page) <= 0:
+                        raise CacheError(f"the prefix index names page {page} of group {g.gid}, which nobody holds")
         held = [rc.slot for rc in self.requests.values()]
         if len(set(held)) != len(held):
             raise CacheError("a state slot is held by two requests")

@@ -45,6 +45,7 @@ class GenerationOutput:
     generated_tokens: list  # list[TokenSample]
     finish_reason: FinishReason
     preemptions: int = 0
+    reused_prompt_tokens: int = 0
 
     def generated_token_ids(self) -> list:
         return [t.token_id for t in self.generated_tokens]
@@ -61,12 +62,14 @@ class StepOutput:
 class Engine:
     def __init__(self, model=None, *, config=None, seed: int = 0, dtype="bfloat16", device=None,
                  page_size: int = 16, num_pages: Optional[int] = None, gpu_memory_fraction: float = 0.5,
-                 scheduler: Optional[SchedulerConfig] = None, init_device="cpu"):
+                 scheduler: Optional[SchedulerConfig] = None, init_device="cpu", prefix_sharing: bool = True):
         """``model``: a model folder (config.json + safetensors).  Or ``config`` (a folder, dict or
         typed configuration) with ``seed``: random weights, no folder needed.
         ``num_pages``: pages per page group; by default what ``gpu_memory_fraction`` of the free device
         memory holds.  ``init_device``: where random weights are drawn ("cpu": the values a model folder
-        written with the same seed holds; a CUDA device: other values, much faster for large models)."""
+        written with the same seed holds; a CUDA device: other values, much faster for large models).
+        ``prefix_sharing``: requests whose prompts begin with the same full pages as a live request's share
+        those pages instead of recomputing them (where every layer keeps all keys)."""
         ops.require_device()
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.dtype = parse_dtype(dtype)
@@ -85,7 +88,8 @@ class Engine:
             num_pages = self._pages_that_fit(needs, page_size, gpu_memory_fraction, sc)
         self.runner = ModelRunner(self.model, self.dtype, self.device, page_size=page_size, num_pages=num_pages,
                                   max_requests=sc.max_batch_size, max_model_len=sc.max_sequence_length,
-                                  extra_states={RNG_STATE: RNG_NEED})
+                                  extra_states={RNG_STATE: RNG_NEED}, prefix_sharing=prefix_sharing,
+                                  min_prefix_share_tokens=sc.min_prefix_share_tokens)
         self.sampler = Sampler(self.runner.cache.state_tensors[RNG_STATE])
         self.scheduler = Scheduler(sc, self.runner.cache, on_admit=self._on_admit, on_preempt=self._on_preempt)
         self._next_id = 0
@@ -138,7 +142,7 @@ class Engine:
         entries, sampling = [], []
         for e in plan.entries:
             seq = e.seq
-            tokens = seq.tokens[e.start:e.start + e.count]
+            tokens = seq.token_slice(e.start, e.count)
             wants = e.samples and len(seq.generated) < seq.max_new_tokens \
                 and seq.num_tokens < self.scheduler_config.max_sequence_length
             entries.append(StepEntry(seq.request_id, tokens, [e.count - 1] if wants else []))
@@ -184,7 +188,7 @@ class Engine:
         return GenerationOutput(
             request_id, list(seq.prompt),
             [TokenSample(t, p) for t, p in zip(seq.generated, seq.probabilities)],
-            seq.finish_reason, seq.preemptions)
+            seq.finish_reason, seq.preemptions, seq.reused_prompt_tokens)
 
 
 def generate(model, prompts, params: Optional[SamplingParams] = None, **engine_options) -> list:

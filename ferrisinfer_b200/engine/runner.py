@@ -73,7 +73,7 @@ class ModelRunner:
 
     def __init__(self, model: DecoderModel, dtype: torch.dtype, device, page_size: int, num_pages: int,
                  max_requests: int, max_model_len: Optional[int] = None, extra_states: Optional[dict] = None,
-                 cuda_graphs: bool = True):
+                 cuda_graphs: bool = True, prefix_sharing: bool = False, min_prefix_share_tokens: int = 0):
         if not model.bound:
             raise FerrisError("the model has no weights bound")
         self.model = model
@@ -82,7 +82,8 @@ class ModelRunner:
         self.vocab_size = model.vocab_size
         self.max_model_len = int(max_model_len or model.plan.max_positions)
         self.cache = CacheManager(model.cache_needs(), page_size, num_pages, max_requests, dtype=dtype,
-                                  device=self.device, extra_states=extra_states)
+                                  device=self.device, extra_states=extra_states, prefix_sharing=prefix_sharing,
+                                  min_prefix_share_tokens=min_prefix_share_tokens)
         self.workspace = Workspace(self.device)
         self.steps_run = 0
         self.last_h2d_bytes = 0
@@ -237,33 +238,34 @@ class ModelRunner:
 
         S = len(entries)
         ps = cache.page_size
-        token_ids = np.empty(T, dtype=np.int32)
-        positions = np.empty(T, dtype=np.int32)
-        token_seq = np.empty(T, dtype=np.int32)
+        rcs = [cache.get(e.request_id) for e in entries]
+        q_lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=S)
+        start_pos = np.fromiter((rc.num_tokens for rc in rcs), dtype=np.int32, count=S)
+        state_slot = np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=S)
         q_start = np.zeros(S + 1, dtype=np.int32)
-        start_pos = np.empty(S, dtype=np.int32)
-        state_slot = np.empty(S, dtype=np.int32)
+        np.cumsum(q_lens, out=q_start[1:])
+        if T == S:  # one token each
+            token_ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=S)
+            token_seq = np.arange(S, dtype=np.int32)
+            positions = start_pos.copy()
+        else:
+            token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+            token_seq = np.repeat(np.arange(S, dtype=np.int32), q_lens)
+            positions = (np.arange(T, dtype=np.int32) - q_start[token_seq] + start_pos[token_seq]).astype(np.int32)
+        if token_ids.min() < 0 or token_ids.max() >= self.vocab_size:
+            raise FerrisError(f"a token id of the step lies outside [0, {self.vocab_size})")
+        token_ids = token_ids.astype(np.int32)
         want_rows = []
         seqs = []
-        max_q = max_kv = 0
-        row = 0
-        for i, e in enumerate(entries):
-            rc = cache.get(e.request_id)
-            n = len(e.tokens)
-            toks = np.asarray(e.tokens, dtype=np.int64)
-            if toks.min() < 0 or toks.max() >= self.vocab_size:
-                raise FerrisError(f"request {e.request_id!r}: a token id lies outside [0, {self.vocab_size})")
-            token_ids[row:row + n] = toks
-            positions[row:row + n] = np.arange(rc.num_tokens, rc.num_tokens + n, dtype=np.int32)
-            token_seq[row:row + n] = i
-            q_start[i + 1] = row + n
-            start_pos[i] = rc.num_tokens
-            state_slot[i] = rc.slot
-            want_rows += [row + w for w in e.want]
-            seqs.append(SeqInfo(e.request_id, row, n, rc.num_tokens, rc.slot))
-            max_q = max(max_q, n)
-            max_kv = max(max_kv, rc.num_tokens + n)
-            row += n
+        for i, (e, rc) in enumerate(zip(entries, rcs)):
+            row = int(q_start[i])
+            if len(e.want) == 1:
+                want_rows.append(row + e.want[0])
+            elif e.want:
+                want_rows += [row + w for w in e.want]
+            seqs.append(SeqInfo(e.request_id, row, int(q_lens[i]), rc.num_tokens, rc.slot))
+        max_q = int(q_lens.max())
+        max_kv = int((start_pos + q_lens).max())
         # block tables are as wide as the next power of two of what the longest request needs, so that the
         # shapes a decode graph is recorded with recur
         need_blocks = max(1, -(-max_kv // ps))
@@ -273,16 +275,14 @@ class ModelRunner:
         max_blocks = min(max_blocks, max(need_blocks, -(-self.max_model_len // ps)))
         group_arrays = []
         for g in cache.groups:
-            slot_mapping = np.empty(T, dtype=np.int32)
             tables = np.full((S, max_blocks), NO_PAGE, dtype=np.int32)
-            for i, (e, s) in enumerate(zip(entries, seqs)):
-                table = cache.block_table(e.request_id, g.gid)
-                tables[i, :len(table)] = table
-                pos = positions[s.q_start:s.q_start + s.q_len]
-                pages = tables[i, pos // ps]
-                if (pages < 0).any():
-                    raise CacheError(f"request {e.request_id!r}: a token of the step has no page in group {g.gid}")
-                slot_mapping[s.q_start:s.q_start + s.q_len] = pages * ps + pos % ps
+            for i, e in enumerate(entries):
+                arr = cache.block_table_array(e.request_id, g.gid)
+                tables[i, :arr.size] = arr
+            pages = tables[token_seq, positions // ps]
+            if (pages < 0).any():
+                raise CacheError(f"a token of the step has no page in group {g.gid}")
+            slot_mapping = (pages * ps + positions % ps).astype(np.int32)
             group_arrays.append((slot_mapping, tables))
         want = np.asarray(want_rows, dtype=np.int32)
         pieces = [token_ids, positions, token_seq, q_start, start_pos, state_slot, want]

@@ -64,6 +64,7 @@ class SchedulerConfig:
     max_prefill_batch_tokens: int = 1024  # token budget of one step (decoded tokens count too)
     max_sequence_length: int = 4096  # prompt + generated tokens of one request
     max_generated_tokens: int = 512  # cap on any request's max_new_tokens
+    min_prefix_share_tokens: int = 64  # shorter common prefixes are not shared
 
 
 @dataclass
@@ -82,6 +83,7 @@ class Sequence:
     slot: Optional[int] = None
     saved_rng_state: Optional[int] = None
     preemptions: int = 0
+    reused_prompt_tokens: int = 0  # tokens taken from other requests' pages instead of being computed
 
     @property
     def tokens(self) -> list:
@@ -90,6 +92,15 @@ class Sequence:
     @property
     def num_tokens(self) -> int:
         return len(self.prompt) + len(self.generated)
+
+    def token_slice(self, start: int, count: int) -> list:
+        """tokens[start : start + count] without building the whole list."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.generated[start - n:start - n + count]
+        if start + count <= n:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.generated[:start + count - n]
 
     @property
     def pending(self) -> int:
@@ -226,17 +237,19 @@ class Scheduler:
             seq = self.waiting[0]
             if seq in plan.preempted:
                 break  # preempted in this very step: it waits for the next one
+            rc = cache.admit(seq.request_id, seq.tokens)
+            seq.num_computed = rc.num_tokens  # > 0 if leading pages are shared with a live request
             first = min(seq.pending, cfg.max_prefill_chunk_tokens, budget)
-            rc = cache.admit(seq.request_id)
-            ok, _ = fits(seq, first)
+            ok, _ = fits(seq, seq.num_computed + first)
             if not ok and self.running:
                 # not even the first portion fits while others run: wait (a lone request takes what fits)
                 cache.release(seq.request_id)
+                seq.num_computed = 0
                 break
             self.waiting.popleft()
             seq.slot = rc.slot
             seq.phase = Phase.PREFILL
-            seq.num_computed = 0
+            seq.reused_prompt_tokens += rc.num_tokens
             self.running.append(seq)
             plan.admitted.append(seq)
             if self.on_admit:

@@ -153,3 +153,115 @@ def test_random_orders_keep_every_page_accounted_for(seed):
         m.release(rid)
     m.check_invariants()
     assert all(g.pool.num_used == 0 for g in m.groups) and m.num_free_slots == 4
+
+
+# ------------------------------------------------------------------------------------ prefix sharing
+def sharing_manager(**kw):
+    return CacheManager([FULL, FULL], 4, kw.pop("num_pages", 32), kw.pop("max_requests", 4), prefix_sharing=True, **kw)
+
+
+def run_prompt(m, rid, prompt, upto=None):
+    rc = m.admit(rid, prompt)
+    total = len(prompt) if upto is None else upto
+    m.extend(rid, total)
+    m.commit(rid, total)
+    return rc
+
+
+def test_full_pages_of_a_common_prefix_are_shared_and_counted():
+    m = sharing_manager()
+    common = list(range(100, 110))  # two full pages of 4 and a half
+    run_prompt(m, "a", common + [1, 2, 3])
+    used = m.groups[0].pool.num_used
+    rc = m.admit("b", common + [7, 8])
+    assert rc.num_tokens == 8 and rc.shared_tokens == 8  # the two full pages; the third differs
+    assert m.block_table("b", 0) == m.block_table("a", 0)[:2]
+    assert [m.groups[0].pool.refcount(p) for p in m.block_table("b", 0)] == [2, 2]
+    assert m.groups[0].pool.num_used == used  # nothing new was taken
+    m.extend("b", 12)
+    m.commit("b", 12)
+    assert m.block_table("b", 0)[2] != m.block_table("a", 0)[2]  # the page that differs is private
+    m.check_invariants()
+    assert m.stats["shared_tokens"] == 8 and m.stats["shared_pages"] == 2 * len(m.groups)
+    # the donor leaves first: its shared pages stay with the borrower and in the index
+    freed = m.release("a")
+    assert freed == 2 * len(m.groups) and m.groups[0].pool.refcount(m.block_table("b", 0)[0]) == 1
+    rc = m.admit("c", common + [9])
+    assert rc.num_tokens == 8
+    m.release("b")
+    m.release("c")
+    m.check_invariants()
+    assert m.groups[0].pool.num_used == 0 and not m.prefix.blocks and not m.prefix.by_page
+
+
+def test_the_whole_prompt_is_never_shared_and_short_prefixes_are_not_worth_it():
+    m = sharing_manager()
+    prompt = list(range(8))
+    run_prompt(m, "a", prompt)
+    assert m.admit("same", list(prompt)).num_tokens == 4  # 8 tokens are two full pages, but one token must be computed
+    assert m.admit("longer", prompt + [5]).num_tokens == 8
+    strict = sharing_manager(min_prefix_share_tokens=12)
+    run_prompt(strict, "a", prompt + [1, 2, 3, 4, 5])
+    assert strict.admit("b", prompt + [9]).num_tokens == 0  # 8 common tokens < 12
+    assert strict.admit("c", prompt + [1, 2, 3, 4, 9]).num_tokens == 12
+
+
+def test_pages_are_shared_only_once_they_are_computed():
+    m = sharing_manager()
+    prompt = list(range(20))
+    run_prompt(m, "a", prompt, upto=6)  # only the first page of a is complete
+    assert m.admit("b", list(prompt)).num_tokens == 4
+    m.extend("a", 20)
+    m.commit("a", 20)
+    assert m.admit("c", list(prompt)).num_tokens == 16
+
+
+def test_generated_tokens_and_other_prompts_do_not_match():
+    m = sharing_manager()
+    run_prompt(m, "a", [1, 2, 3, 4, 5, 6, 7, 8, 9])
+    assert m.admit("b", [1, 2, 3, 4, 5, 6, 7, 0, 9]).num_tokens == 4  # the second page differs in one token
+    assert m.admit("c", [2, 2, 3, 4, 5, 6, 7, 8, 9]).num_tokens == 0  # a chain starts at the first page
+    m.extend("a", 14)  # tokens beyond the prompt (generated) are not offered
+    m.commit("a", 14)
+    assert m.get("a").registered_blocks == 2
+
+
+def test_sharing_is_off_where_a_page_does_not_mean_the_same_for_every_layer():
+    assert CacheManager([FULL, WINDOW], 4, 8, 2, prefix_sharing=True).prefix is None
+    assert CacheManager([FULL, FixedState((3,))], 4, 8, 2, prefix_sharing=True).prefix is None
+    assert CacheManager([FULL], 4, 8, 2).prefix is None
+    assert CacheManager([FULL], 4, 8, 2, prefix_sharing=True).prefix is not None
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_orders_with_shared_prefixes(seed):
+    rng = random.Random(seed)
+    m = CacheManager([FULL, FULL], 4, 48, max_requests=5, prefix_sharing=True)
+    stems = [[rng.randrange(50) for _ in range(rng.choice([5, 9, 16]))] for _ in range(3)]
+    live, counter = {}, 0
+    for _ in range(300):
+        action = rng.random()
+        if action < 0.3 and m.num_free_slots:
+            prompt = list(rng.choice(stems)) + [rng.randrange(50) for _ in range(rng.randrange(1, 6))]
+            rid = f"r{counter}"
+            counter += 1
+            rc = m.admit(rid, prompt)
+            assert rc.num_tokens % 4 == 0 and rc.num_tokens < len(prompt)
+            live[rid] = [rc.num_tokens, len(prompt) + rng.randrange(0, 6)]
+        elif action < 0.8 and live:
+            rid = rng.choice(list(live))
+            have, goal = live[rid]
+            new_total = min(goal, have + rng.choice([1, 2, 5]))
+            if new_total > have and m.can_extend(rid, new_total):
+                m.extend(rid, new_total)
+                m.commit(rid, new_total)
+                live[rid][0] = new_total
+        elif live:
+            rid = rng.choice(list(live))
+            m.release(rid)
+            del live[rid]
+        m.check_invariants()
+    for rid in list(live):
+        m.release(rid)
+    m.check_invariants()
+    assert all(g.pool.num_used == 0 for g in m.groups) and not m.prefix.blocks

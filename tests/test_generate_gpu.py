@@ -137,6 +137,41 @@ def test_preemption_when_pages_run_out_does_not_change_the_tokens(device, folder
     assert all(g.pool.num_used == 0 for g in tight.runner.cache.groups)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_requests_that_begin_alike_share_pages_and_generate_the_same(dtype, device, folders):
+    """Eight requests share a long beginning (the baseline's shared-prefix case, in small): with sharing the later
+    ones compute only what differs, hold the donor's pages, and generate exactly what they generate without it."""
+    from ferrisinfer_b200 import SamplingParams, SchedulerConfig
+
+    vocab = TINY["A"]["vocab_size"]
+    stem = helpers.random_ids(vocab, 50, 77)
+    prompts = [stem + helpers.random_ids(vocab, 3 + i, 200 + i) for i in range(8)]
+    params = SamplingParams.greedy(max_new_tokens=6)
+    sched = SchedulerConfig(max_batch_size=8, max_prefill_chunk_tokens=16, max_prefill_batch_tokens=64,
+                            max_sequence_length=128, max_generated_tokens=32, min_prefix_share_tokens=8)
+
+    def run(sharing):
+        engine = _engine(folders["A"], dtype, device, page_size=4, num_pages=256, scheduler=sched, prefix_sharing=sharing)
+        first = engine.submit(prompts[0], params)
+        while not engine.scheduler.running or engine.scheduler.running[0].num_computed < len(prompts[0]):
+            engine.step()  # until the first request's prompt is in the cache
+        rest = [engine.submit(p, params) for p in prompts[1:]]
+        most_pages = 0
+        while engine.has_unfinished():
+            engine.step()
+            most_pages = max(most_pages, engine.runner.cache.groups[0].pool.num_used)
+            engine.runner.cache.check_invariants()
+        outs = [engine.output_of(i) for i in [first] + rest]
+        assert all(g.pool.num_used == 0 for g in engine.runner.cache.groups)
+        return outs, most_pages, engine.runner.cache.stats
+
+    shared, pages_shared, stats = run(True)
+    alone, pages_alone, _ = run(False)
+    assert [o.generated_token_ids() for o in shared] == [o.generated_token_ids() for o in alone]
+    assert all(o.reused_prompt_tokens == 48 for o in shared[1:]) and shared[0].reused_prompt_tokens == 0
+    assert stats["shared_tokens"] == 7 * 48 and pages_shared <= pages_alone - 60
+
+
 def test_abort_gives_pages_back(device, folders):
     from ferrisinfer_b200 import FinishReason, SamplingParams
 

@@ -194,3 +194,24 @@ def test_random_load_never_overdraws_the_pool(seed):
     assert all(g.pool.num_used == 0 for g in cache.groups) and cache.num_free_slots == 4
     for seq in sched.finished.values():
         assert seq.finish_reason is not None and len(seq.generated) <= seq.max_new_tokens
+
+
+def test_a_new_request_reuses_the_pages_of_a_live_request_with_the_same_beginning():
+    config = SchedulerConfig(max_batch_size=4, max_prefill_chunk_tokens=8, max_prefill_batch_tokens=32,
+                             max_sequence_length=64, max_generated_tokens=32, min_prefix_share_tokens=8)
+    cache = CacheManager([FULL], 4, 64, 4, prefix_sharing=True, min_prefix_share_tokens=8)
+    sched = Scheduler(config, cache)
+    stem = list(range(100, 118))  # 18 tokens: four full pages and a half
+    sched.submit("a", stem + [1, 2], greedy(4))
+    for _ in range(3):
+        run_step(sched, cache)  # a's prompt (20 tokens) is in the cache; it decodes
+    sched.submit("b", stem + [5, 6, 7], greedy(2))
+    plan, _ = run_step(sched, cache)
+    shares = {e.seq.request_id: (e.start, e.count) for e in plan.entries}
+    assert shares["b"] == (16, 5)  # four pages reused, the rest computed
+    b = [s for s in sched.running if s.request_id == "b"][0]
+    assert b.reused_prompt_tokens == 16 and cache.stats["shared_tokens"] == 16
+    while sched.has_unfinished():
+        run_step(sched, cache)
+    assert sched.finished["b"].generated == [1, 1] and cache.free_pages() == {0: 64}
+    assert not cache.prefix.blocks

@@ -66,6 +66,27 @@ inline cudaError_t ferris_launch(Kernel kernel, dim3 grid, dim3 block, size_t sm
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// The same with the CTAs of each (x, y) grouped along z into clusters of `cluster_z`.
+template <typename Kernel, typename... Args>
+inline cudaError_t ferris_launch_cluster(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                         unsigned cluster_z, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = cluster_z;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ferris_pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
 

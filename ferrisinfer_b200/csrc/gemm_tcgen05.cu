@@ -20,6 +20,8 @@
 //
 // Formula of the product: crates/ferrisinfer-kernel/src/cpu/matmul.rs:46-118; bias:
 // crates/ferrisinfer-runtime/src/reference.rs:1132-1191; SwiGLU: crates/ferrisinfer-runtime/src/reference.rs:346-360.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -44,6 +46,7 @@ struct Params {
     int kblocks;        // ceil(K / 64)
     int splits;
     int up_row_offset;  // SwiGLU: row of the weight matrix where the up rows start
+    int cluster;        // 1: the K splits of a tile form a cluster and add their partials through shared memory
     int* status;
     unsigned long long* trace;  // optional: CTA (0,0,0) writes nanosecond timestamps of its phases here (8 slots)
 };
@@ -197,6 +200,23 @@ __global__ void __launch_bounds__(THREADS)
                     }
                 }
             }
+        } else if (p.cluster) {
+            // partials of this split go to this CTA's shared memory, [accumulator][token][weight row]
+            float* part = reinterpret_cast<float*>(smem + (size_t)p.stages * stage_bytes);
+            for (int c0 = half * 16; c0 < p.bt; c0 += 32) {
+                uint32_t ra[16], rb[16];
+                if (have) {
+                    tmem_load_32x16(lane_addr + c0, ra);
+                    if (ACCS == 2) tmem_load_32x16(lane_addr + p.bt + c0, rb);
+                    tmem_load_wait();
+                }
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    part[(c0 + c) * BLOCK_N + quarter * 32 + lane] = have ? __uint_as_float(ra[c]) : 0.0f;
+                    if (ACCS == 2)
+                        part[(p.bt + c0 + c) * BLOCK_N + quarter * 32 + lane] = have ? __uint_as_float(rb[c]) : 0.0f;
+                }
+            }
         } else {
             // partials of this split: scratch[((split * ACCS + a) * T + t) * N + n]
             for (int c0 = half * 16; c0 < p.bt; c0 += 32) {
@@ -261,6 +281,37 @@ __global__ void __launch_bounds__(THREADS)
                 }
             }
         }
+    }
+    if (p.cluster && p.splits > 1) {
+        // every CTA of the cluster has its partial in shared memory: CTA r adds up the tokens r, r + splits, ...
+        // of all of them (in split order, so the sum does not depend on timing) and writes those rows out
+        cluster_sync();
+        if (warp >= 2) {
+            const int quarter = warp & 3, half = (warp - 2) >> 2;
+            const int n = n0 + quarter * 32 + lane;
+            const float bias_v = (p.bias && n < p.N) ? p.bias[n] : 0.0f;
+            const uint32_t part = smem_u32(smem + (size_t)p.stages * stage_bytes);
+            const int rank = (int)cluster_ctarank();
+            for (int tl = rank + half * p.splits; tl < p.bt; tl += 2 * p.splits) {
+                const int t = t0 + tl;
+                if (t >= p.T || n >= p.N) continue;
+                const uint32_t addr = part + (uint32_t)((tl * BLOCK_N + quarter * 32 + lane) * 4);
+                float va[8], vb[8];
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    va[s] = s < p.splits ? ld_peer_shared_f32(addr, s) : 0.0f;
+                    if (ACCS == 2) vb[s] = s < p.splits ? ld_peer_shared_f32(addr + (uint32_t)(p.bt * BLOCK_N * 4), s) : 0.0f;
+                }
+                float a = 0.0f, b = 0.0f;
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    a += va[s];
+                    if (ACCS == 2) b += vb[s];
+                }
+                write_out<MODE>(p, t, n, a, b, bias_v);
+            }
+        }
+        cluster_sync();  // nobody leaves while a peer may still read its shared memory
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -528,6 +579,17 @@ int pt_weight_map(const void* base, uint64_t rows, uint64_t cols, uint64_t ld, u
 }
 
 int g_sms = 0;
+int g_cluster = -1;
+
+// The K splits reduce through a cluster's shared memory unless the environment says FERRIS_GEMM_CLUSTER=0
+// (then: partials in global scratch, added by the CTA that finishes last).
+bool ferris_gemm_cluster_enabled() {
+    if (g_cluster < 0) {
+        const char* v = getenv("FERRIS_GEMM_CLUSTER");
+        g_cluster = (v && v[0] == '0') ? 0 : 1;
+    }
+    return g_cluster != 0;
+}
 
 template <int MODE>
 int launch_pt(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const PTParams& p, int ctas,
@@ -543,13 +605,17 @@ int launch_pt(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& m
 }
 
 template <int MODE>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, size_t smem, cudaStream_t s) {
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, size_t smem, unsigned cluster_z,
+           cudaStream_t s) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
         ferris_set_error("gemm: %s", cudaGetErrorString(e));
         return (int)e;
     }
-    e = ferris_launch(gemm_tcgen05_kernel<MODE>, grid, dim3(THREADS), smem, s, mw, mx, p);
+    if (cluster_z > 1)
+        e = ferris_launch_cluster(gemm_tcgen05_kernel<MODE>, grid, dim3(THREADS), smem, s, cluster_z, mw, mx, p);
+    else
+        e = ferris_launch(gemm_tcgen05_kernel<MODE>, grid, dim3(THREADS), smem, s, mw, mx, p);
     if (e != cudaSuccess) {
         ferris_set_error("gemm: %s", cudaGetErrorString(e));
         return (int)e;
@@ -570,25 +636,23 @@ FERRIS_API int ferris_gemm_tcgen05_plan(int T, int N, int K, int accumulators, i
             g_sms = 148;
     }
     // Start from the widest tile that the step fills (every weight byte is then read once) and narrow it
-    // while the SMs would lack tiles: short steps down to 16 tokens (narrow tiles rather than deep K splits:
-    // more CTAs stream the weights, L2 serves the repeats, and the last CTA of a tile has few tokens to add
-    // up), long steps down to 64.
+    // while the SMs would lack CTAs even with the deepest K split: short steps down to 16 tokens, long
+    // steps down to 64.
     const int n_tiles = (N + BLOCK_N - 1) / BLOCK_N;
+    const int kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+    const int most = kblocks >= 4 ? (kblocks / 2 < 8 ? kblocks / 2 : 8) : 1;  // a cluster has at most 8 CTAs
     int bt = 16;
     while (bt < T && bt < 256) bt <<= 1;
-    const int narrowest = T <= 64 ? 16 : (T <= 256 ? 32 : 64);
-    while (bt > narrowest && n_tiles * ((T + bt - 1) / bt) < g_sms) bt >>= 1;
+    const int narrowest = T <= 256 ? 16 : 64;
+    while (bt > narrowest && n_tiles * ((T + bt - 1) / bt) * (bt <= 128 ? most : 1) < g_sms) bt >>= 1;
     const int t_tiles = (T + bt - 1) / bt;
-    const int kblocks = (K + BLOCK_K - 1) / BLOCK_K;
-    // K split: only where tiles are fewer than SMs, and the fewer splits the wider the token tile (the last
-    // CTA of a tile adds the partials of all splits for every token)
+    // K split: where tiles are fewer than SMs; the CTAs of a tile form a cluster and add their partials
+    // through distributed shared memory
     int splits = 1;
     const int tiles = n_tiles * t_tiles;
-    const int most = bt <= 16 ? 16 : (bt == 32 ? 8 : (bt == 64 ? 4 : (bt == 128 ? 2 : 1)));
-    if (tiles < g_sms && kblocks >= 4 && most > 1) {
-        splits = (g_sms + tiles - 1) / tiles;
+    if (tiles < g_sms && most > 1 && bt <= 128) {
+        splits = g_sms / tiles;  // rounded down: a few CTAs more than SMs would cost a second round
         if (splits > most) splits = most;
-        if (splits > kblocks / 2) splits = kblocks / 2;
         if (splits < 1) splits = 1;
         // no split may be empty
         const int per = (kblocks + splits - 1) / splits;
@@ -596,8 +660,9 @@ FERRIS_API int ferris_gemm_tcgen05_plan(int T, int N, int K, int accumulators, i
     }
     *bt_out = bt;
     *splits_out = splits;
-    *scratch_floats = splits > 1 ? (long long)splits * accumulators * T * N : 0;
-    *counters = splits > 1 ? tiles : 0;
+    const bool cluster = ferris_gemm_cluster_enabled();
+    *scratch_floats = (splits > 1 && !cluster) ? (long long)splits * accumulators * T * N : 0;
+    *counters = (splits > 1 && !cluster) ? tiles : 0;
     return FERRIS_OK;
 }
 
@@ -622,7 +687,9 @@ FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bi
     int bt, splits, n_counters;
     long long scratch_floats;
     ferris_gemm_tcgen05_plan(T, N, K, accs, &bt, &splits, &scratch_floats, &n_counters);
-    if (splits > 1 && (!scratch || !counters)) FERRIS_REFUSE("tensor-core gemm: a K split needs scratch and counters");
+    const bool cluster = splits > 1 && ferris_gemm_cluster_enabled();
+    if (splits > 1 && !cluster && (!scratch || !counters))
+        FERRIS_REFUSE("tensor-core gemm: a K split needs scratch and counters");
 
     cudaStream_t s = (cudaStream_t)stream;
     // long steps: the persistent token-major kernel (its 16-byte stores need aligned output rows)
@@ -683,22 +750,25 @@ FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bi
     p.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
     p.splits = splits;
     p.up_row_offset = up_row_offset;
+    p.cluster = cluster ? 1 : 0;
     p.status = ferris_status_ptr();
     p.trace = trace;
     const int stage_bytes = accs * BLOCK_N * BLOCK_K * 2 + bt * BLOCK_K * 2;
-    int stages = (227 * 1024 - 2048) / stage_bytes;
+    const int part_bytes = cluster ? accs * bt * BLOCK_N * 4 : 0;
+    int stages = (227 * 1024 - 2048 - part_bytes) / stage_bytes;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     const int per_split = (p.kblocks + splits - 1) / splits;
     if (stages > per_split) stages = per_split;
     if (stages < 1) stages = 1;
     p.stages = stages;
-    const size_t smem = (size_t)stages * stage_bytes + 1024;
+    const size_t smem = (size_t)stages * stage_bytes + part_bytes + 1024;
     dim3 grid((N + BLOCK_N - 1) / BLOCK_N, (T + bt - 1) / bt, splits);
     if (grid.y > 65535) FERRIS_REFUSE("tensor-core gemm: %d rows are more than one launch takes", T);
+    const unsigned cz = cluster ? (unsigned)splits : 1u;
     switch (mode) {
-        case STORE_BF16: return launch<STORE_BF16>(mw, mx, p, grid, smem, s);
-        case STORE_F32: return launch<STORE_F32>(mw, mx, p, grid, smem, s);
-        case ACCUM_F32: return launch<ACCUM_F32>(mw, mx, p, grid, smem, s);
-        default: return launch<SWIGLU_BF16>(mw, mx, p, grid, smem, s);
+        case STORE_BF16: return launch<STORE_BF16>(mw, mx, p, grid, smem, cz, s);
+        case STORE_F32: return launch<STORE_F32>(mw, mx, p, grid, smem, cz, s);
+        case ACCUM_F32: return launch<ACCUM_F32>(mw, mx, p, grid, smem, cz, s);
+        default: return launch<SWIGLU_BF16>(mw, mx, p, grid, smem, cz, s);
     }
 }

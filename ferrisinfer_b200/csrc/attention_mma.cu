@@ -23,6 +23,7 @@ namespace {
 
 constexpr int TILE_KEYS = 16;
 constexpr int WARPS = 4;
+constexpr int ROW_CACHE = 64;  // block-table look-ups a warp keeps ahead
 
 // Position limits of one thread's two rows (g and g + 8 of the warp's 16-row slab).
 struct RowLimits {
@@ -147,22 +148,22 @@ __device__ __forceinline__ void attend_tile(WarpState<D>& st, uint32_t k_smem, u
     }
 }
 
-// Four consecutive 16-key tiles (64 keys from `key0`) at once: one running-maximum update and one
-// rescale of the output per 64 keys, and four independent score tiles in flight.  The tiles lie
+// NT consecutive 16-key tiles (16 NT keys from `key0`) at once: one running-maximum update and one
+// rescale of the output per block, and NT independent score tiles in flight.  The tiles lie
 // `tile_bytes` apart in shared memory, each laid out as attend_tile expects.
-template <int D>
-__device__ __forceinline__ void attend_block64(WarpState<D>& st, uint32_t base, uint32_t tile_bytes, int key0,
-                                               const RowLimits& lim, float scale) {
+template <int D, int NT>
+__device__ __forceinline__ void attend_block(WarpState<D>& st, uint32_t base, uint32_t tile_bytes, int key0,
+                                             const RowLimits& lim, float scale) {
     const int lane = threadIdx.x & 31;
     const int t = lane & 3;
     const int mi = lane >> 3, r8 = lane & 7;
-    float s[8][4];
+    float s[2 * NT][4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
+    for (int j = 0; j < 2 * NT; ++j)
 #pragma unroll
         for (int e = 0; e < 4; ++e) s[j][e] = 0.0f;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < NT; ++k) {
         const uint32_t k_smem = base + k * tile_bytes;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -177,11 +178,11 @@ __device__ __forceinline__ void attend_block64(WarpState<D>& st, uint32_t base, 
         }
     }
     float mx[2] = {-INFINITY, -INFINITY};
-    const bool interior = key0 + 63 <= min(lim.hi[0], lim.hi[1]) && key0 >= max(lim.lo[0], lim.lo[1]) &&
+    const bool interior = key0 + 16 * NT - 1 <= min(lim.hi[0], lim.hi[1]) && key0 >= max(lim.lo[0], lim.lo[1]) &&
                           lim.hi[0] >= 0 && lim.hi[1] >= 0;
     if (__all_sync(0xffffffffu, interior)) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < 2 * NT; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 s[j][e] *= scale;
@@ -189,7 +190,7 @@ __device__ __forceinline__ void attend_block64(WarpState<D>& st, uint32_t base, 
             }
     } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < 2 * NT; ++j)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int row = e >> 1;
@@ -218,7 +219,7 @@ __device__ __forceinline__ void attend_block64(WarpState<D>& st, uint32_t base, 
         st.o[n][3] *= corr[1];
     }
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < NT; ++k) {
         uint32_t p[4];
         {
             const float e00 = expf(s[2 * k][0] - sub[0]), e01 = expf(s[2 * k][1] - sub[0]);
@@ -291,8 +292,12 @@ __global__ void __launch_bounds__(WARPS * 32)
                             int splits, int* status) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full[WARPS][STAGES];
+    __shared__ int tile_rows[WARPS][ROW_CACHE];  // cache rows of this warp's next tiles, looked up in one go
     uint8_t* smem = align1024(smem_raw);
-    constexpr int STAGE_BYTES = 2 * TILE_KEYS * D * 2;
+    constexpr int NT = D == 64 ? 4 : 2;  // 16-key tiles per pipeline stage and per softmax update
+    constexpr int TILE_BYTES = 2 * TILE_KEYS * D * 2;
+    constexpr int STAGE_BYTES = NT * TILE_BYTES;
+    constexpr int BLOCK_CACHE = ROW_CACHE / NT;  // blocks whose rows the cache holds
 
     const int split = blockIdx.x, hk = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -315,13 +320,14 @@ __global__ void __launch_bounds__(WARPS * 32)
     const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
     const int* table = block_tables + (size_t)seq * max_blocks;
 
-    // key tiles of this split
+    // key tiles of this split, in blocks of NT; the warps take the blocks in turn
     const int first_tile = lo / TILE_KEYS, last_tile = P / TILE_KEYS;
     const int n_tiles = last_tile - first_tile + 1;
     const int per_split = (n_tiles + splits - 1) / splits;
     const int t_begin = first_tile + split * per_split;
     const int t_end = min(t_begin + per_split, last_tile + 1);
-    const int my_count = t_end > t_begin + warp ? (t_end - t_begin - warp + WARPS - 1) / WARPS : 0;
+    const int n_blocks = t_end > t_begin ? (t_end - t_begin + NT - 1) / NT : 0;
+    const int my_count = n_blocks > warp ? (n_blocks - warp + WARPS - 1) / WARPS : 0;
 
     WarpState<D> st;
     init_state(st);
@@ -335,18 +341,51 @@ __global__ void __launch_bounds__(WARPS * 32)
         lim.lo[0] = lim.lo[1] = lo;
     }
     uint8_t* my_stages = smem + (size_t)warp * STAGES * STAGE_BYTES;
-    auto issue = [&](int i) {
-        const int tile = t_begin + warp + i * WARPS;
-        load_tile<D>(my_stages + (i % STAGES) * STAGE_BYTES, &map_k, &map_v,
-                     cache_row_of(table, tile * TILE_KEYS, page_size, nkv, hk), &full[warp][i % STAGES]);
+    auto first_tile_of = [&](int i) { return t_begin + (warp + i * WARPS) * NT; };
+    // the block-table look-ups of the warp's tiles are independent loads, issued together
+    auto fill_rows = [&](int first_block) {
+        for (int e = lane; e < ROW_CACHE; e += 32) {
+            const int i = first_block + e / NT, tile = first_tile_of(i) + e % NT;
+            if (i < my_count && tile < t_end) tile_rows[warp][e] = cache_row_of(table, tile * TILE_KEYS, page_size, nkv, hk);
+        }
+        __syncwarp();
     };
+    auto issue = [&](int i) {
+        const int tile0 = first_tile_of(i);
+        const int valid = min(NT, t_end - tile0);
+        uint64_t* bar = &full[warp][i % STAGES];
+        uint8_t* stage = my_stages + (i % STAGES) * STAGE_BYTES;
+        mbar_expect_tx(bar, valid * TILE_BYTES);
+        for (int k = 0; k < valid; ++k) {
+            const int row = tile_rows[warp][(i % BLOCK_CACHE) * NT + k];
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c) {
+                tma_load_2d(stage + k * TILE_BYTES + c * 2048, &map_k, 64 * c, row, bar);
+                tma_load_2d(stage + k * TILE_BYTES + (D / 64) * 2048 + c * 2048, &map_v, 64 * c, row, bar);
+            }
+        }
+    };
+    fill_rows(0);
     if (lane == 0)
         for (int i = 0; i < STAGES && i < my_count; ++i) issue(i);
     for (int i = 0; i < my_count; ++i) {
         const int s = i % STAGES;
+        // the row cache holds blocks [c, c + BLOCK_CACHE), c a multiple of BLOCK_CACHE; block i + STAGES is
+        // issued below, and everything before it has been issued, so its window may be filled now
+        if ((i + STAGES) % BLOCK_CACHE == 0 && i + STAGES < my_count) {
+            __syncwarp();
+            fill_rows(i + STAGES);
+        }
         if (!mbar_wait(&full[warp][s], (i / STAGES) & 1, status, 1)) break;
         const uint32_t base = smem_u32(my_stages + s * STAGE_BYTES);
-        attend_tile<D>(st, base, base + (D / 64) * 2048, (t_begin + warp + i * WARPS) * TILE_KEYS, lim, scale);
+        const int tile0 = first_tile_of(i);
+        if (tile0 + NT <= t_end) {
+            attend_block<D, NT>(st, base, TILE_BYTES, tile0 * TILE_KEYS, lim, scale);
+        } else {
+            for (int k = 0; tile0 + k < t_end; ++k)
+                attend_tile<D>(st, base + k * TILE_BYTES, base + k * TILE_BYTES + (D / 64) * 2048,
+                               (tile0 + k) * TILE_KEYS, lim, scale);
+        }
         __syncwarp();
         if (lane == 0 && i + STAGES < my_count) issue(i + STAGES);
     }
@@ -547,7 +586,7 @@ __global__ void __launch_bounds__((WARPS + 1) * 32)
         const int key_base = (s_begin + i) * stage_keys;
         if (key_base + stage_keys - 1 <= my_hi && key_base >= my_lo - (TILE_KEYS - 1)) {
             // all four tiles hold keys that rows of this warp see: one pass over the 64 keys
-            attend_block64<D>(st, smem_u32(smem + (size_t)s * STAGE_BYTES), TILE_BYTES, key_base, lim, scale);
+            attend_block<D, PF_STAGE_TILES>(st, smem_u32(smem + (size_t)s * STAGE_BYTES), TILE_BYTES, key_base, lim, scale);
         } else {
 #pragma unroll
             for (int k = 0; k < PF_STAGE_TILES; ++k) {
@@ -648,15 +687,15 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
     cudaStream_t s = (cudaStream_t)stream;
     int* status = ferris_status_ptr();
     if (d == 64) {
-        constexpr int ST = 3;
-        const size_t smem = (size_t)WARPS * ST * 2 * TILE_KEYS * 64 * 2 + 1024;
+        constexpr int ST = 3;  // per warp 3 stages of 4 tiles (16 KB)
+        const size_t smem = (size_t)WARPS * ST * 4 * 2 * TILE_KEYS * 64 * 2 + 1024;
         if ((rc = set_smem(decode_attention_kernel<64, ST>, smem)) != FERRIS_OK) return rc;
         ferris_launch(decode_attention_kernel<64, ST>, grid, dim3(WARPS * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
             token_list, nh, nkv, page_size, window, scale, splits, status);
         if (splits > 1) ferris_launch(decode_merge_kernel<64>, dim3(tokens, nh), dim3(64), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
     } else {
-        constexpr int ST = 2;
-        const size_t smem = (size_t)WARPS * ST * 2 * TILE_KEYS * 128 * 2 + 1024;
+        constexpr int ST = 3;  // per warp 3 stages of 2 tiles (16 KB)
+        const size_t smem = (size_t)WARPS * ST * 2 * 2 * TILE_KEYS * 128 * 2 + 1024;
         if ((rc = set_smem(decode_attention_kernel<128, ST>, smem)) != FERRIS_OK) return rc;
         ferris_launch(decode_attention_kernel<128, ST>, grid, dim3(WARPS * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
             token_list, nh, nkv, page_size, window, scale, splits, status);

@@ -335,9 +335,11 @@ def tensor_core_attention_takes(dtype, num_heads: int, num_kv_heads: int, head_d
 
 def decode_splits(tokens: int, num_kv_heads: int, max_kv_len: int) -> int:
     """Into how many key ranges a single-token step is split, so that the GPU's SMs have work:
-    about two CTAs per SM, and at least eight 16-key tiles per CTA."""
+    one CTA per SM at most (each streams its keys through four per-warp pipelines and holds most of the
+    SM's shared memory, so a CTA more than there are SMs would wait for a second round), and at least
+    eight 16-key tiles per CTA."""
     base = max(1, tokens * num_kv_heads)
-    want = -(-2 * sm_count() // base)
+    want = max(1, sm_count() // base)
     most = max(1, (max_kv_len // 16) // 8)
     return max(1, min(want, most))
 

@@ -277,6 +277,46 @@ __device__ __forceinline__ int cache_row_of(const int* table, int key, int page_
     return (page * nkv + hk) * page_size + key % page_size;
 }
 
+// What the decode kernel needs to take over the rotary-position / cache-write kernel's work for a step of
+// single tokens: it rotates q in its registers, and the warp that owns the tile of the token's own position
+// rotates k, copies v, stores both to the cache and patches them into the tile it has just loaded.
+// inv_freq == nullptr: nothing is fused (q is rotated and the cache written already).
+struct FusedRope {
+    const float* inv_freq;    // [D / 2]; the whole head is rotated (rotary dims == D)
+    const int* slot_mapping;  // [rows of the step]: page * page_size + slot of the token, < 0 or null: no write
+    bf16* k_cache;
+    bf16* v_cache;
+};
+
+__device__ __forceinline__ float2 unpack_bf16(uint32_t v) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
+}
+
+// Rotate the query fragments of rows g and g + 8 (both of the token at position `pos`):
+// pairs (i, i + D/2): lo' = lo cos - hi sin, hi' = hi cos + lo sin (crates/ferrisinfer-kernel/src/cpu/attention.rs:1288-1291).
+template <int D>
+__device__ __forceinline__ void rotate_q(WarpState<D>& st, const float* __restrict__ inv_freq, float pos) {
+    constexpr int HS = D / 32;  // k-steps per half of the head
+    const int t = threadIdx.x & 3;
+#pragma unroll
+    for (int ks = 0; ks < HS; ++ks) {
+#pragma unroll
+        for (int e2 = 0; e2 < 2; ++e2) {
+            const int c = 16 * ks + 2 * t + 8 * e2;
+            float s0, c0, s1, c1;
+            sincosf(pos * inv_freq[c], &s0, &c0);
+            sincosf(pos * inv_freq[c + 1], &s1, &c1);
+#pragma unroll
+            for (int rowsel = 0; rowsel < 2; ++rowsel) {
+                const int e = 2 * e2 + rowsel;
+                const float2 lo = unpack_bf16(st.q[ks][e]), hi = unpack_bf16(st.q[ks + HS][e]);
+                st.q[ks][e] = pack_bf16(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
+                st.q[ks + HS][e] = pack_bf16(hi.x * c0 + lo.x * s0, hi.y * c1 + lo.y * s1);
+            }
+        }
+    }
+}
+
 // =============================================================================================
 // Decode: one CTA per (split, kv head, token).  Its four warps take the 16-key tiles of the
 // split's key range in turn, each with a pipeline of its own; their results are merged through
@@ -289,7 +329,7 @@ __global__ void __launch_bounds__(WARPS * 32)
                             float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ block_tables,
                             int max_blocks, const int* __restrict__ token_seq, const int* __restrict__ positions,
                             const int* __restrict__ token_list, int nh, int nkv, int page_size, int window, float scale,
-                            int splits, int* status) {
+                            int splits, const FusedRope rope, int* status) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full[WARPS][STAGES];
     __shared__ int tile_rows[WARPS][ROW_CACHE];  // cache rows of this warp's next tiles, looked up in one go
@@ -336,6 +376,7 @@ __global__ void __launch_bounds__(WARPS * 32)
         const int g = lane >> 2;
         const bf16* qrow = q + (size_t)tok * ldq + (size_t)hk * G * D;
         load_q(st, g < G ? qrow + (size_t)g * D : nullptr, g + 8 < G ? qrow + (size_t)(g + 8) * D : nullptr);
+        if (rope.inv_freq) rotate_q<D>(st, rope.inv_freq, (float)P);
         lim.hi[0] = g < G ? P : -1;
         lim.hi[1] = g + 8 < G ? P : -1;
         lim.lo[0] = lim.lo[1] = lo;
@@ -379,6 +420,30 @@ __global__ void __launch_bounds__(WARPS * 32)
         if (!mbar_wait(&full[warp][s], (i / STAGES) & 1, status, 1)) break;
         const uint32_t base = smem_u32(my_stages + s * STAGE_BYTES);
         const int tile0 = first_tile_of(i);
+        if (rope.inv_freq && last_tile >= tile0 && last_tile < tile0 + NT && last_tile < t_end) {
+            // this warp holds the tile of the token's own position: its key (rotated) and value come from the
+            // step's qkv row, go to the cache for the steps to come, and into the tile just loaded
+            uint8_t* tb = my_stages + s * STAGE_BYTES + (last_tile - tile0) * TILE_BYTES;
+            const int r = P % TILE_KEYS;
+            const bf16* krow = q + (size_t)tok * ldq + (size_t)(nh + hk) * D;
+            const bf16* vrow = q + (size_t)tok * ldq + (size_t)(nh + nkv + hk) * D;
+            const int slot = rope.slot_mapping ? rope.slot_mapping[tok] : -1;
+            const size_t crow = slot >= 0 ? ((size_t)(slot / page_size) * nkv + hk) * page_size + slot % page_size : 0;
+            auto put = [&](uint8_t* tile, bf16* cache, int c, bf16 v) {
+                *reinterpret_cast<bf16*>(tile + (c >> 6) * 2048 + swizzle128(r, (c & 63) >> 3) + (c & 7) * 2) = v;
+                if (slot >= 0) cache[crow * D + c] = v;
+            };
+            for (int i2 = lane; i2 < D / 2; i2 += 32) {
+                float sn, cs;
+                sincosf((float)P * rope.inv_freq[i2], &sn, &cs);
+                const float klo = __bfloat162float(krow[i2]), khi = __bfloat162float(krow[i2 + D / 2]);
+                put(tb, rope.k_cache, i2, __float2bfloat16_rn(klo * cs - khi * sn));
+                put(tb, rope.k_cache, i2 + D / 2, __float2bfloat16_rn(khi * cs + klo * sn));
+            }
+            for (int c = lane; c < D; c += 32) put(tb + (D / 64) * 2048, rope.v_cache, c, vrow[c]);
+            fence_proxy_async();
+            __syncwarp();
+        }
         if (tile0 + NT <= t_end) {
             attend_block<D, NT>(st, base, TILE_BYTES, tile0 * TILE_KEYS, lim, scale);
         } else {
@@ -670,7 +735,8 @@ FERRIS_API long long ferris_decode_attention_scratch_floats(int tokens, int nh, 
 static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, const void* k_cache, const void* v_cache,
                                  long long cache_pages, const int* block_tables, int max_blocks, const int* token_seq,
                                  const int* positions, const int* token_list, int tokens, int nh, int nkv, int d,
-                                 int page_size, int window, float scale, int splits, float* scratch, void* stream) {
+                                 int page_size, int window, float scale, int splits, float* scratch, void* stream,
+                                 const float* inv_freq = nullptr, const int* slot_mapping = nullptr) {
     if (tokens <= 0) return FERRIS_OK;
     int rc = check_common(nh, nkv, d, page_size, max_blocks);
     if (rc != FERRIS_OK) return rc;
@@ -686,19 +752,24 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
     dim3 grid(splits, nkv, tokens);
     cudaStream_t s = (cudaStream_t)stream;
     int* status = ferris_status_ptr();
+    FusedRope rope;
+    rope.inv_freq = inv_freq;
+    rope.slot_mapping = slot_mapping;
+    rope.k_cache = (bf16*)const_cast<void*>(k_cache);
+    rope.v_cache = (bf16*)const_cast<void*>(v_cache);
     if (d == 64) {
         constexpr int ST = 3;  // per warp 3 stages of 4 tiles (16 KB)
         const size_t smem = (size_t)WARPS * ST * 4 * 2 * TILE_KEYS * 64 * 2 + 1024;
         if ((rc = set_smem(decode_attention_kernel<64, ST>, smem)) != FERRIS_OK) return rc;
         ferris_launch(decode_attention_kernel<64, ST>, grid, dim3(WARPS * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
-            token_list, nh, nkv, page_size, window, scale, splits, status);
+            token_list, nh, nkv, page_size, window, scale, splits, rope, status);
         if (splits > 1) ferris_launch(decode_merge_kernel<64>, dim3(tokens, nh), dim3(64), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
     } else {
         constexpr int ST = 3;  // per warp 3 stages of 2 tiles (16 KB)
         const size_t smem = (size_t)WARPS * ST * 2 * 2 * TILE_KEYS * 128 * 2 + 1024;
         if ((rc = set_smem(decode_attention_kernel<128, ST>, smem)) != FERRIS_OK) return rc;
         ferris_launch(decode_attention_kernel<128, ST>, grid, dim3(WARPS * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
-            token_list, nh, nkv, page_size, window, scale, splits, status);
+            token_list, nh, nkv, page_size, window, scale, splits, rope, status);
         if (splits > 1) ferris_launch(decode_merge_kernel<128>, dim3(tokens, nh), dim3(128), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
     }
     FERRIS_LAUNCH_CHECK();
@@ -725,6 +796,21 @@ FERRIS_API int ferris_decode_attention_listed(const void* q, int ldq, void* out,
     if (!token_list) FERRIS_REFUSE("decode attention: no token list");
     return decode_attention_impl(q, ldq, out, ldo, k_cache, v_cache, cache_pages, block_tables, max_blocks, token_seq,
                                  positions, token_list, tokens, nh, nkv, d, page_size, window, scale, splits, scratch, stream);
+}
+
+// Single-token steps whose q and k have NOT been rotated and whose k and v are NOT in the cache yet: the kernel
+// does the work of the rotary / cache-write kernel on its way (every dim of a head rotated: rotary dims == d).
+// qkv: the step's [tokens, (nh + 2 nkv) d] rows; slot_mapping null: rotate q only (a layer that reads another
+// layer's cache).
+FERRIS_API int ferris_decode_attention_rope(const void* qkv, int ldq, void* out, int ldo, void* k_cache, void* v_cache,
+                                            long long cache_pages, const int* block_tables, int max_blocks,
+                                            const int* token_seq, const int* positions, const float* inv_freq,
+                                            const int* slot_mapping, int tokens, int nh, int nkv, int d, int page_size,
+                                            int window, float scale, int splits, float* scratch, void* stream) {
+    if (!inv_freq) FERRIS_REFUSE("decode attention with rotation: no frequency table");
+    return decode_attention_impl(qkv, ldq, out, ldo, k_cache, v_cache, cache_pages, block_tables, max_blocks, token_seq,
+                                 positions, nullptr, tokens, nh, nkv, d, page_size, window, scale, splits, scratch, stream,
+                                 inv_freq, slot_mapping);
 }
 
 // Portions of prompts (and anything else: a request with one token is a portion of one, unless

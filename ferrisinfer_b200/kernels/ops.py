@@ -382,6 +382,48 @@ def prefill_attention(qkv, out, k_cache, v_cache, block_tables, seq_q_start, seq
     )
 
 
+def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_heads, head_dim, inv_freq, rotary_dim,
+                   window, scale, write_kv: bool = True):
+    """Everything between the q/k/v product and the output product of an attention layer: rotate q and k by
+    position, put k and v into the paged cache (``meta``: the step's block tables and slots for the cache's
+    page group), attend.  A step of single tokens with whole-head rotation on the tensor-core path is ONE
+    kernel (the split-KV kernel rotates and writes on its way); everything else is the rotary / cache-write
+    kernel followed by ``paged_attention``."""
+    T = qkv.shape[0]
+    page_size = k_cache.shape[2]
+    if (ctx.max_q_len == 1 and rotary_dim == head_dim and inv_freq is not None
+            and tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim, page_size)):
+        _need(k_cache, "key cache", qkv.dtype)
+        _need(v_cache, "value cache", qkv.dtype)
+        _need(meta.block_tables, "block tables", torch.int32)
+        _need(meta.slot_mapping, "slot mapping", torch.int32)
+        _need(inv_freq, "rotary frequencies", torch.float32)
+        if (k_cache.dim() != 4 or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim
+                or v_cache.shape != k_cache.shape or qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim
+                or out.shape != (T, num_heads * head_dim) or out.dtype != qkv.dtype
+                or inv_freq.numel() != head_dim // 2 or meta.slot_mapping.numel() != T):
+            raise KernelError(f"attention step: qkv {tuple(qkv.shape)}, cache {tuple(k_cache.shape)}, out {tuple(out.shape)}")
+        kv_span = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
+        splits = decode_splits(T, num_kv_heads, kv_span)
+        need = T * num_heads * splits * (head_dim + 2) if splits > 1 else 0
+        scratch = ctx.workspace.get("attn_split_scratch", (need,), torch.float32) if need else None
+        _, _, ldq = _rows(qkv, "attention queries")
+        _, _, ldo = _rows(out, "attention output")
+        _check(
+            _lib().ferris_decode_attention_rope(
+                _ptr(qkv), _c_int(ldq), _ptr(out), _c_int(ldo), _ptr(k_cache), _ptr(v_cache),
+                ctypes.c_longlong(k_cache.shape[0]), _ptr(meta.block_tables), _c_int(meta.block_tables.shape[1]),
+                _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(inv_freq), _ptr(meta.slot_mapping if write_kv else None),
+                _c_int(T), _c_int(num_heads), _c_int(num_kv_heads), _c_int(head_dim), _c_int(page_size),
+                _c_int(window or 0), _c_float(scale), _c_int(splits), _ptr(scratch), _stream()),
+            "decode attention with rotation",
+        )
+        return
+    rope_cache_write(qkv, ctx.positions, inv_freq, meta.slot_mapping, k_cache, v_cache, num_heads, num_kv_heads,
+                     head_dim, rotary_dim, page_size, write_kv=write_kv)
+    paged_attention(qkv, out, k_cache, v_cache, meta.block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale)
+
+
 def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale):
     """Attention of the step's tokens over the paged cache (their own keys are in it already).
     ``ctx`` is the step context.  bf16 with head size 64 / 128 runs on the tensor cores: the split-KV

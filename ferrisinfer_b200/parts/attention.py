@@ -88,11 +88,9 @@ class GroupedQueryAttention(Mixer):
             inv_freq, rotary = None, 0
         else:
             inv_freq, rotary = table
-        ops.rope_cache_write(qkv, ctx.positions, inv_freq, meta.slot_mapping, cache.k, cache.v, nh, nkv, d,
-                             rotary, meta.page_size, write_kv=owns_cache)
         out = ctx.workspace.get("attn_out", (T, self.q_size), x.dtype)
-        ops.paged_attention(qkv, out, cache.k, cache.v, meta.block_tables, ctx, nh, nkv, d,
-                            self.window or 0, self.scale)
+        ops.attention_step(qkv, out, cache.k, cache.v, meta, ctx, nh, nkv, d, inv_freq, rotary, self.window or 0,
+                           self.scale, write_kv=owns_cache)
         ops.gemm(out, self.o_weight, None, h, accumulate=True)
 
 

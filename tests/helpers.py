@@ -31,7 +31,14 @@ TINY_C = {  # head_dim that is not hidden / heads, as many kv heads as heads, ha
     "rms_norm_eps": 3e-6, "rope_theta": 50000.0, "partial_rotary_factor": 0.5, "hidden_act": "silu",
     "tie_word_embeddings": False,
 }
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+TINY_D = {  # head size 64 and pages of 16: the geometry that the tensor-core attention kernels take in bfloat16
+    "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
+    "vocab_size": 200, "hidden_size": 128, "intermediate_size": 192, "num_hidden_layers": 2,
+    "num_attention_heads": 6, "num_key_value_heads": 2, "head_dim": 64, "max_position_embeddings": 2048,
+    "rms_norm_eps": 1e-6, "rope_theta": 30000.0, "hidden_act": "silu", "tie_word_embeddings": True,
+    "use_sliding_window": True, "sliding_window": 48, "max_window_layers": 1,
+}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 def make_folder(tmp_path, config: dict, seed: int, store_dtype="bfloat16", optional=True) -> str:

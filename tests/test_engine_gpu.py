@@ -9,8 +9,8 @@ from helpers import TINY, TOL
 pytestmark = pytest.mark.gpu
 
 DTYPES = [torch.float32, torch.bfloat16]
-PAGE = {"A": 4, "B": 8, "C": 16}
-LENGTHS = {"A": (5, 9, 17, 70), "B": (3, 11, 23, 40, 97), "C": (2, 33, 64)}
+PAGE = {"A": 4, "B": 8, "C": 16, "D": 16}
+LENGTHS = {"A": (5, 9, 17, 70), "B": (3, 11, 23, 40, 97), "C": (2, 33, 64), "D": (1, 16, 17, 95, 130)}
 
 
 def _runner(folder, dtype, device, page_size, num_pages, max_requests=8):
@@ -59,7 +59,7 @@ def _pages_for(steps, page):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_each_request_alone_and_whole(name, dtype, device, folders, oracles):
     requests = _requests(name)
     steps = helpers.trace_whole(requests)
@@ -67,7 +67,7 @@ def test_each_request_alone_and_whole(name, dtype, device, folders, oracles):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_last_32_tokens_one_by_one(name, dtype, device, folders, oracles):
     requests = _requests(name, extra=(120,))
     steps = helpers.trace_tail_decoded(requests, tail=32)
@@ -75,7 +75,7 @@ def test_last_32_tokens_one_by_one(name, dtype, device, folders, oracles):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_portions_of_changing_size(name, dtype, device, folders, oracles):
     requests = _requests(name, extra=(131,))
     steps = helpers.trace_portions(requests)
@@ -84,7 +84,7 @@ def test_portions_of_changing_size(name, dtype, device, folders, oracles):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_mixed_requests_with_pages_used_again(name, dtype, device, folders, oracles):
     vocab = TINY[name]["vocab_size"]
     lengths = (45, 23, 61, 18, 37, 52, 29, 40)

@@ -392,6 +392,44 @@ def test_attention_long_context_decode_batch(impl, device):
     assert torch.allclose(got, want, **ATT_TOL[BF16]), (got - want).abs().max()
 
 
+@pytest.mark.parametrize("nh, nkv, d, window", [(14, 2, 64, 0), (12, 2, 128, 0), (4, 4, 64, 40), (7, 1, 64, 0)])
+def test_attention_step_of_single_tokens_rotates_and_writes_on_its_way(nh, nkv, d, window, device):
+    """The one-kernel path of a decode step against the two-kernel path: same output, same cache."""
+    from ferrisinfer_b200.kernels import ops
+    from ferrisinfer_b200.parts.base import PagedMeta
+
+    page = 16
+    seqs = [(4096, 1), (1, 1), (16, 1), (17, 1), (33, 1), (700, 1), (48, 1), (49, 1)]
+    case = AttentionCase(device, BF16, nh, nkv, d, page, seqs, seed=d + nh, window=window)
+    qkv, k, v, tables, ctx, T = case.device_inputs()
+    g = torch.Generator().manual_seed(5)
+    qkv[:, nh * d:] = torch.randn(T, 2 * nkv * d, generator=g).to(BF16).to(device)  # the tokens' own k and v
+    slots = torch.tensor([tables[i, (kv - 1) // page].item() * page + (kv - 1) % page for i, (kv, _) in enumerate(seqs)],
+                         dtype=torch.int32, device=device)
+    inv_freq = torch.tensor(plain.rotary_inverse_frequencies(d, d, 1e6).numpy(), device=device)
+    meta = PagedMeta(block_tables=tables, slot_mapping=slots, page_size=page)
+    scale = 1.0 / math.sqrt(d)
+    # two kernels
+    qkv2, k2, v2 = qkv.clone(), k.clone(), v.clone()
+    want = torch.empty(T, nh * d, dtype=BF16, device=device)
+    ops.rope_cache_write(qkv2, ctx.positions, inv_freq, slots, k2, v2, nh, nkv, d, d, page)
+    ops.paged_attention(qkv2, want, k2, v2, tables, ctx, nh, nkv, d, window, scale)
+    # one kernel
+    qkv1, k1, v1 = qkv.clone(), k.clone(), v.clone()
+    got = torch.full_like(want, float("nan"))
+    ops.attention_step(qkv1, got, k1, v1, meta, ctx, nh, nkv, d, inv_freq, d, window, scale)
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    assert torch.equal(k1, k2) and torch.equal(v1, v2), "the cache holds the same rotated keys and values"
+    assert torch.equal(qkv1, qkv), "the fused path leaves the step's qkv rows alone"
+    assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2), (got.float() - want.float()).abs().max()
+    # a layer that reads another layer's cache: q is rotated, nothing is written
+    k3, v3 = k2.clone(), v2.clone()
+    again = torch.full_like(want, float("nan"))
+    ops.attention_step(qkv.clone(), again, k3, v3, meta, ctx, nh, nkv, d, inv_freq, d, window, scale, write_kv=False)
+    assert torch.equal(k3, k2) and torch.equal(v3, v2)
+
+
 # ------------------------------------------------------------------------------------ sampling
 def test_argmax_takes_the_lowest_index_among_equal_maxima(device):
     from ferrisinfer_b200.kernels import ops

@@ -352,7 +352,11 @@ __global__ void __launch_bounds__(WARPS * 32)
     mbar_fence_init();
     __syncthreads();
     pdl_launch_dependents();
-    pdl_wait();
+    // With the rotation fused, nothing this kernel reads from the cache was written by the kernel before it
+    // (the token's own key and value come from its qkv row), and the step's metadata was uploaded long
+    // before: the first tiles are requested BEFORE the wait, which only the queries need.
+    const bool early = rope.inv_freq != nullptr;
+    if (!early) pdl_wait();
     // with a token list, only the listed rows of the step are attended (the others belong to another kernel)
     const int tok = token_list ? token_list[blockIdx.z] : (int)blockIdx.z;
     const int seq = token_seq[tok];
@@ -372,7 +376,7 @@ __global__ void __launch_bounds__(WARPS * 32)
     WarpState<D> st;
     init_state(st);
     RowLimits lim;
-    {
+    auto load_queries = [&]() {
         const int g = lane >> 2;
         const bf16* qrow = q + (size_t)tok * ldq + (size_t)hk * G * D;
         load_q(st, g < G ? qrow + (size_t)g * D : nullptr, g + 8 < G ? qrow + (size_t)(g + 8) * D : nullptr);
@@ -380,7 +384,8 @@ __global__ void __launch_bounds__(WARPS * 32)
         lim.hi[0] = g < G ? P : -1;
         lim.hi[1] = g + 8 < G ? P : -1;
         lim.lo[0] = lim.lo[1] = lo;
-    }
+    };
+    if (!early) load_queries();
     uint8_t* my_stages = smem + (size_t)warp * STAGES * STAGE_BYTES;
     auto first_tile_of = [&](int i) { return t_begin + (warp + i * WARPS) * NT; };
     // the block-table look-ups of the warp's tiles are independent loads, issued together
@@ -409,6 +414,10 @@ __global__ void __launch_bounds__(WARPS * 32)
     fill_rows(0);
     if (lane == 0)
         for (int i = 0; i < STAGES && i < my_count; ++i) issue(i);
+    if (early) {
+        pdl_wait();
+        load_queries();
+    }
     for (int i = 0; i < my_count; ++i) {
         const int s = i % STAGES;
         // the row cache holds blocks [c, c + BLOCK_CACHE), c a multiple of BLOCK_CACHE; block i + STAGES is

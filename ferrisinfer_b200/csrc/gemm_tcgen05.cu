@@ -111,16 +111,31 @@ __global__ void __launch_bounds__(THREADS)
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem = tmem_base;
-    // everything above touched no global memory: it may overlap the tail of the kernel before this one
+    // Everything above touched no global memory: it may overlap the tail of the kernel before this one.
+    // The WEIGHTS do not depend on that kernel either: the producer requests the first ring of weight tiles
+    // before it waits, so their trip from HBM overlaps the wait; the token tiles follow after it.
     pdl_launch_dependents();
+    if (warp == 0 && lane == 0) {
+        const int first = min(n_kb, p.stages);
+        for (int i = 0; i < first; ++i) {
+            uint8_t* st = smem + (size_t)i * stage_bytes;
+            const int k = (kb0 + i) * BLOCK_K;
+            mbar_expect_tx(&full[i], stage_bytes);
+            tma_load_2d(st, &map_w, k, n0, &full[i]);
+            if (ACCS == 2) tma_load_2d(st + a_bytes, &map_w, k, p.up_row_offset + n0, &full[i]);
+        }
+    }
     pdl_wait();
     if (traced && threadIdx.x == 0) p.trace[0] = p.trace[1] = global_ns();
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < n_kb; ++i) {
+            const int first = min(n_kb, p.stages);
+            for (int i = 0; i < first; ++i)
+                tma_load_2d(smem + (size_t)i * stage_bytes + ACCS * a_bytes, &map_x, (kb0 + i) * BLOCK_K, t0, &full[i]);
+            for (int i = first; i < n_kb; ++i) {
                 const int s = i % p.stages;
-                if (i >= p.stages && !mbar_wait(&empty[s], ((i / p.stages) - 1) & 1, p.status, 10)) break;
+                if (!mbar_wait(&empty[s], ((i / p.stages) - 1) & 1, p.status, 10)) break;
                 uint8_t* st = smem + (size_t)s * stage_bytes;
                 const int k = (kb0 + i) * BLOCK_K;
                 mbar_expect_tx(&full[s], stage_bytes);

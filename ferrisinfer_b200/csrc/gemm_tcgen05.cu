@@ -47,6 +47,11 @@ struct Params {
     int splits;
     int up_row_offset;  // SwiGLU: row of the weight matrix where the up rows start
     int cluster;        // 1: the K splits of a tile form a cluster and add their partials through shared memory
+    // RMSNorm fused into the token operand (steps of at most 16 tokens): the kernel reads the fp32 residual rows
+    // norm_h [T, K] and builds x = bf16((h * rstd) * norm_w) in shared memory itself instead of loading x by TMA
+    const float* norm_h;
+    const float* norm_w;
+    float norm_eps;
     int* status;
     unsigned long long* trace;  // optional: CTA (0,0,0) writes nanosecond timestamps of its phases here (8 slots)
 };
@@ -100,7 +105,7 @@ __global__ void __launch_bounds__(THREADS)
         tma_prefetch_descriptor(&map_w);
         tma_prefetch_descriptor(&map_x);
         for (int s = 0; s < p.stages; ++s) {
-            mbar_init(&full[s], 1);
+            mbar_init(&full[s], p.norm_h ? 2 : 1);  // the weight tiles' TMA (+ the token tile built in the kernel)
             mbar_init(&empty[s], 1);
         }
         mbar_init(&accum_full, 1);
@@ -120,7 +125,7 @@ __global__ void __launch_bounds__(THREADS)
         for (int i = 0; i < first; ++i) {
             uint8_t* st = smem + (size_t)i * stage_bytes;
             const int k = (kb0 + i) * BLOCK_K;
-            mbar_expect_tx(&full[i], stage_bytes);
+            mbar_expect_tx(&full[i], p.norm_h ? ACCS * a_bytes : stage_bytes);
             tma_load_2d(st, &map_w, k, n0, &full[i]);
             if (ACCS == 2) tma_load_2d(st + a_bytes, &map_w, k, p.up_row_offset + n0, &full[i]);
         }
@@ -128,10 +133,56 @@ __global__ void __launch_bounds__(THREADS)
     pdl_wait();
     if (traced && threadIdx.x == 0) p.trace[0] = p.trace[1] = global_ns();
 
+    if (p.norm_h && warp >= 2) {
+        // RMSNorm of the step's rows, then the token tiles of all of this CTA's K slices, written where TMA
+        // would have put them (rows of 128 bytes, 16-byte chunks swizzled).  ms = sum(x^2) / K;
+        // r = 1 / sqrt(ms + eps); y = (x r) w  (crates/ferrisinfer-kernel/src/cpu/reduction.rs:35-41).
+        __shared__ float rstd_s[16];
+        const int e = warp - 2;
+        for (int t = e; t < 16; t += 8) {
+            float ss = 0.0f;
+            if (t < p.T) {
+                const float4* row = reinterpret_cast<const float4*>(p.norm_h + (size_t)t * p.K);
+                for (int i = lane; i < p.K / 4; i += 32) {
+                    const float4 v = row[i];
+                    ss = fmaf(v.x, v.x, ss);
+                    ss = fmaf(v.y, v.y, ss);
+                    ss = fmaf(v.z, v.z, ss);
+                    ss = fmaf(v.w, v.w, ss);
+                }
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) rstd_s[t] = 1.0f / sqrtf(ss / (float)p.K + p.norm_eps);
+        }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const int et = threadIdx.x - 64;  // 0..255
+        for (int idx = et; idx < n_kb * 128; idx += 256) {
+            const int i = idx >> 7, t = (idx >> 3) & 15, c = idx & 7;
+            const int k = (kb0 + i) * BLOCK_K + 8 * c;
+            uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+            if (t < p.T && k < p.K) {  // K is a multiple of 8: a chunk is inside or outside as a whole
+                const float4 h0 = *reinterpret_cast<const float4*>(p.norm_h + (size_t)t * p.K + k);
+                const float4 h1 = *reinterpret_cast<const float4*>(p.norm_h + (size_t)t * p.K + k + 4);
+                const float4 w0 = *reinterpret_cast<const float4*>(p.norm_w + k);
+                const float4 w1 = *reinterpret_cast<const float4*>(p.norm_w + k + 4);
+                const float r = rstd_s[t];
+                packed.x = pack_bf16((h0.x * r) * w0.x, (h0.y * r) * w0.y);
+                packed.y = pack_bf16((h0.z * r) * w0.z, (h0.w * r) * w0.w);
+                packed.z = pack_bf16((h1.x * r) * w1.x, (h1.y * r) * w1.y);
+                packed.w = pack_bf16((h1.z * r) * w1.z, (h1.w * r) * w1.w);
+            }
+            *reinterpret_cast<uint4*>(smem + (size_t)i * stage_bytes + ACCS * a_bytes + swizzle128(t, c)) = packed;
+        }
+        fence_proxy_async();  // the MMA reads these tiles through the async proxy
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (threadIdx.x == 64)
+            for (int i = 0; i < n_kb; ++i) mbar_arrive(&full[i]);
+    }
+
     if (warp == 0) {
         if (lane == 0) {
             const int first = min(n_kb, p.stages);
-            for (int i = 0; i < first; ++i)
+            for (int i = 0; i < first && !p.norm_h; ++i)
                 tma_load_2d(smem + (size_t)i * stage_bytes + ACCS * a_bytes, &map_x, (kb0 + i) * BLOCK_K, t0, &full[i]);
             for (int i = first; i < n_kb; ++i) {
                 const int s = i % p.stages;
@@ -687,9 +738,35 @@ FERRIS_API int ferris_gemm_tcgen05_plan(int T, int N, int K, int accumulators, i
 // scratch / counters: as ferris_gemm_tcgen05_plan says (counters must be zero; they are left zero).
 // trace: null, or 8 device u64: CTA (0,0,0) records nanosecond timestamps of its phases (start, set-up done,
 // first stage landed, last MMA issued, accumulator ready, epilogue done, TMEM freed).
+static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N, int K,
+                             int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch, int* counters,
+                             void* stream, unsigned long long* trace, const float* norm_h, const float* norm_w,
+                             float norm_eps);
+
 FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N,
                                    int K, int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch,
                                    int* counters, void* stream, unsigned long long* trace) {
+    return gemm_tcgen05_impl(x, w, bias, out, mode, T, N, K, ldx, ldw, ldo, rows_w, up_row_offset, scratch, counters,
+                             stream, trace, nullptr, nullptr, 0.0f);
+}
+
+// The same product with RMSNorm fused in front: x = bf16((h * rstd(h)) * norm_w) is formed inside the kernel from the
+// fp32 rows h [T, K] (contiguous).  For steps of at most 16 tokens whose K split leaves each CTA at most 8 slices of
+// 64 (ferris_gemm_tcgen05_plan tells); anything else is refused.
+FERRIS_API int ferris_norm_gemm_tcgen05(const float* h, const float* norm_w, float norm_eps, const void* w,
+                                        const float* bias, void* out, int mode, int T, int N, int K, int ldw, int ldo,
+                                        int rows_w, int up_row_offset, void* stream) {
+    if (!h || !norm_w) FERRIS_REFUSE("norm + gemm: no rows or no norm weight");
+    if (T > 16) FERRIS_REFUSE("norm + gemm: %d tokens (at most 16)", T);
+    if (((uintptr_t)h & 15) || ((uintptr_t)norm_w & 15)) FERRIS_REFUSE("norm + gemm: operands must be 16-byte aligned");
+    return gemm_tcgen05_impl(w, w, bias, out, mode, T, N, K, K, ldw, ldo, rows_w, up_row_offset, nullptr, nullptr, stream,
+                             nullptr, h, norm_w, norm_eps);
+}
+
+static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N, int K,
+                             int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch, int* counters,
+                             void* stream, unsigned long long* trace, const float* norm_h, const float* norm_w,
+                             float norm_eps) {
     if (T <= 0 || N <= 0) return FERRIS_OK;
     if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ldx < K || ldw < K)
         FERRIS_REFUSE("tensor-core gemm: K=%d and row strides %d, %d must be multiples of 8 elements", K, ldx, ldw);
@@ -709,7 +786,7 @@ FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bi
     cudaStream_t s = (cudaStream_t)stream;
     // long steps: the persistent token-major kernel (its 16-byte stores need aligned output rows)
     const int elt = (mode == STORE_BF16 || mode == SWIGLU_BF16) ? 2 : 4;
-    if (T >= PT_BLOCK_M && !trace && ((size_t)ldo * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0) {
+    if (T >= PT_BLOCK_M && !trace && !norm_h && ((size_t)ldo * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0) {
         PTParams q;
         q.out = out;
         q.bias = bias;
@@ -749,8 +826,12 @@ FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bi
     CUtensorMap mw, mx;
     int rc = weight_map(w, (uint64_t)rows_w, (uint64_t)K, (uint64_t)ldw, &mw);
     if (rc != FERRIS_OK) return rc;
-    rc = ferris_make_tensor_map_2d(&mx, x, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bt, BLOCK_K);
-    if (rc != FERRIS_OK) return rc;
+    if (norm_h) {
+        mx = mw;  // unused: the kernel builds the token tiles itself
+    } else {
+        rc = ferris_make_tensor_map_2d(&mx, x, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bt, BLOCK_K);
+        if (rc != FERRIS_OK) return rc;
+    }
 
     Params p;
     p.out = out;
@@ -766,6 +847,9 @@ FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bi
     p.splits = splits;
     p.up_row_offset = up_row_offset;
     p.cluster = cluster ? 1 : 0;
+    p.norm_h = norm_h;
+    p.norm_w = norm_w;
+    p.norm_eps = norm_eps;
     p.status = ferris_status_ptr();
     p.trace = trace;
     const int stage_bytes = accs * BLOCK_N * BLOCK_K * 2 + bt * BLOCK_K * 2;
@@ -776,6 +860,9 @@ FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bi
     if (stages > per_split) stages = per_split;
     if (stages < 1) stages = 1;
     p.stages = stages;
+    if (norm_h && (bt != 16 || per_split > stages || (splits > 1 && !cluster)))
+        FERRIS_REFUSE("norm + gemm: this shape (token tile %d, %d K slices per CTA, %d stages) is not taken", bt, per_split,
+                      stages);
     const size_t smem = (size_t)stages * stage_bytes + part_bytes + 1024;
     dim3 grid((N + BLOCK_N - 1) / BLOCK_N, (T + bt - 1) / bt, splits);
     if (grid.y > 65535) FERRIS_REFUSE("tensor-core gemm: %d rows are more than one launch takes", T);

@@ -209,9 +209,72 @@ def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row
     )
 
 
+class LazyRMSNorm:
+    """The RMSNorm of the residual rows ``h`` that has not been computed yet.  A matrix product that can form
+    it on its way (``gemm`` / ``gemm_swiglu`` for short bf16 steps) takes it as its input and no norm kernel
+    runs; everyone else calls ``materialize()`` and gets the normed rows, computed once."""
+
+    def __init__(self, h: torch.Tensor, weight: torch.Tensor, eps: float, out_buffer: torch.Tensor):
+        self.h, self.weight, self.eps, self._out, self._done = h, weight, float(eps), out_buffer, False
+
+    @property
+    def shape(self):
+        return self._out.shape
+
+    @property
+    def dtype(self):
+        return self._out.dtype
+
+    def materialize(self) -> torch.Tensor:
+        if not self._done:
+            rmsnorm(self.h, self.weight, self.eps, self._out)
+            self._done = True
+        return self._out
+
+
+def _norm_gemm_takes(x: "LazyRMSNorm", w: torch.Tensor, accs: int) -> bool:
+    """Whether the short-step kernel can form the norm itself: bf16, at most 16 tokens, and a K split that
+    leaves every CTA at most 8 slices."""
+    T, K = x.shape
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or T > 16 or K % 8 or x._done:
+        return False
+    if not (x.h.is_cuda and x.h.dtype == torch.float32 and x.h.is_contiguous() and x.h.data_ptr() % 16 == 0
+            and x.weight.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0):
+        return False
+    n = w.shape[0] // accs
+    bt, splits, floats, counters = _c_int(), _c_int(), ctypes.c_longlong(), _c_int()
+    _lib().ferris_gemm_tcgen05_plan(_c_int(T), _c_int(n), _c_int(K), _c_int(accs), ctypes.byref(bt), ctypes.byref(splits),
+                                    ctypes.byref(floats), ctypes.byref(counters))
+    kblocks = -(-K // 64)
+    return bt.value == 16 and -(-kblocks // splits.value) <= 8 and floats.value == 0
+
+
+def norm_gemm_tcgen05(x: "LazyRMSNorm", w, bias, out, mode: int, up_row_offset: int = 0):
+    """out = rmsnorm(h) w^T in one kernel (modes as gemm_tcgen05)."""
+    T, K = x.shape
+    rows_w, K2, ldw = _rows(w, "gemm weight")
+    T2, N, ldo = _rows(out, "gemm output")
+    want_dtype = torch.bfloat16 if mode in (0, 3) else torch.float32
+    if K != K2 or T != T2 or out.dtype != want_dtype:
+        raise KernelError(f"norm + gemm: h {tuple(x.h.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
+    if bias is not None:
+        _need(bias, "gemm bias", torch.float32)
+    _check(
+        _lib().ferris_norm_gemm_tcgen05(_ptr(x.h), _ptr(x.weight), _c_float(x.eps), _ptr(w), _ptr(bias), _ptr(out),
+                                        _c_int(mode), _c_int(T), _c_int(N), _c_int(K), _c_int(ldw), _c_int(ldo),
+                                        _c_int(rows_w), _c_int(up_row_offset), _stream()),
+        "norm + gemm",
+    )
+
+
 def gemm(x, w, bias, out, accumulate: bool = False):
     """The matrix product of the model, out (+)= x w^T + bias: the tcgen05 kernel for bf16 operands it takes,
-    the CUDA-core kernel for everything else (all of the 32-bit path)."""
+    the CUDA-core kernel for everything else (all of the 32-bit path).  ``x`` may be a LazyRMSNorm."""
+    if isinstance(x, LazyRMSNorm):
+        if w.shape[0] == out.shape[1] and _norm_gemm_takes(x, w, 1):
+            norm_gemm_tcgen05(x, w, bias, out, 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1))
+            return
+        x = x.materialize()
     if tensor_core_gemm_takes(x, w) and w.shape[0] == out.shape[1]:
         if accumulate:
             gemm_tcgen05(x, w, bias, out, 2)
@@ -227,6 +290,11 @@ def gemm_swiglu(x, gate_up_weight, out, workspace=None):
     T, I = out.shape
     if gate_up_weight.shape[0] != 2 * I:
         raise KernelError(f"gemm_swiglu: weight {tuple(gate_up_weight.shape)} for {I} outputs")
+    if isinstance(x, LazyRMSNorm):
+        if out.dtype == torch.bfloat16 and _norm_gemm_takes(x, gate_up_weight, 2):
+            norm_gemm_tcgen05(x, gate_up_weight, None, out, 3, up_row_offset=I)
+            return
+        x = x.materialize()
     if tensor_core_gemm_takes(x, gate_up_weight) and out.dtype == torch.bfloat16:
         gemm_tcgen05(x, gate_up_weight, None, out, 3, up_row_offset=I)
         return

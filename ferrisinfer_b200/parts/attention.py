@@ -29,6 +29,7 @@ from .plan import PartSpec, build_part, register_part
 
 class GroupedQueryAttention(Mixer):
     graph_safe = True
+    accepts_lazy_norm = True  # x goes to ops.gemm and nowhere else
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, window: Optional[int] = None, scale: Optional[float] = None):
@@ -82,7 +83,7 @@ class GroupedQueryAttention(Mixer):
         meta = ctx.paged[cache.group]
         qkv = ctx.workspace.get("attn_qkv", (T, self.q_size + 2 * self.kv_size), x.dtype)
         ops.gemm(x, self.qkv_weight, self.qkv_bias, qkv)
-        table = self.position.rotary_table(x.device)
+        table = self.position.rotary_table(qkv.device)
         if table is None:
             self.position.apply(qkv, ctx.positions, nh, nkv, d)
             inv_freq, rotary = None, 0

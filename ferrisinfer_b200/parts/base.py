@@ -123,6 +123,13 @@ class Norm(Part):
         """out[i] = norm(h[row_index[i]] or h[i]); h fp32, out in the compute dtype."""
         raise NotImplementedError
 
+    def lazy(self, h: torch.Tensor, out: torch.Tensor):
+        """An object that stands for norm(h): ``materialize()`` computes it into ``out`` (once).  A norm
+        whose arithmetic a matrix-product kernel can do on its way returns a richer object that such a
+        kernel recognises; the default is to compute at once."""
+        self.forward(h, out)
+        return out
+
 
 class PositionEncoding(Part):
     """How positions enter a mixer.  ``rotary_table`` lets the attention mixer fuse the
@@ -142,6 +149,9 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if forward takes its input ``x`` either as a tensor or as the object that ``Norm.lazy`` returns
+    # (which it hands to ``ops.gemm`` unchanged, or turns into a tensor with ``materialize()``).
+    accepts_lazy_norm = False
     # True if forward only launches kernels on the current stream from device-resident metadata (no host
     # loops over requests, no allocation), so that a decode step can be recorded into a CUDA graph.
     graph_safe = False
@@ -157,6 +167,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_lazy_norm = False  # as for Mixer
+
     def forward(self, x: torch.Tensor, h: torch.Tensor, ctx: StepContext) -> None:
         """h += feed_forward(x)."""
         raise NotImplementedError

@@ -48,10 +48,14 @@ class PreNormResidualBlock(Block):
         return bool(getattr(self.mixer, "graph_safe", False))
 
     def forward(self, h, ctx, cache, owns_cache):
-        x = ctx.workspace.get("block_normed", (h.shape[0], self.hidden_size), ctx.act_dtype)
-        self.mixer_norm.forward(h, x)
+        buf = ctx.workspace.get("block_normed", (h.shape[0], self.hidden_size), ctx.act_dtype)
+        x = self.mixer_norm.lazy(h, buf)
+        if not getattr(self.mixer, "accepts_lazy_norm", False) and hasattr(x, "materialize"):
+            x = x.materialize()
         self.mixer.forward(x, h, ctx, cache, owns_cache)
-        self.feed_forward_norm.forward(h, x)
+        x = self.feed_forward_norm.lazy(h, buf)
+        if not getattr(self.feed_forward, "accepts_lazy_norm", False) and hasattr(x, "materialize"):
+            x = x.materialize()
         self.feed_forward.forward(x, h, ctx)
 
 

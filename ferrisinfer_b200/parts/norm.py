@@ -26,5 +26,8 @@ class RMSNorm(Norm):
     def forward(self, h, out, row_index=None):
         ops.rmsnorm(h, self.weight, self.eps, out, row_index)
 
+    def lazy(self, h, out):
+        return ops.LazyRMSNorm(h, self.weight, self.eps, out)
+
 
 register_part("norm", "rmsnorm", RMSNorm)

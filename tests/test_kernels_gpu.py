@@ -153,6 +153,64 @@ def test_gemm_tcgen05_swiglu(T, I, K, device):
     assert ops.kernel_status() == 0
 
 
+@pytest.mark.parametrize("T", [1, 8, 16])
+@pytest.mark.parametrize("N, K", [(1152, 896), (130, 72), (896, 512), (300, 1000)])
+def test_gemm_with_rmsnorm_formed_on_its_way(T, N, K, device):
+    """ops.gemm given the not-yet-computed norm of the residual rows: one kernel, same numbers as norm then product."""
+    from ferrisinfer_b200.kernels import ops
+
+    h = rnd((T, K), F32, device, 31, scale=2.0)
+    nw = 1 + rnd((K,), F32, device, 32, scale=0.1)
+    w = rnd((N, K), BF16, device, 33, scale=0.1)
+    bias = rnd((N,), F32, device, 34)
+    eps = 1e-5
+    y = torch.empty(T, K, dtype=BF16, device=device)
+    ops.rmsnorm(h, nw, eps, y)
+    want = torch.empty(T, N, dtype=BF16, device=device)
+    ops.gemm(y, w, bias, want)
+    lazy = ops.LazyRMSNorm(h, nw, eps, torch.full((T, K), float("nan"), dtype=BF16, device=device))
+    launches = ops.launch_count()
+    got = torch.full((T, N), float("nan"), dtype=BF16, device=device)
+    ops.gemm(lazy, w, bias, got)
+    assert ops.launch_count() - launches == 1 and not lazy._done, "no norm kernel ran"
+    scale = want.float().abs().max().item()
+    assert (got.float() - want.float()).abs().max().item() <= 2e-2 * scale
+    ref = plain.rms_norm(h.cpu().double(), nw.cpu().double(), eps).to(BF16).double() @ w.cpu().double().t() + bias.cpu().double()
+    assert (got.cpu().double() - ref).abs().max().item() <= 2e-2 * scale
+    # accumulation into the residual, and the gated feed-forward's first product
+    acc = rnd((T, N), F32, device, 35)
+    before = acc.clone()
+    ops.gemm(ops.LazyRMSNorm(h, nw, eps, y.clone()), w, None, acc, accumulate=True)
+    assert ((acc - before).cpu().double() - (ref - bias.cpu().double())).abs().max().item() <= 2e-2 * scale
+    if N % 2 == 0:
+        I = N // 2
+        out = torch.full((T, I), float("nan"), dtype=BF16, device=device)
+        ops.gemm_swiglu(ops.LazyRMSNorm(h, nw, eps, y.clone()), w, out)
+        g = ref - bias.cpu().double()
+        want_act = g[:, I:] * plain.silu(g[:, :I])
+        assert (out.cpu().double() - want_act).abs().max().item() <= 3e-2 * (want_act.abs().max().item() + 1e-3)
+    assert ops.kernel_status() == 0
+
+
+def test_lazy_norm_is_computed_where_no_kernel_can_form_it(device):
+    from ferrisinfer_b200.kernels import ops
+
+    h = rnd((40, 256), F32, device, 36)  # 40 tokens: beyond the fused kernel
+    nw = 1 + rnd((256,), F32, device, 37, scale=0.1)
+    w = rnd((64, 256), BF16, device, 38, scale=0.1)
+    lazy = ops.LazyRMSNorm(h, nw, 1e-6, torch.empty(40, 256, dtype=BF16, device=device))
+    out = torch.empty(40, 64, dtype=BF16, device=device)
+    ops.gemm(lazy, w, None, out)
+    assert lazy._done
+    want = plain.rms_norm(h.cpu().double(), nw.cpu().double(), 1e-6).to(BF16).double() @ w.cpu().double().t()
+    assert (out.cpu().double() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+    h32 = rnd((4, 64), F32, device, 39)  # the 32-bit path always computes the norm
+    lazy32 = ops.LazyRMSNorm(h32, torch.ones(64, device=device), 1e-6, torch.empty(4, 64, device=device))
+    out32 = torch.empty(4, 8, device=device)
+    ops.gemm(lazy32, rnd((8, 64), F32, device, 40), None, out32)
+    assert lazy32._done
+
+
 def test_gemm_dispatch_takes_strided_rows_and_refuses_nothing_silently(device):
     from ferrisinfer_b200.kernels import ops
 

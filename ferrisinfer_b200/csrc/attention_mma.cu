@@ -726,6 +726,7 @@ int check_common(int nh, int nkv, int d, int page_size, int max_blocks) {
 template <typename F>
 int set_smem(F kernel, size_t bytes) {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+
     if (e != cudaSuccess) {
         ferris_set_error("attention: %s", cudaGetErrorString(e));
         return (int)e;

@@ -67,18 +67,88 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<TOut>((xr[i] * inv) * w[i]);
 }
 
+__device__ __forceinline__ void store4(float* o, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(o) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(bf16* o, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<uint32_t*>(&lo);
+    v.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(o) = v;
+}
+
+// The same norm, one WARP per row: the row (up to 4096 floats, a multiple of 4) is read once with 16-byte loads
+// and stays in registers between the sum of squares and the scaling.  For long steps.
+template <typename TOut, int VEC>  // VEC float4 per lane: hidden <= 128 * VEC
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                           const int* __restrict__ row_index, TOut* __restrict__ out,
+                                                           int rows, int hidden, float eps) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int src = row_index ? row_index[r] : r;
+    const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * hidden);
+    const int n4 = hidden >> 2;
+    float4 v[VEC];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+        const int i = lane + 32 * j;
+        v[j] = i < n4 ? xr[i] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        ss = fmaf(v[j].x, v[j].x, ss);
+        ss = fmaf(v[j].y, v[j].y, ss);
+        ss = fmaf(v[j].z, v[j].z, ss);
+        ss = fmaf(v[j].w, v[j].w, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
+    TOut* o = out + (size_t)r * hidden;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+        const int i = lane + 32 * j;
+        if (i < n4) {
+            const float4 g = w4[i];
+            store4(o + 4 * i, (v[j].x * inv) * g.x, (v[j].y * inv) * g.y, (v[j].z * inv) * g.z, (v[j].w * inv) * g.w);
+        }
+    }
+}
+
+template <typename TOut>
+static void launch_rmsnorm_rows(const float* x, const float* w, const int* row_index, TOut* out, int rows, int hidden,
+                                float eps, cudaStream_t s) {
+    const dim3 grid((rows + 7) / 8), block(256);
+    if (hidden <= 1024)
+        ferris_launch(rmsnorm_rows_kernel<TOut, 8>, grid, block, 0, s, x, w, row_index, out, rows, hidden, eps);
+    else if (hidden <= 2048)
+        ferris_launch(rmsnorm_rows_kernel<TOut, 16>, grid, block, 0, s, x, w, row_index, out, rows, hidden, eps);
+    else
+        ferris_launch(rmsnorm_rows_kernel<TOut, 32>, grid, block, 0, s, x, w, row_index, out, rows, hidden, eps);
+}
+
 FERRIS_API int ferris_rmsnorm(const float* x, const float* w, const int* row_index, void* out, int out_dtype,
                               int rows, int hidden, float eps, void* stream) {
     if (rows <= 0) return FERRIS_OK;
     if (hidden <= 0) FERRIS_REFUSE("rmsnorm: hidden=%d", hidden);
-    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype != FERRIS_F32 && out_dtype != FERRIS_BF16) FERRIS_REFUSE("rmsnorm: unknown dtype %d", out_dtype);
+    // many rows: a warp per row with the row in registers; few rows: a block per row
+    const bool aligned = ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    if (rows >= 64 && hidden % 4 == 0 && hidden <= 4096 && aligned) {
+        if (out_dtype == FERRIS_F32)
+            launch_rmsnorm_rows<float>(x, w, row_index, (float*)out, rows, hidden, eps, s);
+        else
+            launch_rmsnorm_rows<bf16>(x, w, row_index, (bf16*)out, rows, hidden, eps, s);
+        FERRIS_LAUNCH_CHECK();
+    }
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     if (out_dtype == FERRIS_F32)
         ferris_launch(rmsnorm_kernel<float>, dim3(rows), dim3(threads), 0, s, x, w, row_index, (float*)out, hidden, eps);
-    else if (out_dtype == FERRIS_BF16)
-        ferris_launch(rmsnorm_kernel<bf16>, dim3(rows), dim3(threads), 0, s, x, w, row_index, (bf16*)out, hidden, eps);
     else
-        FERRIS_REFUSE("rmsnorm: unknown dtype %d", out_dtype);
+        ferris_launch(rmsnorm_kernel<bf16>, dim3(rows), dim3(threads), 0, s, x, w, row_index, (bf16*)out, hidden, eps);
     FERRIS_LAUNCH_CHECK();
 }
 
@@ -144,23 +214,27 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
     const int page = slot >= 0 ? slot / page_size : 0;
     const int in_page = slot >= 0 ? slot % page_size : 0;
 
-    // rotate q and k heads: one thread per (head, pair)
+    // rotate q and k heads: a thread takes a pair index and walks the heads, so that the sine and cosine of a
+    // (token, pair) are formed once; with more threads than pairs, groups of threads share the heads
     const int rot_heads = nh + nkv;
-    for (int w = threadIdx.x; w < rot_heads * half; w += blockDim.x) {
-        const int h = w / half, i = w % half;
+    const int groups = half > 0 ? max(1, (int)blockDim.x / half) : 1;
+    if (half > 0 && (int)threadIdx.x < groups * half) {
+        const int i = threadIdx.x % half, g0 = threadIdx.x / half;
         float sn, cs;
         sincosf(pos * inv_freq[i], &sn, &cs);
-        T* x = row + (size_t)h * d;
-        const float lo = to_float(x[i]), hi = to_float(x[i + half]);
-        const T nlo = from_float<T>(lo * cs - hi * sn);
-        const T nhi = from_float<T>(hi * cs + lo * sn);
-        if (h < nh) {
-            x[i] = nlo;
-            x[i + half] = nhi;
-        } else if (slot >= 0) {
-            T* kc = k_cache + (((size_t)page * nkv + (h - nh)) * page_size + in_page) * d;
-            kc[i] = nlo;
-            kc[i + half] = nhi;
+        for (int h = g0; h < rot_heads; h += groups) {
+            T* x = row + (size_t)h * d;
+            const float lo = to_float(x[i]), hi = to_float(x[i + half]);
+            const T nlo = from_float<T>(lo * cs - hi * sn);
+            const T nhi = from_float<T>(hi * cs + lo * sn);
+            if (h < nh) {
+                x[i] = nlo;
+                x[i + half] = nhi;
+            } else if (slot >= 0) {
+                T* kc = k_cache + (((size_t)page * nkv + (h - nh)) * page_size + in_page) * d;
+                kc[i] = nlo;
+                kc[i + half] = nhi;
+            }
         }
     }
     if (slot < 0) return;

@@ -45,18 +45,20 @@ def test_embed_gather(dtype, device):
 
 # ------------------------------------------------------------------------------------- rmsnorm
 @pytest.mark.parametrize("out_dtype", [F32, BF16])
-@pytest.mark.parametrize("hidden, eps", [(1000, 1e-5), (3584, 1e-6), (48, 3e-3)])
-def test_rmsnorm(hidden, eps, out_dtype, device):
+@pytest.mark.parametrize("hidden, eps", [(1000, 1e-5), (3584, 1e-6), (48, 3e-3), (1538, 1e-6), (4100, 1e-5)])
+@pytest.mark.parametrize("n", [37, 131])  # few rows: a block per row; many: a warp per row
+def test_rmsnorm(n, hidden, eps, out_dtype, device):
     from ferrisinfer_b200.kernels import ops
 
-    x = rnd((37, hidden), F32, device, 2, scale=3.0)
+    x = rnd((n, hidden), F32, device, 2, scale=3.0)
     w = 1 + rnd((hidden,), F32, device, 3, scale=0.1)
     want = plain.rms_norm(x.cpu().double(), w.cpu().double(), eps)
-    out = torch.empty(37, hidden, dtype=out_dtype, device=device)
+    out = torch.empty(n, hidden, dtype=out_dtype, device=device)
     ops.rmsnorm(x, w, eps, out)
     assert torch.allclose(out.cpu().double(), want, **tol(out_dtype))
-    rows = torch.tensor([36, 0, 0, 11], dtype=torch.int32, device=device)
-    out = torch.empty(4, hidden, dtype=out_dtype, device=device)
+    picks = [n - 1, 0, 0, 11] * (1 if n < 64 else 17)
+    rows = torch.tensor(picks, dtype=torch.int32, device=device)
+    out = torch.empty(len(picks), hidden, dtype=out_dtype, device=device)
     ops.rmsnorm(x, w, eps, out, rows)
     assert torch.allclose(out.cpu().double(), want[rows.cpu().long()], **tol(out_dtype))
 

@@ -503,7 +503,8 @@ __global__ void __launch_bounds__(WARPS * 32)
         if (splits == 1) {
             out[(size_t)tok * ldo + (size_t)head * D + c] = __float2bfloat16_rn(oo / ll);
         } else {
-            const size_t slot = ((size_t)tok * nh + head) * splits + split;
+            // partial results are indexed by the row's place in this launch (blockIdx.z), not in the step
+            const size_t slot = ((size_t)blockIdx.z * nh + head) * splits + split;
             part_o[slot * D + c] = oo;
             if (c == 0) {
                 part_ml[slot * 2] = mm;
@@ -521,7 +522,7 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
     pdl_wait();
     pdl_launch_dependents();
     const int tok = token_list ? token_list[blockIdx.x] : (int)blockIdx.x, head = blockIdx.y;
-    const size_t base = ((size_t)tok * nh + head) * splits;
+    const size_t base = ((size_t)blockIdx.x * nh + head) * splits;
     float mm = -INFINITY;
     for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(base + s) * 2]);
     for (int c = threadIdx.x; c < D; c += blockDim.x) {
@@ -746,7 +747,7 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
                                  long long cache_pages, const int* block_tables, int max_blocks, const int* token_seq,
                                  const int* positions, const int* token_list, int tokens, int nh, int nkv, int d,
                                  int page_size, int window, float scale, int splits, float* scratch, void* stream,
-                                 const float* inv_freq = nullptr, const int* slot_mapping = nullptr) {
+                                 const float* inv_freq = nullptr, const int* slot_mapping = nullptr, bool merge = true) {
     if (tokens <= 0) return FERRIS_OK;
     int rc = check_common(nh, nkv, d, page_size, max_blocks);
     if (rc != FERRIS_OK) return rc;
@@ -773,14 +774,14 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
         if ((rc = set_smem(decode_attention_kernel<64, ST>, smem)) != FERRIS_OK) return rc;
         ferris_launch(decode_attention_kernel<64, ST>, grid, dim3(WARPS * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
             token_list, nh, nkv, page_size, window, scale, splits, rope, status);
-        if (splits > 1) ferris_launch(decode_merge_kernel<64>, dim3(tokens, nh), dim3(64), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
+        if (splits > 1 && merge) ferris_launch(decode_merge_kernel<64>, dim3(tokens, nh), dim3(64), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
     } else {
         constexpr int ST = 3;  // per warp 3 stages of 2 tiles (16 KB)
         const size_t smem = (size_t)WARPS * ST * 2 * 2 * TILE_KEYS * 128 * 2 + 1024;
         if ((rc = set_smem(decode_attention_kernel<128, ST>, smem)) != FERRIS_OK) return rc;
         ferris_launch(decode_attention_kernel<128, ST>, grid, dim3(WARPS * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
             token_list, nh, nkv, page_size, window, scale, splits, rope, status);
-        if (splits > 1) ferris_launch(decode_merge_kernel<128>, dim3(tokens, nh), dim3(128), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
+        if (splits > 1 && merge) ferris_launch(decode_merge_kernel<128>, dim3(tokens, nh), dim3(128), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
     }
     FERRIS_LAUNCH_CHECK();
 }
@@ -796,8 +797,7 @@ FERRIS_API int ferris_decode_attention(const void* q, int ldq, void* out, int ld
 }
 
 // The same for the rows of a step that `token_list` (int32 [tokens]) names: the single tokens of a step
-// that also carries portions of prompts.  The scratch is indexed by row of the step, so it must hold
-// step_rows * nh * splits * (d + 2) floats.
+// that also carries portions of prompts.  The scratch is indexed by place in the list.
 FERRIS_API int ferris_decode_attention_listed(const void* q, int ldq, void* out, int ldo, const void* k_cache,
                                               const void* v_cache, long long cache_pages, const int* block_tables,
                                               int max_blocks, const int* token_seq, const int* positions,
@@ -811,16 +811,34 @@ FERRIS_API int ferris_decode_attention_listed(const void* q, int ldq, void* out,
 // Single-token steps whose q and k have NOT been rotated and whose k and v are NOT in the cache yet: the kernel
 // does the work of the rotary / cache-write kernel on its way (every dim of a head rotated: rotary dims == d).
 // qkv: the step's [tokens, (nh + 2 nkv) d] rows; slot_mapping null: rotate q only (a layer that reads another
-// layer's cache).
+// layer's cache).  merge == 0 with splits > 1: the partial results of the key ranges stay in scratch, `out` is
+// not written, and the caller merges them (ferris_decode_merge, or the product that follows does it on its way).
 FERRIS_API int ferris_decode_attention_rope(const void* qkv, int ldq, void* out, int ldo, void* k_cache, void* v_cache,
                                             long long cache_pages, const int* block_tables, int max_blocks,
                                             const int* token_seq, const int* positions, const float* inv_freq,
                                             const int* slot_mapping, int tokens, int nh, int nkv, int d, int page_size,
-                                            int window, float scale, int splits, float* scratch, void* stream) {
+                                            int window, float scale, int splits, float* scratch, int merge, void* stream) {
     if (!inv_freq) FERRIS_REFUSE("decode attention with rotation: no frequency table");
     return decode_attention_impl(qkv, ldq, out, ldo, k_cache, v_cache, cache_pages, block_tables, max_blocks, token_seq,
                                  positions, nullptr, tokens, nh, nkv, d, page_size, window, scale, splits, scratch, stream,
-                                 inv_freq, slot_mapping);
+                                 inv_freq, slot_mapping, merge != 0);
+}
+
+// The merge alone, for partial results that ferris_decode_attention_rope left in scratch (merge == 0):
+// out [tokens, nh * d] bf16 from scratch = [tokens, nh, splits, d] followed by [tokens, nh, splits, 2].
+FERRIS_API int ferris_decode_merge(const float* scratch, void* out, int ldo, int tokens, int nh, int d, int splits,
+                                   void* stream) {
+    if (tokens <= 0) return FERRIS_OK;
+    if (!scratch || splits < 1 || nh <= 0 || nh > 65535) FERRIS_REFUSE("decode merge: %d heads, %d splits", nh, splits);
+    if (d != 64 && d != 128) FERRIS_REFUSE("decode merge: head size %d (64 or 128)", d);
+    const float* part_o = scratch;
+    const float* part_ml = scratch + (size_t)tokens * nh * splits * d;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (d == 64)
+        ferris_launch(decode_merge_kernel<64>, dim3(tokens, nh), dim3(64), 0, s, part_o, part_ml, (bf16*)out, ldo, (const int*)nullptr, nh, splits);
+    else
+        ferris_launch(decode_merge_kernel<128>, dim3(tokens, nh), dim3(128), 0, s, part_o, part_ml, (bf16*)out, ldo, (const int*)nullptr, nh, splits);
+    FERRIS_LAUNCH_CHECK();
 }
 
 // Portions of prompts (and anything else: a request with one token is a portion of one, unless

@@ -52,6 +52,12 @@ struct Params {
     const float* norm_h;
     const float* norm_w;
     float norm_eps;
+    // Merge of split-KV attention fused into the token operand (same limits): x[t, head * d + c] =
+    // sum_s O_s[c] e^{m_s - M} / sum_s l_s e^{m_s - M} from the partial results of the splits,
+    // merge_o [T, heads, splits, d] and merge_ml [T, heads, splits, 2] = (m, l); K = heads * d
+    const float* merge_o;
+    const float* merge_ml;
+    int merge_splits, merge_heads, merge_d;
     int* status;
     unsigned long long* trace;  // optional: CTA (0,0,0) writes nanosecond timestamps of its phases here (8 slots)
 };
@@ -100,12 +106,13 @@ __global__ void __launch_bounds__(THREADS)
     const int n_kb = max(kb1 - kb0, 0);
     uint32_t tmem_cols = 32;
     while (tmem_cols < (uint32_t)(ACCS * p.bt)) tmem_cols <<= 1;
+    const bool built = p.norm_h || p.merge_o;  // the kernel forms the token tiles itself
 
     if (threadIdx.x == 0) {
         tma_prefetch_descriptor(&map_w);
         tma_prefetch_descriptor(&map_x);
         for (int s = 0; s < p.stages; ++s) {
-            mbar_init(&full[s], p.norm_h ? 2 : 1);  // the weight tiles' TMA (+ the token tile built in the kernel)
+            mbar_init(&full[s], built ? 2 : 1);  // the weight tiles' TMA (+ the token tile built in the kernel)
             mbar_init(&empty[s], 1);
         }
         mbar_init(&accum_full, 1);
@@ -125,7 +132,7 @@ __global__ void __launch_bounds__(THREADS)
         for (int i = 0; i < first; ++i) {
             uint8_t* st = smem + (size_t)i * stage_bytes;
             const int k = (kb0 + i) * BLOCK_K;
-            mbar_expect_tx(&full[i], p.norm_h ? ACCS * a_bytes : stage_bytes);
+            mbar_expect_tx(&full[i], built ? ACCS * a_bytes : stage_bytes);
             tma_load_2d(st, &map_w, k, n0, &full[i]);
             if (ACCS == 2) tma_load_2d(st + a_bytes, &map_w, k, p.up_row_offset + n0, &full[i]);
         }
@@ -179,10 +186,54 @@ __global__ void __launch_bounds__(THREADS)
             for (int i = 0; i < n_kb; ++i) mbar_arrive(&full[i]);
     }
 
+    if (p.merge_o && warp >= 2) {
+        // The attention rows of the step from the partial results of the key ranges (the merge of the split-KV
+        // attention kernel, same order of sums), written as the token tiles of this CTA's K slices.
+        const int et = threadIdx.x - 64;  // 0..255
+        const int S = p.merge_splits, d = p.merge_d;
+        for (int idx = et; idx < n_kb * 128; idx += 256) {
+            const int i = idx >> 7, t = (idx >> 3) & 15, c = idx & 7;
+            const int k = (kb0 + i) * BLOCK_K + 8 * c;
+            uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+            if (t < p.T && k < p.K) {  // d is a multiple of 8: a chunk lies within one head
+                const int head = k / d, col = k - head * d;
+                const size_t base = ((size_t)t * p.merge_heads + head) * S;
+                const float2* ml = reinterpret_cast<const float2*>(p.merge_ml) + base;
+                float mm = -INFINITY;
+                for (int sp = 0; sp < S; ++sp) mm = fmaxf(mm, ml[sp].x);
+                float ll = 0.0f, o[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+                for (int sp = 0; sp < S; ++sp) {
+                    const float2 v = ml[sp];
+                    const float f = v.x == -INFINITY ? 0.0f : expf(v.x - mm);
+                    const float4* po = reinterpret_cast<const float4*>(p.merge_o + (base + sp) * d + col);
+                    const float4 o0 = po[0], o1 = po[1];
+                    ll += v.y * f;
+                    o[0] += o0.x * f;
+                    o[1] += o0.y * f;
+                    o[2] += o0.z * f;
+                    o[3] += o0.w * f;
+                    o[4] += o1.x * f;
+                    o[5] += o1.y * f;
+                    o[6] += o1.z * f;
+                    o[7] += o1.w * f;
+                }
+                packed.x = pack_bf16(o[0] / ll, o[1] / ll);
+                packed.y = pack_bf16(o[2] / ll, o[3] / ll);
+                packed.z = pack_bf16(o[4] / ll, o[5] / ll);
+                packed.w = pack_bf16(o[6] / ll, o[7] / ll);
+            }
+            *reinterpret_cast<uint4*>(smem + (size_t)i * stage_bytes + ACCS * a_bytes + swizzle128(t, c)) = packed;
+        }
+        fence_proxy_async();
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        if (threadIdx.x == 64)
+            for (int i = 0; i < n_kb; ++i) mbar_arrive(&full[i]);
+    }
+
     if (warp == 0) {
         if (lane == 0) {
             const int first = min(n_kb, p.stages);
-            for (int i = 0; i < first && !p.norm_h; ++i)
+            for (int i = 0; i < first && !built; ++i)
                 tma_load_2d(smem + (size_t)i * stage_bytes + ACCS * a_bytes, &map_x, (kb0 + i) * BLOCK_K, t0, &full[i]);
             for (int i = first; i < n_kb; ++i) {
                 const int s = i % p.stages;
@@ -738,16 +789,26 @@ FERRIS_API int ferris_gemm_tcgen05_plan(int T, int N, int K, int accumulators, i
 // scratch / counters: as ferris_gemm_tcgen05_plan says (counters must be zero; they are left zero).
 // trace: null, or 8 device u64: CTA (0,0,0) records nanosecond timestamps of its phases (start, set-up done,
 // first stage landed, last MMA issued, accumulator ready, epilogue done, TMEM freed).
+// A token operand that the kernel forms itself instead of loading x: an RMSNorm of fp32 rows, or the merge of the
+// partial results of split-KV attention.
+struct TokenSource {
+    const float* norm_h = nullptr;
+    const float* norm_w = nullptr;
+    float norm_eps = 0.0f;
+    const float* merge_o = nullptr;
+    const float* merge_ml = nullptr;
+    int merge_splits = 0, merge_heads = 0, merge_d = 0;
+};
+
 static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N, int K,
                              int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch, int* counters,
-                             void* stream, unsigned long long* trace, const float* norm_h, const float* norm_w,
-                             float norm_eps);
+                             void* stream, unsigned long long* trace, const TokenSource& src);
 
 FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N,
                                    int K, int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch,
                                    int* counters, void* stream, unsigned long long* trace) {
     return gemm_tcgen05_impl(x, w, bias, out, mode, T, N, K, ldx, ldw, ldo, rows_w, up_row_offset, scratch, counters,
-                             stream, trace, nullptr, nullptr, 0.0f);
+                             stream, trace, TokenSource());
 }
 
 // The same product with RMSNorm fused in front: x = bf16((h * rstd(h)) * norm_w) is formed inside the kernel from the
@@ -759,14 +820,41 @@ FERRIS_API int ferris_norm_gemm_tcgen05(const float* h, const float* norm_w, flo
     if (!h || !norm_w) FERRIS_REFUSE("norm + gemm: no rows or no norm weight");
     if (T > 16) FERRIS_REFUSE("norm + gemm: %d tokens (at most 16)", T);
     if (((uintptr_t)h & 15) || ((uintptr_t)norm_w & 15)) FERRIS_REFUSE("norm + gemm: operands must be 16-byte aligned");
+    TokenSource src;
+    src.norm_h = h;
+    src.norm_w = norm_w;
+    src.norm_eps = norm_eps;
     return gemm_tcgen05_impl(w, w, bias, out, mode, T, N, K, K, ldw, ldo, rows_w, up_row_offset, nullptr, nullptr, stream,
-                             nullptr, h, norm_w, norm_eps);
+                             nullptr, src);
+}
+
+// The same product with the merge of split-KV attention fused in front: the token operand x [T, heads * d] is formed
+// inside the kernel from the partial results that ferris_decode_attention* leaves when it is told not to merge
+// (scratch: fp32 [T, heads, splits, d] followed by [T, heads, splits, 2]).  Same limits as the fused norm.
+FERRIS_API int ferris_merge_gemm_tcgen05(const float* scratch_parts, int heads, int d, int attn_splits, const void* w,
+                                         const float* bias, void* out, int mode, int T, int N, int ldw, int ldo,
+                                         int rows_w, void* stream) {
+    if (!scratch_parts) FERRIS_REFUSE("merge + gemm: no partial results");
+    if (T > 16) FERRIS_REFUSE("merge + gemm: %d tokens (at most 16)", T);
+    if (heads <= 0 || (d != 64 && d != 128) || attn_splits < 1)
+        FERRIS_REFUSE("merge + gemm: %d heads of %d over %d key ranges", heads, d, attn_splits);
+    if ((uintptr_t)scratch_parts & 15) FERRIS_REFUSE("merge + gemm: operands must be 16-byte aligned");
+    if (mode == SWIGLU_BF16) FERRIS_REFUSE("merge + gemm: no SwiGLU mode");
+    TokenSource src;
+    src.merge_o = scratch_parts;
+    src.merge_ml = scratch_parts + (size_t)T * heads * attn_splits * d;
+    src.merge_splits = attn_splits;
+    src.merge_heads = heads;
+    src.merge_d = d;
+    const int K = heads * d;
+    return gemm_tcgen05_impl(w, w, bias, out, mode, T, N, K, K, ldw, ldo, rows_w, 0, nullptr, nullptr, stream, nullptr,
+                             src);
 }
 
 static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N, int K,
                              int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch, int* counters,
-                             void* stream, unsigned long long* trace, const float* norm_h, const float* norm_w,
-                             float norm_eps) {
+                             void* stream, unsigned long long* trace, const TokenSource& src) {
+    const bool built = src.norm_h || src.merge_o;
     if (T <= 0 || N <= 0) return FERRIS_OK;
     if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ldx < K || ldw < K)
         FERRIS_REFUSE("tensor-core gemm: K=%d and row strides %d, %d must be multiples of 8 elements", K, ldx, ldw);
@@ -786,7 +874,7 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
     cudaStream_t s = (cudaStream_t)stream;
     // long steps: the persistent token-major kernel (its 16-byte stores need aligned output rows)
     const int elt = (mode == STORE_BF16 || mode == SWIGLU_BF16) ? 2 : 4;
-    if (T >= PT_BLOCK_M && !trace && !norm_h && ((size_t)ldo * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0) {
+    if (T >= PT_BLOCK_M && !trace && !built && ((size_t)ldo * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0) {
         PTParams q;
         q.out = out;
         q.bias = bias;
@@ -826,7 +914,7 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
     CUtensorMap mw, mx;
     int rc = weight_map(w, (uint64_t)rows_w, (uint64_t)K, (uint64_t)ldw, &mw);
     if (rc != FERRIS_OK) return rc;
-    if (norm_h) {
+    if (built) {
         mx = mw;  // unused: the kernel builds the token tiles itself
     } else {
         rc = ferris_make_tensor_map_2d(&mx, x, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bt, BLOCK_K);
@@ -847,9 +935,14 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
     p.splits = splits;
     p.up_row_offset = up_row_offset;
     p.cluster = cluster ? 1 : 0;
-    p.norm_h = norm_h;
-    p.norm_w = norm_w;
-    p.norm_eps = norm_eps;
+    p.norm_h = src.norm_h;
+    p.norm_w = src.norm_w;
+    p.norm_eps = src.norm_eps;
+    p.merge_o = src.merge_o;
+    p.merge_ml = src.merge_ml;
+    p.merge_splits = src.merge_splits;
+    p.merge_heads = src.merge_heads;
+    p.merge_d = src.merge_d;
     p.status = ferris_status_ptr();
     p.trace = trace;
     const int stage_bytes = accs * BLOCK_N * BLOCK_K * 2 + bt * BLOCK_K * 2;
@@ -859,9 +952,16 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
     const int per_split = (p.kblocks + splits - 1) / splits;
     if (stages > per_split) stages = per_split;
     if (stages < 1) stages = 1;
+    // Many tiles and no K split (the output head over the vocabulary): shallower rings, so that two CTAs share an
+    // SM and one streams weights while the other's epilogue and set-up run.
+    const long long tiles_all = (long long)((N + BLOCK_N - 1) / BLOCK_N) * ((T + bt - 1) / bt);
+    if (splits == 1 && !built && tiles_all >= 4LL * g_sms) {
+        const int fit = (227 * 1024 / 2 - 3072) / stage_bytes;
+        if (fit >= 4 && stages > fit) stages = fit;
+    }
     p.stages = stages;
-    if (norm_h && (bt != 16 || per_split > stages || (splits > 1 && !cluster)))
-        FERRIS_REFUSE("norm + gemm: this shape (token tile %d, %d K slices per CTA, %d stages) is not taken", bt, per_split,
+    if (built && (bt != 16 || per_split > stages || (splits > 1 && !cluster)))
+        FERRIS_REFUSE("norm / merge + gemm: this shape (token tile %d, %d K slices per CTA, %d stages) is not taken", bt, per_split,
                       stages);
     const size_t smem = (size_t)stages * stage_bytes + part_bytes + 1024;
     dim3 grid((N + BLOCK_N - 1) / BLOCK_N, (T + bt - 1) / bt, splits);

@@ -34,6 +34,18 @@ __device__ __constant__ int kWidth[NUM_DIGITS] = {11, 11, 11, 11, 11, 9};
 typedef unsigned long long u64;
 typedef unsigned int u32;
 
+// barrier over all threads of all CTAs of the cluster; an fp32 from CTA `rank`'s shared memory
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float peer_shared_f32(u32 addr, u32 rank) {
+    u32 remote;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ u64 make_key(float logit, int index) {
     u32 u = __float_as_uint(logit);
     u32 k = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
@@ -319,6 +331,109 @@ __global__ void __launch_bounds__(THREADS)
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Greedy rows only: a cluster of eight CTAs per row, each over an eighth of the vocabulary in ONE pass
+// (the running maximum with the sum of exp(l - maximum) rescaled when the maximum moves), combined
+// through the cluster's shared memory.  Same results as the general kernel's greedy branch: the lowest
+// index among equal maxima, probability 1 / sum exp(l - max).
+// ---------------------------------------------------------------------------------------------
+constexpr int GREEDY_CLUSTER = 8;
+constexpr int GREEDY_THREADS = 512;
+
+struct OnlineMax {
+    u64 best = 0;
+    float m = -INFINITY, s = 0.0f;
+    __device__ __forceinline__ void take(float x, int i) {
+        const u64 key = make_key(x, i);
+        best = key > best ? key : best;
+        if (x > m) {
+            s *= expf(m - x);  // exp(-inf) = 0 the first time
+            m = x;
+        }
+        s += m == -INFINITY ? 0.0f : expf(x - m);
+    }
+};
+
+__global__ void __launch_bounds__(GREEDY_THREADS)
+    greedy_kernel(const float* __restrict__ logits, int ldl, int V, int* __restrict__ out_token,
+                  float* __restrict__ out_prob) {
+    __shared__ u64 red[32];
+    __shared__ float fred[33];
+    __shared__ float part[4];  // this CTA's result: key (two words), maximum, sum
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.x;
+    const int rank = (int)(blockIdx.z % GREEDY_CLUSTER);
+    const float* row = logits + (size_t)r * ldl;
+    const int per = ((V + 4 * GREEDY_CLUSTER - 1) / (4 * GREEDY_CLUSTER)) * 4;
+    const int lo = min(V, rank * per), hi = min(V, lo + per);
+    OnlineMax acc;
+    if ((reinterpret_cast<uintptr_t>(row + lo) & 15) == 0) {
+        const int whole = lo + ((hi - lo) & ~3);
+        for (int i = lo + 4 * (int)threadIdx.x; i < whole; i += 4 * GREEDY_THREADS) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i);
+            acc.take(v.x, i);
+            acc.take(v.y, i + 1);
+            acc.take(v.z, i + 2);
+            acc.take(v.w, i + 3);
+        }
+        for (int i = whole + (int)threadIdx.x; i < hi; i += GREEDY_THREADS) acc.take(row[i], i);
+    } else {
+        for (int i = lo + (int)threadIdx.x; i < hi; i += GREEDY_THREADS) acc.take(row[i], i);
+    }
+    // block: best key, maximum, and the sums brought to that maximum
+    u64 best = acc.best;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const u64 t = __shfl_xor_sync(0xffffffffu, best, o);
+        best = t > best ? t : best;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) red[warp] = best;
+    float m = warp_max(acc.m);
+    if (lane == 0) fred[warp] = m;
+    __syncthreads();
+    best = red[0];
+    m = fred[0];
+    for (int w = 1; w < GREEDY_THREADS / 32; ++w) {
+        best = red[w] > best ? red[w] : best;
+        m = fmaxf(m, fred[w]);
+    }
+    __syncthreads();
+    float sum = acc.m == -INFINITY ? 0.0f : acc.s * expf(acc.m - m);
+    sum = warp_sum(sum);
+    if (lane == 0) fred[warp] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+        for (int w = 0; w < GREEDY_THREADS / 32; ++w) total += fred[w];
+        part[0] = __uint_as_float((u32)(best >> 32));
+        part[1] = __uint_as_float((u32)(best & 0xFFFFFFFFu));
+        part[2] = m;
+        part[3] = total;
+    }
+    cluster_sync_all();
+    if (rank == 0 && threadIdx.x == 0) {
+        const u32 addr = (u32)__cvta_generic_to_shared(part);
+        u64 key = 0;
+        float ms[GREEDY_CLUSTER], ss[GREEDY_CLUSTER], mm = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < GREEDY_CLUSTER; ++c) {
+            const u64 k = ((u64)__float_as_uint(peer_shared_f32(addr, c)) << 32) | (u64)__float_as_uint(peer_shared_f32(addr + 4, c));
+            key = k > key ? k : key;
+            ms[c] = peer_shared_f32(addr + 8, c);
+            ss[c] = peer_shared_f32(addr + 12, c);
+            mm = fmaxf(mm, ms[c]);
+        }
+        float denom = 0.0f;
+#pragma unroll
+        for (int c = 0; c < GREEDY_CLUSTER; ++c) denom += ms[c] == -INFINITY ? 0.0f : ss[c] * expf(ms[c] - mm);
+        out_token[r] = (int)(0xFFFFFFFFu - (u32)(key & 0xFFFFFFFFu));
+        if (out_prob) out_prob[r] = 1.0f / denom;
+    }
+    cluster_sync_all();  // nobody leaves while rank 0 may still read its shared memory
+}
+
 }  // namespace
 
 // logits fp32 [rows, V] (row stride ldl).  temperature / top_k / top_p: per row, or null for greedy.
@@ -329,6 +444,15 @@ FERRIS_API int ferris_sample(const float* logits, int ldl, int rows, int V, cons
     if (rows <= 0) return FERRIS_OK;
     if (V <= 0 || ldl < V) FERRIS_REFUSE("sample: vocabulary %d, row stride %d", V, ldl);
     if (temperature && (!slots || !rng_states)) FERRIS_REFUSE("sample: sampling with a temperature needs generator states");
+    if (!temperature) {
+        cudaError_t e = ferris_launch_cluster(greedy_kernel, dim3(rows, 1, GREEDY_CLUSTER), dim3(GREEDY_THREADS), 0,
+                                              (cudaStream_t)stream, GREEDY_CLUSTER, logits, ldl, V, out_token, out_prob);
+        if (e != cudaSuccess) {
+            ferris_set_error("sample: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        FERRIS_LAUNCH_CHECK();
+    }
     static bool configured = false;
     const size_t smem = sizeof(Shared);
     if (!configured) {

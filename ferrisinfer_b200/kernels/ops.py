@@ -267,9 +267,74 @@ def norm_gemm_tcgen05(x: "LazyRMSNorm", w, bias, out, mode: int, up_row_offset: 
     )
 
 
+class LazySplitMerge:
+    """The attention rows of a single-token step whose key ranges (splits) have not been merged yet: the
+    partial results lie in ``scratch``.  A matrix product that can merge them on its way (``gemm`` for short
+    bf16 steps) takes this as its input and no merge kernel runs; everyone else calls ``materialize()``."""
+
+    def __init__(self, scratch: torch.Tensor, out_buffer: torch.Tensor, num_heads: int, head_dim: int, splits: int):
+        self.scratch, self._out, self._done = scratch, out_buffer, False
+        self.num_heads, self.head_dim, self.splits = int(num_heads), int(head_dim), int(splits)
+
+    @property
+    def shape(self):
+        return self._out.shape
+
+    @property
+    def dtype(self):
+        return self._out.dtype
+
+    def materialize(self) -> torch.Tensor:
+        if not self._done:
+            T, _, ldo = _rows(self._out, "attention output")
+            _check(_lib().ferris_decode_merge(_ptr(self.scratch), _ptr(self._out), _c_int(ldo), _c_int(T),
+                                              _c_int(self.num_heads), _c_int(self.head_dim), _c_int(self.splits), _stream()),
+                   "decode merge")
+            self._done = True
+        return self._out
+
+
+def _merge_gemm_takes(x: "LazySplitMerge", w: torch.Tensor) -> bool:
+    """Whether the short-step kernel can merge the key ranges itself (the limits of the fused norm)."""
+    T, K = x.shape
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or T > 16 or x._done or w.shape[1] != K:
+        return False
+    if not (w.data_ptr() % 16 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0 and x.scratch.data_ptr() % 16 == 0):
+        return False
+    bt, splits, floats, counters = _c_int(), _c_int(), ctypes.c_longlong(), _c_int()
+    _lib().ferris_gemm_tcgen05_plan(_c_int(T), _c_int(w.shape[0]), _c_int(K), _c_int(1), ctypes.byref(bt),
+                                    ctypes.byref(splits), ctypes.byref(floats), ctypes.byref(counters))
+    kblocks = -(-K // 64)
+    return bt.value == 16 and -(-kblocks // splits.value) <= 8 and floats.value == 0
+
+
+def merge_gemm_tcgen05(x: "LazySplitMerge", w, bias, out, mode: int):
+    """out (+)= merge(partial attention results) w^T in one kernel (modes 0-2 as gemm_tcgen05)."""
+    T, K = x.shape
+    rows_w, K2, ldw = _rows(w, "gemm weight")
+    T2, N, ldo = _rows(out, "gemm output")
+    want_dtype = torch.bfloat16 if mode == 0 else torch.float32
+    if K != K2 or T != T2 or out.dtype != want_dtype or mode not in (0, 1, 2):
+        raise KernelError(f"merge + gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}")
+    if bias is not None:
+        _need(bias, "gemm bias", torch.float32)
+    _check(
+        _lib().ferris_merge_gemm_tcgen05(_ptr(x.scratch), _c_int(x.num_heads), _c_int(x.head_dim), _c_int(x.splits),
+                                         _ptr(w), _ptr(bias), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(ldw),
+                                         _c_int(ldo), _c_int(rows_w), _stream()),
+        "merge + gemm",
+    )
+
+
 def gemm(x, w, bias, out, accumulate: bool = False):
     """The matrix product of the model, out (+)= x w^T + bias: the tcgen05 kernel for bf16 operands it takes,
-    the CUDA-core kernel for everything else (all of the 32-bit path).  ``x`` may be a LazyRMSNorm."""
+    the CUDA-core kernel for everything else (all of the 32-bit path).  ``x`` may be a LazyRMSNorm or a
+    LazySplitMerge."""
+    if isinstance(x, LazySplitMerge):
+        if w.shape[0] == out.shape[1] and _merge_gemm_takes(x, w):
+            merge_gemm_tcgen05(x, w, bias, out, 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1))
+            return
+        x = x.materialize()
     if isinstance(x, LazyRMSNorm):
         if w.shape[0] == out.shape[1] and _norm_gemm_takes(x, w, 1):
             norm_gemm_tcgen05(x, w, bias, out, 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1))
@@ -418,7 +483,8 @@ def decode_attention(qkv, out, k_cache, v_cache, block_tables, token_seq, positi
     that ``rows`` (int32) names when the step also carries portions of prompts."""
     T, _, ldq = _rows(qkv, "attention queries")
     _, _, ldo = _rows(out, "attention output")
-    need = T * num_heads * splits * (head_dim + 2) if splits > 1 else 0
+    n = T if rows is None else rows.numel()
+    need = n * num_heads * splits * (head_dim + 2) if splits > 1 else 0
     if need and (scratch is None or scratch.numel() < need or scratch.dtype != torch.float32):
         raise KernelError(f"decode attention with {splits} splits needs {need} floats of scratch")
     common = (_ptr(qkv), _c_int(ldq), _ptr(out), _c_int(ldo), _ptr(k_cache), _ptr(v_cache),
@@ -451,12 +517,13 @@ def prefill_attention(qkv, out, k_cache, v_cache, block_tables, seq_q_start, seq
 
 
 def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_heads, head_dim, inv_freq, rotary_dim,
-                   window, scale, write_kv: bool = True):
+                   window, scale, write_kv: bool = True, lazy_merge: bool = False):
     """Everything between the q/k/v product and the output product of an attention layer: rotate q and k by
     position, put k and v into the paged cache (``meta``: the step's block tables and slots for the cache's
     page group), attend.  A step of single tokens with whole-head rotation on the tensor-core path is ONE
     kernel (the split-KV kernel rotates and writes on its way); everything else is the rotary / cache-write
-    kernel followed by ``paged_attention``."""
+    kernel followed by ``paged_attention``.  Returns ``out``; with ``lazy_merge`` it may return a
+    LazySplitMerge instead (``out`` not yet written), which ``gemm`` takes as its input."""
     T = qkv.shape[0]
     page_size = k_cache.shape[2]
     if (ctx.max_q_len == 1 and rotary_dim == head_dim and inv_freq is not None
@@ -475,6 +542,7 @@ def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_head
         splits = decode_splits(T, num_kv_heads, kv_span)
         need = T * num_heads * splits * (head_dim + 2) if splits > 1 else 0
         scratch = ctx.workspace.get("attn_split_scratch", (need,), torch.float32) if need else None
+        leave = bool(lazy_merge and need)
         _, _, ldq = _rows(qkv, "attention queries")
         _, _, ldo = _rows(out, "attention output")
         _check(
@@ -483,13 +551,14 @@ def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_head
                 ctypes.c_longlong(k_cache.shape[0]), _ptr(meta.block_tables), _c_int(meta.block_tables.shape[1]),
                 _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(inv_freq), _ptr(meta.slot_mapping if write_kv else None),
                 _c_int(T), _c_int(num_heads), _c_int(num_kv_heads), _c_int(head_dim), _c_int(page_size),
-                _c_int(window or 0), _c_float(scale), _c_int(splits), _ptr(scratch), _stream()),
+                _c_int(window or 0), _c_float(scale), _c_int(splits), _ptr(scratch), _c_int(0 if leave else 1), _stream()),
             "decode attention with rotation",
         )
-        return
+        return LazySplitMerge(scratch, out, num_heads, head_dim, splits) if leave else out
     rope_cache_write(qkv, ctx.positions, inv_freq, meta.slot_mapping, k_cache, v_cache, num_heads, num_kv_heads,
                      head_dim, rotary_dim, page_size, write_kv=write_kv)
     paged_attention(qkv, out, k_cache, v_cache, meta.block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale)
+    return out
 
 
 def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale):
@@ -518,7 +587,7 @@ def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, nu
         splits = decode_splits(n, num_kv_heads, kv_span)
         scratch = None
         if splits > 1:
-            scratch = ctx.workspace.get("attn_split_scratch", (T * num_heads * splits * (head_dim + 2),), torch.float32)
+            scratch = ctx.workspace.get("attn_split_scratch", (n * num_heads * splits * (head_dim + 2),), torch.float32)
         decode_attention(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
                          num_kv_heads, head_dim, window, scale, splits, scratch,
                          rows=None if ctx.max_q_len == 1 else singles)

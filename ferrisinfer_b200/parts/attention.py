@@ -90,9 +90,9 @@ class GroupedQueryAttention(Mixer):
         else:
             inv_freq, rotary = table
         out = ctx.workspace.get("attn_out", (T, self.q_size), x.dtype)
-        ops.attention_step(qkv, out, cache.k, cache.v, meta, ctx, nh, nkv, d, inv_freq, rotary, self.window or 0,
-                           self.scale, write_kv=owns_cache)
-        ops.gemm(out, self.o_weight, None, h, accumulate=True)
+        attended = ops.attention_step(qkv, out, cache.k, cache.v, meta, ctx, nh, nkv, d, inv_freq, rotary,
+                                      self.window or 0, self.scale, write_kv=owns_cache, lazy_merge=True)
+        ops.gemm(attended, self.o_weight, None, h, accumulate=True)
 
 
 register_part("mixer", "gqa_attention", GroupedQueryAttention)

@@ -490,6 +490,61 @@ def test_attention_step_of_single_tokens_rotates_and_writes_on_its_way(nh, nkv, 
     assert torch.equal(k3, k2) and torch.equal(v3, v2)
 
 
+@pytest.mark.parametrize("impl", ["simt", "dispatch"])
+def test_attention_single_tokens_beside_portions_at_long_context(impl, device):
+    """Single tokens whose keys are split into ranges, at rows of the step that come after portions of prompts
+    (their partial results must not lie where another row's do)."""
+    nh, nkv, d, page = 14, 2, 64, 16
+    seqs = [(600, 3), (4096, 1), (3000, 1), (40, 40), (2048, 1), (1000, 1), (9, 2), (4000, 1)]
+    case = AttentionCase(device, BF16, nh, nkv, d, page, seqs, seed=23)
+    got, want = run_attention(case, impl), case.reference()
+    assert torch.allclose(got, want, **ATT_TOL[BF16]), (got - want).abs().max()
+
+
+@pytest.mark.parametrize("nh, nkv, d, T", [(14, 2, 64, 8), (12, 2, 128, 3), (7, 1, 64, 16), (14, 2, 64, 1)])
+def test_output_product_merges_the_key_ranges_on_its_way(nh, nkv, d, T, device):
+    """A decode step that leaves the partial results of its key ranges to the product that follows, against the
+    same step with the merge kernel."""
+    from ferrisinfer_b200.kernels import ops
+    from ferrisinfer_b200.parts.base import PagedMeta
+
+    page, H = 16, 896
+    lengths = [4096, 2500, 4000, 3333, 4090, 2049, 3000, 3500, 2100, 2200, 2300, 2400, 2600, 2700, 2800, 2900][:T]
+    seqs = [(kv, 1) for kv in lengths]
+    case = AttentionCase(device, BF16, nh, nkv, d, page, seqs, seed=T + d)
+    qkv, k, v, tables, ctx, _ = case.device_inputs()
+    g = torch.Generator().manual_seed(6)
+    qkv[:, nh * d:] = torch.randn(T, 2 * nkv * d, generator=g).to(BF16).to(device)
+    slots = torch.tensor([tables[i, (kv - 1) // page].item() * page + (kv - 1) % page for i, (kv, _) in enumerate(seqs)],
+                         dtype=torch.int32, device=device)
+    inv_freq = torch.tensor(plain.rotary_inverse_frequencies(d, d, 1e6).numpy(), device=device)
+    meta = PagedMeta(block_tables=tables, slot_mapping=slots, page_size=page)
+    scale = 1.0 / math.sqrt(d)
+    w_o = rnd((H, nh * d), BF16, device, 7, scale=0.05)
+    h0 = rnd((T, H), F32, device, 8)
+
+    eager = torch.empty(T, nh * d, dtype=BF16, device=device)
+    k1, v1 = k.clone(), v.clone()
+    assert ops.attention_step(qkv.clone(), eager, k1, v1, meta, ctx, nh, nkv, d, inv_freq, d, 0, scale) is eager
+    want = h0.clone()
+    ops.gemm(eager, w_o, None, want, accumulate=True)
+
+    buf = torch.full_like(eager, float("nan"))
+    k2, v2 = k.clone(), v.clone()
+    lazy = ops.attention_step(qkv.clone(), buf, k2, v2, meta, ctx, nh, nkv, d, inv_freq, d, 0, scale, lazy_merge=True)
+    assert isinstance(lazy, ops.LazySplitMerge), "these lengths are split into key ranges"
+    assert ops._merge_gemm_takes(lazy, w_o)
+    got = h0.clone()
+    ops.gemm(lazy, w_o, None, got, accumulate=True)
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    assert torch.isnan(buf.float()).all(), "no merge kernel ran"
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    assert torch.allclose(got, want, **tol(BF16)), (got - want).abs().max()
+    # a consumer that cannot merge gets the merged rows from the merge kernel
+    assert torch.equal(lazy.materialize(), eager)
+
+
 # ------------------------------------------------------------------------------------ sampling
 def test_argmax_takes_the_lowest_index_among_equal_maxima(device):
     from ferrisinfer_b200.kernels import ops

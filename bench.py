@@ -256,7 +256,7 @@ def time_e2e(engine, batch, context, steps, warmup):
     ms = max(e0.elapsed_time(e1), wall * 1e3) / steps
     for rid in ids:
         sched.cancel(rid)
-    return ms, n, engine.runner.last_h2d_bytes, 16 * batch
+    return ms, n, engine.runner.last_h2d_bytes, 8 * batch  # an int32 token and an fp32 probability per request
 
 
 def reference_arm(args) -> int:
@@ -328,7 +328,9 @@ def main() -> int:
             "l2": "weights and cache exceed L2; no flush", "peaks": peak_source,
         },
         "e2e": {"value": round(e2e_tokens / args.steps / e2e_ms * 1e3, 1), "unit": "tok/s",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4)},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 4),
+                "how": "Engine.step(): step metadata from pinned host memory, sampled tokens back to the host every "
+                       "step; the next step is queued while the GPU runs (it reads its token ids on the device)"},
         "gpu_launches": launches,
         "prefill": {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
                     "ms": round(prefill_ms, 3),

@@ -25,7 +25,7 @@ from ..sampling import RNG_NEED, RNG_STATE, Sampler, SamplingParams
 from ..weights.loader import bind_tensors, load_model, parse_dtype
 from ..weights.random_init import random_tensors
 from .runner import ModelRunner, StepEntry
-from .scheduler import FinishReason, Scheduler, SchedulerConfig, Sequence
+from .scheduler import FinishReason, Phase, ScheduledEntry, Scheduler, SchedulerConfig, Sequence, StepPlan
 
 
 @dataclass
@@ -52,6 +52,17 @@ class GenerationOutput:
 
 
 @dataclass
+class _InFlight:
+    """A step that has been queued on the GPU: its plan, the requests it samples for, the sampled tokens
+    on the device and the pinned host buffers (tokens, probabilities, event) they are copied to."""
+
+    plan: StepPlan
+    sampling: list
+    tokens: Optional[torch.Tensor] = None
+    host: Optional[list] = None
+
+
+@dataclass
 class StepOutput:
     request_id: Any
     token: Optional[TokenSample]
@@ -62,14 +73,16 @@ class StepOutput:
 class Engine:
     def __init__(self, model=None, *, config=None, seed: int = 0, dtype="bfloat16", device=None,
                  page_size: int = 16, num_pages: Optional[int] = None, gpu_memory_fraction: float = 0.5,
-                 scheduler: Optional[SchedulerConfig] = None, init_device="cpu", prefix_sharing: bool = True):
+                 scheduler: Optional[SchedulerConfig] = None, init_device="cpu", prefix_sharing: bool = True,
+                 run_ahead: bool = True):
         """``model``: a model folder (config.json + safetensors).  Or ``config`` (a folder, dict or
         typed configuration) with ``seed``: random weights, no folder needed.
         ``num_pages``: pages per page group; by default what ``gpu_memory_fraction`` of the free device
         memory holds.  ``init_device``: where random weights are drawn ("cpu": the values a model folder
         written with the same seed holds; a CUDA device: other values, much faster for large models).
         ``prefix_sharing``: requests whose prompts begin with the same full pages as a live request's share
-        those pages instead of recomputing them (where every layer keeps all keys)."""
+        those pages instead of recomputing them (where every layer keeps all keys).
+        ``run_ahead``: queue the next decode step while the GPU still runs the current one (see ``step``)."""
         ops.require_device()
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.dtype = parse_dtype(dtype)
@@ -93,6 +106,11 @@ class Engine:
         self.sampler = Sampler(self.runner.cache.state_tensors[RNG_STATE])
         self.scheduler = Scheduler(sc, self.runner.cache, on_admit=self._on_admit, on_preempt=self._on_preempt)
         self._next_id = 0
+        self.run_ahead = bool(run_ahead)
+        self.steps_run_ahead = 0
+        self._in_flight: Optional[_InFlight] = None
+        self._results = [[None, None, None] for _ in range(3)]  # pinned (tokens, probabilities, event), in turn
+        self._results_next = 0
 
     # ------------------------------------------------------------------ set-up
     def _pages_that_fit(self, needs, page_size, fraction, sc) -> int:
@@ -135,35 +153,100 @@ class Engine:
     # -------------------------------------------------------------------- step
     def step(self) -> list:
         """One scheduler step: run it, sample, record.  Returns a StepOutput for every request that
-        got a new token or finished."""
-        plan = self.scheduler.schedule()
+        got a new token or finished.
+
+        While the GPU runs a step of decoding requests, the host prepares and queues the step after it
+        (``run_ahead``): that step needs the requests' lengths, which are known, and their new tokens,
+        which it reads on the device from where the sampler of the running step puts them.  The host
+        then waits for the running step's tokens and records them.  A request that ends on a stop token
+        (or is cancelled) has one step too many in flight; its share of that step is dropped."""
+        if self._in_flight is None:
+            self._in_flight = self._launch(self.scheduler.schedule())
+            if self._in_flight is None:
+                return []
+        current = self._in_flight
+        self._in_flight = self._launch_ahead(current) if self.run_ahead else None
+        out, void = self._complete(current)
+        if void and self._in_flight is None and self.scheduler.has_unfinished():
+            return self.step()  # every request of that step had ended before it: run a fresh one
+        return out
+
+    def _launch(self, plan, device_tokens=None) -> Optional["_InFlight"]:
         if not plan.entries:
-            return []
+            return None
         entries, sampling = [], []
+        ahead = device_tokens is not None
         for e in plan.entries:
             seq = e.seq
-            tokens = seq.token_slice(e.start, e.count)
-            wants = e.samples and len(seq.generated) < seq.max_new_tokens \
-                and seq.num_tokens < self.scheduler_config.max_sequence_length
+            tokens = [0] if ahead else seq.token_slice(e.start, e.count)
+            wants = ahead or (e.samples and len(seq.generated) < seq.max_new_tokens
+                              and seq.num_tokens < self.scheduler_config.max_sequence_length)
             entries.append(StepEntry(seq.request_id, tokens, [e.count - 1] if wants else []))
             if wants:
                 sampling.append(seq)
-        logits = self.runner.step(entries)
-        sampled = {}
+        logits = self.runner.step(entries, device_tokens=device_tokens)
+        flight = _InFlight(plan, sampling)
         if sampling:
-            tokens, probs = self.sampler.sample(logits, [s.params for s in sampling], [s.slot for s in sampling])
-            host = torch.stack([tokens.to(torch.float64), probs.to(torch.float64)]).cpu()
-            for i, s in enumerate(sampling):
-                sampled[s.request_id] = (int(host[0, i].item()), float(host[1, i].item()))
-        self.scheduler.update(plan, sampled)
-        out = []
+            n = len(sampling)
+            flight.tokens, probs = self.sampler.sample(logits, [s.params for s in sampling], [s.slot for s in sampling])
+            buf = self._results[self._results_next]
+            self._results_next = (self._results_next + 1) % len(self._results)
+            if buf[0] is None or buf[0].numel() < n:
+                size = max(n, self.scheduler_config.max_batch_size)
+                buf[0] = torch.empty(size, dtype=torch.int32).pin_memory()
+                buf[1] = torch.empty(size, dtype=torch.float32).pin_memory()
+                buf[2] = torch.cuda.Event()
+            buf[0][:n].copy_(flight.tokens, non_blocking=True)
+            buf[1][:n].copy_(probs, non_blocking=True)
+            buf[2].record(torch.cuda.current_stream(self.device))
+            flight.host = buf
+        return flight
+
+    def _launch_ahead(self, current: "_InFlight") -> Optional["_InFlight"]:
+        """Queue the step after ``current`` if it is sure to be the same requests decoding one token more."""
+        sched, cfg = self.scheduler, self.scheduler_config
+        plan = current.plan
+        if sched.waiting or plan.preempted or len(plan.entries) != len(sched.running) \
+                or len(current.sampling) != len(plan.entries):
+            return None
+        cache = self.runner.cache
+        short = {g.gid: 0 for g in cache.groups}
         for e in plan.entries:
+            seq = e.seq
+            if not e.samples or seq.phase is Phase.FINISHED or seq.phase is Phase.WAITING:
+                return None
+            # after the running step the request has one token more; it must be sure to go on after that
+            if len(seq.generated) + 2 > seq.max_new_tokens or seq.num_tokens + 2 > cfg.max_sequence_length:
+                return None
+            for gid, n in cache.pages_needed(seq.request_id, e.start + e.count + 1).items():
+                short[gid] += n
+        free = cache.free_pages()
+        if any(short[g] > free[g] for g in short):
+            return None  # pages are short: the scheduler decides who waits, with the tokens in hand
+        nxt = StepPlan([ScheduledEntry(e.seq, e.start + e.count, 1, True) for e in plan.entries])
+        self.steps_run_ahead += 1
+        return self._launch(nxt, device_tokens=current.tokens)
+
+    def _complete(self, flight: "_InFlight") -> list:
+        """Wait for the step's tokens, hand them to the scheduler, report."""
+        sampled = {}
+        if flight.sampling:
+            tok, prob, event = flight.host
+            event.synchronize()
+            n = len(flight.sampling)
+            toks, probs = tok[:n].tolist(), prob[:n].tolist()
+            for i, s in enumerate(flight.sampling):
+                sampled[s.request_id] = (toks[i], probs[i])
+        live = [e for e in flight.plan.entries if e.seq.phase is not Phase.FINISHED and e.seq.phase is not Phase.WAITING]
+        self.scheduler.update(flight.plan, sampled)
+        out = []
+        for e in live:
             seq = e.seq
             got = sampled.get(seq.request_id)
             finished = seq.finish_reason is not None
             if got is not None or finished:
                 out.append(StepOutput(seq.request_id, TokenSample(*got) if got else None, finished, seq.finish_reason))
-        return out
+        return out, not live
 
     # ---------------------------------------------------------------- generate
     def generate(self, prompts, params=None) -> list:

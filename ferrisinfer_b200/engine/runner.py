@@ -108,20 +108,30 @@ class ModelRunner:
         return self.cache.get(request_id).num_tokens
 
     # ---------------------------------------------------------------------- step
-    def step(self, entries: Sequence[StepEntry], out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], out: Optional[torch.Tensor] = None,
+             device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Run the tokens of ``entries`` as one batch from the cache that earlier steps left.
         Returns fp32 logits [wanted, vocab] in the order of the entries and of their ``want``
         (None if nothing is wanted).  Requests that are not admitted yet are admitted.
-        The returned tensor is the runner's own buffer: it is overwritten by the next step."""
+        The returned tensor is the runner's own buffer: it is overwritten by the next step.
+        ``device_tokens`` (int32 on the device, one per entry): every entry brings one token whose id the
+        host does not know yet (it was sampled by a step that is still running); the ids in ``entries`` are
+        placeholders and the step reads the real ones from this tensor."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return None
+        if device_tokens is not None and (any(len(e.tokens) != 1 for e in entries) or device_tokens.numel() != len(entries)
+                                          or device_tokens.dtype != torch.int32):
+            raise FerrisError("tokens on the device: one int32 for each entry of one token is needed")
         host = self._layout(entries)
         decode = host.max_q == 1 and host.n_want == host.S and all(list(e.want) == [0] for e in entries)
         if self.cuda_graphs and decode and out is None:
-            logits = self._step_graph(host)
+            logits = self._step_graph(host, device_tokens)
         else:
-            ctx, logits_index = self._context(host, self._upload(host.pieces))
+            dev = self._upload(host.pieces)
+            if device_tokens is not None:
+                dev[:host.T].copy_(device_tokens)
+            ctx, logits_index = self._context(host, dev)
             logits = None
             if host.n_want:
                 logits = out if out is not None else self.workspace.get("logits", (host.n_want, self.vocab_size),
@@ -132,13 +142,15 @@ class ModelRunner:
         self.steps_run += 1
         return logits
 
-    def _step_graph(self, host: _HostStep) -> torch.Tensor:
+    def _step_graph(self, host: _HostStep, device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         key = (host.S, host.max_blocks)
         entry = self._graphs.get(key)
         if entry is None:
             total = sum(p.size for p in host.pieces)
             meta = torch.zeros(total, dtype=torch.int32, device=self.device)
             self._upload(host.pieces, meta)
+            if device_tokens is not None:
+                meta[:host.T].copy_(device_tokens)
             ctx, logits_index = self._context(host, meta)
             # launch geometry that depends on the keys' length is fixed for the width of the block table
             ctx.max_kv_len = host.max_blocks * self.cache.page_size
@@ -158,6 +170,8 @@ class ModelRunner:
             # the capture itself ran nothing, but the eager run before it did: the result is in ``logits``
             return logits
         self._upload(host.pieces, entry.meta)
+        if device_tokens is not None:
+            entry.meta[:host.T].copy_(device_tokens)  # the token ids are the first piece of the metadata
         entry.ctx.seqs = host.seqs
         entry.graph.replay()
         self.graph_replays += 1

@@ -297,6 +297,8 @@ class Scheduler:
         self.stats["tokens"] += plan.num_tokens
         for e in plan.entries:
             seq = e.seq
+            if seq.phase is Phase.FINISHED or seq.phase is Phase.WAITING:
+                continue  # finished or cancelled while this step was running: its share is void
             seq.num_computed = e.start + e.count
             if not e.samples:
                 continue

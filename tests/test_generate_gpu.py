@@ -210,3 +210,48 @@ def test_command_line(device, folders):
     assert code == 1 and "error" in err
     code, _, _ = run("no-such-command")
     assert code == 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_a_step_ahead_changes_nothing_but_the_timing(dtype, device, folders):
+    """While a decode step runs, the engine queues the next one with the tokens still on the device.  The
+    outputs are those of the engine that waits for every step: greedy and seeded sampling, requests that end
+    on a stop token with a step too many in flight, one cancelled on the way, new ones joining late."""
+    from ferrisinfer_b200 import FinishReason, SamplingParams
+
+    config, _ = helpers.read_folder(folders["B"])
+    prompts = [helpers.random_ids(config["vocab_size"], n, 50 + n) for n in (4, 13, 22, 7)]
+
+    def run(run_ahead, stops):
+        engine = _engine(folders["B"], dtype, device, page_size=8, num_pages=64, run_ahead=run_ahead)
+        params = [SamplingParams.greedy(max_new_tokens=20, stop_token_id=stops[0]),
+                  SamplingParams(temperature=0.9, top_k=40, top_p=0.95, seed=7, max_new_tokens=20, stop_token_id=stops[1]),
+                  SamplingParams.greedy(max_new_tokens=20),
+                  SamplingParams(temperature=1.3, top_k=0, seed=11, max_new_tokens=9)]
+        ids = [engine.submit(p, sp) for p, sp in zip(prompts[:3], params[:3])]
+        seen, steps = {i: [] for i in ids}, 0
+        while engine.has_unfinished():
+            for o in engine.step():
+                if o.token is not None:
+                    seen.setdefault(o.request_id, []).append(o.token.token_id)
+            steps += 1
+            if steps == 9:
+                assert engine.abort(ids[2])
+            if steps == 12:
+                ids.append(engine.submit(prompts[3], params[3]))
+        outs = [engine.output_of(i) for i in ids]
+        for i, o in zip(ids, outs):
+            if o.finish_reason is not FinishReason.CANCELLED:
+                assert seen[i] == o.generated_token_ids()
+        engine.runner.cache.check_invariants()
+        assert all(g.pool.num_used == 0 for g in engine.runner.cache.groups)
+        return [(o.generated_token_ids(), o.finish_reason) for o in outs], engine.steps_run_ahead
+
+    free, _ = run(False, (None, None))
+    stops = (free[0][0][6], free[1][0][10])  # tokens that the first two requests do generate
+    want, none_ahead = run(False, stops)
+    got, ahead = run(True, stops)
+    assert none_ahead == 0 and ahead >= 10
+    assert want[0][1] is FinishReason.STOP_TOKEN and want[1][1] is FinishReason.STOP_TOKEN
+    assert want[2][1] is FinishReason.CANCELLED
+    assert got == want

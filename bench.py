@@ -268,6 +268,45 @@ def reference_arm(args) -> int:
     return 0
 
 
+def timeline(args) -> int:
+    """One decode step at the bench's sizes, seen from inside: when each kernel's CTAs entered, passed their
+    programmatic-launch wait and ended, and the marks of its phases."""
+    os.environ["FERRIS_NVCC_FLAGS"] = (os.environ.get("FERRIS_NVCC_FLAGS", "") + " -DFERRIS_TIMELINE").strip()
+    import torch
+
+    from ferrisinfer_b200.engine.runner import StepEntry
+    from ferrisinfer_b200.kernels import ops
+    from ferrisinfer_b200.kernels.timeline import StepTimeline, summarize
+
+    cfg = dict(QWEN25_05B)
+    if args.layers:
+        cfg["num_hidden_layers"] = cfg["max_window_layers"] = args.layers
+    engine = build_engine(cfg, args.batch, CONTEXT)
+    tl = StepTimeline(engine.device)
+    ids = fill_cache(engine, args.batch, CONTEXT - 16)
+    out_tok = torch.empty(args.batch, dtype=torch.int32, device=engine.device)
+
+    def one(i):
+        logits = engine.runner.step([StepEntry(rid, [(7 * i + b) % 1000], [0]) for b, rid in enumerate(ids)])
+        ops.sample(logits, out_tok)
+
+    for i in range(4):
+        one(i)
+    tl.reset()
+    one(4)
+    launches = tl.read()
+    print(f"decode step, batch {args.batch}, context {CONTEXT}, {cfg['num_hidden_layers']} layers "
+          "(times in us; 'start' = first CTA past its launch wait)")
+    per_layer = 5
+    first = next(i for i, l in enumerate(launches) if "attention" in l.kernel) - 1
+    for l in launches[first + per_layer:first + 2 * per_layer] + launches[-3:]:
+        marks = " ".join("  -  " if m is None else f"{m:5.2f}" for m in l.marks_us[:6])
+        print(f"{l.kernel:26s} ctas {l.ctas:5d}  entry {l.entry_us:8.2f}  start {l.start_us:8.2f}  end {l.end_us:8.2f}"
+              f"  marks {marks}")
+    print(summarize(launches))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -277,9 +316,14 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--timeline", action="store_true",
+                    help="instead of the measurement: the timeline of one decode step from hooks inside the kernels "
+                         "(a build of the kernel library of its own; prints a table, no JSON line)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.timeline:
+        return timeline(args)
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported (nothing here spans GPUs)")
         return 2

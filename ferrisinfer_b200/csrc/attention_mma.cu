@@ -330,6 +330,7 @@ __global__ void __launch_bounds__(WARPS * 32)
                             int max_blocks, const int* __restrict__ token_seq, const int* __restrict__ positions,
                             const int* __restrict__ token_list, int nh, int nkv, int page_size, int window, float scale,
                             int splits, const FusedRope rope, int* status) {
+    FERRIS_TL_ENTRY();
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full[WARPS][STAGES];
     __shared__ int tile_rows[WARPS][ROW_CACHE];  // cache rows of this warp's next tiles, looked up in one go
@@ -356,7 +357,10 @@ __global__ void __launch_bounds__(WARPS * 32)
     // (the token's own key and value come from its qkv row), and the step's metadata was uploaded long
     // before: the first tiles are requested BEFORE the wait, which only the queries need.
     const bool early = rope.inv_freq != nullptr;
-    if (!early) pdl_wait();
+    if (!early) {
+        pdl_wait();
+        FERRIS_TL_BEGIN();
+    }
     // with a token list, only the listed rows of the step are attended (the others belong to another kernel)
     const int tok = token_list ? token_list[blockIdx.z] : (int)blockIdx.z;
     const int seq = token_seq[tok];
@@ -414,10 +418,15 @@ __global__ void __launch_bounds__(WARPS * 32)
     fill_rows(0);
     if (lane == 0)
         for (int i = 0; i < STAGES && i < my_count; ++i) issue(i);
+    // marks of the timeline build: thread 0 of the CTA of the last key range of token 0, kv head 0
+    const bool tl_mark = threadIdx.x == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0;
     if (early) {
         pdl_wait();
+        FERRIS_TL_BEGIN();
+        FERRIS_TL_MARK(tl_mark, 9);
         load_queries();
     }
+    FERRIS_TL_MARK(tl_mark, 0);
     for (int i = 0; i < my_count; ++i) {
         const int s = i % STAGES;
         // the row cache holds blocks [c, c + BLOCK_CACHE), c a multiple of BLOCK_CACHE; block i + STAGES is
@@ -427,6 +436,7 @@ __global__ void __launch_bounds__(WARPS * 32)
             fill_rows(i + STAGES);
         }
         if (!mbar_wait(&full[warp][s], (i / STAGES) & 1, status, 1)) break;
+        FERRIS_TL_MARK(tl_mark && i == 0, 1);
         const uint32_t base = smem_u32(my_stages + s * STAGE_BYTES);
         const int tile0 = first_tile_of(i);
         if (rope.inv_freq && last_tile >= tile0 && last_tile < tile0 + NT && last_tile < t_end) {
@@ -464,9 +474,11 @@ __global__ void __launch_bounds__(WARPS * 32)
         if (lane == 0 && i + STAGES < my_count) issue(i + STAGES);
     }
     finish_rows(st);
+    FERRIS_TL_MARK(tl_mark, 2);
 
     // merge the four warps through shared memory (the stages are no longer read)
     __syncthreads();
+    FERRIS_TL_MARK(tl_mark, 3);
     float* merge = reinterpret_cast<float*>(smem);  // [WARPS][16][D + 2]
     {
         const int g = lane >> 2, t = lane & 3;
@@ -512,6 +524,11 @@ __global__ void __launch_bounds__(WARPS * 32)
             }
         }
     }
+#ifdef FERRIS_TIMELINE
+    __syncthreads();
+#endif
+    FERRIS_TL_MARK(tl_mark, 4);
+    FERRIS_TL_END(4);
 }
 
 // Merge of the splits: out = sum_s O_s e^{m_s - M} / sum_s l_s e^{m_s - M}.  One block per (token, head).
@@ -931,3 +948,5 @@ int ferris_decode_attention_static_scratch(const void* q, int ldq, void* out, in
     return ferris_decode_attention(q, ldq, out, ldo, k_cache, v_cache, cache_pages, block_tables, max_blocks, token_seq,
                                    positions, tokens, nh, nkv, d, page_size, window, scale, splits, scratch, stream);
 }
+
+FERRIS_TIMELINE_TU(attention_mma)

@@ -87,6 +87,75 @@ inline cudaError_t ferris_launch_cluster(Kernel kernel, dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Timeline of a step as it runs (compiled in with -DFERRIS_TIMELINE only; otherwise the hooks are
+// empty).  Every instrumented kernel records, per launch, the earliest entry of a CTA, the earliest
+// moment a CTA passed its programmatic-launch wait and the latest end of a CTA, in nanoseconds of
+// %globaltimer.  Launches take slots in the order in which they complete.  buf[0] = next slot,
+// buf[1] = slots, then sixteen words per slot: kernel id, CTAs, entry, start, end, CTAs done, and ten
+// marks that one chosen thread of the grid may set on its way (FERRIS_TL_MARK, after the wait only).
+// The host fills entry and start with ones before a run.
+// ---------------------------------------------------------------------------------------------
+#ifdef FERRIS_TIMELINE
+static __device__ unsigned long long* ferris_tl_buf;  // one per translation unit, all pointing at the same buffer
+struct FerrisTl {
+    unsigned long long entry;
+    int slot;
+};
+__device__ __forceinline__ unsigned long long ferris_tl_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool ferris_tl_first_thread() { return threadIdx.x == 0 && threadIdx.y == 0 && threadIdx.z == 0; }
+__device__ __forceinline__ void ferris_tl_begin(FerrisTl& tl) {
+    tl.slot = -1;
+    if (!ferris_tl_first_thread() || !ferris_tl_buf) return;
+    volatile unsigned long long* b = ferris_tl_buf;
+    const int slot = (int)b[0];
+    if (slot >= (int)b[1]) return;
+    unsigned long long* s = ferris_tl_buf + 2 + (size_t)slot * 16;
+    atomicMin(&s[2], tl.entry);
+    atomicMin(&s[3], ferris_tl_now());
+    tl.slot = slot;
+}
+__device__ __forceinline__ void ferris_tl_end(const FerrisTl& tl, int id) {
+    if (!ferris_tl_first_thread() || tl.slot < 0) return;
+    unsigned long long* s = ferris_tl_buf + 2 + (size_t)tl.slot * 16;
+    atomicMax(&s[4], ferris_tl_now());
+    const unsigned long long total = (unsigned long long)gridDim.x * gridDim.y * gridDim.z;
+    if (atomicAdd(&s[5], 1ull) == total - 1) {
+        s[0] = (unsigned long long)id;
+        s[1] = total;
+        __threadfence();
+        atomicExch(ferris_tl_buf, (unsigned long long)(tl.slot + 1));
+    }
+}
+__device__ __forceinline__ void ferris_tl_mark(int k) {
+    if (!ferris_tl_buf) return;
+    volatile unsigned long long* b = ferris_tl_buf;
+    const int slot = (int)b[0];  // this launch's slot: the launches before it have completed
+    if (slot < (int)b[1]) ferris_tl_buf[2 + (size_t)slot * 16 + 6 + k] = ferris_tl_now();
+}
+#define FERRIS_TL_MARK(cond, k) \
+    do {                        \
+        if (cond) ferris_tl_mark(k); \
+    } while (0)
+#define FERRIS_TL_ENTRY() FerrisTl ferris_tl_ = {ferris_tl_now(), -1}
+#define FERRIS_TL_BEGIN() ferris_tl_begin(ferris_tl_)
+#define FERRIS_TL_END(id) ferris_tl_end(ferris_tl_, (id))
+#define FERRIS_TIMELINE_TU(name)                                                                  \
+    FERRIS_API int ferris_timeline_install_##name(unsigned long long* buf) {                      \
+        return (int)cudaMemcpyToSymbol(ferris_tl_buf, &buf, sizeof(buf));                         \
+    }
+#else
+#define FERRIS_TL_ENTRY()
+#define FERRIS_TL_BEGIN()
+#define FERRIS_TL_END(id)
+#define FERRIS_TL_MARK(cond, k)
+#define FERRIS_TIMELINE_TU(name)
+#endif
+
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
 

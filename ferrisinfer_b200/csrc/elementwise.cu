@@ -10,18 +10,21 @@
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int hidden, int vocab, int* status) {
+    FERRIS_TL_ENTRY();
     pdl_wait();
     pdl_launch_dependents();
+    FERRIS_TL_BEGIN();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * hidden;
     if (id < 0 || id >= vocab) {
         if (threadIdx.x == 0 && status) atomicCAS(status, 0, t + 1);
         for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.0f;
-        return;
+    } else {
+        const T* row = table + (size_t)id * hidden;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
     }
-    const T* row = table + (size_t)id * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
+    FERRIS_TL_END(1);
 }
 
 FERRIS_API int ferris_embed_gather(const void* table, int dtype, const int* ids, float* out, int tokens,
@@ -51,8 +54,10 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
                                const int* __restrict__ row_index, TOut* __restrict__ out, int hidden,
                                float eps) {
     __shared__ float scratch[33];
+    FERRIS_TL_ENTRY();
     pdl_wait();
     pdl_launch_dependents();
+    FERRIS_TL_BEGIN();
     const int r = blockIdx.x;
     const int src = row_index ? row_index[r] : r;
     const float* xr = x + (size_t)src * hidden;
@@ -65,6 +70,7 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restr
     const float inv = 1.0f / sqrtf(ss / (float)hidden + eps);
     TOut* o = out + (size_t)r * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_float<TOut>((xr[i] * inv) * w[i]);
+    FERRIS_TL_END(2);
 }
 
 __device__ __forceinline__ void store4(float* o, float a, float b, float c, float d) {
@@ -273,3 +279,5 @@ FERRIS_API int ferris_rope_cache_write(void* qkv, int dtype, const int* position
         FERRIS_REFUSE("rope_cache_write: unknown dtype %d", dtype);
     FERRIS_LAUNCH_CHECK();
 }
+
+FERRIS_TIMELINE_TU(elementwise)

@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(THREADS)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                         const Params p) {
     constexpr int ACCS = MODE == SWIGLU_BF16 ? 2 : 1;
+    FERRIS_TL_ENTRY();
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full[MAX_STAGES], empty[MAX_STAGES], accum_full;
     __shared__ uint32_t tmem_base;
@@ -138,7 +139,11 @@ __global__ void __launch_bounds__(THREADS)
         }
     }
     pdl_wait();
+    FERRIS_TL_BEGIN();
     if (traced && threadIdx.x == 0) p.trace[0] = p.trace[1] = global_ns();
+    // marks of the timeline build: the first epilogue thread of CTA (0, 0, 0)
+    const bool tl_mark = threadIdx.x == 64 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    FERRIS_TL_MARK(tl_mark, 9);  // this thread is past the wait
 
     if (p.norm_h && warp >= 2) {
         // RMSNorm of the step's rows, then the token tiles of all of this CTA's K slices, written where TMA
@@ -230,6 +235,7 @@ __global__ void __launch_bounds__(THREADS)
             for (int i = 0; i < n_kb; ++i) mbar_arrive(&full[i]);
     }
 
+    FERRIS_TL_MARK(tl_mark, 0);  // token tiles built (or nothing to build)
     if (warp == 0) {
         if (lane == 0) {
             const int first = min(n_kb, p.stages);
@@ -281,6 +287,7 @@ __global__ void __launch_bounds__(THREADS)
         const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
         const bool have = n_kb > 0 && mbar_wait(&accum_full, 0, p.status, 12);
         tcgen05_fence_after();
+        FERRIS_TL_MARK(tl_mark, 1);  // accumulator ready
         if (traced && threadIdx.x == 64) p.trace[4] = global_ns();
         const bool n_ok = n < p.N;
         const float bias_v = (p.bias && n_ok) ? p.bias[n] : 0.0f;
@@ -402,7 +409,9 @@ __global__ void __launch_bounds__(THREADS)
     if (p.cluster && p.splits > 1) {
         // every CTA of the cluster has its partial in shared memory: CTA r adds up the tokens r, r + splits, ...
         // of all of them (in split order, so the sum does not depend on timing) and writes those rows out
+        FERRIS_TL_MARK(tl_mark, 2);  // partial in shared memory
         cluster_sync();
+        FERRIS_TL_MARK(tl_mark, 3);  // all partials of the cluster in place
         if (warp >= 2) {
             const int quarter = warp & 3, half = (warp - 2) >> 2;
             const int n = n0 + quarter * 32 + lane;
@@ -428,7 +437,9 @@ __global__ void __launch_bounds__(THREADS)
                 write_out<MODE>(p, t, n, a, b, bias_v);
             }
         }
+        FERRIS_TL_MARK(tl_mark, 4);  // rows summed and written
         cluster_sync();  // nobody leaves while a peer may still read its shared memory
+        FERRIS_TL_MARK(tl_mark, 5);
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -437,6 +448,7 @@ __global__ void __launch_bounds__(THREADS)
         tmem_dealloc(tmem, tmem_cols);
     }
     if (traced && threadIdx.x == 32) p.trace[6] = global_ns();
+    FERRIS_TL_END(10 + MODE + (p.norm_h ? 4 : 0) + (p.merge_o ? 8 : 0));
 }
 
 // =============================================================================================
@@ -974,3 +986,5 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
         default: return launch<SWIGLU_BF16>(mw, mx, p, grid, smem, cz, s);
     }
 }
+
+FERRIS_TIMELINE_TU(gemm_tcgen05)

@@ -360,8 +360,10 @@ __global__ void __launch_bounds__(GREEDY_THREADS)
     __shared__ u64 red[32];
     __shared__ float fred[33];
     __shared__ float part[4];  // this CTA's result: key (two words), maximum, sum
+    FERRIS_TL_ENTRY();
     pdl_wait();
     pdl_launch_dependents();
+    FERRIS_TL_BEGIN();
     const int r = blockIdx.x;
     const int rank = (int)(blockIdx.z % GREEDY_CLUSTER);
     const float* row = logits + (size_t)r * ldl;
@@ -432,6 +434,7 @@ __global__ void __launch_bounds__(GREEDY_THREADS)
         if (out_prob) out_prob[r] = 1.0f / denom;
     }
     cluster_sync_all();  // nobody leaves while rank 0 may still read its shared memory
+    FERRIS_TL_END(5);
 }
 
 }  // namespace
@@ -467,3 +470,5 @@ FERRIS_API int ferris_sample(const float* logits, int ldl, int rows, int V, cons
                                                               rng_states, out_token, out_prob);
     FERRIS_LAUNCH_CHECK();
 }
+
+FERRIS_TIMELINE_TU(sampling)

@@ -29,6 +29,8 @@ _PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(_PKG, "csrc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+# more flags from the environment, e.g. FERRIS_NVCC_FLAGS=-DFERRIS_TIMELINE for the build with timeline hooks
+NVCC_FLAGS += os.environ.get("FERRIS_NVCC_FLAGS", "").split()
 
 _lock = threading.Lock()
 _lib = None

@@ -41,6 +41,28 @@ TINY_D = {  # head size 64 and pages of 16: the geometry that the tensor-core at
 TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
+def random_config(rng: random.Random) -> dict:
+    """A configuration of the architecture with sizes drawn at random: head sizes in steps of 16 from 16 to 128,
+    any grouping of heads, widths that are multiples of 8 or only of 2, with and without a window, tied or not."""
+    d = rng.choice([16, 32, 48, 64, 64, 80, 96, 128, 128])
+    nkv = rng.choice([1, 2, 3, 4])
+    nh = nkv * rng.choice([1, 2, 3, 4, 7])
+    hidden = rng.choice([nh * d if nh * d <= 640 else 8 * rng.randint(6, 40), 8 * rng.randint(6, 40),
+                         4 * rng.randint(11, 70) + 2 * rng.randint(0, 1)])
+    layers = rng.randint(1, 4)
+    window_on = rng.random() < 0.5
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": rng.randint(150, 700),
+           "hidden_size": hidden, "intermediate_size": rng.choice([8 * rng.randint(10, 90), 2 * rng.randint(40, 300)]),
+           "num_hidden_layers": layers, "num_attention_heads": nh, "num_key_value_heads": nkv, "head_dim": d,
+           "max_position_embeddings": 1024, "rms_norm_eps": rng.choice([1e-6, 1e-5, 3e-6]),
+           "rope_theta": rng.choice([10000.0, 1e6, 50000.0]), "hidden_act": "silu",
+           "tie_word_embeddings": rng.random() < 0.5, "use_sliding_window": window_on,
+           "sliding_window": rng.randint(5, 90) if window_on else None, "max_window_layers": rng.randint(0, layers)}
+    if rng.random() < 0.2:
+        cfg["partial_rotary_factor"] = 0.5
+    return cfg
+
+
 def make_folder(tmp_path, config: dict, seed: int, store_dtype="bfloat16", optional=True) -> str:
     from ferrisinfer_b200.weights import write_model_folder
 
@@ -117,7 +139,7 @@ def trace_mixed(requests: dict, seed: int, max_live: int = 4, prompt_fraction: f
     while waiting or live:
         while waiting and len(live) < max_live:
             rid, ids = waiting.pop(0)
-            live[rid] = [ids, 0, max(2, int(len(ids) * prompt_fraction)), rng.randrange(len(sizes))]
+            live[rid] = [ids, 0, min(len(ids), max(2, int(len(ids) * prompt_fraction))), rng.randrange(len(sizes))]
         entries, ended = [], []
         order = list(live)
         rng.shuffle(order)

@@ -107,6 +107,61 @@ def test_long_decoding(dtype, device, folders, oracles):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_decoding_a_batch_at_a_context_of_hundreds_of_keys(dtype, device, folders, oracles):
+    """Three requests of D (head size 64) with prompts of several hundred tokens, then decoded side by side: in
+    bfloat16 the keys of each are split into ranges over several CTAs, merged inside the output product, and the
+    steps are replayed from a graph.  One of them ends early and a fourth takes its place."""
+    name = "D"
+    vocab = TINY[name]["vocab_size"]
+    requests = {"a": helpers.random_ids(vocab, 700, 1), "b": helpers.random_ids(vocab, 450, 2),
+                "c": helpers.random_ids(vocab, 300, 3), "d": helpers.random_ids(vocab, 520, 4)}
+    tail = {"a": 24, "b": 24, "c": 10, "d": 14}
+    steps, n = [], 0
+    for rid in ("a", "b", "c"):
+        ids = requests[rid]
+        head = len(ids) - tail[rid]
+        for lo in range(0, head, 256):
+            part = ids[lo:min(lo + 256, head)]
+            steps.append({"step": n, "entries": [{"id": rid, "tokens": part, "want": [len(part) - 1]}], "end": []})
+            n += 1
+    done = {rid: len(requests[rid]) - tail[rid] for rid in ("a", "b", "c")}
+    live = ["a", "b", "c"]
+    while live:
+        entries, ended = [], []
+        for rid in live:
+            p = done[rid]
+            entries.append({"id": rid, "tokens": [requests[rid][p]], "want": [0]})
+            done[rid] = p + 1
+            if p + 1 == len(requests[rid]):
+                ended.append(rid)
+        steps.append({"step": n, "entries": entries, "end": ended})
+        n += 1
+        live = [r for r in live if r not in ended]
+        if "c" in ended:  # the fourth request: its prompt whole beside the others' single tokens, then decoded with them
+            ids = requests["d"]
+            head = len(ids) - tail["d"]
+            entries = [{"id": r, "tokens": [requests[r][done[r]]], "want": [0]} for r in live]
+            for r in live:
+                done[r] += 1
+            entries.append({"id": "d", "tokens": ids[:head], "want": [head - 1]})
+            steps.append({"step": n, "entries": entries, "end": []})
+            n += 1
+            done["d"] = head
+            live.append("d")
+    runner = _runner(folders[name], dtype, device, PAGE[name], _pages_for(steps, PAGE[name]))
+    got = helpers.replay(runner, steps)
+    runner.cache.check_invariants()
+    config, weights = oracles[name]
+    want = helpers.oracle_logits(config, weights, requests)
+    want = {k: v for k, v in want.items() if k in got}
+    assert len(got) > 70
+    bad = helpers.first_mismatch(got, want, **TOL[dtype])
+    assert bad is None, bad
+    if dtype is torch.bfloat16:
+        assert runner.graph_replays > 10
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_first_tokens_of_a_sequence(name, dtype, device, folders, oracles):
     """Positions 0, 1, 2: a sequence of one token, and the first tokens fed one by one."""

@@ -149,9 +149,9 @@ __global__ void __launch_bounds__(THREADS)
         // RMSNorm of the step's rows, then the token tiles of all of this CTA's K slices, written where TMA
         // would have put them (rows of 128 bytes, 16-byte chunks swizzled).  ms = sum(x^2) / K;
         // r = 1 / sqrt(ms + eps); y = (x r) w  (crates/ferrisinfer-kernel/src/cpu/reduction.rs:35-41).
-        __shared__ float rstd_s[16];
+        __shared__ float rstd_s[64];
         const int e = warp - 2;
-        for (int t = e; t < 16; t += 8) {
+        for (int t = e; t < p.bt; t += 8) {
             float ss = 0.0f;
             if (t < p.T) {
                 const float4* row = reinterpret_cast<const float4*>(p.norm_h + (size_t)t * p.K);
@@ -168,8 +168,9 @@ __global__ void __launch_bounds__(THREADS)
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
         const int et = threadIdx.x - 64;  // 0..255
-        for (int idx = et; idx < n_kb * 128; idx += 256) {
-            const int i = idx >> 7, t = (idx >> 3) & 15, c = idx & 7;
+        const int per_kb = p.bt * 8;      // 16-byte chunks of one token tile
+        for (int idx = et; idx < n_kb * per_kb; idx += 256) {
+            const int i = idx / per_kb, t = (idx % per_kb) >> 3, c = idx & 7;
             const int k = (kb0 + i) * BLOCK_K + 8 * c;
             uint4 packed = make_uint4(0u, 0u, 0u, 0u);
             if (t < p.T && k < p.K) {  // K is a multiple of 8: a chunk is inside or outside as a whole
@@ -196,8 +197,9 @@ __global__ void __launch_bounds__(THREADS)
         // attention kernel, same order of sums), written as the token tiles of this CTA's K slices.
         const int et = threadIdx.x - 64;  // 0..255
         const int S = p.merge_splits, d = p.merge_d;
-        for (int idx = et; idx < n_kb * 128; idx += 256) {
-            const int i = idx >> 7, t = (idx >> 3) & 15, c = idx & 7;
+        const int per_kb = p.bt * 8;  // 16-byte chunks of one token tile
+        for (int idx = et; idx < n_kb * per_kb; idx += 256) {
+            const int i = idx / per_kb, t = (idx % per_kb) >> 3, c = idx & 7;
             const int k = (kb0 + i) * BLOCK_K + 8 * c;
             uint4 packed = make_uint4(0u, 0u, 0u, 0u);
             if (t < p.T && k < p.K) {  // d is a multiple of 8: a chunk lies within one head
@@ -764,16 +766,21 @@ FERRIS_API int ferris_gemm_tcgen05_plan(int T, int N, int K, int accumulators, i
             cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sms <= 0)
             g_sms = 148;
     }
-    // Start from the widest tile that the step fills (every weight byte is then read once) and narrow it
-    // while the SMs would lack CTAs even with the deepest K split: short steps down to 16 tokens, long
-    // steps down to 64.
+    // Steps of up to 128 tokens are one tile; longer ones start from the widest tile and narrow it (down to 64)
+    // while the SMs would lack CTAs even with the deepest K split.
     const int n_tiles = (N + BLOCK_N - 1) / BLOCK_N;
     const int kblocks = (K + BLOCK_K - 1) / BLOCK_K;
     const int most = kblocks >= 4 ? (kblocks / 2 < 8 ? kblocks / 2 : 8) : 1;  // a cluster has at most 8 CTAs
-    int bt = 16;
-    while (bt < T && bt < 256) bt <<= 1;
-    const int narrowest = T <= 256 ? 16 : 64;
-    while (bt > narrowest && n_tiles * ((T + bt - 1) / bt) * (bt <= 128 ? most : 1) < g_sms) bt >>= 1;
+    int bt;
+    if (T <= 128) {
+        // One token tile: a tcgen05.mma costs about the same ~100 cycles for any width up to 128 (measured), so a
+        // narrower tile would only multiply the instructions and stream the weights once per tile.
+        bt = (T + 15) / 16 * 16;
+    } else {
+        bt = 16;
+        while (bt < T && bt < 256) bt <<= 1;
+        while (bt > 64 && n_tiles * ((T + bt - 1) / bt) * (bt <= 128 ? most : 1) < g_sms) bt >>= 1;
+    }
     const int t_tiles = (T + bt - 1) / bt;
     // K split: where tiles are fewer than SMs; the CTAs of a tile form a cluster and add their partials
     // through distributed shared memory
@@ -793,6 +800,31 @@ FERRIS_API int ferris_gemm_tcgen05_plan(int T, int N, int K, int accumulators, i
     *scratch_floats = (splits > 1 && !cluster) ? (long long)splits * accumulators * T * N : 0;
     *counters = (splits > 1 && !cluster) ? tiles : 0;
     return FERRIS_OK;
+}
+
+// Stages of the weight / token ring of the short-step kernel: what shared memory holds beside the K-split partials,
+// at most MAX_STAGES, and no more than a CTA has K slices.
+static int ring_stages(int accs, int bt, bool cluster, int per_split) {
+    const int stage_bytes = accs * BLOCK_N * BLOCK_K * 2 + bt * BLOCK_K * 2;
+    const int part_bytes = cluster ? accs * bt * BLOCK_N * 4 : 0;
+    int stages = (227 * 1024 - 2048 - part_bytes) / stage_bytes;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages > per_split) stages = per_split;
+    return stages < 1 ? 1 : stages;
+}
+
+// Whether the short-step kernel can form its token operand itself (fused RMSNorm or merge) for this product: at most
+// 16 tokens (beyond that every CTA repeating the norm of all rows costs more than a norm kernel saves: measured at
+// 32 and 64), a K split that sums through the cluster (or none), and all K slices of a CTA resident at once.
+FERRIS_API int ferris_gemm_tcgen05_builds_tokens(int T, int N, int K, int accumulators) {
+    if (T <= 0 || T > 16 || (K & 7)) return 0;
+    int bt, splits, n_counters;
+    long long scratch_floats;
+    ferris_gemm_tcgen05_plan(T, N, K, accumulators, &bt, &splits, &scratch_floats, &n_counters);
+    const bool cluster = splits > 1 && ferris_gemm_cluster_enabled();
+    if (bt > 16 || (splits > 1 && !cluster)) return 0;
+    const int per_split = ((K + BLOCK_K - 1) / BLOCK_K + splits - 1) / splits;
+    return per_split <= ring_stages(accumulators, bt, cluster, per_split) ? 1 : 0;
 }
 
 // x: bf16 [T, K] rows ldx apart; w: bf16 [rows_w, K] rows ldw apart (rows_w = N, or for SwiGLU at
@@ -824,8 +856,8 @@ FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bi
 }
 
 // The same product with RMSNorm fused in front: x = bf16((h * rstd(h)) * norm_w) is formed inside the kernel from the
-// fp32 rows h [T, K] (contiguous).  For steps of at most 16 tokens whose K split leaves each CTA at most 8 slices of
-// 64 (ferris_gemm_tcgen05_plan tells); anything else is refused.
+// fp32 rows h [T, K] (contiguous).  For steps of at most 16 tokens whose K split leaves each CTA no more slices of
+// 64 than its shared memory has stages (ferris_gemm_tcgen05_builds_tokens tells); anything else is refused.
 FERRIS_API int ferris_norm_gemm_tcgen05(const float* h, const float* norm_w, float norm_eps, const void* w,
                                         const float* bias, void* out, int mode, int T, int N, int K, int ldw, int ldo,
                                         int rows_w, int up_row_offset, void* stream) {
@@ -959,11 +991,8 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
     p.trace = trace;
     const int stage_bytes = accs * BLOCK_N * BLOCK_K * 2 + bt * BLOCK_K * 2;
     const int part_bytes = cluster ? accs * bt * BLOCK_N * 4 : 0;
-    int stages = (227 * 1024 - 2048 - part_bytes) / stage_bytes;
-    if (stages > MAX_STAGES) stages = MAX_STAGES;
     const int per_split = (p.kblocks + splits - 1) / splits;
-    if (stages > per_split) stages = per_split;
-    if (stages < 1) stages = 1;
+    int stages = ring_stages(accs, bt, cluster, per_split);
     // Many tiles and no K split (the output head over the vocabulary): shallower rings, so that two CTAs share an
     // SM and one streams weights while the other's epilogue and set-up run.
     const long long tiles_all = (long long)((N + BLOCK_N - 1) / BLOCK_N) * ((T + bt - 1) / bt);
@@ -972,7 +1001,7 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
         if (fit >= 4 && stages > fit) stages = fit;
     }
     p.stages = stages;
-    if (built && (bt != 16 || per_split > stages || (splits > 1 && !cluster)))
+    if (built && (bt > 16 || per_split > stages || (splits > 1 && !cluster)))
         FERRIS_REFUSE("norm / merge + gemm: this shape (token tile %d, %d K slices per CTA, %d stages) is not taken", bt, per_split,
                       stages);
     const size_t smem = (size_t)stages * stage_bytes + part_bytes + 1024;

@@ -234,19 +234,14 @@ class LazyRMSNorm:
 
 def _norm_gemm_takes(x: "LazyRMSNorm", w: torch.Tensor, accs: int) -> bool:
     """Whether the short-step kernel can form the norm itself: bf16, at most 16 tokens, and a K split that
-    leaves every CTA at most 8 slices."""
+    leaves all of a CTA's slices resident at once."""
     T, K = x.shape
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or T > 16 or K % 8 or x._done:
         return False
     if not (x.h.is_cuda and x.h.dtype == torch.float32 and x.h.is_contiguous() and x.h.data_ptr() % 16 == 0
             and x.weight.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0):
         return False
-    n = w.shape[0] // accs
-    bt, splits, floats, counters = _c_int(), _c_int(), ctypes.c_longlong(), _c_int()
-    _lib().ferris_gemm_tcgen05_plan(_c_int(T), _c_int(n), _c_int(K), _c_int(accs), ctypes.byref(bt), ctypes.byref(splits),
-                                    ctypes.byref(floats), ctypes.byref(counters))
-    kblocks = -(-K // 64)
-    return bt.value == 16 and -(-kblocks // splits.value) <= 8 and floats.value == 0
+    return bool(_lib().ferris_gemm_tcgen05_builds_tokens(_c_int(T), _c_int(w.shape[0] // accs), _c_int(K), _c_int(accs)))
 
 
 def norm_gemm_tcgen05(x: "LazyRMSNorm", w, bias, out, mode: int, up_row_offset: int = 0):
@@ -301,11 +296,7 @@ def _merge_gemm_takes(x: "LazySplitMerge", w: torch.Tensor) -> bool:
         return False
     if not (w.data_ptr() % 16 == 0 and w.stride(1) == 1 and w.stride(0) % 8 == 0 and x.scratch.data_ptr() % 16 == 0):
         return False
-    bt, splits, floats, counters = _c_int(), _c_int(), ctypes.c_longlong(), _c_int()
-    _lib().ferris_gemm_tcgen05_plan(_c_int(T), _c_int(w.shape[0]), _c_int(K), _c_int(1), ctypes.byref(bt),
-                                    ctypes.byref(splits), ctypes.byref(floats), ctypes.byref(counters))
-    kblocks = -(-K // 64)
-    return bt.value == 16 and -(-kblocks // splits.value) <= 8 and floats.value == 0
+    return bool(_lib().ferris_gemm_tcgen05_builds_tokens(_c_int(T), _c_int(w.shape[0]), _c_int(K), _c_int(1)))
 
 
 def merge_gemm_tcgen05(x: "LazySplitMerge", w, bias, out, mode: int):

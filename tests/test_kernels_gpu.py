@@ -197,11 +197,11 @@ def test_gemm_with_rmsnorm_formed_on_its_way(T, N, K, device):
 def test_lazy_norm_is_computed_where_no_kernel_can_form_it(device):
     from ferrisinfer_b200.kernels import ops
 
-    h = rnd((40, 256), F32, device, 36)  # 40 tokens: beyond the fused kernel
+    h = rnd((100, 256), F32, device, 36)  # 100 tokens: beyond the fused kernel
     nw = 1 + rnd((256,), F32, device, 37, scale=0.1)
     w = rnd((64, 256), BF16, device, 38, scale=0.1)
-    lazy = ops.LazyRMSNorm(h, nw, 1e-6, torch.empty(40, 256, dtype=BF16, device=device))
-    out = torch.empty(40, 64, dtype=BF16, device=device)
+    lazy = ops.LazyRMSNorm(h, nw, 1e-6, torch.empty(100, 256, dtype=BF16, device=device))
+    out = torch.empty(100, 64, dtype=BF16, device=device)
     ops.gemm(lazy, w, None, out)
     assert lazy._done
     want = plain.rms_norm(h.cpu().double(), nw.cpu().double(), 1e-6).to(BF16).double() @ w.cpu().double().t()

@@ -141,6 +141,18 @@ __device__ __forceinline__ void ferris_tl_mark(int k) {
     do {                        \
         if (cond) ferris_tl_mark(k); \
     } while (0)
+// a value of the kernel's own choice (e.g. clock cycles spent in one kind of wait) in place of a mark
+__device__ __forceinline__ void ferris_tl_value(int k, unsigned long long v) {
+    if (!ferris_tl_buf) return;
+    volatile unsigned long long* b = ferris_tl_buf;
+    const int slot = (int)b[0];
+    if (slot < (int)b[1]) ferris_tl_buf[2 + (size_t)slot * 16 + 6 + k] = v;
+}
+#define FERRIS_TL_VALUE(cond, k, v) \
+    do {                            \
+        if (cond) ferris_tl_value((k), (v)); \
+    } while (0)
+#define FERRIS_TL_CLOCK() clock64()
 #define FERRIS_TL_ENTRY() FerrisTl ferris_tl_ = {ferris_tl_now(), -1}
 #define FERRIS_TL_BEGIN() ferris_tl_begin(ferris_tl_)
 #define FERRIS_TL_END(id) ferris_tl_end(ferris_tl_, (id))
@@ -153,6 +165,8 @@ __device__ __forceinline__ void ferris_tl_mark(int k) {
 #define FERRIS_TL_BEGIN()
 #define FERRIS_TL_END(id)
 #define FERRIS_TL_MARK(cond, k)
+#define FERRIS_TL_VALUE(cond, k, v)
+#define FERRIS_TL_CLOCK() 0ll
 #define FERRIS_TIMELINE_TU(name)
 #endif
 

@@ -476,6 +476,78 @@ struct PTParams {
     int* status;
 };
 
+// The epilogue of one token-major tile for one warp: its 32 tokens (TMEM lanes, lane = token t) and every second
+// 32-column chunk of the accumulator buffer at d0 (gate columns first, up columns p.bn further in SwiGLU mode).
+template <int MODE>
+__device__ __forceinline__ void pt_epilogue_tile(const PTParams& p, const CUtensorMap& map_out, uint32_t d0, int m0, int n0,
+                                                 int quarter, int half, int lane, int t, uint8_t* out_stage) {
+    constexpr int ACCS = MODE == SWIGLU_BF16 ? 2 : 1;
+    const int cols = p.bn;  // output columns of this tile
+    for (int c0 = half * 32; c0 < cols; c0 += 64) {
+        uint32_t ra[32], rb[32];
+        tmem_load_32x32(d0 + c0, ra);
+        if (ACCS == 2) tmem_load_32x32(d0 + p.bn + c0, rb);
+        tmem_load_wait();
+        const int n = n0 + c0;
+        if (MODE == STORE_F32 || MODE == ACCUM_F32) {
+            // the warp's 32 x 32 block goes to shared memory (lane = row, 16-byte chunks swizzled as the
+            // tensor map expects) and from there to global memory by one TMA store / add-reduction,
+            // which also clips rows >= T and columns >= N
+            if (n >= p.N || m0 + quarter * 32 >= p.T) continue;  // warp-uniform
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+                float4 r;
+                r.x = __uint_as_float(ra[4 * v]) + ((p.bias && n + 4 * v < p.N) ? __ldg(p.bias + n + 4 * v) : 0.0f);
+                r.y = __uint_as_float(ra[4 * v + 1]) + ((p.bias && n + 4 * v + 1 < p.N) ? __ldg(p.bias + n + 4 * v + 1) : 0.0f);
+                r.z = __uint_as_float(ra[4 * v + 2]) + ((p.bias && n + 4 * v + 2 < p.N) ? __ldg(p.bias + n + 4 * v + 2) : 0.0f);
+                r.w = __uint_as_float(ra[4 * v + 3]) + ((p.bias && n + 4 * v + 3 < p.N) ? __ldg(p.bias + n + 4 * v + 3) : 0.0f);
+                *reinterpret_cast<float4*>(out_stage + swizzle128(lane, v)) = r;
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                if (MODE == ACCUM_F32)
+                    tma_reduce_add_2d(&map_out, out_stage, n, m0 + quarter * 32);
+                else
+                    tma_store_2d(&map_out, out_stage, n, m0 + quarter * 32);
+                tma_store_commit();
+            }
+            continue;
+        }
+        if (t >= p.T || n >= p.N) continue;
+        const bool whole = n + 32 <= p.N;
+        if (MODE == STORE_BF16 || MODE == SWIGLU_BF16) {
+            bf16* o = reinterpret_cast<bf16*>(p.out) + (size_t)t * p.ldo + n;
+            uint32_t packed[16];
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+                float v0, v1;
+                if (MODE == SWIGLU_BF16) {
+                    v0 = silu_mul(__uint_as_float(ra[c]), __uint_as_float(rb[c]));
+                    v1 = silu_mul(__uint_as_float(ra[c + 1]), __uint_as_float(rb[c + 1]));
+                } else {
+                    v0 = __uint_as_float(ra[c]) + ((p.bias && n + c < p.N) ? __ldg(p.bias + n + c) : 0.0f);
+                    v1 = __uint_as_float(ra[c + 1]) + ((p.bias && n + c + 1 < p.N) ? __ldg(p.bias + n + c + 1) : 0.0f);
+                }
+                packed[c >> 1] = pack_bf16(v0, v1);
+            }
+            if (whole) {
+#pragma unroll
+                for (int v = 0; v < 4; ++v)
+                    reinterpret_cast<uint4*>(o)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c)
+                    if (n + c < p.N)
+                        o[c] = __ushort_as_bfloat16(
+                            (unsigned short)((c & 1) ? (packed[c >> 1] >> 16) : (packed[c >> 1] & 0xffffu)));
+            }
+        }
+    }
+}
+
 template <int MODE>
 __global__ void __launch_bounds__(PT_THREADS)
     gemm_tokens_m_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -581,70 +653,7 @@ __global__ void __launch_bounds__(PT_THREADS)
             if (!mbar_wait(&tmem_full[buf], (local >> 1) & 1, p.status, 23)) break;
             tcgen05_fence_after();
             const uint32_t d0 = lane_addr + buf * acc_cols;
-            const int cols = p.bn;  // output columns of this tile
-            for (int c0 = half * 32; c0 < cols; c0 += 64) {
-                uint32_t ra[32], rb[32];
-                tmem_load_32x32(d0 + c0, ra);
-                if (ACCS == 2) tmem_load_32x32(d0 + p.bn + c0, rb);
-                tmem_load_wait();
-                const int n = n0 + c0;
-                if (MODE == STORE_F32 || MODE == ACCUM_F32) {
-                    // the warp's 32 x 32 block goes to shared memory (lane = row, 16-byte chunks swizzled as the
-                    // tensor map expects) and from there to global memory by one TMA store / add-reduction,
-                    // which also clips rows >= T and columns >= N
-                    if (n >= p.N || m0 + quarter * 32 >= p.T) continue;  // warp-uniform
-                    if (lane == 0) tma_store_wait_read();
-                    __syncwarp();
-#pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        float4 r;
-                        r.x = __uint_as_float(ra[4 * v]) + ((p.bias && n + 4 * v < p.N) ? __ldg(p.bias + n + 4 * v) : 0.0f);
-                        r.y = __uint_as_float(ra[4 * v + 1]) + ((p.bias && n + 4 * v + 1 < p.N) ? __ldg(p.bias + n + 4 * v + 1) : 0.0f);
-                        r.z = __uint_as_float(ra[4 * v + 2]) + ((p.bias && n + 4 * v + 2 < p.N) ? __ldg(p.bias + n + 4 * v + 2) : 0.0f);
-                        r.w = __uint_as_float(ra[4 * v + 3]) + ((p.bias && n + 4 * v + 3 < p.N) ? __ldg(p.bias + n + 4 * v + 3) : 0.0f);
-                        *reinterpret_cast<float4*>(out_stage + swizzle128(lane, v)) = r;
-                    }
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (MODE == ACCUM_F32)
-                            tma_reduce_add_2d(&map_out, out_stage, n, m0 + quarter * 32);
-                        else
-                            tma_store_2d(&map_out, out_stage, n, m0 + quarter * 32);
-                        tma_store_commit();
-                    }
-                    continue;
-                }
-                if (t >= p.T || n >= p.N) continue;
-                const bool whole = n + 32 <= p.N;
-                if (MODE == STORE_BF16 || MODE == SWIGLU_BF16) {
-                    bf16* o = reinterpret_cast<bf16*>(p.out) + (size_t)t * p.ldo + n;
-                    uint32_t packed[16];
-#pragma unroll
-                    for (int c = 0; c < 32; c += 2) {
-                        float v0, v1;
-                        if (MODE == SWIGLU_BF16) {
-                            v0 = silu_mul(__uint_as_float(ra[c]), __uint_as_float(rb[c]));
-                            v1 = silu_mul(__uint_as_float(ra[c + 1]), __uint_as_float(rb[c + 1]));
-                        } else {
-                            v0 = __uint_as_float(ra[c]) + ((p.bias && n + c < p.N) ? __ldg(p.bias + n + c) : 0.0f);
-                            v1 = __uint_as_float(ra[c + 1]) + ((p.bias && n + c + 1 < p.N) ? __ldg(p.bias + n + c + 1) : 0.0f);
-                        }
-                        packed[c >> 1] = pack_bf16(v0, v1);
-                    }
-                    if (whole) {
-#pragma unroll
-                        for (int v = 0; v < 4; ++v)
-                            reinterpret_cast<uint4*>(o)[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 32; ++c)
-                            if (n + c < p.N)
-                                o[c] = __ushort_as_bfloat16(
-                                    (unsigned short)((c & 1) ? (packed[c >> 1] >> 16) : (packed[c >> 1] & 0xffffu)));
-                    }
-                }
-            }
+            pt_epilogue_tile<MODE>(p, map_out, d0, m0, n0, quarter, half, lane, t, out_stage);
             // this warp has read its part of the buffer: the MMA warp may overwrite it
             tcgen05_fence_before();
             __syncwarp();
@@ -657,6 +666,153 @@ __global__ void __launch_bounds__(PT_THREADS)
     if (warp == 1) {
         tcgen05_fence_after();
         tmem_dealloc(tmem, 512);
+    }
+}
+
+// =============================================================================================
+// The same for CTA PAIRS (cta_group::2): a cluster of two CTAs on one TPC takes tiles of 256 tokens (128 per
+// CTA) x 256 or 128 weight rows with ONE MMA over both.  Each CTA loads its own token rows and only HALF of the
+// weight rows of the tile, so a pair moves two thirds of the bytes that two single CTAs move from L2 for the same
+// work, and L2-to-SM traffic is what bounds the single-CTA kernel at these sizes.  The even CTA issues the MMAs;
+// both CTAs' TMA loads count on its `full` barrier; tcgen05.commit arrives on `empty` / `tmem_full` of both;
+// the epilogue warps of both arrive on its `tmem_empty`.  In SwiGLU mode CTA 0 holds the gate rows and CTA 1 the
+// up rows of the tile: accumulator columns [0, 128) are gate, [128, 256) up, as in the single-CTA kernel.
+// =============================================================================================
+constexpr int PP_STAGES = 6;
+
+template <int MODE>
+__global__ void __launch_bounds__(PT_THREADS)
+    gemm_tokens_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                            const __grid_constant__ CUtensorMap map_out, const PTParams p) {
+    constexpr int ACCS = MODE == SWIGLU_BF16 ? 2 : 1;
+    FERRIS_TL_ENTRY();
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full[PP_STAGES], empty[PP_STAGES], tmem_full[2], tmem_empty[2];
+    __shared__ uint32_t tmem_base;
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();  // 0: the leader
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int n_mma = ACCS * p.bn;            // columns of the pair's MMA and of one accumulator buffer
+    const int half_rows = n_mma / 2;          // weight rows this CTA holds per K slice
+    const int a_bytes = PT_BLOCK_M * BLOCK_K * 2, b_bytes = half_rows * BLOCK_K * 2;
+    const int stage_bytes = a_bytes + b_bytes;
+    const int tiles = p.m_tiles * p.n_tiles;  // m_tiles counts pairs of token tiles here
+    uint8_t* out_stage = smem + (size_t)PP_STAGES * stage_bytes + (size_t)(warp >= 2 ? warp - 2 : 0) * 4096;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&map_x);
+        tma_prefetch_descriptor(&map_w);
+        for (int s = 0; s < PP_STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], 2 * PT_EPI_WARPS);  // the epilogue warps of both CTAs (used in the leader only)
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc_pair(&tmem_base, 512);
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();  // the peer's barriers exist before anything arrives on them
+    tcgen05_fence_after();
+    const uint32_t tmem = tmem_base;
+    pdl_launch_dependents();
+    pdl_wait();
+    FERRIS_TL_BEGIN();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t leader_full = map_to_cta(smem_u32(&full[0]), 0);
+            int it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < tiles && ok; tile += pairs) {
+                const int m0 = (tile % p.m_tiles) * (2 * PT_BLOCK_M) + (int)rank * PT_BLOCK_M;
+                const int n0 = (tile / p.m_tiles) * p.bn;
+                // SwiGLU: the leader holds the gate rows, its peer the up rows; else each holds one half of the rows
+                const int w_row = ACCS == 2 ? (rank == 0 ? n0 : p.up_row_offset + n0) : n0 + (int)rank * half_rows;
+                for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+                    const int s = it % PP_STAGES;
+                    if (it >= PP_STAGES && !mbar_wait(&empty[s], ((it / PP_STAGES) - 1) & 1, p.status, 30)) {
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* st = smem + (size_t)s * stage_bytes;
+                    if (rank == 0) mbar_expect_tx(&full[s], 2 * stage_bytes);  // both CTAs' bytes
+                    tma_load_2d_pair(st, &map_x, kb * BLOCK_K, m0, leader_full + 8u * s);
+                    tma_load_2d_pair(st + a_bytes, &map_w, kb * BLOCK_K, w_row, leader_full + 8u * s);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = umma_idesc_bf16(2 * PT_BLOCK_M, n_mma);
+            int it = 0, local = 0;
+            bool ok = true;
+            long long wait_load = 0, wait_drain = 0, c0 = FERRIS_TL_CLOCK();  // timeline build: where the MMA thread waits
+            const long long began = c0;
+            for (int tile = pair; tile < tiles && ok; tile += pairs, ++local) {
+                const int buf = local & 1;
+                c0 = FERRIS_TL_CLOCK();
+                if (local >= 2 && !mbar_wait(&tmem_empty[buf], ((local >> 1) - 1) & 1, p.status, 31)) break;
+                wait_drain += FERRIS_TL_CLOCK() - c0;
+                tcgen05_fence_after();
+                const uint32_t d0 = tmem + buf * n_mma;
+                for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+                    const int s = it % PP_STAGES;
+                    c0 = FERRIS_TL_CLOCK();
+                    if (!mbar_wait(&full[s], (it / PP_STAGES) & 1, p.status, 32)) {
+                        ok = false;
+                        break;
+                    }
+                    wait_load += FERRIS_TL_CLOCK() - c0;
+                    tcgen05_fence_after();
+                    const uint32_t st = smem_u32(smem + (size_t)s * stage_bytes);
+                    const uint64_t a_desc = umma_desc_k_major_sw128(st);
+                    const uint64_t b_desc = umma_desc_k_major_sw128(st + a_bytes);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                        const uint64_t adv = (uint64_t)((k * UMMA_K * 2) >> 4);
+                        tcgen05_mma_bf16_pair(d0, a_desc + adv, b_desc + adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    tcgen05_commit_pair(&empty[s], 3);  // the stage is free in both CTAs
+                }
+                if (ok) tcgen05_commit_pair(&tmem_full[buf], 3);
+            }
+            FERRIS_TL_VALUE(pair == 0, 0, (unsigned long long)wait_load);
+            FERRIS_TL_VALUE(pair == 0, 1, (unsigned long long)wait_drain);
+            FERRIS_TL_VALUE(pair == 0, 2, (unsigned long long)(FERRIS_TL_CLOCK() - began));
+            FERRIS_TL_VALUE(pair == 0, 3, (unsigned long long)local);
+        }
+    } else {
+        const int e = warp - 2;
+        const int quarter = warp & 3, half = e >> 2;
+        const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+        int local = 0;
+        for (int tile = pair; tile < tiles; tile += pairs, ++local) {
+            const int buf = local & 1;
+            const int m0 = (tile % p.m_tiles) * (2 * PT_BLOCK_M) + (int)rank * PT_BLOCK_M;
+            const int n0 = (tile / p.m_tiles) * p.bn;
+            const int t = m0 + quarter * 32 + lane;
+            if (!mbar_wait(&tmem_full[buf], (local >> 1) & 1, p.status, 33)) break;
+            tcgen05_fence_after();
+            const uint32_t d0 = lane_addr + buf * n_mma;
+            pt_epilogue_tile<MODE>(p, map_out, d0, m0, n0, quarter, half, lane, t, out_stage);
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty[buf]), 0));
+        }
+    }
+    if ((MODE == STORE_F32 || MODE == ACCUM_F32) && warp >= 2 && lane == 0) tma_store_wait_all();
+    tcgen05_fence_before();
+    __syncthreads();
+    FERRIS_TL_END(30 + MODE);
+    cluster_sync();  // neither CTA frees tensor memory or leaves while the pair's MMAs or arrivals may still come
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc_pair(tmem, 512);
     }
 }
 
@@ -722,6 +878,47 @@ bool ferris_gemm_cluster_enabled() {
     return g_cluster != 0;
 }
 
+// CTA pairs are OFF unless the environment says FERRIS_GEMM_PAIR=1 or ferris_set_gemm_pair(1) was called: at the
+// sizes measured (2,048 tokens, 0.5B layer sizes) the gate / up product alone is 9 % faster with pairs (36.5 us
+// against 40.1 us), but inside the prefill step, between kernels that are launched programmatically, the step is
+// 4 % slower (4.52 ms against 4.35 ms); the products with one accumulator are slower with pairs in both settings.
+int g_pair = -1;
+bool ferris_gemm_pair_enabled() {
+    if (g_pair < 0) {
+        const char* v = getenv("FERRIS_GEMM_PAIR");
+        g_pair = (v && v[0] == '1') ? 1 : 0;
+    }
+    return g_pair != 0;
+}
+
+template <int MODE>
+int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const PTParams& p, int pairs,
+                size_t smem, cudaStream_t s) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tokens_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * pairs);
+        cfg.blockDim = dim3(PT_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = ferris_pdl_enabled() ? 2 : 1;
+        e = cudaLaunchKernelEx(&cfg, gemm_tokens_pair_kernel<MODE>, mx, mw, mo, p);
+    }
+    if (e != cudaSuccess) {
+        ferris_set_error("gemm: %s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    FERRIS_LAUNCH_CHECK();
+}
+
 template <int MODE>
 int launch_pt(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const PTParams& p, int ctas,
               size_t smem, cudaStream_t s) {
@@ -755,6 +952,12 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
 }
 
 }  // namespace
+
+// Long steps on CTA pairs (cta_group::2) instead of single CTAs: 1 on, 0 off (the default).
+FERRIS_API int ferris_set_gemm_pair(int on) {
+    g_pair = on ? 1 : 0;
+    return FERRIS_OK;
+}
 
 // How the launcher would cut a product: token tile, K splits, and the fp32 scratch / counters it needs.
 // accumulators: 2 for SwiGLU, else 1.
@@ -918,7 +1121,47 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
     cudaStream_t s = (cudaStream_t)stream;
     // long steps: the persistent token-major kernel (its 16-byte stores need aligned output rows)
     const int elt = (mode == STORE_BF16 || mode == SWIGLU_BF16) ? 2 : 4;
-    if (T >= PT_BLOCK_M && !trace && !built && ((size_t)ldo * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0) {
+    const bool long_step = T >= PT_BLOCK_M && !trace && !built && ((size_t)ldo * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0;
+    if (long_step && T > PT_BLOCK_M && ferris_gemm_pair_enabled()) {
+        // CTA pairs (opt-in): tiles of 256 tokens x 256 weight rows (128 + 128 in SwiGLU mode), or x 128 where the
+        // wider tile would leave pairs of SMs without work
+        PTParams q;
+        q.out = out;
+        q.bias = bias;
+        q.T = T;
+        q.N = N;
+        q.K = K;
+        q.ldo = ldo;
+        q.m_tiles = (T + 2 * PT_BLOCK_M - 1) / (2 * PT_BLOCK_M);
+        const int pairs_all = g_sms / 2;
+        q.bn = (accs == 2 || q.m_tiles * ((N + 255) / 256) < pairs_all) ? 128 : 256;
+        q.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+        q.n_tiles = (N + q.bn - 1) / q.bn;
+        q.up_row_offset = up_row_offset;
+        q.status = ferris_status_ptr();
+        const int half_rows = accs * q.bn / 2;
+        CUtensorMap mx, mw;
+        int rc = ferris_make_tensor_map_2d(&mx, x, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, PT_BLOCK_M, BLOCK_K);
+        if (rc != FERRIS_OK) return rc;
+        rc = pt_weight_map(w, (uint64_t)rows_w, (uint64_t)K, (uint64_t)ldw, (uint32_t)half_rows, &mw);
+        if (rc != FERRIS_OK) return rc;
+        CUtensorMap mo = mx;  // unused by the bf16 modes
+        if (elt == 4) {
+            rc = ferris_make_tensor_map_2d_f32(&mo, out, (uint64_t)T, (uint64_t)N, (uint64_t)ldo, 32);
+            if (rc != FERRIS_OK) return rc;
+        }
+        const int stage_bytes = PT_BLOCK_M * BLOCK_K * 2 + half_rows * BLOCK_K * 2;
+        const size_t smem = (size_t)PP_STAGES * stage_bytes + (size_t)PT_EPI_WARPS * 4096 + 1024;
+        int pairs = q.m_tiles * q.n_tiles;
+        if (pairs > pairs_all) pairs = pairs_all;
+        switch (mode) {
+            case STORE_BF16: return launch_pair<STORE_BF16>(mx, mw, mo, q, pairs, smem, s);
+            case STORE_F32: return launch_pair<STORE_F32>(mx, mw, mo, q, pairs, smem, s);
+            case ACCUM_F32: return launch_pair<ACCUM_F32>(mx, mw, mo, q, pairs, smem, s);
+            default: return launch_pair<SWIGLU_BF16>(mx, mw, mo, q, pairs, smem, s);
+        }
+    }
+    if (long_step) {
         PTParams q;
         q.out = out;
         q.bias = bias;

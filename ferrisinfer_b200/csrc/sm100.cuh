@@ -245,6 +245,64 @@ __device__ __forceinline__ uint32_t umma_idesc_bf16(int M, int N) {
 }
 
 // ---------------------------------------------------------------------------------------------
+// CTA pairs (cta_group::2): two CTAs of a cluster with ranks 2i and 2i + 1 run ONE MMA of 256 rows, 128 per
+// CTA, with each CTA holding its own A rows and one half of the B rows in its shared memory, and each CTA's
+// half of the accumulator in its own tensor memory.  The even CTA (the leader) issues the MMAs; both CTAs load
+// with TMA and signal the LEADER's mbarrier; tcgen05.commit arrives on a barrier at the same offset in both.
+// ---------------------------------------------------------------------------------------------
+// The shared::cluster address of this CTA's shared address `addr` in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    return remote;
+}
+
+// One arrival on an mbarrier given by its shared::cluster address (own or a peer's).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// TMA tile load into THIS CTA's shared memory whose bytes count on the mbarrier at `bar_cluster_addr` (the leader's).
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
+// Tensor memory for a pair: the same warp of BOTH CTAs calls this with the same `dst` offset.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst)), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// D[tmem of both CTAs] (+)= A * B^T over the pair: 256 rows (128 from each CTA's A tile), N columns (each CTA holds
+// N / 2 rows of B).  Issued by ONE thread of the leader CTA; the descriptors are the leader's (same offsets in the peer).
+__device__ __forceinline__ void tcgen05_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                      uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// One arrival on the mbarrier at `bar`'s offset in every CTA of `cta_mask` (bit r = CTA rank r of the cluster) when all
+// MMAs issued so far by this thread are done.
+__device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(cta_mask)
+                 : "memory");
+}
+
+// ---------------------------------------------------------------------------------------------
 // host: tensor maps
 // ---------------------------------------------------------------------------------------------
 // A 2-D bf16 tensor [rows, cols] with `row_stride` elements between rows, read in boxes of

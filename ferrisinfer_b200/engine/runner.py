@@ -13,6 +13,7 @@ and forms logits only at the rows asked for.  Afterwards the requests' token cou
 
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Any, Optional, Sequence
 
@@ -162,8 +163,16 @@ class ModelRunner:
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
-            with torch.cuda.graph(graph):
-                self.model.forward(ctx, self.cache.layer_caches, logits_index, logits)
+            # No garbage collection while the stream records: a collection that frees pinned buffers or events of
+            # an engine that is no longer used would issue calls that are not permitted during capture.
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    self.model.forward(ctx, self.cache.layer_caches, logits_index, logits)
+            finally:
+                if collecting:
+                    gc.enable()
             entry.kernels = ops.launch_count() - before
             entry.graph = graph
             self._graphs[key] = entry

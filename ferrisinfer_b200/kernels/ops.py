@@ -209,6 +209,12 @@ def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row
     )
 
 
+def set_gemm_pairs(on: bool) -> None:
+    """Long steps (more than 128 tokens) on pairs of CTAs that share one 256-row MMA (cta_group::2) instead of
+    single CTAs.  Off by default: see the measurements beside ferris_gemm_pair_enabled in csrc/gemm_tcgen05.cu."""
+    _lib().ferris_set_gemm_pair(_c_int(1 if on else 0))
+
+
 class LazyRMSNorm:
     """The RMSNorm of the residual rows ``h`` that has not been computed yet.  A matrix product that can form
     it on its way (``gemm`` / ``gemm_swiglu`` for short bf16 steps) takes it as its input and no norm kernel

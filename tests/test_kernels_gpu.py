@@ -155,6 +155,41 @@ def test_gemm_tcgen05_swiglu(T, I, K, device):
     assert ops.kernel_status() == 0
 
 
+@pytest.mark.parametrize("T, N, K, mode", [(300, 256, 128, 0), (2048, 384, 256, 2), (257, 129, 200, 1), (700, 448, 96, 3),
+                                           (2048, 9728, 896, 3), (130, 256, 64, 3), (1000, 896, 4864, 2)])
+def test_gemm_on_cta_pairs(T, N, K, mode, device):
+    """Long steps on pairs of CTAs (one MMA of 256 rows over two SMs, each holding half of the weight rows): the same
+    numbers as the kernel on single CTAs, and as the plain product."""
+    from ferrisinfer_b200.kernels import ops
+
+    x, w = rnd((T, K), BF16, device, 41), rnd((N, K), BF16, device, 42, scale=0.1)
+    bias = rnd((N,), F32, device, 43) if mode in (0, 1) else None
+    n_out = N // 2 if mode == 3 else N
+    dtype = BF16 if mode in (0, 3) else F32
+    base = rnd((T, n_out), F32, device, 44) if mode == 2 else None
+
+    def run():
+        out = base.clone() if mode == 2 else torch.full((T, n_out), float("nan"), dtype=dtype, device=device)
+        ops.gemm_tcgen05(x, w, bias, out, mode, up_row_offset=n_out if mode == 3 else 0)
+        torch.cuda.synchronize()
+        assert ops.kernel_status() == 0
+        return out
+
+    single = run()
+    ops.set_gemm_pairs(True)
+    try:
+        paired = run()
+    finally:
+        ops.set_gemm_pairs(False)
+    assert torch.equal(paired, single), (paired.float() - single.float()).abs().max()
+    ref = _gemm_reference(x, w, bias)
+    if mode == 3:
+        ref = ref[:, n_out:] * plain.silu(ref[:, :n_out])
+    if mode == 2:
+        ref = ref + base.cpu().double()
+    _close(paired, ref, K, dtype)
+
+
 @pytest.mark.parametrize("T", [1, 8, 16])
 @pytest.mark.parametrize("N, K", [(1152, 896), (130, 72), (896, 512), (300, 1000)])
 def test_gemm_with_rmsnorm_formed_on_its_way(T, N, K, device):

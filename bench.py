@@ -281,6 +281,24 @@ def timeline(args) -> int:
     cfg = dict(QWEN25_05B)
     if args.layers:
         cfg["num_hidden_layers"] = cfg["max_window_layers"] = args.layers
+    if args.timeline == "prefill":
+        engine = build_engine(cfg, 1, CONTEXT, extra_tokens=PREFILL_TOKENS)
+        tl = StepTimeline(engine.device)
+        gen = torch.Generator().manual_seed(2)
+        for i in range(3):
+            prompt = torch.randint(0, engine.model.vocab_size, (PREFILL_TOKENS,), generator=gen).tolist()
+            if i == 2:
+                tl.reset()
+            engine.runner.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+            torch.cuda.synchronize()
+            engine.runner.free_request("p")
+        launches = tl.read()
+        print(f"prefill of {PREFILL_TOKENS} tokens, {cfg['num_hidden_layers']} layers (times in us)")
+        first = next(i for i, l in enumerate(launches) if "attention" in l.kernel)
+        for l in launches[first + 6:first + 14]:
+            print(f"{l.kernel:26s} ctas {l.ctas:5d}  entry {l.entry_us:8.2f}  start {l.start_us:8.2f}  end {l.end_us:8.2f}")
+        print(summarize(launches))
+        return 0
     engine = build_engine(cfg, args.batch, CONTEXT)
     tl = StepTimeline(engine.device)
     ids = fill_cache(engine, args.batch, CONTEXT - 16)
@@ -316,9 +334,10 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--timeline", action="store_true",
-                    help="instead of the measurement: the timeline of one decode step from hooks inside the kernels "
-                         "(a build of the kernel library of its own; prints a table, no JSON line)")
+    ap.add_argument("--timeline", nargs="?", const="decode", choices=["decode", "prefill"], default=None,
+                    help="instead of the measurement: the timeline of one decode step (or of one prefill of 2,048 "
+                         "tokens) from hooks inside the kernels (a build of the kernel library of its own; prints a "
+                         "table, no JSON line)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

@@ -14,6 +14,7 @@
 // Every mbarrier wait is bounded; a wait that runs out records its place in the status word and
 // the kernel runs on to its end with a wrong result instead of hanging.
 #include <limits.h>
+#include <stdlib.h>
 #include <math.h>
 
 #include "common.cuh"
@@ -578,14 +579,22 @@ __global__ void __launch_bounds__((WARPS + 1) * 32)
 
     const int G = nh / nkv;
     const int seq = blockIdx.z, hk = blockIdx.y;
+    FERRIS_TL_ENTRY();
     pdl_wait();
     pdl_launch_dependents();
+    FERRIS_TL_BEGIN();
     const int q_start = seq_q_start[seq], q_len = seq_q_start[seq + 1] - q_start;
-    if (skip_single && q_len == 1) return;  // single tokens are the decode kernel's
+    if (skip_single && q_len == 1) {  // single tokens are the decode kernel's
+        FERRIS_TL_END(7);
+        return;
+    }
     const int rows_total = q_len * G;
     // heavy row blocks (the last tokens see the most keys) first
     const int n_blocks = (rows_total + PF_ROWS - 1) / PF_ROWS;
-    if ((int)blockIdx.x >= n_blocks) return;
+    if ((int)blockIdx.x >= n_blocks) {
+        FERRIS_TL_END(7);
+        return;
+    }
     const int block = n_blocks - 1 - blockIdx.x;
     const int row0 = block * PF_ROWS;
     const int start_pos = seq_start_pos[seq];
@@ -704,6 +713,10 @@ __global__ void __launch_bounds__((WARPS + 1) * 32)
                     pack_bf16(st.o[n][2 * r] * inv, st.o[n][2 * r + 1] * inv);
         }
     }
+#ifdef FERRIS_TIMELINE
+    __syncthreads();
+#endif
+    FERRIS_TL_END(7);
 }
 
 struct MapCacheEntry {
@@ -712,6 +725,329 @@ struct MapCacheEntry {
     int d;
     CUtensorMap map;
 };
+
+// =============================================================================================
+// Prefill on the 5th-generation tensor cores (head size 64): one CTA per block of 128 rows ((token,
+// head of the group) pairs of one kv head) and a loop over blocks of 128 keys:
+//   S = Q K^T      tcgen05.mma 128 x 128 x 64 from shared memory (Q written once by the CTA, K by TMA) into
+//                  tensor memory;
+//   softmax        four warps, one thread per row: tcgen05.ld of S, scale, causal / window mask, running
+//                  maximum and sum in fp32 (base-2 exponentials of scores pre-multiplied by log2 e), P as
+//                  bf16 into shared memory in the layout of an MMA A operand;
+//   PV = P V       tcgen05.mma 128 x 64 x 128 with V as TMA wrote it (keys x head size: an MN-major B
+//                  operand) into a second accumulator, folded into the thread's fp32 output row
+//                  (o = (o + PV_before) * correction) one block later.
+// A TMA warp streams K and V blocks through two stages; an MMA warp issues S of the next block as soon
+// as the softmax warps have read the current one, so the tensor core works while they exponentiate.
+// Two CTAs share an SM (112 KB of shared memory, 256 columns of tensor memory each).
+// =============================================================================================
+// 2^x by the special-function unit (ex2.approx: about two units in the last place; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+constexpr int T5_ROWS = 128;
+constexpr int T5_KEYS = 128;
+constexpr int T5_STAGES = 2;
+constexpr int T5_SOFTMAX_WARPS = 8;  // two threads per row: warps 0-3 take keys 0-63 of a block, warps 4-7 keys 64-127
+constexpr int T5_THREADS = (T5_SOFTMAX_WARPS + 2) * 32;  // + a TMA warp and an MMA warp
+
+__global__ void __launch_bounds__(T5_THREADS, 1)
+    prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                                 const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
+                                 const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ seq_q_start,
+                                 const int* __restrict__ seq_start_pos, int nh, int nkv, int page_size, int window,
+                                 float scale, int skip_single, int* status) {
+    constexpr int D = 64;
+    constexpr int TILE = TILE_KEYS * D * 2;            // one 16-key box of K or of V: 2 KB
+    constexpr int BLOCK_BYTES = T5_KEYS * D * 2;       // 128 keys of K or of V: 16 KB
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t kv_full[T5_STAGES], kv_empty[T5_STAGES], q_ready, s_ready, s_free, p_ready, pv_done;
+    __shared__ uint32_t tmem_base;
+    __shared__ float row_share[2][2][T5_ROWS];  // [block parity][key half][row]: what the two threads of a row tell each other
+    uint8_t* smem = align1024(smem_raw);
+    uint8_t* q_smem = smem;                    // [128 rows][64] bf16, 128-byte swizzle
+    uint8_t* p_smem = smem + 16384;            // [2 halves of 64 keys][128 rows][64] bf16
+    uint8_t* kv_smem = smem + 16384 + 32768;   // stages x (K block, V block)
+
+    const int G = nh / nkv;
+    const int seq = blockIdx.z, hk = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    FERRIS_TL_ENTRY();
+    pdl_wait();
+    pdl_launch_dependents();
+    FERRIS_TL_BEGIN();
+    const int q_start = seq_q_start[seq], q_len = seq_q_start[seq + 1] - q_start;
+    const int rows_total = q_len * G;
+    const int n_blocks = (rows_total + T5_ROWS - 1) / T5_ROWS;
+    if ((skip_single && q_len == 1) || (int)blockIdx.x >= n_blocks) {  // single tokens are the decode kernel's
+        FERRIS_TL_END(8);
+        return;
+    }
+    const int block = n_blocks - 1 - blockIdx.x;  // heavy row blocks (the last tokens see the most keys) first
+    const int row0 = block * T5_ROWS;
+    const int start_pos = seq_start_pos[seq];
+    const int* table = block_tables + (size_t)seq * max_blocks;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_descriptor(&map_k);
+        tma_prefetch_descriptor(&map_v);
+        for (int s = 0; s < T5_STAGES; ++s) {
+            mbar_init(&kv_full[s], 1);
+            mbar_init(&kv_empty[s], 1);
+        }
+        mbar_init(&q_ready, 4);
+        mbar_init(&s_ready, 1);
+        mbar_init(&s_free, T5_SOFTMAX_WARPS);
+        mbar_init(&p_ready, T5_SOFTMAX_WARPS);
+        mbar_init(&pv_done, 1);
+        mbar_fence_init();
+    }
+    if (warp == T5_SOFTMAX_WARPS + 1) tmem_alloc(&tmem_base, 256);
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128;
+
+    // keys of the block: from the first key its first token may see to its last token's position
+    const int tok_first = row0 / G;
+    const int tok_last = min(row0 + T5_ROWS - 1, rows_total - 1) / G;
+    const int p_first = start_pos + tok_first, p_last = start_pos + tok_last;
+    const int lo_block = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+    const int kb_begin = lo_block / T5_KEYS, n_kb = p_last / T5_KEYS + 1 - kb_begin;
+
+    if (warp == T5_SOFTMAX_WARPS) {
+        if (lane == 0) {
+            constexpr int TILES = T5_KEYS / TILE_KEYS;
+            const int last_tile_key = (p_last / TILE_KEYS) * TILE_KEYS;
+            // the block-table look-ups of a block are independent loads issued together, one block ahead of its copies
+            int rows[TILES], next_rows[TILES];
+            auto look_up = [&](int i, int (&into)[TILES]) {
+#pragma unroll
+                for (int t = 0; t < TILES; ++t) {
+                    // tiles past the last key anybody sees repeat the last one that holds keys (they are masked,
+                    // but what the MMA multiplies by zero must be finite)
+                    const int key0 = min((kb_begin + i) * T5_KEYS + t * TILE_KEYS, last_tile_key);
+                    into[t] = cache_row_of(table, key0, page_size, nkv, hk);
+                }
+            };
+            look_up(0, rows);
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % T5_STAGES;
+                if (i + 1 < n_kb) look_up(i + 1, next_rows);
+                if (i >= T5_STAGES && !mbar_wait(&kv_empty[s], ((i / T5_STAGES) - 1) & 1, status, 40)) break;
+                uint8_t* ks = kv_smem + (size_t)s * 2 * BLOCK_BYTES;
+                uint8_t* vs = ks + BLOCK_BYTES;
+                mbar_expect_tx(&kv_full[s], 2 * BLOCK_BYTES);
+#pragma unroll
+                for (int t = 0; t < TILES; ++t) {
+                    tma_load_2d(ks + t * TILE, &map_k, 0, rows[t], &kv_full[s]);
+                    tma_load_2d(vs + t * TILE, &map_v, 0, rows[t], &kv_full[s]);
+                }
+#pragma unroll
+                for (int t = 0; t < TILES; ++t) rows[t] = next_rows[t];
+            }
+        }
+    } else if (warp == T5_SOFTMAX_WARPS + 1) {
+        if (lane == 0) {
+            const uint32_t idesc_qk = umma_idesc_bf16(T5_ROWS, T5_KEYS);
+            const uint32_t idesc_pv = umma_idesc_bf16(T5_ROWS, D) | (1u << 16);  // B = V is MN-major (keys x head size)
+            const uint64_t q_desc = umma_desc_k_major_sw128(smem_u32(q_smem));
+            bool ok = mbar_wait(&q_ready, 0, status, 41);
+            auto issue_qk = [&](int i) {
+                const int s = i % T5_STAGES;
+                if (!mbar_wait(&kv_full[s], (i / T5_STAGES) & 1, status, 42)) return false;
+                if (i > 0 && !mbar_wait(&s_free, (i - 1) & 1, status, 43)) return false;
+                tcgen05_fence_after();
+                const uint64_t k_desc = umma_desc_k_major_sw128(smem_u32(kv_smem + (size_t)s * 2 * BLOCK_BYTES));
+#pragma unroll
+                for (int k = 0; k < D / 16; ++k)
+                    tcgen05_mma_bf16(tmem_s, q_desc + (uint64_t)(2 * k), k_desc + (uint64_t)(2 * k), idesc_qk, k > 0 ? 1u : 0u);
+                tcgen05_commit(&s_ready);
+                return true;
+            };
+            ok = ok && issue_qk(0);
+            for (int i = 0; i < n_kb && ok; ++i) {
+                if (i + 1 < n_kb) ok = issue_qk(i + 1);
+                if (!ok || !mbar_wait(&p_ready, i & 1, status, 44)) break;
+                tcgen05_fence_after();
+                const int s = i % T5_STAGES;
+                const uint64_t v_desc = umma_desc_k_major_sw128(smem_u32(kv_smem + (size_t)s * 2 * BLOCK_BYTES + BLOCK_BYTES));
+#pragma unroll
+                for (int k = 0; k < T5_KEYS / 16; ++k) {
+                    // A: 16 keys of P = 32 bytes along the row within the half of 64 keys; B: 16 rows of V = 2 KB further
+                    const uint64_t a = umma_desc_k_major_sw128(smem_u32(p_smem + (k >> 2) * 16384)) + (uint64_t)(2 * (k & 3));
+                    tcgen05_mma_bf16(tmem_pv, a, v_desc + (uint64_t)(k * (TILE >> 4)), idesc_pv, k > 0 ? 1u : 0u);
+                }
+                tcgen05_commit(&pv_done);
+                tcgen05_commit(&kv_empty[s]);
+            }
+        }
+    } else {
+        // softmax: two threads per row; this one takes the keys [64 kh, 64 kh + 64) of every block and the output
+        // columns [32 kh, 32 kh + 32)
+        const int wq = warp & 3, kh = warp >> 2;
+        const int r = wq * 32 + lane;
+        const int R = row0 + r;
+        const bool valid = R < rows_total;
+        const int tok = valid ? R / G : 0, head = hk * G + (valid ? R % G : 0);
+        const int pos = start_pos + tok;
+        const int hi = valid ? pos : -1;
+        const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+        if (kh == 0) {
+            const uint4* src = reinterpret_cast<const uint4*>(q + (size_t)(q_start + tok) * ldq + (size_t)head * D);
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(q_smem + swizzle128(r, c)) = valid ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&q_ready);
+        }
+        const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+        const float scale2 = scale * 1.4426950408889634f;  // scores in units of log 2
+        float m = -INFINITY, l = 0.0f;
+        float o[D / 2];
+#pragma unroll
+        for (int j = 0; j < D / 2; ++j) o[j] = 0.0f;
+        bool ok = true;
+        // timeline build: where the first thread of the heaviest CTA spends its cycles
+        const bool tl_probe = threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+        long long t_wait_s = 0, t_max = 0, t_fold = 0, t_exp = 0, c0 = FERRIS_TL_CLOCK(), c1;
+        for (int i = 0; i < n_kb && ok; ++i) {
+            if (!mbar_wait(&s_ready, i & 1, status, 45)) break;
+            tcgen05_fence_after();
+            c1 = FERRIS_TL_CLOCK();
+            t_wait_s += c1 - c0;
+            c0 = c1;
+            const int key_base = (kb_begin + i) * T5_KEYS + 64 * kh;
+            const bool interior = key_base >= lo && key_base + 63 <= hi;
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                uint32_t sv[32];
+                tmem_load_32x32(tmem_s + lane_addr + 64 * kh + 32 * c, sv);
+                tmem_load_wait();
+                if (interior) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(sv[j]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int key = key_base + 32 * c + j;
+                        mx = fmaxf(mx, (key <= hi && key >= lo) ? __uint_as_float(sv[j]) : -INFINITY);
+                    }
+                }
+            }
+            mx *= scale2;  // the scale is positive: the maximum of the scaled scores
+            // the row's maximum over both halves of the block
+            row_share[i & 1][kh][r] = mx;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            mx = fmaxf(mx, row_share[i & 1][kh ^ 1][r]);
+            c1 = FERRIS_TL_CLOCK();
+            t_max += c1 - c0;
+            c0 = c1;
+            const float m_new = fmaxf(m, mx);
+            const float base = m_new == -INFINITY ? 0.0f : m_new;
+            const float corr = m == -INFINITY ? 0.0f : fast_exp2(m - base);
+            if (i > 0) {
+                // the product of the block before (relative to its maximum m) joins the row before the row is rescaled
+                if (!mbar_wait(&pv_done, (i - 1) & 1, status, 46)) break;
+                tcgen05_fence_after();
+                uint32_t pv[32];
+                tmem_load_32x32(tmem_pv + lane_addr + 32 * kh, pv);
+                tmem_load_wait();
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[j] = (o[j] + __uint_as_float(pv[j])) * corr;
+            }
+            l *= corr;
+            c1 = FERRIS_TL_CLOCK();
+            t_fold += c1 - c0;
+            c0 = c1;
+#pragma unroll 1
+            for (int c = 0; c < 2; ++c) {
+                uint32_t sv[32];
+                tmem_load_32x32(tmem_s + lane_addr + 64 * kh + 32 * c, sv);
+                tmem_load_wait();
+                if (c == 1) {
+                    // S has been read for the last time: the next block's scores may overwrite it
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&s_free);
+                }
+                uint32_t packed[16];
+                float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four partial sums: the additions do not wait for one another
+                if (interior) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const float p0 = fast_exp2(fmaf(__uint_as_float(sv[j]), scale2, -base));
+                        const float p1 = fast_exp2(fmaf(__uint_as_float(sv[j + 1]), scale2, -base));
+                        sum4[(j >> 1) & 3] += p0 + p1;
+                        packed[j >> 1] = pack_bf16(p0, p1);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2) {
+                        const int key = key_base + 32 * c + j;
+                        const float e0 = fast_exp2(fmaf(__uint_as_float(sv[j]), scale2, -base));
+                        const float e1 = fast_exp2(fmaf(__uint_as_float(sv[j + 1]), scale2, -base));
+                        const float p0 = (key <= hi && key >= lo) ? e0 : 0.0f;
+                        const float p1 = (key + 1 <= hi && key + 1 >= lo) ? e1 : 0.0f;
+                        sum4[(j >> 1) & 3] += p0 + p1;
+                        packed[j >> 1] = pack_bf16(p0, p1);
+                    }
+                }
+                l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+                uint8_t* half = p_smem + kh * 16384;
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    *reinterpret_cast<uint4*>(half + swizzle128(r, 4 * c + u)) =
+                        make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+            }
+            m = m_new;
+            fence_proxy_async();  // the MMA reads P through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_ready);
+            c1 = FERRIS_TL_CLOCK();
+            t_exp += c1 - c0;
+            c0 = c1;
+        }
+        FERRIS_TL_VALUE(tl_probe, 0, (unsigned long long)t_wait_s);
+        FERRIS_TL_VALUE(tl_probe, 1, (unsigned long long)t_max);
+        FERRIS_TL_VALUE(tl_probe, 2, (unsigned long long)t_fold);
+        FERRIS_TL_VALUE(tl_probe, 3, (unsigned long long)t_exp);
+        FERRIS_TL_VALUE(tl_probe, 4, (unsigned long long)n_kb);
+        // the row's sum over both halves of the keys
+        row_share[n_kb & 1][kh][r] = l;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        l += row_share[n_kb & 1][kh ^ 1][r];
+        if (n_kb > 0 && mbar_wait(&pv_done, (n_kb - 1) & 1, status, 47)) {
+            tcgen05_fence_after();
+            uint32_t packed[D / 4];
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            uint32_t pv[32];
+            tmem_load_32x32(tmem_pv + lane_addr + 32 * kh, pv);
+            tmem_load_wait();
+#pragma unroll
+            for (int j = 0; j < 32; j += 2)
+                packed[j >> 1] = pack_bf16((o[j] + __uint_as_float(pv[j])) * inv, (o[j + 1] + __uint_as_float(pv[j + 1])) * inv);
+            if (valid) {
+                uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(q_start + tok) * ldo + (size_t)head * D + 32 * kh);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) dst[u] = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == T5_SOFTMAX_WARPS + 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, 256);
+    }
+    FERRIS_TL_END(8);
+}
+
 constexpr int MAP_CACHE = 512;
 MapCacheEntry g_maps[MAP_CACHE];
 int g_map_count = 0;
@@ -741,15 +1077,20 @@ int check_common(int nh, int nkv, int d, int page_size, int max_blocks) {
     return FERRIS_OK;
 }
 
+// Head size 64 runs the tcgen05 prefill kernel unless the environment says FERRIS_ATTN_TCGEN05=0 (then, and for
+// head size 128, the mma.sync kernel).
+int g_prefill_tc5 = -1;
+bool prefill_on_tcgen05() {
+    if (g_prefill_tc5 < 0) {
+        const char* v = getenv("FERRIS_ATTN_TCGEN05");
+        g_prefill_tc5 = (v && v[0] == '0') ? 0 : 1;
+    }
+    return g_prefill_tc5 != 0;
+}
+
 template <typename F>
 int set_smem(F kernel, size_t bytes) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-
-    if (e != cudaSuccess) {
-        ferris_set_error("attention: %s", cudaGetErrorString(e));
-        return (int)e;
-    }
-    return FERRIS_OK;
+    return ferris_allow_dynamic_smem((const void*)kernel, bytes);
 }
 
 }  // namespace
@@ -874,9 +1215,17 @@ FERRIS_API int ferris_prefill_attention(const void* q, int ldq, void* out, int l
     if ((rc = cache_map(k_cache, rows, d, &mk)) != FERRIS_OK) return rc;
     if ((rc = cache_map(v_cache, rows, d, &mv)) != FERRIS_OK) return rc;
     const int G = nh / nkv;
-    dim3 grid(((size_t)max_q_len * G + PF_ROWS - 1) / PF_ROWS, nkv, num_seqs);
     cudaStream_t s = (cudaStream_t)stream;
     int* status = ferris_status_ptr();
+    if (d == 64 && prefill_on_tcgen05()) {
+        dim3 grid5(((size_t)max_q_len * G + T5_ROWS - 1) / T5_ROWS, nkv, num_seqs);
+        const size_t smem = 16384 + 32768 + (size_t)T5_STAGES * 2 * T5_KEYS * 64 * 2 + 1024;
+        if ((rc = set_smem(prefill_attention_tc5_kernel, smem)) != FERRIS_OK) return rc;
+        ferris_launch(prefill_attention_tc5_kernel, grid5, dim3(T5_THREADS), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo,
+                      block_tables, max_blocks, seq_q_start, seq_start_pos, nh, nkv, page_size, window, scale, skip_single, status);
+        FERRIS_LAUNCH_CHECK();
+    }
+    dim3 grid(((size_t)max_q_len * G + PF_ROWS - 1) / PF_ROWS, nkv, num_seqs);
     if (d == 64) {
         constexpr int ST = 3;
         const size_t smem = (size_t)ST * PF_STAGE_TILES * 2 * TILE_KEYS * 64 * 2 + 1024;

@@ -19,6 +19,10 @@
 
 void ferris_set_error(const char* fmt, ...);
 
+// Allow `fn` (a kernel) `bytes` of dynamic shared memory on the current device; the driver is asked only when the
+// size grows.  Returns FERRIS_OK or a cudaError_t (text in ferris_last_error()).
+int ferris_allow_dynamic_smem(const void* fn, size_t bytes);
+
 #define FERRIS_REFUSE(...)            \
     do {                              \
         ferris_set_error(__VA_ARGS__); \

@@ -90,11 +90,13 @@ template <typename TOut, int VEC>  // VEC float4 per lane: hidden <= 128 * VEC
 __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
                                                            const int* __restrict__ row_index, TOut* __restrict__ out,
                                                            int rows, int hidden, float eps) {
+    FERRIS_TL_ENTRY();
     pdl_wait();
     pdl_launch_dependents();
+    FERRIS_TL_BEGIN();
     const int lane = threadIdx.x & 31;
     const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (r >= rows) return;
+    if (r >= rows) return;  // never the block's first thread, which ends the timeline record below
     const int src = row_index ? row_index[r] : r;
     const float4* xr = reinterpret_cast<const float4*>(x + (size_t)src * hidden);
     const int n4 = hidden >> 2;
@@ -121,6 +123,7 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restri
             store4(o + 4 * i, (v[j].x * inv) * g.x, (v[j].y * inv) * g.y, (v[j].z * inv) * g.z, (v[j].w * inv) * g.w);
         }
     }
+    FERRIS_TL_END(6);
 }
 
 template <typename TOut>
@@ -210,8 +213,10 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
                                         const float* __restrict__ inv_freq, const int* __restrict__ slot_mapping,
                                         T* __restrict__ k_cache, T* __restrict__ v_cache, int nh, int nkv, int d,
                                         int rotary, int page_size, int write_kv) {
+    FERRIS_TL_ENTRY();
     pdl_wait();
     pdl_launch_dependents();
+    FERRIS_TL_BEGIN();
     const int t = blockIdx.x;
     const int half = rotary / 2;
     const float pos = (float)positions[t];
@@ -243,7 +248,10 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
             }
         }
     }
-    if (slot < 0) return;
+    if (slot < 0) {
+        FERRIS_TL_END(3);
+        return;
+    }
     // unrotated tail of k, and all of v
     const int tail = d - rotary;
     for (int w = threadIdx.x; w < nkv * tail; w += blockDim.x) {
@@ -254,6 +262,7 @@ __global__ void rope_cache_write_kernel(T* __restrict__ qkv, const int* __restri
         const int h = w / d, i = w % d;
         v_cache[(((size_t)page * nkv + h) * page_size + in_page) * d + i] = row[(size_t)(nh + nkv + h) * d + i];
     }
+    FERRIS_TL_END(3);
 }
 
 FERRIS_API int ferris_rope_cache_write(void* qkv, int dtype, const int* positions, const float* inv_freq,

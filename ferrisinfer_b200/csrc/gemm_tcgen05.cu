@@ -553,6 +553,7 @@ __global__ void __launch_bounds__(PT_THREADS)
     gemm_tokens_m_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                          const __grid_constant__ CUtensorMap map_out, const PTParams p) {
     constexpr int ACCS = MODE == SWIGLU_BF16 ? 2 : 1;
+    FERRIS_TL_ENTRY();
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full[PT_STAGES], empty[PT_STAGES], tmem_full[2], tmem_empty[2];
     __shared__ uint32_t tmem_base;
@@ -585,6 +586,7 @@ __global__ void __launch_bounds__(PT_THREADS)
     const uint32_t tmem = tmem_base;
     pdl_launch_dependents();
     pdl_wait();
+    FERRIS_TL_BEGIN();
 
     if (warp == 0) {
         if (lane == 0) {
@@ -667,6 +669,7 @@ __global__ void __launch_bounds__(PT_THREADS)
         tcgen05_fence_after();
         tmem_dealloc(tmem, 512);
     }
+    FERRIS_TL_END(22 + MODE);
 }
 
 // =============================================================================================
@@ -894,8 +897,10 @@ bool ferris_gemm_pair_enabled() {
 template <int MODE>
 int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const PTParams& p, int pairs,
                 size_t smem, cudaStream_t s) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tokens_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess) {
+    int rc = ferris_allow_dynamic_smem((const void*)gemm_tokens_pair_kernel<MODE>, smem);
+    if (rc != FERRIS_OK) return rc;
+    cudaError_t e = cudaSuccess;
+    {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * pairs);
         cfg.blockDim = dim3(PT_THREADS);
@@ -922,9 +927,9 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap&
 template <int MODE>
 int launch_pt(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const PTParams& p, int ctas,
               size_t smem, cudaStream_t s) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tokens_m_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess)
-        e = ferris_launch(gemm_tokens_m_kernel<MODE>, dim3(ctas), dim3(PT_THREADS), smem, s, mx, mw, mo, p);
+    int rc = ferris_allow_dynamic_smem((const void*)gemm_tokens_m_kernel<MODE>, smem);
+    if (rc != FERRIS_OK) return rc;
+    cudaError_t e = ferris_launch(gemm_tokens_m_kernel<MODE>, dim3(ctas), dim3(PT_THREADS), smem, s, mx, mw, mo, p);
     if (e != cudaSuccess) {
         ferris_set_error("gemm: %s", cudaGetErrorString(e));
         return (int)e;
@@ -935,11 +940,9 @@ int launch_pt(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& m
 template <int MODE>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, size_t smem, unsigned cluster_z,
            cudaStream_t s) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) {
-        ferris_set_error("gemm: %s", cudaGetErrorString(e));
-        return (int)e;
-    }
+    int rc = ferris_allow_dynamic_smem((const void*)gemm_tcgen05_kernel<MODE>, smem);
+    if (rc != FERRIS_OK) return rc;
+    cudaError_t e = cudaSuccess;
     if (cluster_z > 1)
         e = ferris_launch_cluster(gemm_tcgen05_kernel<MODE>, grid, dim3(THREADS), smem, s, cluster_z, mw, mx, p);
     else
@@ -952,6 +955,10 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
 }
 
 }  // namespace
+
+// 1 if the K splits of the short-step kernel add up through a cluster's shared memory (then no product needs the
+// scratch and counters that ferris_gemm_tcgen05_plan speaks of), 0 if through global scratch.
+FERRIS_API int ferris_gemm_uses_clusters() { return ferris_gemm_cluster_enabled() ? 1 : 0; }
 
 // Long steps on CTA pairs (cta_group::2) instead of single CTAs: 1 on, 0 off (the default).
 FERRIS_API int ferris_set_gemm_pair(int on) {

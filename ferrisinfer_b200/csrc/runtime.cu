@@ -92,8 +92,51 @@ static EncodeTiledFn encode_tiled() {
     return fn;
 }
 
+int ferris_encode_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                                uint32_t box_rows, uint32_t box_cols);
+int ferris_encode_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                                    uint64_t row_stride, uint32_t box_rows);
+
+// The launchers make a tensor map for their activations at every call, and the same few buffers of the workspace
+// come back step after step: a small direct-mapped table of the maps made last saves the driver call.
+namespace {
+struct MapKey {
+    const void* base;
+    uint64_t rows, cols, row_stride;
+    uint32_t box_rows, box_cols, kind;
+};
+struct MapSlot {
+    MapKey key;
+    CUtensorMap map;
+    bool used;
+};
+constexpr int MAP_SLOTS = 256;
+MapSlot g_map_slots[MAP_SLOTS];
+inline bool same(const MapKey& a, const MapKey& b) {
+    return a.base == b.base && a.rows == b.rows && a.cols == b.cols && a.row_stride == b.row_stride &&
+           a.box_rows == b.box_rows && a.box_cols == b.box_cols && a.kind == b.kind;
+}
+inline MapSlot& slot_of(const MapKey& k) {
+    uint64_t h = (uint64_t)(uintptr_t)k.base * 0x9E3779B97F4A7C15ull ^ (k.rows * 31 + k.cols * 131 + k.box_rows * 7 + k.kind);
+    return g_map_slots[(h >> 32) % MAP_SLOTS];
+}
+}  // namespace
+
 int ferris_make_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
                               uint32_t box_rows, uint32_t box_cols) {
+    const MapKey key = {base, rows, cols, row_stride, box_rows, box_cols, 0u};
+    MapSlot& slot = slot_of(key);
+    if (slot.used && same(slot.key, key)) {
+        *map = slot.map;
+        return FERRIS_OK;
+    }
+    int rc = ferris_encode_tensor_map_2d(map, base, rows, cols, row_stride, box_rows, box_cols);
+    if (rc == FERRIS_OK) slot = {key, *map, true};
+    return rc;
+}
+
+int ferris_encode_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                                uint32_t box_rows, uint32_t box_cols) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) FERRIS_REFUSE("tensor map: the driver offers no cuTensorMapEncodeTiled");
     if (((uintptr_t)base & 15) || ((row_stride * 2) & 15) || box_cols * 2 != 128 || box_rows == 0 || box_rows > 256)
@@ -112,6 +155,19 @@ int ferris_make_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t rows,
 
 int ferris_make_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                                   uint64_t row_stride, uint32_t box_rows) {
+    const MapKey key = {base, rows, cols, row_stride, box_rows, 32u, 1u};
+    MapSlot& slot = slot_of(key);
+    if (slot.used && same(slot.key, key)) {
+        *map = slot.map;
+        return FERRIS_OK;
+    }
+    int rc = ferris_encode_tensor_map_2d_f32(map, base, rows, cols, row_stride, box_rows);
+    if (rc == FERRIS_OK) slot = {key, *map, true};
+    return rc;
+}
+
+int ferris_encode_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                                    uint64_t row_stride, uint32_t box_rows) {
     EncodeTiledFn fn = encode_tiled();
     if (!fn) FERRIS_REFUSE("tensor map: the driver offers no cuTensorMapEncodeTiled");
     if (((uintptr_t)base & 15) || ((row_stride * 4) & 15) || box_rows == 0 || box_rows > 256)
@@ -125,5 +181,44 @@ int ferris_make_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t r
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) FERRIS_REFUSE("tensor map: cuTensorMapEncodeTiled failed with %d", (int)r);
+    return FERRIS_OK;
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is a driver call; the launchers would make it at every launch.
+// This remembers, per kernel and device, the largest size already allowed.
+namespace {
+struct SmemAllowance {
+    const void* fn;
+    int device;
+    size_t bytes;
+};
+constexpr int ALLOWANCES = 256;
+SmemAllowance g_allowances[ALLOWANCES];
+int g_allowance_count = 0;
+}  // namespace
+
+int ferris_allow_dynamic_smem(const void* fn, size_t bytes) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        ferris_set_error("%s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    SmemAllowance* hit = nullptr;
+    for (int i = 0; i < g_allowance_count; ++i)
+        if (g_allowances[i].fn == fn && g_allowances[i].device == dev) {
+            hit = &g_allowances[i];
+            break;
+        }
+    if (hit && hit->bytes >= bytes) return FERRIS_OK;
+    e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) {
+        ferris_set_error("%s", cudaGetErrorString(e));
+        return (int)e;
+    }
+    if (hit)
+        hit->bytes = bytes;
+    else if (g_allowance_count < ALLOWANCES)
+        g_allowances[g_allowance_count++] = {fn, dev, bytes};
     return FERRIS_OK;
 }

@@ -24,8 +24,33 @@ _c_float = ctypes.c_float
 _c_void_p = ctypes.c_void_p
 
 
+_VP, _I, _F, _LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
+# Argument types of the launchers on the model's path: with these declared, plain Python ints and floats go straight
+# to C (a pointer would otherwise be cut to 32 bits, and wrapping every argument in a ctypes object costs microseconds).
+_SIGNATURES = {
+    "ferris_gemm_tcgen05": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _I, _VP, _VP, _VP, _VP],
+    "ferris_norm_gemm_tcgen05": [_VP, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _VP],
+    "ferris_merge_gemm_tcgen05": [_VP, _I, _I, _I, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _VP],
+    "ferris_rmsnorm": [_VP, _VP, _VP, _VP, _I, _I, _I, _F, _VP],
+    "ferris_rope_cache_write": [_VP, _I, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP],
+    "ferris_prefill_attention": [_VP, _I, _VP, _I, _VP, _VP, _LL, _VP, _I, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _F, _I, _VP],
+    "ferris_decode_attention_rope": [_VP, _I, _VP, _I, _VP, _VP, _LL, _VP, _I, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I,
+                                     _F, _I, _VP, _I, _VP],
+    "ferris_embed_gather": [_VP, _I, _VP, _VP, _I, _I, _I, _VP, _VP],
+}
+_declared = False
+
+
 def _lib():
-    return build.load_library()
+    global _declared
+    lib = build.load_library()
+    if not _declared:
+        for name, args in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = ctypes.c_int
+        _declared = True
+    return lib
 
 
 def _dt(t: torch.Tensor, what: str) -> int:
@@ -40,7 +65,8 @@ def _ptr(t: Optional[torch.Tensor]) -> _c_void_p:
 
 
 def _stream() -> _c_void_p:
-    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+    """The raw handle of torch's current stream on the current device."""
+    return _c_void_p(torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice()))
 
 
 def _need(t: torch.Tensor, what: str, dtype=None, contiguous: bool = True) -> None:
@@ -121,8 +147,8 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
     elif x.shape[0] != rows:
         raise KernelError("rmsnorm: input and output row counts differ")
     _check(
-        _lib().ferris_rmsnorm(_ptr(x), _ptr(weight), _ptr(row_index), _ptr(out), _dt(out, "rmsnorm output"),
-                              _c_int(rows), _c_int(H), _c_float(eps), _stream()),
+        _lib().ferris_rmsnorm(x.data_ptr(), weight.data_ptr(), None if row_index is None else row_index.data_ptr(),
+                              out.data_ptr(), _dt(out, "rmsnorm output"), rows, H, eps, _stream()),
         "rmsnorm",
     )
 
@@ -178,10 +204,14 @@ def tensor_core_gemm_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
             and (K <= 1 or (x.stride(1) == 1 and w.stride(1) == 1)))
 
 
+_uses_clusters = None
+
+
 def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row_offset: int = 0,
                  trace: Optional[torch.Tensor] = None):
     """out = x w^T on the tcgen05 tensor cores.  mode 0: bf16 store (+bias); 1: fp32 store (+bias);
     2: fp32 out += ; 3: bf16 silu(x w[:N]^T) * (x w[up_row_offset:up_row_offset+N]^T)."""
+    global _uses_clusters
     T, K, ldx = _rows(x, "gemm input")
     rows_w, K2, ldw = _rows(w, "gemm weight")
     T2, N, ldo = _rows(out, "gemm output")
@@ -194,17 +224,22 @@ def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row
         _need(bias, "gemm bias", torch.float32)
         if bias.numel() != N:
             raise KernelError("gemm: bias length differs from the output width")
-    accs = 2 if mode == 3 else 1
-    bt, splits, floats, counters = _c_int(), _c_int(), ctypes.c_longlong(), _c_int()
-    _lib().ferris_gemm_tcgen05_plan(_c_int(T), _c_int(N), _c_int(K), _c_int(accs), ctypes.byref(bt), ctypes.byref(splits),
-                                    ctypes.byref(floats), ctypes.byref(counters))
+    lib = _lib()
+    if _uses_clusters is None:
+        _uses_clusters = bool(lib.ferris_gemm_uses_clusters())
     scratch = cnt = None
-    if splits.value > 1:
-        scratch, cnt = _gemm_scratch(x.device, floats.value, counters.value)
+    if not _uses_clusters:
+        # K splits that add up through global memory need scratch and counters
+        bt, splits, floats, counters = _c_int(), _c_int(), ctypes.c_longlong(), _c_int()
+        lib.ferris_gemm_tcgen05_plan(_c_int(T), _c_int(N), _c_int(K), _c_int(2 if mode == 3 else 1), ctypes.byref(bt),
+                                     ctypes.byref(splits), ctypes.byref(floats), ctypes.byref(counters))
+        if splits.value > 1:
+            scratch, cnt = _gemm_scratch(x.device, floats.value, counters.value)
     _check(
-        _lib().ferris_gemm_tcgen05(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(mode), _c_int(T), _c_int(N), _c_int(K),
-                                   _c_int(ldx), _c_int(ldw), _c_int(ldo), _c_int(rows_w), _c_int(up_row_offset),
-                                   _ptr(scratch), _ptr(cnt), _stream(), _ptr(trace)),
+        lib.ferris_gemm_tcgen05(x.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(),
+                                mode, T, N, K, ldx, ldw, ldo, rows_w, up_row_offset,
+                                None if scratch is None else scratch.data_ptr(), None if cnt is None else cnt.data_ptr(),
+                                _stream(), None if trace is None else trace.data_ptr()),
         "tensor-core gemm",
     )
 
@@ -261,9 +296,9 @@ def norm_gemm_tcgen05(x: "LazyRMSNorm", w, bias, out, mode: int, up_row_offset: 
     if bias is not None:
         _need(bias, "gemm bias", torch.float32)
     _check(
-        _lib().ferris_norm_gemm_tcgen05(_ptr(x.h), _ptr(x.weight), _c_float(x.eps), _ptr(w), _ptr(bias), _ptr(out),
-                                        _c_int(mode), _c_int(T), _c_int(N), _c_int(K), _c_int(ldw), _c_int(ldo),
-                                        _c_int(rows_w), _c_int(up_row_offset), _stream()),
+        _lib().ferris_norm_gemm_tcgen05(x.h.data_ptr(), x.weight.data_ptr(), x.eps, w.data_ptr(),
+                                        None if bias is None else bias.data_ptr(), out.data_ptr(), mode, T, N, K, ldw,
+                                        ldo, rows_w, up_row_offset, _stream()),
         "norm + gemm",
     )
 

@@ -66,11 +66,14 @@ class ModelRunner:
     """Owns the model, the cache manager and the workspace; ``step`` is the only way tokens run.
 
     Steps in which every request brings exactly one token and wants its logits (decoding) are replayed
-    from CUDA graphs, one per (number of requests, block-table width): the ~200 kernel launches of a step
-    become one.  Their metadata lives in a static device buffer that is rewritten before each replay.
-    Every other step launches its kernels one by one."""
+    from CUDA graphs, one per shape of step (counts of tokens, requests and wanted rows, width of the block
+    tables): the ~150 kernel launches of a step become one.  Their metadata lives in a static device buffer
+    that is rewritten before each replay.  Any other shape of step is recorded when it comes a second time
+    (portions of a fixed size recur); the rest launch their kernels one by one."""
 
     N_FIXED = 7  # token_ids, positions, token_seq, q_start, start_pos, state_slot, want
+    MAX_GRAPHS = 64  # recorded shapes of step
+    MAX_GRAPH_LOGITS_BYTES = 64 << 20  # a recorded step owns its logits buffer
 
     def __init__(self, model: DecoderModel, dtype: torch.dtype, device, page_size: int, num_pages: int,
                  max_requests: int, max_model_len: Optional[int] = None, extra_states: Optional[dict] = None,
@@ -92,6 +95,7 @@ class ModelRunner:
         self._staging_next = 0
         self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda" and getattr(model, "graph_safe", False)
         self._graphs: dict = {}
+        self._shapes_seen: dict = {}
         self.graph_replays = 0
         self.graph_kernels = 0  # kernel launches made through graph replays
 
@@ -126,7 +130,7 @@ class ModelRunner:
             raise FerrisError("tokens on the device: one int32 for each entry of one token is needed")
         host = self._layout(entries)
         decode = host.max_q == 1 and host.n_want == host.S and all(list(e.want) == [0] for e in entries)
-        if self.cuda_graphs and decode and out is None:
+        if self.cuda_graphs and out is None and self._graph_worthwhile(host, decode):
             logits = self._step_graph(host, device_tokens)
         else:
             dev = self._upload(host.pieces)
@@ -143,8 +147,30 @@ class ModelRunner:
         self.steps_run += 1
         return logits
 
+    @staticmethod
+    def _shape_key(host: _HostStep) -> tuple:
+        """What fixes every launch of a step: the counts of tokens, requests, wanted rows and single tokens beside
+        portions, the longest share and the width of the block tables.  Everything else (which tokens, positions,
+        pages, how the tokens divide among the requests) is data in the step's metadata buffer."""
+        return (host.T, host.S, host.max_q, host.max_blocks, host.n_want, int(host.pieces[-1].size))
+
+    def _graph_worthwhile(self, host: _HostStep, decode: bool) -> bool:
+        """Decode steps are recorded at first sight; any other shape of step when it comes a second time (portions of
+        a fixed size recur, most mixed steps do not), unless its logits would make the graph's own buffer large."""
+        if decode:
+            return True
+        key = self._shape_key(host)
+        if key in self._graphs:
+            return True
+        seen = self._shapes_seen.get(key, 0)
+        if len(self._shapes_seen) > 4096:
+            self._shapes_seen.clear()
+        self._shapes_seen[key] = seen + 1
+        return seen >= 1 and host.n_want * self.vocab_size * 4 <= self.MAX_GRAPH_LOGITS_BYTES \
+            and len(self._graphs) < self.MAX_GRAPHS
+
     def _step_graph(self, host: _HostStep, device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
-        key = (host.S, host.max_blocks)
+        key = self._shape_key(host)
         entry = self._graphs.get(key)
         if entry is None:
             total = sum(p.size for p in host.pieces)
@@ -155,7 +181,9 @@ class ModelRunner:
             ctx, logits_index = self._context(host, meta)
             # launch geometry that depends on the keys' length is fixed for the width of the block table
             ctx.max_kv_len = host.max_blocks * self.cache.page_size
-            logits = torch.empty(host.S, self.vocab_size, dtype=torch.float32, device=self.device)
+            logits = None
+            if host.n_want:
+                logits = torch.empty(host.n_want, self.vocab_size, dtype=torch.float32, device=self.device)
             entry = _GraphEntry(meta, ctx, logits_index, logits)
             # the first step of this shape runs eagerly (it also sizes every workspace buffer) ...
             self.model.forward(ctx, self.cache.layer_caches, logits_index, logits)

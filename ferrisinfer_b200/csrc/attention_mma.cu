@@ -739,7 +739,10 @@ struct MapCacheEntry {
 //                  (o = (o + PV_before) * correction) one block later.
 // A TMA warp streams K and V blocks through two stages; an MMA warp issues S of the next block as soon
 // as the softmax warps have read the current one, so the tensor core works while they exponentiate.
-// Two CTAs share an SM (112 KB of shared memory, 256 columns of tensor memory each).
+// One CTA per SM: 113 KB of shared memory and 102 registers x 320 threads are each a little more than half an SM.
+// (Measured with two per SM, by giving K a single stage and capping registers at 96: batches of short prompts
+// gain 10 %, but one long prompt loses 15 %, because its time is that of the CTA of its last rows, which then
+// shares its SM.)
 // =============================================================================================
 // 2^x by the special-function unit (ex2.approx: about two units in the last place; -inf gives 0).
 __device__ __forceinline__ float fast_exp2(float x) {

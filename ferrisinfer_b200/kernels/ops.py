@@ -91,13 +91,13 @@ _launches = 0
 
 
 def launch_count() -> int:
-    """How many kernel launches this process has made through this module."""
+    """How many kernels this process has launched through this module."""
     return _launches
 
 
-def _check(code: int, what: str) -> None:
+def _check(code: int, what: str, kernels: int = 1) -> None:
     global _launches
-    _launches += 1
+    _launches += kernels
     if code != 0:
         msg = _lib().ferris_last_error().decode("utf-8", "replace")
         kind = "refused its arguments" if code < 0 else f"failed (CUDA error {code})"
@@ -524,11 +524,13 @@ def decode_attention(qkv, out, k_cache, v_cache, block_tables, token_seq, positi
               _ptr(positions))
     tail = (_c_int(num_heads), _c_int(num_kv_heads), _c_int(head_dim), _c_int(k_cache.shape[2]), _c_int(window or 0),
             _c_float(scale), _c_int(splits), _ptr(scratch if need else None), _stream())
+    kernels = 2 if splits > 1 else 1  # the attention kernel and the merge of its key ranges
     if rows is None:
-        _check(_lib().ferris_decode_attention(*common, _c_int(T), *tail), "decode attention")
+        _check(_lib().ferris_decode_attention(*common, _c_int(T), *tail), "decode attention", kernels)
     else:
         _need(rows, "rows of the single tokens", torch.int32)
-        _check(_lib().ferris_decode_attention_listed(*common, _ptr(rows), _c_int(rows.numel()), *tail), "decode attention")
+        _check(_lib().ferris_decode_attention_listed(*common, _ptr(rows), _c_int(rows.numel()), *tail), "decode attention",
+               kernels)
 
 
 def prefill_attention(qkv, out, k_cache, v_cache, block_tables, seq_q_start, seq_start_pos, num_seqs, max_q_len,
@@ -584,7 +586,7 @@ def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_head
                 _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(inv_freq), _ptr(meta.slot_mapping if write_kv else None),
                 _c_int(T), _c_int(num_heads), _c_int(num_kv_heads), _c_int(head_dim), _c_int(page_size),
                 _c_int(window or 0), _c_float(scale), _c_int(splits), _ptr(scratch), _c_int(0 if leave else 1), _stream()),
-            "decode attention with rotation",
+            "decode attention with rotation", 2 if (splits > 1 and not leave) else 1,
         )
         return LazySplitMerge(scratch, out, num_heads, head_dim, splits) if leave else out
     rope_cache_write(qkv, ctx.positions, inv_freq, meta.slot_mapping, k_cache, v_cache, num_heads, num_kv_heads,

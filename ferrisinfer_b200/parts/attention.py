@@ -28,8 +28,12 @@ from .plan import PartSpec, build_part, register_part
 
 
 class GroupedQueryAttention(Mixer):
-    graph_safe = True
     accepts_lazy_norm = True  # x goes to ops.gemm and nowhere else
+
+    @property
+    def graph_safe(self):
+        # its own work is kernels on device-resident metadata; the position encoding's ``apply`` may be anything
+        return bool(getattr(self.position, "graph_safe", False))
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, window: Optional[int] = None, scale: Optional[float] = None):

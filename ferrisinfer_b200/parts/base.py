@@ -135,6 +135,9 @@ class PositionEncoding(Part):
     """How positions enter a mixer.  ``rotary_table`` lets the attention mixer fuse the
     rotation with its cache write; a kind without one is applied through ``apply``."""
 
+    # as for Mixer: True if ``apply`` may be recorded into a CUDA graph (kinds with a rotary table never run it)
+    graph_safe = False
+
     def rotary_table(self, device=None) -> Optional[tuple]:
         """``(inv_freq, R)`` if the encoding is a rotate-half rotation of the first R dims of
         each head by ``pos * inv_freq[i]`` (inv_freq fp32 [R/2] on ``device``; ``(None, 0)`` =
@@ -168,6 +171,7 @@ class Mixer(Part):
 
 class FeedForward(Part):
     accepts_lazy_norm = False  # as for Mixer
+    graph_safe = False  # as for Mixer
 
     def forward(self, x: torch.Tensor, h: torch.Tensor, ctx: StepContext) -> None:
         """h += feed_forward(x)."""

@@ -45,7 +45,7 @@ class PreNormResidualBlock(Block):
 
     @property
     def graph_safe(self):
-        return bool(getattr(self.mixer, "graph_safe", False))
+        return bool(getattr(self.mixer, "graph_safe", False) and getattr(self.feed_forward, "graph_safe", False))
 
     def forward(self, h, ctx, cache, owns_cache):
         buf = ctx.workspace.get("block_normed", (h.shape[0], self.hidden_size), ctx.act_dtype)

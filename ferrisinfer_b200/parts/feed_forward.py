@@ -17,6 +17,7 @@ from .plan import register_part
 
 class SwiGLU(FeedForward):
     accepts_lazy_norm = True  # x goes to ops.gemm_swiglu and nowhere else
+    graph_safe = True
 
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)

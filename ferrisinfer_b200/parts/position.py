@@ -31,6 +31,8 @@ def rotary_inverse_frequencies(head_dim: int, rotary_dim: int, theta: float) -> 
 
 
 class RotaryEncoding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, head_dim: int, rotary_dim: int, theta: float):
         if rotary_dim % 2 or not (0 <= rotary_dim <= head_dim):
             raise ValueError(f"rotary_dim {rotary_dim} must be even and at most head_dim {head_dim}")
@@ -49,6 +51,8 @@ class RotaryEncoding(PositionEncoding):
 
 
 class NoPosition(PositionEncoding):
+    graph_safe = True
+
     def rotary_table(self, device=None):
         return None, 0
 

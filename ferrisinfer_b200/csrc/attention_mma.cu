@@ -926,21 +926,22 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
             c0 = c1;
             const int key_base = (kb_begin + i) * T5_KEYS + 64 * kh;
             const bool interior = key_base >= lo && key_base + 63 <= hi;
+            // this thread's 64 scores of the block, read once; then the next block's scores may overwrite them
+            uint32_t sv[64];
+            tmem_load_32x64(tmem_s + lane_addr + 64 * kh, sv);
+            tmem_load_wait();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&s_free);
             float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t sv[32];
-                tmem_load_32x32(tmem_s + lane_addr + 64 * kh + 32 * c, sv);
-                tmem_load_wait();
-                if (interior) {
+            if (interior) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(sv[j]));
-                } else {
+                for (int j = 0; j < 64; ++j) mx = fmaxf(mx, __uint_as_float(sv[j]));
+            } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int key = key_base + 32 * c + j;
-                        mx = fmaxf(mx, (key <= hi && key >= lo) ? __uint_as_float(sv[j]) : -INFINITY);
-                    }
+                for (int j = 0; j < 64; ++j) {
+                    const int key = key_base + j;
+                    mx = fmaxf(mx, (key <= hi && key >= lo) ? __uint_as_float(sv[j]) : -INFINITY);
                 }
             }
             mx *= scale2;  // the scale is positive: the maximum of the scaled scores
@@ -968,22 +969,12 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
             c1 = FERRIS_TL_CLOCK();
             t_fold += c1 - c0;
             c0 = c1;
-#pragma unroll 1
-            for (int c = 0; c < 2; ++c) {
-                uint32_t sv[32];
-                tmem_load_32x32(tmem_s + lane_addr + 64 * kh + 32 * c, sv);
-                tmem_load_wait();
-                if (c == 1) {
-                    // S has been read for the last time: the next block's scores may overwrite it
-                    tcgen05_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&s_free);
-                }
-                uint32_t packed[16];
+            {
+                uint32_t packed[32];
                 float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four partial sums: the additions do not wait for one another
                 if (interior) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
+                    for (int j = 0; j < 64; j += 2) {
                         const float p0 = fast_exp2(fmaf(__uint_as_float(sv[j]), scale2, -base));
                         const float p1 = fast_exp2(fmaf(__uint_as_float(sv[j + 1]), scale2, -base));
                         sum4[(j >> 1) & 3] += p0 + p1;
@@ -991,8 +982,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
                     }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        const int key = key_base + 32 * c + j;
+                    for (int j = 0; j < 64; j += 2) {
+                        const int key = key_base + j;
                         const float e0 = fast_exp2(fmaf(__uint_as_float(sv[j]), scale2, -base));
                         const float e1 = fast_exp2(fmaf(__uint_as_float(sv[j + 1]), scale2, -base));
                         const float p0 = (key <= hi && key >= lo) ? e0 : 0.0f;
@@ -1004,8 +995,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
                 l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
                 uint8_t* half = p_smem + kh * 16384;
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    *reinterpret_cast<uint4*>(half + swizzle128(r, 4 * c + u)) =
+                for (int u = 0; u < 8; ++u)
+                    *reinterpret_cast<uint4*>(half + swizzle128(r, u)) =
                         make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
             }
             m = m_new;

@@ -144,8 +144,16 @@ class Engine:
         self.scheduler.submit(request_id, prompt_token_ids, params or SamplingParams())
         return request_id
 
+    add_request = submit
+
     def abort(self, request_id) -> bool:
         return self.scheduler.cancel(request_id) is not None
+
+    def step_raw(self, entries) -> Optional[torch.Tensor]:
+        """The step function itself, below the scheduler: ``entries`` is a list of ``StepEntry`` (request id, its next
+        tokens, the places among them whose logits are wanted); returns fp32 logits [wanted, vocab] or None.  This is
+        what trace replay drives; requests stepped this way are the caller's to end (``runner.free_request``)."""
+        return self.runner.step(entries)
 
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished()

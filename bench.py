@@ -29,7 +29,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# layer sizes of BASELINE.json configs[2] (Qwen2.5-0.5B)
+# layer sizes of Qwen2.5-0.5B (the configuration the benchmark is quoted on)
 QWEN25_05B = {
     "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2",
     "vocab_size": 151936, "hidden_size": 896, "intermediate_size": 4864, "num_hidden_layers": 24,

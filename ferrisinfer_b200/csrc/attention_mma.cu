@@ -727,7 +727,7 @@ struct MapCacheEntry {
 };
 
 // =============================================================================================
-// Prefill on the 5th-generation tensor cores (head size 64): one CTA per block of 128 rows ((token,
+// Prefill on the 5th-generation tensor cores (head sizes 64 and 128): one CTA per block of 128 rows ((token,
 // head of the group) pairs of one kv head) and a loop over blocks of 128 keys:
 //   S = Q K^T      tcgen05.mma 128 x 128 x 64 from shared memory (Q written once by the CTA, K by TMA) into
 //                  tensor memory;
@@ -757,23 +757,25 @@ constexpr int T5_STAGES = 2;
 constexpr int T5_SOFTMAX_WARPS = 8;  // two threads per row: warps 0-3 take keys 0-63 of a block, warps 4-7 keys 64-127
 constexpr int T5_THREADS = (T5_SOFTMAX_WARPS + 2) * 32;  // + a TMA warp and an MMA warp
 
+template <int D>
 __global__ void __launch_bounds__(T5_THREADS, 1)
     prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                                  const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
                                  const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ seq_q_start,
                                  const int* __restrict__ seq_start_pos, int nh, int nkv, int page_size, int window,
                                  float scale, int skip_single, int* status) {
-    constexpr int D = 64;
-    constexpr int TILE = TILE_KEYS * D * 2;            // one 16-key box of K or of V: 2 KB
-    constexpr int BLOCK_BYTES = T5_KEYS * D * 2;       // 128 keys of K or of V: 16 KB
+    constexpr int ATOMS = D / 64;                      // 64-wide column groups of a head (one 128-byte swizzle row each)
+    constexpr int TILE = TILE_KEYS * 64 * 2;           // one 16-key x 64-column box of K or of V: 2 KB
+    constexpr int ATOM_BYTES = T5_KEYS * 64 * 2;       // 128 rows x 64 columns: 16 KB
+    constexpr int BLOCK_BYTES = ATOMS * ATOM_BYTES;    // 128 keys of K or of V
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t kv_full[T5_STAGES], kv_empty[T5_STAGES], q_ready, s_ready, s_free, p_ready, pv_done;
     __shared__ uint32_t tmem_base;
     __shared__ float row_share[2][2][T5_ROWS];  // [block parity][key half][row]: what the two threads of a row tell each other
     uint8_t* smem = align1024(smem_raw);
-    uint8_t* q_smem = smem;                    // [128 rows][64] bf16, 128-byte swizzle
-    uint8_t* p_smem = smem + 16384;            // [2 halves of 64 keys][128 rows][64] bf16
-    uint8_t* kv_smem = smem + 16384 + 32768;   // stages x (K block, V block)
+    uint8_t* q_smem = smem;                              // [column group][128 rows][64] bf16, 128-byte swizzle
+    uint8_t* p_smem = smem + BLOCK_BYTES;                // [2 halves of 64 keys][128 rows][64] bf16
+    uint8_t* kv_smem = smem + BLOCK_BYTES + 32768;       // stages x (K block, V block), each [column group][128 keys][64]
 
     const int G = nh / nkv;
     const int seq = blockIdx.z, hk = blockIdx.y;
@@ -812,7 +814,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
-    const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128;
+    const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128;  // 128 columns of scores, D of the product
 
     // keys of the block: from the first key its first token may see to its last token's position
     const int tok_first = row0 / G;
@@ -846,8 +848,11 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
                 mbar_expect_tx(&kv_full[s], 2 * BLOCK_BYTES);
 #pragma unroll
                 for (int t = 0; t < TILES; ++t) {
-                    tma_load_2d(ks + t * TILE, &map_k, 0, rows[t], &kv_full[s]);
-                    tma_load_2d(vs + t * TILE, &map_v, 0, rows[t], &kv_full[s]);
+#pragma unroll
+                    for (int a = 0; a < ATOMS; ++a) {
+                        tma_load_2d(ks + a * ATOM_BYTES + t * TILE, &map_k, 64 * a, rows[t], &kv_full[s]);
+                        tma_load_2d(vs + a * ATOM_BYTES + t * TILE, &map_v, 64 * a, rows[t], &kv_full[s]);
+                    }
                 }
 #pragma unroll
                 for (int t = 0; t < TILES; ++t) rows[t] = next_rows[t];
@@ -857,17 +862,20 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
         if (lane == 0) {
             const uint32_t idesc_qk = umma_idesc_bf16(T5_ROWS, T5_KEYS);
             const uint32_t idesc_pv = umma_idesc_bf16(T5_ROWS, D) | (1u << 16);  // B = V is MN-major (keys x head size)
-            const uint64_t q_desc = umma_desc_k_major_sw128(smem_u32(q_smem));
             bool ok = mbar_wait(&q_ready, 0, status, 41);
             auto issue_qk = [&](int i) {
                 const int s = i % T5_STAGES;
                 if (!mbar_wait(&kv_full[s], (i / T5_STAGES) & 1, status, 42)) return false;
                 if (i > 0 && !mbar_wait(&s_free, (i - 1) & 1, status, 43)) return false;
                 tcgen05_fence_after();
-                const uint64_t k_desc = umma_desc_k_major_sw128(smem_u32(kv_smem + (size_t)s * 2 * BLOCK_BYTES));
+                const uint32_t k_addr = smem_u32(kv_smem + (size_t)s * 2 * BLOCK_BYTES);
 #pragma unroll
-                for (int k = 0; k < D / 16; ++k)
-                    tcgen05_mma_bf16(tmem_s, q_desc + (uint64_t)(2 * k), k_desc + (uint64_t)(2 * k), idesc_qk, k > 0 ? 1u : 0u);
+                for (int k = 0; k < D / 16; ++k) {
+                    // 16 columns of Q and of K: 32 bytes along the row within the column group of 64
+                    const uint64_t qd = umma_desc_k_major_sw128(smem_u32(q_smem) + (k >> 2) * ATOM_BYTES) + (uint64_t)(2 * (k & 3));
+                    const uint64_t kd = umma_desc_k_major_sw128(k_addr + (k >> 2) * ATOM_BYTES) + (uint64_t)(2 * (k & 3));
+                    tcgen05_mma_bf16(tmem_s, qd, kd, idesc_qk, k > 0 ? 1u : 0u);
+                }
                 tcgen05_commit(&s_ready);
                 return true;
             };
@@ -877,7 +885,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
                 if (!ok || !mbar_wait(&p_ready, i & 1, status, 44)) break;
                 tcgen05_fence_after();
                 const int s = i % T5_STAGES;
-                const uint64_t v_desc = umma_desc_k_major_sw128(smem_u32(kv_smem + (size_t)s * 2 * BLOCK_BYTES + BLOCK_BYTES));
+                // V as an MN-major operand: column groups of 64 lie ATOM_BYTES apart (the leading byte offset)
+                const uint64_t v_desc = umma_desc_mn_major_sw128(smem_u32(kv_smem + (size_t)s * 2 * BLOCK_BYTES + BLOCK_BYTES), ATOM_BYTES);
 #pragma unroll
                 for (int k = 0; k < T5_KEYS / 16; ++k) {
                     // A: 16 keys of P = 32 bytes along the row within the half of 64 keys; B: 16 rows of V = 2 KB further
@@ -890,7 +899,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
         }
     } else {
         // softmax: two threads per row; this one takes the keys [64 kh, 64 kh + 64) of every block and the output
-        // columns [32 kh, 32 kh + 32)
+        // columns [D/2 kh, D/2 kh + D/2)
         const int wq = warp & 3, kh = warp >> 2;
         const int r = wq * 32 + lane;
         const int R = row0 + r;
@@ -902,8 +911,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
         if (kh == 0) {
             const uint4* src = reinterpret_cast<const uint4*>(q + (size_t)(q_start + tok) * ldq + (size_t)head * D);
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(q_smem + swizzle128(r, c)) = valid ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+            for (int c = 0; c < D / 8; ++c)
+                *reinterpret_cast<uint4*>(q_smem + (c >> 3) * ATOM_BYTES + swizzle128(r, c & 7)) =
+                    valid ? src[c] : make_uint4(0u, 0u, 0u, 0u);
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(&q_ready);
@@ -959,11 +969,14 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
                 // the product of the block before (relative to its maximum m) joins the row before the row is rescaled
                 if (!mbar_wait(&pv_done, (i - 1) & 1, status, 46)) break;
                 tcgen05_fence_after();
-                uint32_t pv[32];
-                tmem_load_32x32(tmem_pv + lane_addr + 32 * kh, pv);
-                tmem_load_wait();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) o[j] = (o[j] + __uint_as_float(pv[j])) * corr;
+                for (int c = 0; c < D / 64; ++c) {
+                    uint32_t pv[32];
+                    tmem_load_32x32(tmem_pv + lane_addr + (D / 2) * kh + 32 * c, pv);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[32 * c + j] = (o[32 * c + j] + __uint_as_float(pv[j])) * corr;
+                }
             }
             l *= corr;
             c1 = FERRIS_TL_CLOCK();
@@ -1020,16 +1033,20 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
             tcgen05_fence_after();
             uint32_t packed[D / 4];
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            uint32_t pv[32];
-            tmem_load_32x32(tmem_pv + lane_addr + 32 * kh, pv);
-            tmem_load_wait();
 #pragma unroll
-            for (int j = 0; j < 32; j += 2)
-                packed[j >> 1] = pack_bf16((o[j] + __uint_as_float(pv[j])) * inv, (o[j + 1] + __uint_as_float(pv[j + 1])) * inv);
+            for (int c = 0; c < D / 64; ++c) {
+                uint32_t pv[32];
+                tmem_load_32x32(tmem_pv + lane_addr + (D / 2) * kh + 32 * c, pv);
+                tmem_load_wait();
+#pragma unroll
+                for (int j = 0; j < 32; j += 2)
+                    packed[(32 * c + j) >> 1] = pack_bf16((o[32 * c + j] + __uint_as_float(pv[j])) * inv,
+                                                          (o[32 * c + j + 1] + __uint_as_float(pv[j + 1])) * inv);
+            }
             if (valid) {
-                uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(q_start + tok) * ldo + (size_t)head * D + 32 * kh);
+                uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(q_start + tok) * ldo + (size_t)head * D + (D / 2) * kh);
 #pragma unroll
-                for (int u = 0; u < 4; ++u) dst[u] = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+                for (int u = 0; u < D / 16; ++u) dst[u] = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
             }
         }
     }
@@ -1071,8 +1088,7 @@ int check_common(int nh, int nkv, int d, int page_size, int max_blocks) {
     return FERRIS_OK;
 }
 
-// Head size 64 runs the tcgen05 prefill kernel unless the environment says FERRIS_ATTN_TCGEN05=0 (then, and for
-// head size 128, the mma.sync kernel).
+// Prefill runs the tcgen05 kernel unless the environment says FERRIS_ATTN_TCGEN05=0 (then the mma.sync kernel).
 int g_prefill_tc5 = -1;
 bool prefill_on_tcgen05() {
     if (g_prefill_tc5 < 0) {
@@ -1211,12 +1227,21 @@ FERRIS_API int ferris_prefill_attention(const void* q, int ldq, void* out, int l
     const int G = nh / nkv;
     cudaStream_t s = (cudaStream_t)stream;
     int* status = ferris_status_ptr();
-    if (d == 64 && prefill_on_tcgen05()) {
+    if (prefill_on_tcgen05()) {
         dim3 grid5(((size_t)max_q_len * G + T5_ROWS - 1) / T5_ROWS, nkv, num_seqs);
-        const size_t smem = 16384 + 32768 + (size_t)T5_STAGES * 2 * T5_KEYS * 64 * 2 + 1024;
-        if ((rc = set_smem(prefill_attention_tc5_kernel, smem)) != FERRIS_OK) return rc;
-        ferris_launch(prefill_attention_tc5_kernel, grid5, dim3(T5_THREADS), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo,
-                      block_tables, max_blocks, seq_q_start, seq_start_pos, nh, nkv, page_size, window, scale, skip_single, status);
+        // Q, P, stages of (K block, V block)
+        const size_t smem = (size_t)T5_ROWS * d * 2 + 32768 + (size_t)T5_STAGES * 2 * T5_KEYS * d * 2 + 1024;
+        if (d == 64) {
+            if ((rc = set_smem(prefill_attention_tc5_kernel<64>, smem)) != FERRIS_OK) return rc;
+            ferris_launch(prefill_attention_tc5_kernel<64>, grid5, dim3(T5_THREADS), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out,
+                          ldo, block_tables, max_blocks, seq_q_start, seq_start_pos, nh, nkv, page_size, window, scale,
+                          skip_single, status);
+        } else {
+            if ((rc = set_smem(prefill_attention_tc5_kernel<128>, smem)) != FERRIS_OK) return rc;
+            ferris_launch(prefill_attention_tc5_kernel<128>, grid5, dim3(T5_THREADS), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out,
+                          ldo, block_tables, max_blocks, seq_q_start, seq_start_pos, nh, nkv, page_size, window, scale,
+                          skip_single, status);
+        }
         FERRIS_LAUNCH_CHECK();
     }
     dim3 grid(((size_t)max_q_len * G + PF_ROWS - 1) / PF_ROWS, nkv, num_seqs);

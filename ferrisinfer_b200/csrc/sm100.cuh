@@ -256,6 +256,18 @@ __device__ __forceinline__ uint64_t umma_desc_k_major_sw128(uint32_t smem_addr) 
     return d;
 }
 
+// The same for an MN-major operand (rows of the tile run along K, as TMA writes a [K rows x 64 columns] box): groups of
+// 8 K rows 1024 bytes apart; column groups of 64 (when the operand is wider than 64) `mn_group_bytes` apart.
+__device__ __forceinline__ uint64_t umma_desc_mn_major_sw128(uint32_t smem_addr, uint32_t mn_group_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);        // start address
+    d |= (uint64_t)((mn_group_bytes >> 4) & 0x3FFF) << 16;  // leading byte offset: between column groups of 64
+    d |= (uint64_t)(1024 >> 4) << 32;                    // stride byte offset: 8 K rows x 128 bytes
+    d |= (uint64_t)1 << 46;                              // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                              // 128-byte swizzle
+    return d;
+}
+
 // Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, tile M x N.
 __device__ __forceinline__ uint32_t umma_idesc_bf16(int M, int N) {
     return (1u << 4)                 // D is fp32

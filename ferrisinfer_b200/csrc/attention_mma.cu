@@ -1209,6 +1209,12 @@ FERRIS_API int ferris_decode_merge(const float* scratch, void* out, int ldo, int
     FERRIS_LAUNCH_CHECK();
 }
 
+// Which prefill kernel runs: 1 the tcgen05 kernel (the default), 0 the mma.sync kernel.
+FERRIS_API int ferris_set_prefill_tcgen05(int on) {
+    g_prefill_tc5 = on ? 1 : 0;
+    return FERRIS_OK;
+}
+
 // Portions of prompts (and anything else: a request with one token is a portion of one, unless
 // skip_single leaves those to the decode kernel).
 FERRIS_API int ferris_prefill_attention(const void* q, int ldq, void* out, int ldo, const void* k_cache,

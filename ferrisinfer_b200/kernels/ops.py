@@ -550,6 +550,11 @@ def prefill_attention(qkv, out, k_cache, v_cache, block_tables, seq_q_start, seq
     )
 
 
+def set_prefill_tcgen05(on: bool) -> None:
+    """Portions of prompts on the tcgen05 attention kernel (the default) or on the mma.sync kernel it replaced."""
+    _lib().ferris_set_prefill_tcgen05(_c_int(1 if on else 0))
+
+
 def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_heads, head_dim, inv_freq, rotary_dim,
                    window, scale, write_kv: bool = True, lazy_merge: bool = False):
     """Everything between the q/k/v product and the output product of an attention layer: rotate q and k by

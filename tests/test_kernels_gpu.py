@@ -525,6 +525,28 @@ def test_attention_step_of_single_tokens_rotates_and_writes_on_its_way(nh, nkv, 
     assert torch.equal(k3, k2) and torch.equal(v3, v2)
 
 
+@pytest.mark.parametrize("nh, nkv, d, window", [(14, 2, 64, 0), (12, 2, 128, 0), (8, 8, 64, 100), (3, 1, 128, 0)])
+def test_prefill_attention_on_tcgen05_and_on_mma_sync(nh, nkv, d, window, device):
+    """The two prefill kernels (scores and products in tensor memory by tcgen05.mma; mma.sync fragments in registers)
+    against the plain attention and against each other: whole prompts past several blocks of 128 keys, a portion at
+    the end of a long context, rows that end inside a block of 128, a single token beside them."""
+    from ferrisinfer_b200.kernels import ops
+
+    seqs = [(700, 700), (1500, 130), (129, 129), (4, 4), (300, 1), (128, 128)]
+    case = AttentionCase(device, BF16, nh, nkv, d, 16, seqs, seed=nh + d, window=window)
+    want = case.reference()
+    got = {}
+    try:
+        for on in (True, False):
+            ops.set_prefill_tcgen05(on)
+            got[on] = run_attention(case, "dispatch")
+    finally:
+        ops.set_prefill_tcgen05(True)
+    for on in (True, False):
+        assert torch.allclose(got[on], want, **ATT_TOL[BF16]), (on, (got[on] - want).abs().max())
+    assert (got[True] - got[False]).abs().max() <= 2 * ATT_TOL[BF16]["atol"]
+
+
 @pytest.mark.parametrize("impl", ["simt", "dispatch"])
 def test_attention_single_tokens_beside_portions_at_long_context(impl, device):
     """Single tokens whose keys are split into ranges, at rows of the step that come after portions of prompts

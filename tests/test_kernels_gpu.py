@@ -712,3 +712,21 @@ def test_sampling_distribution(device):
     freq = torch.bincount(tok.cpu().long(), minlength=5).double() / n
     want = torch.softmax(row[0].double(), 0)
     assert (freq - want).abs().max() < 0.02, (freq, want)
+
+
+# ------------------------------------------------------------------------- switches of the library
+def test_products_with_the_older_k_split_and_without_programmatic_launch():
+    """FERRIS_GEMM_CLUSTER=0 (partials of a K split in global scratch, added by the CTA that finishes last) and
+    FERRIS_PDL=0 (plain stream order) are read once per process: the product tests run again in a process of
+    their own with both set."""
+    import os
+    import subprocess
+    import sys
+
+    env = dict(os.environ, FERRIS_GEMM_CLUSTER="0", FERRIS_PDL="0")
+    here = os.path.dirname(os.path.abspath(__file__))
+    done = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_kernels_gpu.py"), "-q", "-x", "-m", "gpu",
+                           "-k", "gemm_tcgen05_store or gemm_tcgen05_swiglu or rows_do_not_depend", "-p", "no:cacheprovider"],
+                          env=env, capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stdout[-2000:] + done.stderr[-2000:]
+    assert " passed" in done.stdout

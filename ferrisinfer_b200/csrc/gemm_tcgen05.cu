@@ -924,6 +924,44 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap&
     FERRIS_LAUNCH_CHECK();
 }
 
+// How many clusters of `size` CTAs of the short-step kernel (one CTA per SM) the GPU holds at once: the CTAs of a
+// cluster share a GPC, so the answer is less than SMs / size where the size does not divide a GPC's SMs.
+int g_active_clusters[17] = {};
+int active_clusters(int size) {
+    if (size < 1 || size > 16) return 0;
+    if (size == 1) return g_sms;
+    if (g_active_clusters[size] != 0) return g_active_clusters[size] > 0 ? g_active_clusters[size] : g_sms / size;
+    g_active_clusters[size] = -1;  // unknown: assume perfect packing
+    auto kernel = gemm_tcgen05_kernel<ACCUM_F32>;
+    const int smem = 200 * 1024;
+    if (ferris_allow_dynamic_smem((const void*)kernel, smem) != FERRIS_OK) {  // only ever raises the allowance
+        cudaGetLastError();
+        return g_sms / size;
+    }
+    if (size > 8 && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+        cudaGetLastError();
+        return g_sms / size;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, size);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = size;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters <= 0) {
+        cudaGetLastError();
+        return g_sms / size;
+    }
+    g_active_clusters[size] = clusters;
+    return clusters;
+}
+
 template <int MODE>
 int launch_pt(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const PTParams& p, int ctas,
               size_t smem, cudaStream_t s) {
@@ -1000,6 +1038,9 @@ FERRIS_API int ferris_gemm_tcgen05_plan(int T, int N, int K, int accumulators, i
         splits = g_sms / tiles;  // rounded down: a few CTAs more than SMs would cost a second round
         if (splits > most) splits = most;
         if (splits < 1) splits = 1;
+        // the clusters of all tiles must be resident at once (a cluster that waits for SMs of one GPC costs a second
+        // round): fewer, longer splits where the cluster size packs badly into the GPCs
+        while (splits > 1 && ferris_gemm_cluster_enabled() && tiles > active_clusters(splits)) --splits;
         // no split may be empty
         const int per = (kblocks + splits - 1) / splits;
         splits = (kblocks + per - 1) / per;

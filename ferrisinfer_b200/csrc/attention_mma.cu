@@ -293,10 +293,11 @@ __device__ __forceinline__ float2 unpack_bf16(uint32_t v) {
     return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
 }
 
-// Rotate the query fragments of rows g and g + 8 (both of the token at position `pos`):
+// Rotate the query fragments of rows g and g + 8 (both of the token whose angles `cos_sin` holds: (cos, sin) of
+// pos * inv_freq[i] for i < D/2):
 // pairs (i, i + D/2): lo' = lo cos - hi sin, hi' = hi cos + lo sin (crates/ferrisinfer-kernel/src/cpu/attention.rs:1288-1291).
 template <int D>
-__device__ __forceinline__ void rotate_q(WarpState<D>& st, const float* __restrict__ inv_freq, float pos) {
+__device__ __forceinline__ void rotate_q(WarpState<D>& st, const float2* cos_sin) {
     constexpr int HS = D / 32;  // k-steps per half of the head
     const int t = threadIdx.x & 3;
 #pragma unroll
@@ -304,15 +305,13 @@ __device__ __forceinline__ void rotate_q(WarpState<D>& st, const float* __restri
 #pragma unroll
         for (int e2 = 0; e2 < 2; ++e2) {
             const int c = 16 * ks + 2 * t + 8 * e2;
-            float s0, c0, s1, c1;
-            sincosf(pos * inv_freq[c], &s0, &c0);
-            sincosf(pos * inv_freq[c + 1], &s1, &c1);
+            const float2 a0 = cos_sin[c], a1 = cos_sin[c + 1];
 #pragma unroll
             for (int rowsel = 0; rowsel < 2; ++rowsel) {
                 const int e = 2 * e2 + rowsel;
                 const float2 lo = unpack_bf16(st.q[ks][e]), hi = unpack_bf16(st.q[ks + HS][e]);
-                st.q[ks][e] = pack_bf16(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
-                st.q[ks + HS][e] = pack_bf16(hi.x * c0 + lo.x * s0, hi.y * c1 + lo.y * s1);
+                st.q[ks][e] = pack_bf16(lo.x * a0.x - hi.x * a0.y, lo.y * a1.x - hi.y * a1.y);
+                st.q[ks + HS][e] = pack_bf16(hi.x * a0.x + lo.x * a0.y, hi.y * a1.x + lo.y * a1.y);
             }
         }
     }
@@ -335,6 +334,7 @@ __global__ void __launch_bounds__(WARPS * 32)
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full[WARPS][STAGES];
     __shared__ int tile_rows[WARPS][ROW_CACHE];  // cache rows of this warp's next tiles, looked up in one go
+    __shared__ float2 cos_sin[D / 2];            // (cos, sin) of the token's rotation angles, when the rotation is fused
     uint8_t* smem = align1024(smem_raw);
     constexpr int NT = D == 64 ? 4 : 2;  // 16-key tiles per pipeline stage and per softmax update
     constexpr int TILE_BYTES = 2 * TILE_KEYS * D * 2;
@@ -385,7 +385,7 @@ __global__ void __launch_bounds__(WARPS * 32)
         const int g = lane >> 2;
         const bf16* qrow = q + (size_t)tok * ldq + (size_t)hk * G * D;
         load_q(st, g < G ? qrow + (size_t)g * D : nullptr, g + 8 < G ? qrow + (size_t)(g + 8) * D : nullptr);
-        if (rope.inv_freq) rotate_q<D>(st, rope.inv_freq, (float)P);
+        if (rope.inv_freq) rotate_q<D>(st, cos_sin);
         lim.hi[0] = g < G ? P : -1;
         lim.hi[1] = g + 8 < G ? P : -1;
         lim.lo[0] = lim.lo[1] = lo;
@@ -421,10 +421,34 @@ __global__ void __launch_bounds__(WARPS * 32)
         for (int i = 0; i < STAGES && i < my_count; ++i) issue(i);
     // marks of the timeline build: thread 0 of the CTA of the last key range of token 0, kv head 0
     const bool tl_mark = threadIdx.x == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0;
+    // the warp whose tiles include the token's own position (in the CTA of the last key range) will rotate k and copy v
+    const int own_block = (last_tile >= t_begin && last_tile < t_end) ? (last_tile - t_begin) / NT : -1;
+    const bool owns_token = rope.inv_freq && own_block >= 0 && own_block % WARPS == warp;
+    float k_lo[D / 64], k_hi[D / 64];
+    bf16 v_own[D / 32];
     if (early) {
+        // the angles depend on the position alone: formed before the wait, off the step's critical path
+        for (int i = threadIdx.x; i < D / 2; i += WARPS * 32) {
+            float sn, cs;
+            sincosf((float)P * rope.inv_freq[i], &sn, &cs);
+            cos_sin[i] = make_float2(cs, sn);
+        }
+        __syncthreads();
         pdl_wait();
         FERRIS_TL_BEGIN();
         FERRIS_TL_MARK(tl_mark, 9);
+        if (owns_token) {
+            // the token's own k and v (from the q/k/v product that has just finished) are requested with the queries
+            const bf16* krow = q + (size_t)tok * ldq + (size_t)(nh + hk) * D;
+            const bf16* vrow = q + (size_t)tok * ldq + (size_t)(nh + nkv + hk) * D;
+#pragma unroll
+            for (int j = 0; j < D / 64; ++j) {
+                k_lo[j] = __bfloat162float(krow[lane + 32 * j]);
+                k_hi[j] = __bfloat162float(krow[lane + 32 * j + D / 2]);
+            }
+#pragma unroll
+            for (int j = 0; j < D / 32; ++j) v_own[j] = vrow[lane + 32 * j];
+        }
         load_queries();
     }
     FERRIS_TL_MARK(tl_mark, 0);
@@ -445,22 +469,21 @@ __global__ void __launch_bounds__(WARPS * 32)
             // step's qkv row, go to the cache for the steps to come, and into the tile just loaded
             uint8_t* tb = my_stages + s * STAGE_BYTES + (last_tile - tile0) * TILE_BYTES;
             const int r = P % TILE_KEYS;
-            const bf16* krow = q + (size_t)tok * ldq + (size_t)(nh + hk) * D;
-            const bf16* vrow = q + (size_t)tok * ldq + (size_t)(nh + nkv + hk) * D;
             const int slot = rope.slot_mapping ? rope.slot_mapping[tok] : -1;
             const size_t crow = slot >= 0 ? ((size_t)(slot / page_size) * nkv + hk) * page_size + slot % page_size : 0;
             auto put = [&](uint8_t* tile, bf16* cache, int c, bf16 v) {
                 *reinterpret_cast<bf16*>(tile + (c >> 6) * 2048 + swizzle128(r, (c & 63) >> 3) + (c & 7) * 2) = v;
                 if (slot >= 0) cache[crow * D + c] = v;
             };
-            for (int i2 = lane; i2 < D / 2; i2 += 32) {
-                float sn, cs;
-                sincosf((float)P * rope.inv_freq[i2], &sn, &cs);
-                const float klo = __bfloat162float(krow[i2]), khi = __bfloat162float(krow[i2 + D / 2]);
-                put(tb, rope.k_cache, i2, __float2bfloat16_rn(klo * cs - khi * sn));
-                put(tb, rope.k_cache, i2 + D / 2, __float2bfloat16_rn(khi * cs + klo * sn));
+#pragma unroll
+            for (int j = 0; j < D / 64; ++j) {
+                const int i2 = lane + 32 * j;
+                const float2 a = cos_sin[i2];
+                put(tb, rope.k_cache, i2, __float2bfloat16_rn(k_lo[j] * a.x - k_hi[j] * a.y));
+                put(tb, rope.k_cache, i2 + D / 2, __float2bfloat16_rn(k_hi[j] * a.x + k_lo[j] * a.y));
             }
-            for (int c = lane; c < D; c += 32) put(tb + (D / 64) * 2048, rope.v_cache, c, vrow[c]);
+#pragma unroll
+            for (int j = 0; j < D / 32; ++j) put(tb + (D / 64) * 2048, rope.v_cache, lane + 32 * j, v_own[j]);
             fence_proxy_async();
             __syncwarp();
         }

@@ -426,6 +426,8 @@ __global__ void __launch_bounds__(WARPS * 32)
     const bool owns_token = rope.inv_freq && own_block >= 0 && own_block % WARPS == warp;
     float k_lo[D / 64], k_hi[D / 64];
     bf16 v_own[D / 32];
+    // where the token's k and v go in the cache: step metadata, read before the wait as well
+    const int own_slot = (owns_token && rope.slot_mapping) ? rope.slot_mapping[tok] : -1;
     if (early) {
         // the angles depend on the position alone: formed before the wait, off the step's critical path
         for (int i = threadIdx.x; i < D / 2; i += WARPS * 32) {
@@ -469,7 +471,7 @@ __global__ void __launch_bounds__(WARPS * 32)
             // step's qkv row, go to the cache for the steps to come, and into the tile just loaded
             uint8_t* tb = my_stages + s * STAGE_BYTES + (last_tile - tile0) * TILE_BYTES;
             const int r = P % TILE_KEYS;
-            const int slot = rope.slot_mapping ? rope.slot_mapping[tok] : -1;
+            const int slot = own_slot;
             const size_t crow = slot >= 0 ? ((size_t)(slot / page_size) * nkv + hk) * page_size + slot % page_size : 0;
             auto put = [&](uint8_t* tile, bf16* cache, int c, bf16 v) {
                 *reinterpret_cast<bf16*>(tile + (c >> 6) * 2048 + swizzle128(r, (c & 63) >> 3) + (c & 7) * 2) = v;

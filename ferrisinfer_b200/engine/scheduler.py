@@ -314,7 +314,7 @@ class Scheduler:
                 seq.probabilities.append(float(prob))
                 seq.phase = Phase.DECODE
                 self.stats["sampled"] += 1
-                if seq.params.stop_token_id is not None and int(token) == seq.params.stop_token_id:
+                if seq.params.stops(int(token)):
                     reason = FinishReason.STOP_TOKEN
                 elif len(seq.generated) >= seq.max_new_tokens:
                     reason = self._budget_reason(seq)

@@ -25,6 +25,9 @@ class SamplingParams:
     seed: int = 0
     max_new_tokens: int = 128
     stop_token_id: Optional[int] = None
+    # further ids that end the request (the reference's command line stops on the end-of-turn marker or on
+    # eos_token_id: crates/ferrisinfer-cli/src/main.rs:904-919)
+    stop_token_ids: tuple = ()
 
     @classmethod
     def greedy(cls, **kw) -> "SamplingParams":
@@ -33,6 +36,10 @@ class SamplingParams:
     @classmethod
     def chat_default(cls, **kw) -> "SamplingParams":
         return cls(temperature=0.7, top_k=20, top_p=0.9, seed=42, **kw)
+
+    def stops(self, token: int) -> bool:
+        """Whether ``token`` ends the request."""
+        return (self.stop_token_id is not None and token == self.stop_token_id) or token in self.stop_token_ids
 
     @property
     def is_greedy(self) -> bool:
@@ -43,3 +50,4 @@ class SamplingParams:
             raise ValueError("max_new_tokens must be >= 0")
         if self.seed < 0 or self.seed >= 1 << 64:
             raise ValueError("seed must fit in 64 bits")
+        object.__setattr__(self, "stop_token_ids", tuple(int(t) for t in self.stop_token_ids))

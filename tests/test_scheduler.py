@@ -73,6 +73,26 @@ def test_batch_size_limits_live_requests():
     assert sorted(sched.finished) == [0, 1, 2]
 
 
+def test_any_of_several_stop_tokens_ends_a_request():
+    sched, cache = make(max_generated_tokens=8, max_sequence_length=32)
+    sched.submit("either", [1, 2], SamplingParams.greedy(max_new_tokens=8, stop_token_id=7, stop_token_ids=[9, 11]))
+    sched.submit("only", [1, 2], SamplingParams.greedy(max_new_tokens=4, stop_token_ids=(5,)))
+    counts = {}
+
+    def token(seq):
+        counts[seq.request_id] = counts.get(seq.request_id, 0) + 1
+        if seq.request_id == "either":
+            return 11 if counts["either"] == 3 else 2
+        return 7  # not among this request's stop tokens
+
+    while sched.has_unfinished():
+        run_step(sched, cache, token)
+    f = sched.finished
+    assert f["either"].finish_reason is FinishReason.STOP_TOKEN and f["either"].generated == [2, 2, 11]
+    assert f["only"].finish_reason is FinishReason.MAX_NEW_TOKENS and f["only"].generated == [7, 7, 7, 7]
+    assert SamplingParams(stop_token_ids=[3]).stop_token_ids == (3,)
+
+
 def test_finish_reasons():
     sched, cache = make(max_generated_tokens=3, max_sequence_length=12)
     sched.submit("stop", [1, 2], SamplingParams.greedy(max_new_tokens=8, stop_token_id=7))

@@ -255,3 +255,65 @@ def test_running_a_step_ahead_changes_nothing_but_the_timing(dtype, device, fold
     assert want[0][1] is FinishReason.STOP_TOKEN and want[1][1] is FinishReason.STOP_TOKEN
     assert want[2][1] is FinishReason.CANCELLED
     assert got == want
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3])
+def test_requests_arriving_ending_and_preempted_at_random_with_a_step_in_flight(seed, device, folders):
+    """Twelve requests arrive at random steps into a pool that is too small for them, some are cancelled on the way,
+    some end on a stop token, greedy and seeded sampling mixed: what each request generates is what it generates
+    alone in a roomy engine, with and without a step running ahead."""
+    import random
+
+    from ferrisinfer_b200 import FinishReason, SamplingParams, SchedulerConfig
+
+    rng = random.Random(seed)
+    vocab = TINY["A"]["vocab_size"]
+    n = 12
+    prompts = [helpers.random_ids(vocab, rng.randint(2, 30), 900 + 13 * seed + i) for i in range(n)]
+    budgets = [rng.randint(1, 24) for _ in range(n)]
+    sampled = [rng.random() < 0.5 for _ in range(n)]
+
+    def params(i, stop=None):
+        if sampled[i]:
+            return SamplingParams(temperature=0.9, top_k=0, top_p=0.9, seed=100 + i, max_new_tokens=budgets[i], stop_token_id=stop)
+        return SamplingParams.greedy(max_new_tokens=budgets[i], stop_token_id=stop)
+
+    sched = SchedulerConfig(max_batch_size=5, max_prefill_chunk_tokens=8, max_prefill_batch_tokens=20,
+                            max_sequence_length=64, max_generated_tokens=32)
+    roomy = _engine(folders["A"], "float32", device, page_size=4, num_pages=256, scheduler=sched, run_ahead=False)
+    alone = [roomy.generate(prompts[i], params(i)).generated_token_ids() for i in range(n)]
+    stops = [alone[i][len(alone[i]) // 2] if (i % 3 == 0 and len(alone[i]) > 2) else None for i in range(n)]
+    arrive = sorted(rng.randint(0, 14) for _ in range(n))
+    cancel_at = {i: arrive[i] + rng.randint(2, 12) for i in range(n) if i % 4 == 1}
+
+    def run(run_ahead):
+        engine = _engine(folders["A"], "float32", device, page_size=4, num_pages=20, scheduler=sched, run_ahead=run_ahead)
+        ids, step = {}, 0
+        while len(ids) < n or engine.has_unfinished():
+            for i in range(n):
+                if i not in ids and arrive[i] <= step:
+                    ids[i] = engine.submit(prompts[i], params(i, stops[i]))
+            for i, at in cancel_at.items():
+                if at == step and i in ids:
+                    engine.abort(ids[i])
+            engine.step()
+            engine.runner.cache.check_invariants()
+            step += 1
+            assert step < 2000
+        outs = {i: engine.output_of(ids[i]) for i in range(n)}
+        assert all(g.pool.num_used == 0 for g in engine.runner.cache.groups)
+        return outs, engine.scheduler.stats["preemptions"], engine.steps_run_ahead
+
+    for run_ahead in (False, True):
+        outs, preemptions, ahead = run(run_ahead)
+        assert preemptions >= 1, "the pool is small enough to force a request out"
+        assert (ahead > 0) == run_ahead
+        for i in range(n):
+            got, reason = outs[i].generated_token_ids(), outs[i].finish_reason
+            if reason is FinishReason.CANCELLED:
+                assert got == alone[i][:len(got)]
+            elif stops[i] is not None:
+                first = alone[i].index(stops[i])
+                assert got == alone[i][:first + 1] and reason is FinishReason.STOP_TOKEN
+            else:
+                assert got == alone[i] and reason in (FinishReason.MAX_NEW_TOKENS, FinishReason.SESSION_LIMIT)

@@ -4,6 +4,9 @@ Every function checks dtypes, contiguity and sizes, then launches on the current
 CUDA stream through the C ABI of the compiled library.  Nothing here computes on
 the CPU or falls back to a library: a tensor that is not on a CUDA device, or a
 library that cannot be built or loaded, raises ``KernelError``.
+
+The library keeps small tables (tensor maps it has made, shared-memory allowances, the text of the
+last error) without locks: one thread at a time may call into it, which is how the engine drives it.
 """
 
 from __future__ import annotations

@@ -289,4 +289,35 @@ FERRIS_API int ferris_rope_cache_write(void* qkv, int dtype, const int* position
     FERRIS_LAUNCH_CHECK();
 }
 
+// ---------------------------------------------------------------------------------------------
+// The rotation angles of a step, once for all layers that share the frequencies:
+// out[t][i] = (cos, sin)(float(position[t]) * inv_freq[i]), the same fp32 expression as the kernel above.
+// ---------------------------------------------------------------------------------------------
+__global__ void rotary_angles_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                     float2* __restrict__ out, int tokens, int half) {
+    FERRIS_TL_ENTRY();
+    pdl_wait();
+    pdl_launch_dependents();
+    FERRIS_TL_BEGIN();
+    const long long total = (long long)tokens * half;
+    for (long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (long long)gridDim.x * blockDim.x) {
+        const int t = (int)(w / half), i = (int)(w % half);
+        float sn, cs;
+        sincosf((float)positions[t] * inv_freq[i], &sn, &cs);
+        out[w] = make_float2(cs, sn);
+    }
+    FERRIS_TL_END(9);
+}
+
+FERRIS_API int ferris_rotary_angles(const int* positions, const float* inv_freq, float* out, int tokens, int half,
+                                    void* stream) {
+    if (tokens <= 0 || half <= 0) return FERRIS_OK;
+    const long long total = (long long)tokens * half;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 4096 ? (total + threads - 1) / threads : 4096);
+    ferris_launch(rotary_angles_kernel, dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, positions, inv_freq,
+                  reinterpret_cast<float2*>(out), tokens, half);
+    FERRIS_LAUNCH_CHECK();
+}
+
 FERRIS_TIMELINE_TU(elementwise)

@@ -33,7 +33,19 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 320;  // TMA warp, MMA warp, eight epilogue warps
 constexpr int MAX_STAGES = 8;
 
-enum Mode { STORE_BF16 = 0, STORE_F32 = 1, ACCUM_F32 = 2, SWIGLU_BF16 = 3 };
+enum Mode { STORE_BF16 = 0, STORE_F32 = 1, ACCUM_F32 = 2, SWIGLU_BF16 = 3, QKV_ROPE_BF16 = 4 };
+
+// Where the q/k/v product of a long step leaves its output (mode QKV_ROPE_BF16 of the token-major kernel): the
+// columns are heads of d values, nh query heads, then nkv key heads, then nkv value heads.  Query and key heads are
+// rotated by the token's position (pairs (i, i + d/2), whole-head rotation); queries go to the output rows, keys
+// and values straight into the paged cache [pages][nkv][page_size][d] at the token's slot.
+struct RopeEpilogue {
+    const float2* angles;  // [T][d/2] (cos, sin) of position x frequency, fp32
+    const int* slots;      // [T] cache slot of each token; null or < 0: keys and values are not stored
+    bf16* k_cache;
+    bf16* v_cache;
+    int nh, nkv, d, page_size;
+};
 
 struct Params {
     void* out;
@@ -474,7 +486,75 @@ struct PTParams {
     int m_tiles, n_tiles;
     int up_row_offset;
     int* status;
+    RopeEpilogue rope;  // mode QKV_ROPE_BF16 only
 };
+
+// The epilogue of one q/k/v tile for one warp: its 32 tokens (lane = token t) and every second item of 64
+// accumulator columns.  An item is a low and a high chunk of 32 columns of ONE head, d/2 apart, so that a thread
+// holds both members of 32 rotation pairs: with d = 64 item w is head w of the tile, with d = 128 it is head
+// w / 2, pairs i in [32 (w % 2), 32 (w % 2) + 32).  Bias, rotation and rounding happen once, in fp32, on the
+// accumulator.
+__device__ __forceinline__ void pt_epilogue_qkv_rope(const PTParams& p, uint32_t d0, int n0, int half, int t) {
+    const RopeEpilogue& r = p.rope;
+    const int d = r.d, hd = d >> 1;
+    const int items = p.bn >> 6;
+    const bool live = t < p.T;
+    int slot = -1;
+    if (live && r.slots) slot = __ldg(r.slots + t);
+    const int page = slot >= 0 ? slot / r.page_size : 0, in_page = slot >= 0 ? slot % r.page_size : 0;
+    for (int w = half; w < items; w += 2) {
+        const int head_col = d == 64 ? w * 64 : (w >> 1) * 128;
+        const int i0 = d == 64 ? 0 : (w & 1) * 32;
+        uint32_t lo[32], hi[32];
+        tmem_load_32x32(d0 + head_col + i0, lo);
+        tmem_load_32x32(d0 + head_col + i0 + hd, hi);
+        tmem_load_wait();
+        const int n = n0 + head_col;  // the head's first output column; N is a multiple of d
+        const int head = n / d;
+        bf16* dst = nullptr;
+        if (live && n < p.N) {
+            if (head < r.nh)
+                dst = reinterpret_cast<bf16*>(p.out) + (size_t)t * p.ldo + n;
+            else if (slot >= 0 && head < r.nh + r.nkv)
+                dst = r.k_cache + (((size_t)page * r.nkv + (head - r.nh)) * r.page_size + in_page) * d;
+            else if (slot >= 0)
+                dst = r.v_cache + (((size_t)page * r.nkv + (head - r.nh - r.nkv)) * r.page_size + in_page) * d;
+        }
+        if (dst) {
+            const bool rotate = head < r.nh + r.nkv;
+            const float* bl = p.bias ? p.bias + n + i0 : nullptr;
+            const float4* ang = reinterpret_cast<const float4*>(r.angles + (size_t)t * hd + i0);
+            uint32_t plo[16], phi[16];
+#pragma unroll
+            for (int c = 0; c < 32; c += 2) {
+                float l0 = __uint_as_float(lo[c]), l1 = __uint_as_float(lo[c + 1]);
+                float h0 = __uint_as_float(hi[c]), h1 = __uint_as_float(hi[c + 1]);
+                if (bl) {
+                    l0 += __ldg(bl + c);
+                    l1 += __ldg(bl + c + 1);
+                    h0 += __ldg(bl + hd + c);
+                    h1 += __ldg(bl + hd + c + 1);
+                }
+                if (rotate) {
+                    const float4 cs = __ldg(ang + (c >> 1));  // (cos, sin) of pair i0 + c and of pair i0 + c + 1
+                    const float a0 = l0 * cs.x - h0 * cs.y, b0 = h0 * cs.x + l0 * cs.y;
+                    const float a1 = l1 * cs.z - h1 * cs.w, b1 = h1 * cs.z + l1 * cs.w;
+                    l0 = a0, h0 = b0, l1 = a1, h1 = b1;
+                }
+                plo[c >> 1] = pack_bf16(l0, l1);
+                phi[c >> 1] = pack_bf16(h0, h1);
+            }
+            uint4* olo = reinterpret_cast<uint4*>(dst + i0);
+            uint4* ohi = reinterpret_cast<uint4*>(dst + i0 + hd);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                olo[v] = make_uint4(plo[4 * v], plo[4 * v + 1], plo[4 * v + 2], plo[4 * v + 3]);
+                ohi[v] = make_uint4(phi[4 * v], phi[4 * v + 1], phi[4 * v + 2], phi[4 * v + 3]);
+            }
+        }
+        __syncwarp();
+    }
+}
 
 // The epilogue of one token-major tile for one warp: its 32 tokens (TMEM lanes, lane = token t) and every second
 // 32-column chunk of the accumulator buffer at d0 (gate columns first, up columns p.bn further in SwiGLU mode).
@@ -655,7 +735,10 @@ __global__ void __launch_bounds__(PT_THREADS)
             if (!mbar_wait(&tmem_full[buf], (local >> 1) & 1, p.status, 23)) break;
             tcgen05_fence_after();
             const uint32_t d0 = lane_addr + buf * acc_cols;
-            pt_epilogue_tile<MODE>(p, map_out, d0, m0, n0, quarter, half, lane, t, out_stage);
+            if constexpr (MODE == QKV_ROPE_BF16)
+                pt_epilogue_qkv_rope(p, d0, n0, half, t);
+            else
+                pt_epilogue_tile<MODE>(p, map_out, d0, m0, n0, quarter, half, lane, t, out_stage);
             // this warp has read its part of the buffer: the MMA warp may overwrite it
             tcgen05_fence_before();
             __syncwarp();
@@ -869,6 +952,17 @@ int pt_weight_map(const void* base, uint64_t rows, uint64_t cols, uint64_t ld, u
 }
 
 int g_sms = 0;
+
+// The device's SM count, asked once.
+static int sm_count() {
+    if (g_sms <= 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sms <= 0)
+            g_sms = 148;
+    }
+    return g_sms;
+}
 int g_cluster = -1;
 
 // The K splits reduce through a cluster's shared memory unless the environment says FERRIS_GEMM_CLUSTER=0
@@ -1008,12 +1102,7 @@ FERRIS_API int ferris_set_gemm_pair(int on) {
 // accumulators: 2 for SwiGLU, else 1.
 FERRIS_API int ferris_gemm_tcgen05_plan(int T, int N, int K, int accumulators, int* bt_out, int* splits_out,
                                         long long* scratch_floats, int* counters) {
-    if (g_sms <= 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || g_sms <= 0)
-            g_sms = 148;
-    }
+    sm_count();
     // Steps of up to 128 tokens are one tile; longer ones start from the widest tile and narrow it (down to 64)
     // while the SMs would lack CTAs even with the deepest K split.
     const int n_tiles = (N + BLOCK_N - 1) / BLOCK_N;
@@ -1146,6 +1235,51 @@ FERRIS_API int ferris_merge_gemm_tcgen05(const float* scratch_parts, int heads, 
                              src);
 }
 
+// The persistent token-major kernel for a long step (T >= 128 tokens; output rows aligned for 16-byte stores).
+static int run_tokens_m(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N, int K,
+                        int ldx, int ldw, int ldo, int rows_w, int up_row_offset, const RopeEpilogue* rope,
+                        cudaStream_t s) {
+    const int accs = mode == SWIGLU_BF16 ? 2 : 1;
+    const int elt = (mode == STORE_F32 || mode == ACCUM_F32) ? 4 : 2;
+    sm_count();
+    PTParams q;
+    q.out = out;
+    q.bias = bias;
+    q.T = T;
+    q.N = N;
+    q.K = K;
+    q.ldo = ldo;
+    q.m_tiles = (T + PT_BLOCK_M - 1) / PT_BLOCK_M;
+    // 256 weight rows per tile where that still gives every SM a tile, else 128 (always 128 + 128 for SwiGLU)
+    q.bn = (accs == 2 || q.m_tiles * ((N + 255) / 256) < g_sms) ? 128 : 256;
+    q.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+    q.n_tiles = (N + q.bn - 1) / q.bn;
+    q.up_row_offset = up_row_offset;
+    q.status = ferris_status_ptr();
+    q.rope = rope ? *rope : RopeEpilogue{};
+    CUtensorMap mx, mw;
+    int rc = ferris_make_tensor_map_2d(&mx, x, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, PT_BLOCK_M, BLOCK_K);
+    if (rc != FERRIS_OK) return rc;
+    rc = pt_weight_map(w, (uint64_t)rows_w, (uint64_t)K, (uint64_t)ldw, (uint32_t)q.bn, &mw);
+    if (rc != FERRIS_OK) return rc;
+    CUtensorMap mo = mx;  // unused by the bf16 modes
+    if (elt == 4) {
+        rc = ferris_make_tensor_map_2d_f32(&mo, out, (uint64_t)T, (uint64_t)N, (uint64_t)ldo, 32);
+        if (rc != FERRIS_OK) return rc;
+    }
+    const int stage_bytes = PT_BLOCK_M * BLOCK_K * 2 + accs * q.bn * BLOCK_K * 2;
+    const size_t smem = (size_t)PT_STAGES * stage_bytes + (size_t)PT_EPI_WARPS * 4096 + 1024;
+    int ctas = q.m_tiles * q.n_tiles;
+    if (ctas > g_sms) ctas = g_sms;
+    switch (mode) {
+        case STORE_BF16: return launch_pt<STORE_BF16>(mx, mw, mo, q, ctas, smem, s);
+        case STORE_F32: return launch_pt<STORE_F32>(mx, mw, mo, q, ctas, smem, s);
+        case ACCUM_F32: return launch_pt<ACCUM_F32>(mx, mw, mo, q, ctas, smem, s);
+        case SWIGLU_BF16: return launch_pt<SWIGLU_BF16>(mx, mw, mo, q, ctas, smem, s);
+        default: return launch_pt<QKV_ROPE_BF16>(mx, mw, mo, q, ctas, smem, s);
+    }
+}
+
 static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N, int K,
                              int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch, int* counters,
                              void* stream, unsigned long long* trace, const TokenSource& src) {
@@ -1209,42 +1343,8 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
             default: return launch_pair<SWIGLU_BF16>(mx, mw, mo, q, pairs, smem, s);
         }
     }
-    if (long_step) {
-        PTParams q;
-        q.out = out;
-        q.bias = bias;
-        q.T = T;
-        q.N = N;
-        q.K = K;
-        q.ldo = ldo;
-        q.m_tiles = (T + PT_BLOCK_M - 1) / PT_BLOCK_M;
-        // 256 weight rows per tile where that still gives every SM a tile, else 128 (always 128 + 128 for SwiGLU)
-        q.bn = (accs == 2 || q.m_tiles * ((N + 255) / 256) < g_sms) ? 128 : 256;
-        q.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
-        q.n_tiles = (N + q.bn - 1) / q.bn;
-        q.up_row_offset = up_row_offset;
-        q.status = ferris_status_ptr();
-        CUtensorMap mx, mw;
-        int rc = ferris_make_tensor_map_2d(&mx, x, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, PT_BLOCK_M, BLOCK_K);
-        if (rc != FERRIS_OK) return rc;
-        rc = pt_weight_map(w, (uint64_t)rows_w, (uint64_t)K, (uint64_t)ldw, (uint32_t)q.bn, &mw);
-        if (rc != FERRIS_OK) return rc;
-        CUtensorMap mo = mx;  // unused by the bf16 modes
-        if (elt == 4) {
-            rc = ferris_make_tensor_map_2d_f32(&mo, out, (uint64_t)T, (uint64_t)N, (uint64_t)ldo, 32);
-            if (rc != FERRIS_OK) return rc;
-        }
-        const int stage_bytes = PT_BLOCK_M * BLOCK_K * 2 + accs * q.bn * BLOCK_K * 2;
-        const size_t smem = (size_t)PT_STAGES * stage_bytes + (size_t)PT_EPI_WARPS * 4096 + 1024;
-        int ctas = q.m_tiles * q.n_tiles;
-        if (ctas > g_sms) ctas = g_sms;
-        switch (mode) {
-            case STORE_BF16: return launch_pt<STORE_BF16>(mx, mw, mo, q, ctas, smem, s);
-            case STORE_F32: return launch_pt<STORE_F32>(mx, mw, mo, q, ctas, smem, s);
-            case ACCUM_F32: return launch_pt<ACCUM_F32>(mx, mw, mo, q, ctas, smem, s);
-            default: return launch_pt<SWIGLU_BF16>(mx, mw, mo, q, ctas, smem, s);
-        }
-    }
+    if (long_step)
+        return run_tokens_m(x, w, bias, out, mode, T, N, K, ldx, ldw, ldo, rows_w, up_row_offset, nullptr, s);
 
     CUtensorMap mw, mx;
     int rc = weight_map(w, (uint64_t)rows_w, (uint64_t)K, (uint64_t)ldw, &mw);
@@ -1305,6 +1405,37 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
         case ACCUM_F32: return launch<ACCUM_F32>(mw, mx, p, grid, smem, cz, s);
         default: return launch<SWIGLU_BF16>(mw, mx, p, grid, smem, cz, s);
     }
+}
+
+// The q/k/v product of a long step with its rotation and cache write in the epilogue: out[:, :nh d] gets the rotated
+// queries (the key and value columns of `out` are NOT written), the paged cache gets the rotated keys and the
+// values of the tokens whose slot is >= 0.  Whole-head rotation of heads of 64 or 128, T >= 128 tokens, bf16.
+FERRIS_API int ferris_qkv_rope_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int T, int K, int ldx,
+                                            int ldw, int ldo, int rows_w, const float* angles, const int* slots,
+                                            void* k_cache, void* v_cache, int nh, int nkv, int d, int page_size,
+                                            void* stream) {
+    if (T <= 0) return FERRIS_OK;
+    if (nh <= 0 || nkv <= 0 || page_size <= 0 || (d != 64 && d != 128))
+        FERRIS_REFUSE("q/k/v product with rotation: %d + 2 x %d heads of %d, pages of %d", nh, nkv, d, page_size);
+    const int N = (nh + 2 * nkv) * d;
+    if (T < PT_BLOCK_M) FERRIS_REFUSE("q/k/v product with rotation: %d tokens are fewer than the %d it takes", T, PT_BLOCK_M);
+    if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ldx < K || ldw < K)
+        FERRIS_REFUSE("q/k/v product with rotation: K=%d and row strides %d, %d must be multiples of 8 elements", K, ldx, ldw);
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || ((uintptr_t)angles & 15) || (ldo & 7) ||
+        ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
+        FERRIS_REFUSE("q/k/v product with rotation: operands must be 16-byte aligned");
+    if (N > rows_w || ldo < nh * d) FERRIS_REFUSE("q/k/v product with rotation: %d outputs from %d weight rows, output stride %d", N, rows_w, ldo);
+    if (!angles || (slots && (!k_cache || !v_cache))) FERRIS_REFUSE("q/k/v product with rotation: angles or cache missing");
+    RopeEpilogue r;
+    r.angles = reinterpret_cast<const float2*>(angles);
+    r.slots = slots;
+    r.k_cache = (bf16*)k_cache;
+    r.v_cache = (bf16*)v_cache;
+    r.nh = nh;
+    r.nkv = nkv;
+    r.d = d;
+    r.page_size = page_size;
+    return run_tokens_m(x, w, bias, out, QKV_ROPE_BF16, T, N, K, ldx, ldw, ldo, rows_w, 0, &r, (cudaStream_t)stream);
 }
 
 FERRIS_TIMELINE_TU(gemm_tcgen05)

@@ -34,6 +34,8 @@ _SIGNATURES = {
     "ferris_gemm_tcgen05": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _I, _VP, _VP, _VP, _VP],
     "ferris_norm_gemm_tcgen05": [_VP, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _VP],
     "ferris_merge_gemm_tcgen05": [_VP, _I, _I, _I, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _VP],
+    "ferris_qkv_rope_gemm_tcgen05": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP],
+    "ferris_rotary_angles": [_VP, _VP, _VP, _I, _I, _VP],
     "ferris_rmsnorm": [_VP, _VP, _VP, _VP, _I, _I, _I, _F, _VP],
     "ferris_rope_cache_write": [_VP, _I, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP],
     "ferris_prefill_attention": [_VP, _I, _VP, _I, _VP, _VP, _LL, _VP, _I, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _F, _I, _VP],
@@ -416,6 +418,64 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor):
     _check(_lib().ferris_swiglu(_ptr(gate_up), _ptr(out), _dt(out, "swiglu"), _c_int(T), _c_int(I), _stream()), "swiglu")
 
 
+def rotary_angles(positions: torch.Tensor, inv_freq: torch.Tensor, out: torch.Tensor):
+    """out [T, len(inv_freq), 2] fp32 = (cos, sin)(float(position) * inv_freq), as the rotary kernels form them."""
+    _need(positions, "positions", torch.int32)
+    _need(inv_freq, "rotary frequencies", torch.float32)
+    _need(out, "rotary angles", torch.float32)
+    T, half = positions.numel(), inv_freq.numel()
+    if out.numel() != 2 * T * half:
+        raise KernelError(f"rotary_angles: output {tuple(out.shape)} for {T} positions x {half} frequencies")
+    _check(_lib().ferris_rotary_angles(_ptr(positions), _ptr(inv_freq), _ptr(out), T, half, _stream()), "rotary angles")
+
+
+QKV_ROPE_MIN_TOKENS = 128
+
+
+def qkv_rope_gemm_takes(x, w, qkv, num_heads, num_kv_heads, head_dim, rotary_dim, k_cache) -> bool:
+    """Whether ``qkv_rope_gemm`` takes this step: bf16 on the tensor cores, at least 128 tokens, heads of 64 or
+    128 rotated whole."""
+    return (isinstance(x, torch.Tensor) and qkv.shape[0] >= QKV_ROPE_MIN_TOKENS and head_dim in (64, 128)
+            and rotary_dim == head_dim and qkv.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
+            and w.shape[0] == (num_heads + 2 * num_kv_heads) * head_dim == qkv.shape[1]
+            and qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0 and tensor_core_gemm_takes(x, w))
+
+
+def qkv_rope_gemm(x, w, bias, qkv, angles, slot_mapping, k_cache, v_cache, num_heads, num_kv_heads, head_dim):
+    """The q/k/v product of a long step with rotation and cache write in its epilogue: ``qkv[:, :nh d]`` gets the
+    rotated queries (its key and value columns are left as they were), the paged cache the rotated keys and
+    the values at ``slot_mapping`` (None: nothing is stored, for a layer that reads another layer's cache).
+    ``angles``: from ``rotary_angles`` for the step's positions."""
+    T, K, ldx = _rows(x, "q/k/v input")
+    rows_w, K2, ldw = _rows(w, "q/k/v weight")
+    T2, N, ldo = _rows(qkv, "q/k/v output")
+    _need(angles, "rotary angles", torch.float32)
+    _need(k_cache, "key cache", torch.bfloat16)
+    _need(v_cache, "value cache", torch.bfloat16)
+    page_size = k_cache.shape[2]
+    if (K != K2 or T != T2 or qkv.dtype != torch.bfloat16 or N != (num_heads + 2 * num_kv_heads) * head_dim
+            or angles.numel() != T * head_dim or k_cache.dim() != 4
+            or k_cache.shape[1:] != (num_kv_heads, page_size, head_dim) or v_cache.shape != k_cache.shape):
+        raise KernelError(f"qkv_rope_gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, qkv {tuple(qkv.shape)}, "
+                          f"cache {tuple(k_cache.shape)}, angles {tuple(angles.shape)}")
+    if bias is not None:
+        _need(bias, "q/k/v bias", torch.float32)
+        if bias.numel() != N:
+            raise KernelError("qkv_rope_gemm: bias length differs from the output width")
+    if slot_mapping is not None:
+        _need(slot_mapping, "slot mapping", torch.int32)
+        if slot_mapping.numel() != T:
+            raise KernelError("qkv_rope_gemm: one cache slot per token is needed")
+    _check(
+        _lib().ferris_qkv_rope_gemm_tcgen05(x.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(),
+                                            qkv.data_ptr(), T, K, ldx, ldw, ldo, rows_w, angles.data_ptr(),
+                                            None if slot_mapping is None else slot_mapping.data_ptr(),
+                                            k_cache.data_ptr(), v_cache.data_ptr(), num_heads, num_kv_heads, head_dim,
+                                            page_size, _stream()),
+        "q/k/v product with rotation",
+    )
+
+
 def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
                      slot_mapping: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
                      v_cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
@@ -559,15 +619,19 @@ def set_prefill_tcgen05(on: bool) -> None:
 
 
 def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_heads, head_dim, inv_freq, rotary_dim,
-                   window, scale, write_kv: bool = True, lazy_merge: bool = False):
+                   window, scale, write_kv: bool = True, lazy_merge: bool = False, rotated: bool = False):
     """Everything between the q/k/v product and the output product of an attention layer: rotate q and k by
     position, put k and v into the paged cache (``meta``: the step's block tables and slots for the cache's
     page group), attend.  A step of single tokens with whole-head rotation on the tensor-core path is ONE
     kernel (the split-KV kernel rotates and writes on its way); everything else is the rotary / cache-write
     kernel followed by ``paged_attention``.  Returns ``out``; with ``lazy_merge`` it may return a
-    LazySplitMerge instead (``out`` not yet written), which ``gemm`` takes as its input."""
+    LazySplitMerge instead (``out`` not yet written), which ``gemm`` takes as its input.  ``rotated``: the
+    q/k/v product has rotated and stored already (``qkv_rope_gemm``), only attention is left."""
     T = qkv.shape[0]
     page_size = k_cache.shape[2]
+    if rotated:
+        paged_attention(qkv, out, k_cache, v_cache, meta.block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale)
+        return out
     if (ctx.max_q_len == 1 and rotary_dim == head_dim and inv_freq is not None
             and tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim, page_size)):
         _need(k_cache, "key cache", qkv.dtype)

@@ -24,6 +24,7 @@ UNITS = ("elementwise", "gemm_tcgen05", "attention_mma", "sampling")
 KERNELS = {
     1: "embedding", 2: "rmsnorm", 3: "rotary + cache write", 4: "decode attention", 5: "greedy sampling",
     6: "rmsnorm (warp per row)", 7: "prefill attention (mma.sync)", 8: "prefill attention (tcgen05)",
+    9: "rotary angles", 26: "long q/k/v gemm + rotary + cache write",
     22: "long gemm -> bf16", 23: "long gemm -> fp32", 24: "long gemm += fp32", 25: "long gemm swiglu",
     30: "pair gemm -> bf16", 31: "pair gemm -> fp32", 32: "pair gemm += fp32", 33: "pair gemm swiglu",
     10: "gemm -> bf16", 11: "gemm -> fp32", 12: "gemm += fp32", 13: "gemm swiglu",

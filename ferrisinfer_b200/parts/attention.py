@@ -86,16 +86,25 @@ class GroupedQueryAttention(Mixer):
         nh, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
         meta = ctx.paged[cache.group]
         qkv = ctx.workspace.get("attn_qkv", (T, self.q_size + 2 * self.kv_size), x.dtype)
-        ops.gemm(x, self.qkv_weight, self.qkv_bias, qkv)
         table = self.position.rotary_table(qkv.device)
-        if table is None:
-            self.position.apply(qkv, ctx.positions, nh, nkv, d)
-            inv_freq, rotary = None, 0
+        inv_freq, rotary = table if table is not None else (None, 0)
+        # a long step of prompt portions: rotation and cache write ride in the product's epilogue
+        fused = False
+        if (inv_freq is not None and ctx.max_q_len > 1 and T >= ops.QKV_ROPE_MIN_TOKENS
+                and hasattr(self.position, "angles")):
+            x = x.materialize() if hasattr(x, "materialize") else x
+            fused = ops.qkv_rope_gemm_takes(x, self.qkv_weight, qkv, nh, nkv, d, rotary, cache.k)
+        if fused:
+            ops.qkv_rope_gemm(x, self.qkv_weight, self.qkv_bias, qkv, self.position.angles(ctx),
+                              meta.slot_mapping if owns_cache else None, cache.k, cache.v, nh, nkv, d)
         else:
-            inv_freq, rotary = table
+            ops.gemm(x, self.qkv_weight, self.qkv_bias, qkv)
+            if table is None:
+                self.position.apply(qkv, ctx.positions, nh, nkv, d)
         out = ctx.workspace.get("attn_out", (T, self.q_size), x.dtype)
         attended = ops.attention_step(qkv, out, cache.k, cache.v, meta, ctx, nh, nkv, d, inv_freq, rotary,
-                                      self.window or 0, self.scale, write_kv=owns_cache, lazy_merge=True)
+                                      self.window or 0, self.scale, write_kv=owns_cache, lazy_merge=True,
+                                      rotated=fused)
         ops.gemm(attended, self.o_weight, None, h, accumulate=True)
 
 

@@ -84,6 +84,9 @@ class StepContext:
     # in a step that mixes portions of prompts with single tokens: the rows (int32, device) of the
     # requests that bring exactly one token, so that kernels made for either kind can share the step
     single_rows: Optional[torch.Tensor] = None
+    # what parts compute once per pass of the model and share across layers, under keys of their own; the
+    # model empties it when a pass begins
+    shared: dict = field(default_factory=dict)
 
     @property
     def all_decode(self) -> bool:

@@ -87,6 +87,7 @@ class DecoderModel:
         LayerCache of entry i (None if it has no need).  Logits (fp32 [n, V]) are formed for the
         rows that ``logits_index`` names, into ``logits_out``."""
         T = ctx.num_tokens
+        ctx.shared.clear()  # what parts share belongs to one pass; a context may be run again (to record a graph)
         h = ctx.workspace.get("residual", (T, self.hidden_size), torch.float32)
         self.embedding.forward(ctx.token_ids, h)
         for i, step in enumerate(self.plan.run_order):

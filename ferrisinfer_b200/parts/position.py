@@ -16,6 +16,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
+from ..kernels import ops
 from .base import PositionEncoding
 from .plan import register_part
 
@@ -48,6 +49,19 @@ class RotaryEncoding(PositionEncoding):
         if key not in self._device:
             self._device[key] = torch.from_numpy(self._host.copy()).to(device)
         return self._device[key], self.rotary_dim
+
+    def angles(self, ctx):
+        """(cos, sin) of position x frequency for the tokens of the step, fp32 [T, rotary_dim / 2, 2]: computed by
+        the first layer of a pass that asks, shared with the other layers of the same frequencies."""
+        key = ("rotary_angles", self.head_dim, self.rotary_dim, self.theta)
+        angles = ctx.shared.get(key)
+        if angles is None:
+            inv_freq, _ = self.rotary_table(ctx.positions.device)
+            angles = ctx.workspace.get(f"rotary_angles_{len(ctx.shared)}", (ctx.positions.numel(), inv_freq.numel(), 2),
+                                       torch.float32)
+            ops.rotary_angles(ctx.positions, inv_freq, angles)
+            ctx.shared[key] = angles
+        return angles
 
 
 class NoPosition(PositionEncoding):

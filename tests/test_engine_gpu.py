@@ -9,6 +9,7 @@ from helpers import TINY, TOL
 pytestmark = pytest.mark.gpu
 
 DTYPES = [torch.float32, torch.bfloat16]
+SHARPEN = 6.0
 PAGE = {"A": 4, "B": 8, "C": 16, "D": 16}
 LENGTHS = {"A": (5, 9, 17, 70), "B": (3, 11, 23, 40, 97), "C": (2, 33, 64), "D": (1, 16, 17, 95, 130)}
 
@@ -30,7 +31,9 @@ def _requests(name, extra=()):
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
     root = tmp_path_factory.mktemp("models")
-    return {name: helpers.make_folder(root, cfg, seed=11 + i) for i, (name, cfg) in enumerate(TINY.items())}
+    # queries and keys scaled up, so that the attention weights are far from uniform and the logits show a key
+    # that is rotated wrongly, missing, or read from the wrong page
+    return {name: helpers.make_folder(root, cfg, seed=11 + i, sharpen=SHARPEN) for i, (name, cfg) in enumerate(TINY.items())}
 
 
 @pytest.fixture(scope="module")
@@ -107,10 +110,16 @@ def test_long_decoding(dtype, device, folders, oracles):
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
-def test_decoding_a_batch_at_a_context_of_hundreds_of_keys(dtype, device, folders, oracles):
+def test_decoding_a_batch_at_a_context_of_hundreds_of_keys(dtype, device, folders, oracles, monkeypatch):
     """Three requests of D (head size 64) with prompts of several hundred tokens, then decoded side by side: in
-    bfloat16 the keys of each are split into ranges over several CTAs, merged inside the output product, and the
-    steps are replayed from a graph.  One of them ends early and a fourth takes its place."""
+    bfloat16 the prompts' q/k/v products rotate and write the cache in their epilogue, the keys of each request
+    are split into ranges over several CTAs, merged inside the output product, and the steps are replayed from
+    a graph.  One of them ends early and a fourth takes its place."""
+    from ferrisinfer_b200.kernels import ops
+
+    fused_products = []
+    real = ops.qkv_rope_gemm
+    monkeypatch.setattr(ops, "qkv_rope_gemm", lambda *a, **k: (fused_products.append(1), real(*a, **k))[1])
     name = "D"
     vocab = TINY[name]["vocab_size"]
     requests = {"a": helpers.random_ids(vocab, 700, 1), "b": helpers.random_ids(vocab, 450, 2),
@@ -159,6 +168,34 @@ def test_decoding_a_batch_at_a_context_of_hundreds_of_keys(dtype, device, folder
     assert bad is None, bad
     if dtype is torch.bfloat16:
         assert runner.graph_replays > 10
+        assert len(fused_products) >= 3 * TINY[name]["num_hidden_layers"]
+    else:
+        assert not fused_products
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])
+def test_a_recorded_long_step_runs_again_at_other_positions(dtype, device, folders, oracles):
+    """Four requests of D whose second portions have the same shape (256 tokens, one request, block tables of
+    the same width) but begin at different positions: the second is recorded as a graph, the third and fourth
+    replay it.  Whatever a recorded step computes from the positions (rotation angles, cache slots) it has to
+    compute again in every replay."""
+    name = "D"
+    vocab = TINY[name]["vocab_size"]
+    firsts = {"a": 130, "b": 140, "c": 133, "d": 143}
+    requests = {rid: helpers.random_ids(vocab, n + 256, 40 + i) for i, (rid, n) in enumerate(firsts.items())}
+    steps = []
+    for rid, n in firsts.items():
+        ids = requests[rid]
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": ids[:n], "want": [n - 1]}], "end": []})
+        steps.append({"step": len(steps), "entries": [{"id": rid, "tokens": ids[n:], "want": [0, 100, 255]}], "end": [rid]})
+    runner = _runner(folders[name], dtype, device, PAGE[name], _pages_for(steps, PAGE[name]))
+    got = helpers.replay(runner, steps)
+    assert runner.graph_replays >= 2
+    config, weights = oracles[name]
+    want = {k: v for k, v in helpers.oracle_logits(config, weights, requests).items() if k in got}
+    assert len(want) == 16
+    bad = helpers.first_mismatch(got, want, **TOL[dtype])
+    assert bad is None, bad
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=["f32", "bf16"])

@@ -324,6 +324,76 @@ def test_rope_cache_write(nh, nkv, d, rotary, page, dtype, device):
     assert torch.equal(again.view(T, -1, d)[:, :nh], qkv.view(T, -1, d)[:, :nh])
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("T,nh,nkv,d,K,page", [(128, 2, 1, 64, 64, 16), (300, 14, 2, 64, 896, 64), (257, 3, 1, 128, 136, 32),
+                                               (6400, 5, 2, 64, 72, 64), (1000, 1, 1, 128, 264, 16)])
+def test_qkv_product_with_rotation_and_cache_write_in_its_epilogue(T, nh, nkv, d, K, page, device):
+    """Queries rotated into the output rows, keys rotated and values straight into the paged cache, against the
+    product in fp64 rotated by the plain implementation; tokens with slot -1 and all other slots stay untouched."""
+    from ferrisinfer_b200.kernels import ops
+
+    N = (nh + 2 * nkv) * d
+    x = rnd((T, K), BF16, device, 31)
+    w = rnd((N, K), BF16, device, 32) * (K ** -0.5)
+    bias = rnd((N,), F32, device, 33)
+    g = torch.Generator().manual_seed(5)
+    positions = torch.randint(0, 5000, (T,), generator=g, dtype=torch.int32)
+    positions[:3] = torch.tensor([0, 1, 32000])
+    pages = (T + page - 1) // page + 3
+    slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32)
+    slots[7] = -1
+    slots[T - 1] = -1
+    positions, slots = positions.to(device), slots.to(device)
+    k_cache = torch.full((pages, nkv, page, d), 7.0, dtype=BF16, device=device)
+    v_cache = torch.full_like(k_cache, 7.0)
+    qkv = torch.full((T, N), 7.0, dtype=BF16, device=device)
+    inv_freq = torch.tensor(plain.rotary_inverse_frequencies(d, d, 1e6).numpy(), device=device)
+    angles = torch.empty(T, d // 2, 2, dtype=F32, device=device)
+    ops.rotary_angles(positions, inv_freq, angles)
+    a = (positions.cpu().float()[:, None] * inv_freq.cpu()[None, :])  # the same fp32 product
+    assert torch.allclose(angles[..., 0].cpu().double(), torch.cos(a.double()), atol=1e-6)
+    assert torch.allclose(angles[..., 1].cpu().double(), torch.sin(a.double()), atol=1e-6)
+    assert ops.qkv_rope_gemm_takes(x, w, qkv, nh, nkv, d, d, k_cache)
+    ops.qkv_rope_gemm(x, w, bias, qkv, angles, slots, k_cache, v_cache, nh, nkv, d)
+
+    y = (x.cpu().double() @ w.cpu().double().t() + bias.cpu().double()).view(T, nh + 2 * nkv, d)
+    pos = positions.cpu().tolist()
+    q_want = plain.rope(y[:, :nh], pos, d, d, 1e6)
+    k_want = plain.rope(y[:, nh:nh + nkv], pos, d, d, 1e6)
+    v_want = y[:, nh + nkv:]
+    t = dict(atol=3e-2, rtol=2e-2)
+    small = [i for i, p in enumerate(pos) if p < 32000]  # the angle at 32000 differs in the last fp32 bits
+    got = qkv.cpu().double().view(T, nh + 2 * nkv, d)
+    assert torch.allclose(got[small, :nh], q_want[small], **tol(BF16))
+    assert torch.allclose(got[:, :nh], q_want, **t)
+    assert (got[:, nh:] == 7.0).all()  # the key and value columns of the buffer are not written
+    sl = slots.cpu()
+    live = sl >= 0
+    kc, vc = k_cache.cpu().double(), v_cache.cpu().double()
+    k_got = kc[sl[live] // page, :, sl[live] % page]
+    v_got = vc[sl[live] // page, :, sl[live] % page]
+    assert torch.allclose(k_got, k_want[live], **t)
+    assert torch.allclose(v_got, v_want[live], **tol(BF16))
+    untouched = torch.ones(pages * page, dtype=torch.bool)
+    untouched[sl[live].long()] = False
+    flat_k = kc.permute(0, 2, 1, 3).reshape(pages * page, nkv, d)
+    flat_v = vc.permute(0, 2, 1, 3).reshape(pages * page, nkv, d)
+    assert (flat_k[untouched] == 7.0).all() and (flat_v[untouched] == 7.0).all()
+
+    # a layer that reads another layer's cache: queries only
+    k2, v2 = torch.full_like(k_cache, 7.0), torch.full_like(v_cache, 7.0)
+    q2 = torch.full_like(qkv, 7.0)
+    ops.qkv_rope_gemm(x, w, bias, q2, angles, None, k2, v2, nh, nkv, d)
+    assert torch.equal(q2, qkv) and (k2 == 7.0).all() and (v2 == 7.0).all()
+    # and the same numbers as the product followed by the rotary kernel, up to one more rounding to bf16
+    ref = torch.empty_like(qkv)
+    ops.gemm(x, w, bias, ref)
+    ops.rope_cache_write(ref, positions, inv_freq, slots, k2, v2, nh, nkv, d, d, page)
+    assert torch.allclose(ref.view(T, -1, d)[:, :nh].float(), qkv.view(T, -1, d)[:, :nh].float(), atol=3e-2, rtol=2e-2)
+    assert torch.allclose(k2.float(), k_cache.float(), atol=3e-2, rtol=2e-2)
+
+
+
 # ----------------------------------------------------------------------------------- attention
 class AttentionCase:
     """A batch of requests over a shuffled page pool; keys and values are set by position."""

@@ -63,23 +63,25 @@ def random_config(rng: random.Random) -> dict:
     return cfg
 
 
-def make_folder(tmp_path, config: dict, seed: int, store_dtype="bfloat16", optional=True, sharpen: float = 1.0) -> str:
+def make_folder(tmp_path, config: dict, seed: int, store_dtype="bfloat16", optional=True, score_std: float = None) -> str:
     """A model folder of random weights.  Weights of N(0, 0.02) give attention scores of a few hundredths: every
     key gets nearly the same weight, and a wrong rotation, a wrong key or a wrong window's edge hardly moves the
-    logits.  ``sharpen`` multiplies the query and key projections (and their biases), so that the scores
-    spread over several units and the logits depend on which key is where."""
+    logits.  ``score_std`` multiplies the query and key projections (and their biases) so that the scores of
+    random tokens have about this standard deviation (hidden x 0.02^2 without it): the attention weights are
+    then far from uniform and the logits depend on which key is where."""
     from ferrisinfer_b200.weights import write_model_folder
 
-    folder = os.path.join(str(tmp_path), f"model-{seed}-{store_dtype}" + (f"-sharp{sharpen:g}" if sharpen != 1.0 else ""))
+    folder = os.path.join(str(tmp_path), f"model-{seed}-{store_dtype}" + (f"-scores{score_std:g}" if score_std else ""))
     write_model_folder(config, seed, folder, store_dtype=store_dtype, optional=optional)
-    if sharpen != 1.0:
+    if score_std:
         from safetensors.torch import load_file, save_file
 
+        factor = (score_std / (config["hidden_size"] * 0.02 ** 2)) ** 0.5
         path = os.path.join(folder, "model.safetensors")
         tensors = load_file(path)
         for name, t in tensors.items():
             if ".q_proj." in name or ".k_proj." in name:
-                tensors[name] = (t.float() * sharpen).to(t.dtype)
+                tensors[name] = (t.float() * factor).to(t.dtype)
         save_file(tensors, path)
     return folder
 

@@ -9,7 +9,7 @@ from helpers import TINY, TOL
 pytestmark = pytest.mark.gpu
 
 DTYPES = [torch.float32, torch.bfloat16]
-SHARPEN = 6.0
+SCORE_STD = 1.8
 PAGE = {"A": 4, "B": 8, "C": 16, "D": 16}
 LENGTHS = {"A": (5, 9, 17, 70), "B": (3, 11, 23, 40, 97), "C": (2, 33, 64), "D": (1, 16, 17, 95, 130)}
 
@@ -33,7 +33,7 @@ def folders(tmp_path_factory):
     root = tmp_path_factory.mktemp("models")
     # queries and keys scaled up, so that the attention weights are far from uniform and the logits show a key
     # that is rotated wrongly, missing, or read from the wrong page
-    return {name: helpers.make_folder(root, cfg, seed=11 + i, sharpen=SHARPEN) for i, (name, cfg) in enumerate(TINY.items())}
+    return {name: helpers.make_folder(root, cfg, seed=11 + i, score_std=SCORE_STD) for i, (name, cfg) in enumerate(TINY.items())}
 
 
 @pytest.fixture(scope="module")

@@ -23,7 +23,7 @@ def test_random_configuration_in_every_way_of_cutting(seed, device, tmp_path):
     page = rng.choice([4, 8, 16, 16, 32])
     lengths = [rng.randint(1, 40), rng.randint(20, 140), rng.randint(2, 70), rng.randint(60, 300), rng.randint(1, 20)]
     requests = {f"r{i}": helpers.random_ids(cfg["vocab_size"], n, seed * 10 + i) for i, n in enumerate(lengths)}
-    folder = helpers.make_folder(tmp_path, cfg, seed=seed, optional=rng.random() < 0.7, sharpen=rng.choice((1.0, 4.0, 6.0)))
+    folder = helpers.make_folder(tmp_path, cfg, seed=seed, optional=rng.random() < 0.7, score_std=rng.choice((None, 0.5, 1.0)))
     config, weights = helpers.read_folder(folder)
     want = helpers.oracle_logits(config, weights, requests)
     traces = {"whole": helpers.trace_whole(requests), "tail": helpers.trace_tail_decoded(requests),

@@ -49,7 +49,7 @@ def run_trace(folder, dtype, steps, out_dir, max_tokens, vocab):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_replay_in_every_way_of_cutting(name, dtype, device, tmp_path):
-    folder = helpers.make_folder(tmp_path, TINY[name], seed=41, sharpen=6.0)
+    folder = helpers.make_folder(tmp_path, TINY[name], seed=41, score_std=1.8)
     config, weights = helpers.read_folder(folder)
     vocab = config["vocab_size"]
     lengths = (70, 33, 101, 48, 64, 90)

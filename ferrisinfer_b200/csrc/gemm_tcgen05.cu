@@ -975,17 +975,18 @@ bool ferris_gemm_cluster_enabled() {
     return g_cluster != 0;
 }
 
-// CTA pairs are OFF unless the environment says FERRIS_GEMM_PAIR=1 or ferris_set_gemm_pair(1) was called: at the
-// sizes measured (2,048 tokens, 0.5B layer sizes) the gate / up product alone is 9 % faster with pairs (36.5 us
-// against 40.1 us), but inside the prefill step, between kernels that are launched programmatically, the step is
-// 4 % slower (4.52 ms against 4.35 ms); the products with one accumulator are slower with pairs in both settings.
-int g_pair = -1;
-bool ferris_gemm_pair_enabled() {
+// Which long-step products run on CTA pairs: FERRIS_GEMM_PAIR / ferris_set_gemm_pair = 0 none, 1 all, 2 (the
+// default) the gate / up product only.  Measured inside the prefill step of 2,048 tokens, per launch: gate / up
+// 38.4 us on pairs against 41.6 us, the products with one accumulator 20.5 us against 19.3 us (same number of
+// CTAs either way, and the pair's barriers cost more than the halved weight traffic saves).  Prefill with the
+// default against no pairs: 0.5B sizes 3.49-3.58 against 3.51-3.59 ms, 1.5B sizes 8.13-8.20 against 8.47-8.51 ms.
+int g_pair = -1;  // 0: no product on pairs, 1: every long-step product, 2: the SwiGLU product only
+bool ferris_gemm_pair_enabled(int mode) {
     if (g_pair < 0) {
         const char* v = getenv("FERRIS_GEMM_PAIR");
-        g_pair = (v && v[0] == '1') ? 1 : 0;
+        g_pair = (v && v[0] >= '0' && v[0] <= '2') ? v[0] - '0' : 2;
     }
-    return g_pair != 0;
+    return g_pair == 1 || (g_pair == 2 && mode == SWIGLU_BF16);
 }
 
 template <int MODE>
@@ -1092,9 +1093,10 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
 // scratch and counters that ferris_gemm_tcgen05_plan speaks of), 0 if through global scratch.
 FERRIS_API int ferris_gemm_uses_clusters() { return ferris_gemm_cluster_enabled() ? 1 : 0; }
 
-// Long steps on CTA pairs (cta_group::2) instead of single CTAs: 1 on, 0 off (the default).
+// Long steps on CTA pairs (cta_group::2) instead of single CTAs: 0 none, 1 every product, 2 the gate / up product
+// only (the default); any other value selects the default.
 FERRIS_API int ferris_set_gemm_pair(int on) {
-    g_pair = on ? 1 : 0;
+    g_pair = (on >= 0 && on <= 2) ? on : 2;
     return FERRIS_OK;
 }
 
@@ -1304,8 +1306,8 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
     // long steps: the persistent token-major kernel (its 16-byte stores need aligned output rows)
     const int elt = (mode == STORE_BF16 || mode == SWIGLU_BF16) ? 2 : 4;
     const bool long_step = T >= PT_BLOCK_M && !trace && !built && ((size_t)ldo * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0;
-    if (long_step && T > PT_BLOCK_M && ferris_gemm_pair_enabled()) {
-        // CTA pairs (opt-in): tiles of 256 tokens x 256 weight rows (128 + 128 in SwiGLU mode), or x 128 where the
+    if (long_step && T > PT_BLOCK_M && ferris_gemm_pair_enabled(mode)) {
+        // CTA pairs: tiles of 256 tokens x 256 weight rows (128 + 128 in SwiGLU mode), or x 128 where the
         // wider tile would leave pairs of SMs without work
         PTParams q;
         q.out = out;

@@ -249,10 +249,14 @@ def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row
     )
 
 
-def set_gemm_pairs(on: bool) -> None:
-    """Long steps (more than 128 tokens) on pairs of CTAs that share one 256-row MMA (cta_group::2) instead of
-    single CTAs.  Off by default: see the measurements beside ferris_gemm_pair_enabled in csrc/gemm_tcgen05.cu."""
-    _lib().ferris_set_gemm_pair(_c_int(1 if on else 0))
+GEMM_PAIRS_NONE, GEMM_PAIRS_ALL, GEMM_PAIRS_SWIGLU = 0, 1, 2
+
+
+def set_gemm_pairs(which=GEMM_PAIRS_SWIGLU) -> None:
+    """Which products of long steps (more than 128 tokens) run on pairs of CTAs that share one 256-row MMA
+    (cta_group::2): none, all, or the gate / up product only (the default, also of the library: see the
+    measurements beside ferris_gemm_pair_enabled in csrc/gemm_tcgen05.cu).  True / False mean all / none."""
+    _lib().ferris_set_gemm_pair(_c_int(int(which)))
 
 
 class LazyRMSNorm:

@@ -176,12 +176,13 @@ def test_gemm_on_cta_pairs(T, N, K, mode, device):
         assert ops.kernel_status() == 0
         return out
 
-    single = run()
-    ops.set_gemm_pairs(True)
+    ops.set_gemm_pairs(ops.GEMM_PAIRS_NONE)
     try:
+        single = run()
+        ops.set_gemm_pairs(ops.GEMM_PAIRS_ALL)
         paired = run()
     finally:
-        ops.set_gemm_pairs(False)
+        ops.set_gemm_pairs()  # back to the default
     assert torch.equal(paired, single), (paired.float() - single.float()).abs().max()
     ref = _gemm_reference(x, w, bias)
     if mode == 3:

@@ -756,18 +756,23 @@ struct MapCacheEntry {
 // head of the group) pairs of one kv head) and a loop over blocks of 128 keys:
 //   S = Q K^T      tcgen05.mma 128 x 128 x 64 from shared memory (Q written once by the CTA, K by TMA) into
 //                  tensor memory;
-//   softmax        four warps, one thread per row: tcgen05.ld of S, scale, causal / window mask, running
+//   softmax        eight warps, two threads per row: tcgen05.ld of S, scale, causal / window mask, running
 //                  maximum and sum in fp32 (base-2 exponentials of scores pre-multiplied by log2 e), P as
 //                  bf16 into shared memory in the layout of an MMA A operand;
 //   PV = P V       tcgen05.mma 128 x 64 x 128 with V as TMA wrote it (keys x head size: an MN-major B
 //                  operand) into a second accumulator, folded into the thread's fp32 output row
 //                  (o = (o + PV_before) * correction) one block later.
-// A TMA warp streams K and V blocks through two stages; an MMA warp issues S of the next block as soon
+// A TMA warp streams K and V blocks through a ring of stages; an MMA warp issues S of the next block as soon
 // as the softmax warps have read the current one, so the tensor core works while they exponentiate.
-// One CTA per SM: 113 KB of shared memory and 102 registers x 320 threads are each a little more than half an SM.
-// (Measured with two per SM, by giving K a single stage and capping registers at 96: batches of short prompts
-// gain 10 %, but one long prompt loses 15 %, because its time is that of the CTA of its last rows, which then
-// shares its SM.)
+// One CTA per SM (shared memory and registers are each more than half an SM).  Measured with two per SM, by giving
+// K a single stage and capping registers at 96: batches of short prompts gain 10 %, but one long prompt loses 15 %,
+// because its time is that of the CTA of its last rows, which then shares its SM.
+// Head size 64 runs two groups of softmax warps and four stages, head size 128 one group and two stages (what
+// fits in shared memory).  Per block of keys the one-group chain costs about 2,600 cycles (wait for S 260, maximum
+// and exchange 400, fold 400, exponentials and P 1,500, of which 1,024 is the special-function unit's time for
+// 16,384 exponentials); two groups take about 4,400 cycles for two blocks (the second group's wait for the tensor
+// core and the shared special-function unit keep it from halving): 2,048-token prompt 31.2 -> 29.8 us, a portion of
+// 512 at the end of 4,096 keys 53.4 -> 44.9 us, 8,192-token prompt 326 -> 281 us.
 // =============================================================================================
 // 2^x by the special-function unit (ex2.approx: about two units in the last place; -inf gives 0).
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -778,12 +783,17 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 constexpr int T5_ROWS = 128;
 constexpr int T5_KEYS = 128;
-constexpr int T5_STAGES = 2;
-constexpr int T5_SOFTMAX_WARPS = 8;  // two threads per row: warps 0-3 take keys 0-63 of a block, warps 4-7 keys 64-127
-constexpr int T5_THREADS = (T5_SOFTMAX_WARPS + 2) * 32;  // + a TMA warp and an MMA warp
+constexpr int T5_GROUP_WARPS = 8;  // softmax warps of a group, two threads per row: warps 0-3 take keys 0-63 of a block, warps 4-7 keys 64-127
+constexpr int t5_threads(int groups) { return (T5_GROUP_WARPS * groups + 2) * 32; }  // + a TMA warp and an MMA warp
 
-template <int D>
-__global__ void __launch_bounds__(T5_THREADS, 1)
+// GROUPS = 2: two groups of softmax warps work on the SAME 128 rows, group g on the key blocks g, g + 2, ...,
+// each with its own score and product accumulators in tensor memory, its own P tile and its own running
+// (maximum, sum, output row); the two are merged through shared memory at the end.  A row block's time is that
+// of its chain of key blocks (wait for S, maximum, exchange, fold, exponentials, one after the other: about
+// 1.4 us per block, of which the exponentials' share of the special-function unit is 0.54 us), and the kernel
+// lasts as long as the CTA of the prompt's last rows: two chains side by side shorten it.
+template <int D, int GROUPS, int STAGES>
+__global__ void __launch_bounds__(t5_threads(GROUPS), 1)
     prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                                  const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
                                  const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ seq_q_start,
@@ -793,14 +803,22 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
     constexpr int TILE = TILE_KEYS * 64 * 2;           // one 16-key x 64-column box of K or of V: 2 KB
     constexpr int ATOM_BYTES = T5_KEYS * 64 * 2;       // 128 rows x 64 columns: 16 KB
     constexpr int BLOCK_BYTES = ATOMS * ATOM_BYTES;    // 128 keys of K or of V
+    constexpr int P_BYTES = 32768;                     // a group's P tile: [2 halves of 64 keys][128 rows][64] bf16
+    constexpr int SW = T5_GROUP_WARPS * GROUPS;        // softmax warps; then the TMA warp and the MMA warp
+    constexpr int TMEM_COLS = GROUPS == 1 ? 256 : 512; // per group 128 columns of scores and D of the product
+    static_assert(GROUPS == 1 || GROUPS == 2, "one or two softmax groups");
+    static_assert(128 * GROUPS + D * GROUPS <= TMEM_COLS, "tensor memory");
+    static_assert(GROUPS == 1 || T5_ROWS * D * 4 <= P_BYTES, "the merge goes through a P tile");
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t kv_full[T5_STAGES], kv_empty[T5_STAGES], q_ready, s_ready, s_free, p_ready, pv_done;
+    __shared__ uint64_t kv_full[STAGES], kv_empty[STAGES], q_ready, s_ready[GROUPS], s_free[GROUPS], p_ready[GROUPS],
+        pv_done[GROUPS];
     __shared__ uint32_t tmem_base;
-    __shared__ float row_share[2][2][T5_ROWS];  // [block parity][key half][row]: what the two threads of a row tell each other
+    __shared__ float row_share[GROUPS][2][2][T5_ROWS];  // [group][block parity][key half][row]: what the two threads of a row tell each other
+    __shared__ float merge_ml[2][T5_ROWS];              // maximum and sum of the second group's rows
     uint8_t* smem = align1024(smem_raw);
-    uint8_t* q_smem = smem;                              // [column group][128 rows][64] bf16, 128-byte swizzle
-    uint8_t* p_smem = smem + BLOCK_BYTES;                // [2 halves of 64 keys][128 rows][64] bf16
-    uint8_t* kv_smem = smem + BLOCK_BYTES + 32768;       // stages x (K block, V block), each [column group][128 keys][64]
+    uint8_t* q_smem = smem;                                  // [column group][128 rows][64] bf16, 128-byte swizzle
+    uint8_t* p_smem = smem + BLOCK_BYTES;                    // per group: a P tile
+    uint8_t* kv_smem = smem + BLOCK_BYTES + GROUPS * P_BYTES;  // stages x (K block, V block), each [column group][128 keys][64]
 
     const int G = nh / nkv;
     const int seq = blockIdx.z, hk = blockIdx.y;
@@ -824,22 +842,24 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
     if (threadIdx.x == 0) {
         tma_prefetch_descriptor(&map_k);
         tma_prefetch_descriptor(&map_v);
-        for (int s = 0; s < T5_STAGES; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             mbar_init(&kv_full[s], 1);
             mbar_init(&kv_empty[s], 1);
         }
         mbar_init(&q_ready, 4);
-        mbar_init(&s_ready, 1);
-        mbar_init(&s_free, T5_SOFTMAX_WARPS);
-        mbar_init(&p_ready, T5_SOFTMAX_WARPS);
-        mbar_init(&pv_done, 1);
+        for (int g = 0; g < GROUPS; ++g) {
+            mbar_init(&s_ready[g], 1);
+            mbar_init(&s_free[g], T5_GROUP_WARPS);
+            mbar_init(&p_ready[g], T5_GROUP_WARPS);
+            mbar_init(&pv_done[g], 1);
+        }
         mbar_fence_init();
     }
-    if (warp == T5_SOFTMAX_WARPS + 1) tmem_alloc(&tmem_base, 256);
+    if (warp == SW + 1) tmem_alloc(&tmem_base, TMEM_COLS);
     tcgen05_fence_before();
     __syncthreads();
     tcgen05_fence_after();
-    const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128;  // 128 columns of scores, D of the product
+    const uint32_t tmem_s = tmem_base, tmem_pv = tmem_base + 128 * GROUPS;  // group g: scores at + 128 g, product at + D g
 
     // keys of the block: from the first key its first token may see to its last token's position
     const int tok_first = row0 / G;
@@ -848,7 +868,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
     const int lo_block = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
     const int kb_begin = lo_block / T5_KEYS, n_kb = p_last / T5_KEYS + 1 - kb_begin;
 
-    if (warp == T5_SOFTMAX_WARPS) {
+    if (warp == SW) {
         if (lane == 0) {
             constexpr int TILES = T5_KEYS / TILE_KEYS;
             const int last_tile_key = (p_last / TILE_KEYS) * TILE_KEYS;
@@ -865,9 +885,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
             };
             look_up(0, rows);
             for (int i = 0; i < n_kb; ++i) {
-                const int s = i % T5_STAGES;
+                const int s = i % STAGES;
                 if (i + 1 < n_kb) look_up(i + 1, next_rows);
-                if (i >= T5_STAGES && !mbar_wait(&kv_empty[s], ((i / T5_STAGES) - 1) & 1, status, 40)) break;
+                if (i >= STAGES && !mbar_wait(&kv_empty[s], ((i / STAGES) - 1) & 1, status, 40)) break;
                 uint8_t* ks = kv_smem + (size_t)s * 2 * BLOCK_BYTES;
                 uint8_t* vs = ks + BLOCK_BYTES;
                 mbar_expect_tx(&kv_full[s], 2 * BLOCK_BYTES);
@@ -883,15 +903,16 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
                 for (int t = 0; t < TILES; ++t) rows[t] = next_rows[t];
             }
         }
-    } else if (warp == T5_SOFTMAX_WARPS + 1) {
+    } else if (warp == SW + 1) {
         if (lane == 0) {
             const uint32_t idesc_qk = umma_idesc_bf16(T5_ROWS, T5_KEYS);
             const uint32_t idesc_pv = umma_idesc_bf16(T5_ROWS, D) | (1u << 16);  // B = V is MN-major (keys x head size)
             bool ok = mbar_wait(&q_ready, 0, status, 41);
+            // block i belongs to group i % GROUPS and is that group's block number i / GROUPS
             auto issue_qk = [&](int i) {
-                const int s = i % T5_STAGES;
-                if (!mbar_wait(&kv_full[s], (i / T5_STAGES) & 1, status, 42)) return false;
-                if (i > 0 && !mbar_wait(&s_free, (i - 1) & 1, status, 43)) return false;
+                const int s = i % STAGES, g = i % GROUPS, j = i / GROUPS;
+                if (!mbar_wait(&kv_full[s], (i / STAGES) & 1, status, 42)) return false;
+                if (j > 0 && !mbar_wait(&s_free[g], (j - 1) & 1, status, 43)) return false;
                 tcgen05_fence_after();
                 const uint32_t k_addr = smem_u32(kv_smem + (size_t)s * 2 * BLOCK_BYTES);
 #pragma unroll
@@ -899,33 +920,40 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
                     // 16 columns of Q and of K: 32 bytes along the row within the column group of 64
                     const uint64_t qd = umma_desc_k_major_sw128(smem_u32(q_smem) + (k >> 2) * ATOM_BYTES) + (uint64_t)(2 * (k & 3));
                     const uint64_t kd = umma_desc_k_major_sw128(k_addr + (k >> 2) * ATOM_BYTES) + (uint64_t)(2 * (k & 3));
-                    tcgen05_mma_bf16(tmem_s, qd, kd, idesc_qk, k > 0 ? 1u : 0u);
+                    tcgen05_mma_bf16(tmem_s + 128 * g, qd, kd, idesc_qk, k > 0 ? 1u : 0u);
                 }
-                tcgen05_commit(&s_ready);
+                tcgen05_commit(&s_ready[g]);
                 return true;
             };
-            ok = ok && issue_qk(0);
-            for (int i = 0; i < n_kb && ok; ++i) {
-                if (i + 1 < n_kb) ok = issue_qk(i + 1);
-                if (!ok || !mbar_wait(&p_ready, i & 1, status, 44)) break;
+            auto issue_pv = [&](int i) {
+                const int s = i % STAGES, g = i % GROUPS;
                 tcgen05_fence_after();
-                const int s = i % T5_STAGES;
                 // V as an MN-major operand: column groups of 64 lie ATOM_BYTES apart (the leading byte offset)
                 const uint64_t v_desc = umma_desc_mn_major_sw128(smem_u32(kv_smem + (size_t)s * 2 * BLOCK_BYTES + BLOCK_BYTES), ATOM_BYTES);
 #pragma unroll
                 for (int k = 0; k < T5_KEYS / 16; ++k) {
                     // A: 16 keys of P = 32 bytes along the row within the half of 64 keys; B: 16 rows of V = 2 KB further
-                    const uint64_t a = umma_desc_k_major_sw128(smem_u32(p_smem + (k >> 2) * 16384)) + (uint64_t)(2 * (k & 3));
-                    tcgen05_mma_bf16(tmem_pv, a, v_desc + (uint64_t)(k * (TILE >> 4)), idesc_pv, k > 0 ? 1u : 0u);
+                    const uint64_t a = umma_desc_k_major_sw128(smem_u32(p_smem + g * P_BYTES + (k >> 2) * 16384)) + (uint64_t)(2 * (k & 3));
+                    tcgen05_mma_bf16(tmem_pv + D * g, a, v_desc + (uint64_t)(k * (TILE >> 4)), idesc_pv, k > 0 ? 1u : 0u);
                 }
-                tcgen05_commit(&pv_done);
+                tcgen05_commit(&pv_done[g]);
                 tcgen05_commit(&kv_empty[s]);
+            };
+            // In block order: the scores of block i + GROUPS as soon as its group has read those of block i, then the
+            // product of block i.  (Measured for two groups: serving whichever group is ready first, by polling the
+            // barriers, is 5 % slower; a group mostly waits for the tensor core, not for its turn.)
+            for (int i = 0; i < GROUPS && i < n_kb && ok; ++i) ok = issue_qk(i);
+            for (int i = 0; i < n_kb && ok; ++i) {
+                if (i + GROUPS < n_kb) ok = issue_qk(i + GROUPS);
+                if (!ok || !mbar_wait(&p_ready[i % GROUPS], (i / GROUPS) & 1, status, 44)) break;
+                issue_pv(i);
             }
         }
     } else {
-        // softmax: two threads per row; this one takes the keys [64 kh, 64 kh + 64) of every block and the output
-        // columns [D/2 kh, D/2 kh + D/2)
-        const int wq = warp & 3, kh = warp >> 2;
+        // softmax: two threads per row; this one takes the keys [64 kh, 64 kh + 64) of its group's blocks and the
+        // output columns [D/2 kh, D/2 kh + D/2)
+        const int g = warp / T5_GROUP_WARPS, gw = warp % T5_GROUP_WARPS;
+        const int wq = gw & 3, kh = gw >> 2;  // a warp reads the TMEM lanes 32 (warp % 4) ..: T5_GROUP_WARPS is a multiple of 4
         const int r = wq * 32 + lane;
         const int R = row0 + r;
         const bool valid = R < rows_total;
@@ -933,7 +961,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
         const int pos = start_pos + tok;
         const int hi = valid ? pos : -1;
         const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-        if (kh == 0) {
+        if (g == 0 && kh == 0) {
             const uint4* src = reinterpret_cast<const uint4*>(q + (size_t)(q_start + tok) * ldq + (size_t)head * D);
 #pragma unroll
             for (int c = 0; c < D / 8; ++c)
@@ -944,63 +972,92 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
             if (lane == 0) mbar_arrive(&q_ready);
         }
         const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+        const uint32_t my_s = tmem_s + 128 * g + lane_addr + 64 * kh;
+        const uint32_t my_pv = tmem_pv + D * g + lane_addr + (D / 2) * kh;
         const float scale2 = scale * 1.4426950408889634f;  // scores in units of log 2
         float m = -INFINITY, l = 0.0f;
         float o[D / 2];
 #pragma unroll
         for (int j = 0; j < D / 2; ++j) o[j] = 0.0f;
-        bool ok = true;
+        const int n_own = n_kb > g ? (n_kb - g + GROUPS - 1) / GROUPS : 0;  // this group's key blocks: g, g + GROUPS, ...
         // timeline build: where the first thread of the heaviest CTA spends its cycles
         const bool tl_probe = threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
         long long t_wait_s = 0, t_max = 0, t_fold = 0, t_exp = 0, c0 = FERRIS_TL_CLOCK(), c1;
-        for (int i = 0; i < n_kb && ok; ++i) {
-            if (!mbar_wait(&s_ready, i & 1, status, 45)) break;
+        for (int j = 0; j < n_own; ++j) {
+            const int i = j * GROUPS + g;
+            if (!mbar_wait(&s_ready[g], j & 1, status, 45)) break;
             tcgen05_fence_after();
             c1 = FERRIS_TL_CLOCK();
             t_wait_s += c1 - c0;
             c0 = c1;
             const int key_base = (kb_begin + i) * T5_KEYS + 64 * kh;
             const bool interior = key_base >= lo && key_base + 63 <= hi;
-            // this thread's 64 scores of the block, read once; then the next block's scores may overwrite them
-            uint32_t sv[64];
-            tmem_load_32x64(tmem_s + lane_addr + 64 * kh, sv);
-            tmem_load_wait();
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&s_free);
+            // One group: this thread's 64 scores are read once and kept, so that the next block's scores may overwrite
+            // them while the exponentials are taken.  Two groups (18 warps leave a thread 96 registers): the scores
+            // stay in tensor memory, read in chunks for the maximum and again for the exponentials; the other group
+            // keeps the tensor core busy meanwhile.
+            constexpr int KEEP = GROUPS == 1 ? 64 : 1;
+            uint32_t sv[KEEP];
             float mx = -INFINITY;
-            if (interior) {
+            if constexpr (GROUPS == 1) {
+                tmem_load_32x64(my_s, reinterpret_cast<uint32_t (&)[64]>(sv));
+                tmem_load_wait();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_free[g]);
+                if (interior) {
 #pragma unroll
-                for (int j = 0; j < 64; ++j) mx = fmaxf(mx, __uint_as_float(sv[j]));
+                    for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sv[c % KEEP]));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 64; ++c) {
+                        const int key = key_base + c;
+                        mx = fmaxf(mx, (key <= hi && key >= lo) ? __uint_as_float(sv[c % KEEP]) : -INFINITY);
+                    }
+                }
             } else {
 #pragma unroll
-                for (int j = 0; j < 64; ++j) {
-                    const int key = key_base + j;
-                    mx = fmaxf(mx, (key <= hi && key >= lo) ? __uint_as_float(sv[j]) : -INFINITY);
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t sc[32];
+                    tmem_load_32x32(my_s + 32 * h, sc);
+                    tmem_load_wait();
+                    if (interior) {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(sc[c]));
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) {
+                            const int key = key_base + 32 * h + c;
+                            mx = fmaxf(mx, (key <= hi && key >= lo) ? __uint_as_float(sc[c]) : -INFINITY);
+                        }
+                    }
                 }
             }
             mx *= scale2;  // the scale is positive: the maximum of the scaled scores
             // the row's maximum over both halves of the block
-            row_share[i & 1][kh][r] = mx;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            mx = fmaxf(mx, row_share[i & 1][kh ^ 1][r]);
+            row_share[g][j & 1][kh][r] = mx;
+            if (g == 0)
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+            else
+                asm volatile("bar.sync 2, 256;" ::: "memory");
+            mx = fmaxf(mx, row_share[g][j & 1][kh ^ 1][r]);
             c1 = FERRIS_TL_CLOCK();
             t_max += c1 - c0;
             c0 = c1;
             const float m_new = fmaxf(m, mx);
             const float base = m_new == -INFINITY ? 0.0f : m_new;
             const float corr = m == -INFINITY ? 0.0f : fast_exp2(m - base);
-            if (i > 0) {
-                // the product of the block before (relative to its maximum m) joins the row before the row is rescaled
-                if (!mbar_wait(&pv_done, (i - 1) & 1, status, 46)) break;
+            if (j > 0) {
+                // the product of the group's block before (relative to its maximum m) joins the row before the row is rescaled
+                if (!mbar_wait(&pv_done[g], (j - 1) & 1, status, 46)) break;
                 tcgen05_fence_after();
 #pragma unroll
                 for (int c = 0; c < D / 64; ++c) {
                     uint32_t pv[32];
-                    tmem_load_32x32(tmem_pv + lane_addr + (D / 2) * kh + 32 * c, pv);
+                    tmem_load_32x32(my_pv + 32 * c, pv);
                     tmem_load_wait();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) o[32 * c + j] = (o[32 * c + j] + __uint_as_float(pv[j])) * corr;
+                    for (int e = 0; e < 32; ++e) o[32 * c + e] = (o[32 * c + e] + __uint_as_float(pv[e])) * corr;
                 }
             }
             l *= corr;
@@ -1008,39 +1065,53 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
             t_fold += c1 - c0;
             c0 = c1;
             {
-                uint32_t packed[32];
                 float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // four partial sums: the additions do not wait for one another
-                if (interior) {
+                uint8_t* half = p_smem + g * P_BYTES + kh * 16384;
 #pragma unroll
-                    for (int j = 0; j < 64; j += 2) {
-                        const float p0 = fast_exp2(fmaf(__uint_as_float(sv[j]), scale2, -base));
-                        const float p1 = fast_exp2(fmaf(__uint_as_float(sv[j + 1]), scale2, -base));
-                        sum4[(j >> 1) & 3] += p0 + p1;
-                        packed[j >> 1] = pack_bf16(p0, p1);
-                    }
-                } else {
+                for (int h = 0; h < 4; ++h) {  // 16 keys at a time
+                    uint32_t sc[16], packed[8];
+                    if constexpr (GROUPS == 1) {
 #pragma unroll
-                    for (int j = 0; j < 64; j += 2) {
-                        const int key = key_base + j;
-                        const float e0 = fast_exp2(fmaf(__uint_as_float(sv[j]), scale2, -base));
-                        const float e1 = fast_exp2(fmaf(__uint_as_float(sv[j + 1]), scale2, -base));
-                        const float p0 = (key <= hi && key >= lo) ? e0 : 0.0f;
-                        const float p1 = (key + 1 <= hi && key + 1 >= lo) ? e1 : 0.0f;
-                        sum4[(j >> 1) & 3] += p0 + p1;
-                        packed[j >> 1] = pack_bf16(p0, p1);
+                        for (int c = 0; c < 16; ++c) sc[c] = sv[(16 * h + c) % KEEP];
+                    } else {
+                        tmem_load_32x16(my_s + 16 * h, sc);
+                        tmem_load_wait();
                     }
+                    if (interior) {
+#pragma unroll
+                        for (int c = 0; c < 16; c += 2) {
+                            const float p0 = fast_exp2(fmaf(__uint_as_float(sc[c]), scale2, -base));
+                            const float p1 = fast_exp2(fmaf(__uint_as_float(sc[c + 1]), scale2, -base));
+                            sum4[(c >> 1) & 3] += p0 + p1;
+                            packed[c >> 1] = pack_bf16(p0, p1);
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 16; c += 2) {
+                            const int key = key_base + 16 * h + c;
+                            const float e0 = fast_exp2(fmaf(__uint_as_float(sc[c]), scale2, -base));
+                            const float e1 = fast_exp2(fmaf(__uint_as_float(sc[c + 1]), scale2, -base));
+                            const float p0 = (key <= hi && key >= lo) ? e0 : 0.0f;
+                            const float p1 = (key + 1 <= hi && key + 1 >= lo) ? e1 : 0.0f;
+                            sum4[(c >> 1) & 3] += p0 + p1;
+                            packed[c >> 1] = pack_bf16(p0, p1);
+                        }
+                    }
+                    *reinterpret_cast<uint4*>(half + swizzle128(r, 2 * h)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    *reinterpret_cast<uint4*>(half + swizzle128(r, 2 * h + 1)) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
                 }
                 l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-                uint8_t* half = p_smem + kh * 16384;
-#pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    *reinterpret_cast<uint4*>(half + swizzle128(r, u)) =
-                        make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
+            }
+            if constexpr (GROUPS == 2) {
+                // the scores have been read for the last time: the group's next block may overwrite them
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s_free[g]);
             }
             m = m_new;
             fence_proxy_async();  // the MMA reads P through the async proxy
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_ready);
+            if (lane == 0) mbar_arrive(&p_ready[g]);
             c1 = FERRIS_TL_CLOCK();
             t_exp += c1 - c0;
             c0 = c1;
@@ -1049,37 +1120,68 @@ __global__ void __launch_bounds__(T5_THREADS, 1)
         FERRIS_TL_VALUE(tl_probe, 1, (unsigned long long)t_max);
         FERRIS_TL_VALUE(tl_probe, 2, (unsigned long long)t_fold);
         FERRIS_TL_VALUE(tl_probe, 3, (unsigned long long)t_exp);
-        FERRIS_TL_VALUE(tl_probe, 4, (unsigned long long)n_kb);
+        FERRIS_TL_VALUE(tl_probe, 4, (unsigned long long)n_own);
         // the row's sum over both halves of the keys
-        row_share[n_kb & 1][kh][r] = l;
-        asm volatile("bar.sync 1, 256;" ::: "memory");
-        l += row_share[n_kb & 1][kh ^ 1][r];
-        if (n_kb > 0 && mbar_wait(&pv_done, (n_kb - 1) & 1, status, 47)) {
-            tcgen05_fence_after();
+        row_share[g][n_own & 1][kh][r] = l;
+        if (g == 0)
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+        else
+            asm volatile("bar.sync 2, 256;" ::: "memory");
+        l += row_share[g][n_own & 1][kh ^ 1][r];
+        // the group's last product joins the row (still relative to m, not yet divided by the sum)
+        bool done = true;
+        if (n_own > 0) {
+            done = mbar_wait(&pv_done[g], (n_own - 1) & 1, status, 47);
+            if (done) {
+                tcgen05_fence_after();
+#pragma unroll
+                for (int c = 0; c < D / 64; ++c) {
+                    uint32_t pv[32];
+                    tmem_load_32x32(my_pv + 32 * c, pv);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) o[32 * c + e] += __uint_as_float(pv[e]);
+                }
+            }
+        }
+        if constexpr (GROUPS == 2) {
+            // the second group hands its rows over through its own P tile (its last product has been read out of
+            // it): [output column][row] fp32, so that a warp's 32 rows are 32 consecutive words
+            float* merge_o = reinterpret_cast<float*>(p_smem + P_BYTES);
+            if (g == 1) {
+#pragma unroll
+                for (int c = 0; c < D / 2; ++c) merge_o[((D / 2) * kh + c) * T5_ROWS + r] = o[c];
+                if (kh == 0) {
+                    merge_ml[0][r] = m;
+                    merge_ml[1][r] = l;
+                }
+            }
+            asm volatile("bar.sync 3, 512;" ::: "memory");
+            if (g == 0) {
+                const float m1 = merge_ml[0][r], l1 = merge_ml[1][r];
+                const float mm = fmaxf(m, m1);
+                const float a0 = m == -INFINITY ? 0.0f : fast_exp2(m - mm);
+                const float a1 = m1 == -INFINITY ? 0.0f : fast_exp2(m1 - mm);
+                l = l * a0 + l1 * a1;
+#pragma unroll
+                for (int c = 0; c < D / 2; ++c) o[c] = o[c] * a0 + merge_o[((D / 2) * kh + c) * T5_ROWS + r] * a1;
+            }
+        }
+        if (g == 0 && done && n_kb > 0 && valid) {
             uint32_t packed[D / 4];
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
 #pragma unroll
-            for (int c = 0; c < D / 64; ++c) {
-                uint32_t pv[32];
-                tmem_load_32x32(tmem_pv + lane_addr + (D / 2) * kh + 32 * c, pv);
-                tmem_load_wait();
+            for (int c = 0; c < D / 2; c += 2) packed[c >> 1] = pack_bf16(o[c] * inv, o[c + 1] * inv);
+            uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(q_start + tok) * ldo + (size_t)head * D + (D / 2) * kh);
 #pragma unroll
-                for (int j = 0; j < 32; j += 2)
-                    packed[(32 * c + j) >> 1] = pack_bf16((o[32 * c + j] + __uint_as_float(pv[j])) * inv,
-                                                          (o[32 * c + j + 1] + __uint_as_float(pv[j + 1])) * inv);
-            }
-            if (valid) {
-                uint4* dst = reinterpret_cast<uint4*>(out + (size_t)(q_start + tok) * ldo + (size_t)head * D + (D / 2) * kh);
-#pragma unroll
-                for (int u = 0; u < D / 16; ++u) dst[u] = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
-            }
+            for (int u = 0; u < D / 16; ++u) dst[u] = make_uint4(packed[4 * u], packed[4 * u + 1], packed[4 * u + 2], packed[4 * u + 3]);
         }
     }
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == T5_SOFTMAX_WARPS + 1) {
+    if (warp == SW + 1) {
         tcgen05_fence_after();
-        tmem_dealloc(tmem_base, 256);
+        tmem_dealloc(tmem_base, TMEM_COLS);
     }
     FERRIS_TL_END(8);
 }
@@ -1113,12 +1215,13 @@ int check_common(int nh, int nkv, int d, int page_size, int max_blocks) {
     return FERRIS_OK;
 }
 
-// Prefill runs the tcgen05 kernel unless the environment says FERRIS_ATTN_TCGEN05=0 (then the mma.sync kernel).
+// Prefill runs the tcgen05 kernel unless the environment says FERRIS_ATTN_TCGEN05=0 (then the mma.sync kernel);
+// FERRIS_ATTN_TCGEN05=2: the tcgen05 kernel with one softmax group at every head size.
 int g_prefill_tc5 = -1;
 bool prefill_on_tcgen05() {
     if (g_prefill_tc5 < 0) {
         const char* v = getenv("FERRIS_ATTN_TCGEN05");
-        g_prefill_tc5 = (v && v[0] == '0') ? 0 : 1;
+        g_prefill_tc5 = (v && (v[0] == '0' || v[0] == '2')) ? v[0] - '0' : 1;
     }
     return g_prefill_tc5 != 0;
 }
@@ -1234,9 +1337,10 @@ FERRIS_API int ferris_decode_merge(const float* scratch, void* out, int ldo, int
     FERRIS_LAUNCH_CHECK();
 }
 
-// Which prefill kernel runs: 1 the tcgen05 kernel (the default), 0 the mma.sync kernel.
+// Which prefill kernel runs: 1 the tcgen05 kernel (the default), 0 the mma.sync kernel, 2 the tcgen05 kernel with
+// one softmax group at every head size.
 FERRIS_API int ferris_set_prefill_tcgen05(int on) {
-    g_prefill_tc5 = on ? 1 : 0;
+    g_prefill_tc5 = (on >= 0 && on <= 2) ? on : 1;
     return FERRIS_OK;
 }
 
@@ -1260,19 +1364,26 @@ FERRIS_API int ferris_prefill_attention(const void* q, int ldq, void* out, int l
     int* status = ferris_status_ptr();
     if (prefill_on_tcgen05()) {
         dim3 grid5(((size_t)max_q_len * G + T5_ROWS - 1) / T5_ROWS, nkv, num_seqs);
-        // Q, P, stages of (K block, V block)
-        const size_t smem = (size_t)T5_ROWS * d * 2 + 32768 + (size_t)T5_STAGES * 2 * T5_KEYS * d * 2 + 1024;
-        if (d == 64) {
-            if ((rc = set_smem(prefill_attention_tc5_kernel<64>, smem)) != FERRIS_OK) return rc;
-            ferris_launch(prefill_attention_tc5_kernel<64>, grid5, dim3(T5_THREADS), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out,
-                          ldo, block_tables, max_blocks, seq_q_start, seq_start_pos, nh, nkv, page_size, window, scale,
-                          skip_single, status);
-        } else {
-            if ((rc = set_smem(prefill_attention_tc5_kernel<128>, smem)) != FERRIS_OK) return rc;
-            ferris_launch(prefill_attention_tc5_kernel<128>, grid5, dim3(T5_THREADS), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out,
-                          ldo, block_tables, max_blocks, seq_q_start, seq_start_pos, nh, nkv, page_size, window, scale,
-                          skip_single, status);
-        }
+        // Q, a P tile per softmax group, stages of (K block, V block).  Head size 64: two groups and four stages
+        // (209 KB); head size 128: one group and two stages (193 KB), two groups would not fit.
+        auto bytes = [&](int groups, int stages) {
+            return (size_t)T5_ROWS * d * 2 + (size_t)groups * 32768 + (size_t)stages * 2 * T5_KEYS * d * 2 + 1024;
+        };
+#define FERRIS_T5_LAUNCH(DD, GG, SS)                                                                                       \
+    do {                                                                                                                   \
+        const size_t smem = bytes(GG, SS);                                                                                 \
+        if ((rc = set_smem(prefill_attention_tc5_kernel<DD, GG, SS>, smem)) != FERRIS_OK) return rc;                       \
+        ferris_launch(prefill_attention_tc5_kernel<DD, GG, SS>, grid5, dim3(t5_threads(GG)), smem, s, mk, mv, (const bf16*)q, \
+                      ldq, (bf16*)out, ldo, block_tables, max_blocks, seq_q_start, seq_start_pos, nh, nkv, page_size,      \
+                      window, scale, skip_single, status);                                                                 \
+    } while (0)
+        if (d == 64 && g_prefill_tc5 != 2)
+            FERRIS_T5_LAUNCH(64, 2, 4);
+        else if (d == 64)
+            FERRIS_T5_LAUNCH(64, 1, 4);
+        else
+            FERRIS_T5_LAUNCH(128, 1, 2);
+#undef FERRIS_T5_LAUNCH
         FERRIS_LAUNCH_CHECK();
     }
     dim3 grid(((size_t)max_q_len * G + PF_ROWS - 1) / PF_ROWS, nkv, num_seqs);

@@ -617,9 +617,10 @@ def prefill_attention(qkv, out, k_cache, v_cache, block_tables, seq_q_start, seq
     )
 
 
-def set_prefill_tcgen05(on: bool) -> None:
-    """Portions of prompts on the tcgen05 attention kernel (the default) or on the mma.sync kernel it replaced."""
-    _lib().ferris_set_prefill_tcgen05(_c_int(1 if on else 0))
+def set_prefill_tcgen05(on=True) -> None:
+    """Portions of prompts on the tcgen05 attention kernel (True / 1, the default), on the mma.sync kernel it
+    replaced (False / 0), or on the tcgen05 kernel with one softmax group at every head size (2)."""
+    _lib().ferris_set_prefill_tcgen05(_c_int(int(on)))
 
 
 def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_heads, head_dim, inv_freq, rotary_dim,

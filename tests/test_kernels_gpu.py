@@ -599,24 +599,27 @@ def test_attention_step_of_single_tokens_rotates_and_writes_on_its_way(nh, nkv, 
 
 @pytest.mark.parametrize("nh, nkv, d, window", [(14, 2, 64, 0), (12, 2, 128, 0), (8, 8, 64, 100), (3, 1, 128, 0)])
 def test_prefill_attention_on_tcgen05_and_on_mma_sync(nh, nkv, d, window, device):
-    """The two prefill kernels (scores and products in tensor memory by tcgen05.mma; mma.sync fragments in registers)
-    against the plain attention and against each other: whole prompts past several blocks of 128 keys, a portion at
-    the end of a long context, rows that end inside a block of 128, a single token beside them."""
+    """The prefill kernels (scores and products in tensor memory by tcgen05.mma, with two groups of softmax warps on
+    alternate blocks of keys where they fit and with one; mma.sync fragments in registers) against the plain
+    attention and against each other: whole prompts past several blocks of 128 keys, a portion at the end of a long
+    context, rows that end inside a block of 128, prompts of one and of two blocks (the second group has no block
+    or one), a single token beside them."""
     from ferrisinfer_b200.kernels import ops
 
-    seqs = [(700, 700), (1500, 130), (129, 129), (4, 4), (300, 1), (128, 128)]
+    seqs = [(700, 700), (1500, 130), (129, 129), (4, 4), (300, 1), (128, 128), (256, 256)]
     case = AttentionCase(device, BF16, nh, nkv, d, 16, seqs, seed=nh + d, window=window)
     want = case.reference()
     got = {}
     try:
-        for on in (True, False):
-            ops.set_prefill_tcgen05(on)
-            got[on] = run_attention(case, "dispatch")
+        for mode in (1, 0, 2):
+            ops.set_prefill_tcgen05(mode)
+            got[mode] = run_attention(case, "dispatch")
     finally:
         ops.set_prefill_tcgen05(True)
-    for on in (True, False):
-        assert torch.allclose(got[on], want, **ATT_TOL[BF16]), (on, (got[on] - want).abs().max())
-    assert (got[True] - got[False]).abs().max() <= 2 * ATT_TOL[BF16]["atol"]
+    for mode in (1, 0, 2):
+        assert torch.allclose(got[mode], want, **ATT_TOL[BF16]), (mode, (got[mode] - want).abs().max())
+    assert (got[1] - got[0]).abs().max() <= 2 * ATT_TOL[BF16]["atol"]
+    assert (got[1] - got[2]).abs().max() <= 2 * ATT_TOL[BF16]["atol"]
 
 
 @pytest.mark.parametrize("impl", ["simt", "dispatch"])

@@ -773,6 +773,8 @@ struct MapCacheEntry {
 // 16,384 exponentials); two groups take about 4,400 cycles for two blocks (the second group's wait for the tensor
 // core and the shared special-function unit keep it from halving): 2,048-token prompt 31.2 -> 29.8 us, a portion of
 // 512 at the end of 4,096 keys 53.4 -> 44.9 us, 8,192-token prompt 326 -> 281 us.
+// Measured and not kept: a ring of K blocks apart from a ring of V blocks, so that a K stage is free as soon as
+// its scores are done (8,192-token prompt 281 -> 322 us at head size 64, 2,048 tokens at head size 128 43.7 -> 46.9 us).
 // =============================================================================================
 // 2^x by the special-function unit (ex2.approx: about two units in the last place; -inf gives 0).
 __device__ __forceinline__ float fast_exp2(float x) {

@@ -21,10 +21,15 @@ Here ONE manager serves all requests:
 * Mixers with a ``FixedState`` need, and the engine itself (sampler state), get a tensor
   ``[slots, *shape]``; a request holds one slot id from admission to release, and the slot's rows
   are zeroed at admission.
+* With prefix sharing, full pages of prompts are found by later requests through a chain hash and
+  shared, not copied.  With ``keep_finished`` the index holds a reference of its own, so the pages of
+  a prompt outlive the request that computed them; they count as free, and the least recently used
+  of them are given up (ends of chains first) when a request needs pages that the free list lacks.
 """
 
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Any, Optional
 
@@ -88,12 +93,23 @@ class PrefixIndex:
             return None
         return entry[0]
 
-    def insert(self, key, prev, tokens, pages: tuple) -> None:
+    def insert(self, key, prev, tokens, pages: tuple) -> bool:
+        """True if the block is new to the index."""
         if key in self.blocks:
-            return
+            return False
         self.blocks[key] = (pages, prev, tuple(tokens))
         for gid, page in enumerate(pages):
             self.by_page[(gid, page)] = key
+        return True
+
+    def remove(self, key):
+        """Forget the block; returns its pages (or None)."""
+        entry = self.blocks.pop(key, None)
+        if entry is None:
+            return None
+        for gid, page in enumerate(entry[0]):
+            self.by_page.pop((gid, page), None)
+        return entry[0]
 
     def forget_page(self, gid: int, page: int) -> None:
         key = self.by_page.pop((gid, page), None)
@@ -107,10 +123,12 @@ class PrefixIndex:
 class CacheManager:
     def __init__(self, needs: list, page_size: int, num_pages, max_requests: int,
                  dtype: torch.dtype = torch.float32, device=None, extra_states: Optional[dict] = None,
-                 prefix_sharing: bool = False, min_prefix_share_tokens: int = 0):
+                 prefix_sharing: bool = False, min_prefix_share_tokens: int = 0, keep_finished: bool = False):
         """``needs[i]``: the cache need of run-order entry i (PagedKV, FixedState or None).
         ``num_pages``: pages per group (an int for all groups, or a dict gid -> int).
-        ``device`` None: bookkeeping only (no tensors), as the CPU tests use it."""
+        ``device`` None: bookkeeping only (no tensors), as the CPU tests use it.
+        ``keep_finished`` (with prefix sharing): shareable pages stay in the cache after their last
+        holder has gone, until their room is needed."""
         if page_size <= 0:
             raise CacheError(f"page size must be positive, not {page_size}")
         if max_requests <= 0:
@@ -156,7 +174,11 @@ class CacheManager:
             isinstance(n, FixedState) for n in needs)
         self.prefix = PrefixIndex() if (prefix_sharing and shareable) else None
         self.min_prefix_share_tokens = int(min_prefix_share_tokens)
-        self.stats = {"shared_tokens": 0, "shared_pages": 0}
+        self.keep_finished = bool(keep_finished) and self.prefix is not None
+        # blocks of the index that no request holds (the index's own reference keeps their pages), least
+        # recently used first; a block's descendants in a chain always come before it
+        self._idle: OrderedDict = OrderedDict()
+        self.stats = {"shared_tokens": 0, "shared_pages": 0, "revived_pages": 0, "evicted_pages": 0}
 
     # ------------------------------------------------------------------ requests
     def has(self, request_id) -> bool:
@@ -196,6 +218,9 @@ class CacheManager:
                         g.pool.retain(page)
                         rc.tables[g.gid].append(page)
                     rc.block_keys.append(key)
+                    if key in self._idle:  # pages that had outlived their last holder
+                        del self._idle[key]
+                        self.stats["revived_pages"] += len(self.groups)
                 rc.registered_blocks = len(found)
                 rc.num_tokens = rc.shared_tokens = len(found) * ps
                 self.stats["shared_tokens"] += rc.shared_tokens
@@ -234,13 +259,39 @@ class CacheManager:
         return out
 
     def free_pages(self) -> dict:
-        return {g.gid: g.pool.num_free for g in self.groups}
+        """gid -> pages that a request can get: the free list and the pages that only the prefix index holds."""
+        return {g.gid: g.pool.num_free + len(self._idle) for g in self.groups}
+
+    @property
+    def num_idle_blocks(self) -> int:
+        """Blocks of finished prompts that are kept for later requests (one page per group each)."""
+        return len(self._idle)
 
     def can_extend(self, request_id, new_total: int, reserve: Optional[dict] = None) -> bool:
         """Whether the pools can cover ``new_total`` tokens of the request, leaving ``reserve``
         (gid -> pages) for others."""
         need = self.pages_needed(request_id, new_total)
-        return all(need[g.gid] + (reserve or {}).get(g.gid, 0) <= g.pool.num_free for g in self.groups)
+        free = self.free_pages()
+        return all(need[g.gid] + (reserve or {}).get(g.gid, 0) <= free[g.gid] for g in self.groups)
+
+    def _evict_idle(self, count: int) -> int:
+        """Give up to ``count`` idle blocks' pages back to the free lists, least recently used first."""
+        done = 0
+        while done < count and self._idle:
+            key, _ = self._idle.popitem(last=False)
+            pages = self.prefix.remove(key)
+            if pages is None:
+                continue
+            for g, page in zip(self.groups, pages):
+                if not g.pool.release(page):
+                    raise CacheError(f"idle page {page} of group {g.gid} still had a holder")
+            self.stats["evicted_pages"] += len(self.groups)
+            done += 1
+        return done
+
+    def drop_idle(self) -> int:
+        """Forget every kept prompt page that no request holds; returns the blocks dropped."""
+        return self._evict_idle(len(self._idle))
 
     def extend(self, request_id, new_total: int) -> None:
         """Make every position below ``new_total`` that the next step can read or write addressable.
@@ -249,12 +300,16 @@ class CacheManager:
         if new_total < rc.num_tokens:
             raise CacheError(f"request {request_id!r} holds {rc.num_tokens} tokens; cannot extend to {new_total}")
         need = self.pages_needed(request_id, new_total)
+        free = self.free_pages()
         for g in self.groups:
-            if need[g.gid] > g.pool.num_free:
+            if need[g.gid] > free[g.gid]:
                 raise OutOfPages(
                     f"request {request_id!r} needs {need[g.gid]} more pages in group {g.gid} "
-                    f"({g.pool.num_free} of {g.pool.num_pages} free)"
+                    f"({free[g.gid]} of {g.pool.num_pages} free)"
                 )
+        short = max(need[g.gid] - g.pool.num_free for g in self.groups) if self.groups else 0
+        if short > 0:
+            self._evict_idle(short)
         blocks = -(-new_total // self.page_size)
         for g in self.groups:
             table = rc.tables[g.gid]
@@ -285,7 +340,10 @@ class CacheManager:
                 tokens = rc.prompt[b * ps:(b + 1) * ps]
                 key = PrefixIndex.chain(prev, tokens)
                 rc.block_keys.append(key)
-                self.prefix.insert(key, prev, tokens, tuple(rc.tables[g.gid][b] for g in self.groups))
+                pages = tuple(rc.tables[g.gid][b] for g in self.groups)
+                if self.prefix.insert(key, prev, tokens, pages) and self.keep_finished:
+                    for g, page in zip(self.groups, pages):
+                        g.pool.retain(page)  # the index's own reference
                 rc.registered_blocks += 1
         freed = 0
         for g in self.groups:
@@ -315,6 +373,14 @@ class CacheManager:
                     freed += 1
                     if self.prefix is not None:
                         self.prefix.forget_page(g.gid, page)
+        if self.keep_finished:
+            # blocks that only the index holds now wait for a later request or for their room to be needed;
+            # the end of the chain first, so that it is given up before what leads to it
+            for key in reversed(rc.block_keys):
+                entry = self.prefix.blocks.get(key)
+                if entry is not None and all(g.pool.refcount(p) == 1 for g, p in zip(self.groups, entry[0])):
+                    self._idle.pop(key, None)
+                    self._idle[key] = None
         self._free_slots.append(rc.slot)
         return freed
 
@@ -354,7 +420,14 @@ class CacheManager:
                 for page in rc.tables[g.gid]:
                     if page != NO_PAGE:
                         holders[page] = holders.get(page, 0) + 1
+            if self.keep_finished:
+                for entry in self.prefix.blocks.values():
+                    holders[entry[0][g.gid]] = holders.get(entry[0][g.gid], 0) + 1
             g.pool.check(holders)
+        for key in self._idle:
+            entry = self.prefix.blocks.get(key)
+            if entry is None or any(g.pool.refcount(p) != 1 for g, p in zip(self.groups, entry[0])):
+                raise CacheError("a block is listed as idle but is held by a request or gone from the index")
         if self.prefix is not None:
             for key, entry in self.prefix.blocks.items():
                 for g, page in zip(self.groups, entry[0]):

@@ -74,14 +74,16 @@ class Engine:
     def __init__(self, model=None, *, config=None, seed: int = 0, dtype="bfloat16", device=None,
                  page_size: int = 16, num_pages: Optional[int] = None, gpu_memory_fraction: float = 0.5,
                  scheduler: Optional[SchedulerConfig] = None, init_device="cpu", prefix_sharing: bool = True,
-                 run_ahead: bool = True):
+                 run_ahead: bool = True, keep_finished_prefixes: bool = True):
         """``model``: a model folder (config.json + safetensors).  Or ``config`` (a folder, dict or
         typed configuration) with ``seed``: random weights, no folder needed.
         ``num_pages``: pages per page group; by default what ``gpu_memory_fraction`` of the free device
         memory holds.  ``init_device``: where random weights are drawn ("cpu": the values a model folder
         written with the same seed holds; a CUDA device: other values, much faster for large models).
         ``prefix_sharing``: requests whose prompts begin with the same full pages as a live request's share
-        those pages instead of recomputing them (where every layer keeps all keys).
+        those pages instead of recomputing them (where every layer keeps all keys).  ``keep_finished_prefixes``:
+        such pages stay in the cache after the last request that held them has ended (or was preempted), for
+        later requests with the same beginning, until a request needs their room.
         ``run_ahead``: queue the next decode step while the GPU still runs the current one (see ``step``)."""
         ops.require_device()
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
@@ -102,7 +104,8 @@ class Engine:
         self.runner = ModelRunner(self.model, self.dtype, self.device, page_size=page_size, num_pages=num_pages,
                                   max_requests=sc.max_batch_size, max_model_len=sc.max_sequence_length,
                                   extra_states={RNG_STATE: RNG_NEED}, prefix_sharing=prefix_sharing,
-                                  min_prefix_share_tokens=sc.min_prefix_share_tokens)
+                                  min_prefix_share_tokens=sc.min_prefix_share_tokens,
+                                  keep_finished=keep_finished_prefixes)
         self.sampler = Sampler(self.runner.cache.state_tensors[RNG_STATE])
         self.scheduler = Scheduler(sc, self.runner.cache, on_admit=self._on_admit, on_preempt=self._on_preempt)
         self._next_id = 0

@@ -77,7 +77,8 @@ class ModelRunner:
 
     def __init__(self, model: DecoderModel, dtype: torch.dtype, device, page_size: int, num_pages: int,
                  max_requests: int, max_model_len: Optional[int] = None, extra_states: Optional[dict] = None,
-                 cuda_graphs: bool = True, prefix_sharing: bool = False, min_prefix_share_tokens: int = 0):
+                 cuda_graphs: bool = True, prefix_sharing: bool = False, min_prefix_share_tokens: int = 0,
+                 keep_finished: bool = False):
         if not model.bound:
             raise FerrisError("the model has no weights bound")
         self.model = model
@@ -87,7 +88,7 @@ class ModelRunner:
         self.max_model_len = int(max_model_len or model.plan.max_positions)
         self.cache = CacheManager(model.cache_needs(), page_size, num_pages, max_requests, dtype=dtype,
                                   device=self.device, extra_states=extra_states, prefix_sharing=prefix_sharing,
-                                  min_prefix_share_tokens=min_prefix_share_tokens)
+                                  min_prefix_share_tokens=min_prefix_share_tokens, keep_finished=keep_finished)
         self.workspace = Workspace(self.device)
         self.steps_run = 0
         self.last_h2d_bytes = 0
@@ -276,10 +277,11 @@ class ModelRunner:
                         f"request {e.request_id!r} would reach {total} tokens; the limit is {self.max_model_len}")
                 for gid, n in cache.pages_needed(e.request_id, total).items():
                     short[gid] += n
+            free = cache.free_pages()
             for g in cache.groups:
-                if short[g.gid] > g.pool.num_free:
+                if short[g.gid] > free[g.gid]:
                     raise OutOfPages(f"the step needs {short[g.gid]} new pages in group {g.gid}; "
-                                     f"{g.pool.num_free} of {g.pool.num_pages} are free")
+                                     f"{free[g.gid]} of {g.pool.num_pages} are free")
         except FerrisError:
             for rid in admitted_here:
                 cache.release(rid)

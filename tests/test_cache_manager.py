@@ -233,10 +233,11 @@ def test_sharing_is_off_where_a_page_does_not_mean_the_same_for_every_layer():
     assert CacheManager([FULL], 4, 8, 2, prefix_sharing=True).prefix is not None
 
 
+@pytest.mark.parametrize("keep", [False, True])
 @pytest.mark.parametrize("seed", range(8))
-def test_random_orders_with_shared_prefixes(seed):
+def test_random_orders_with_shared_prefixes(seed, keep):
     rng = random.Random(seed)
-    m = CacheManager([FULL, FULL], 4, 48, max_requests=5, prefix_sharing=True)
+    m = CacheManager([FULL, FULL], 4, 48 if not keep else 14, max_requests=5, prefix_sharing=True, keep_finished=keep)
     stems = [[rng.randrange(50) for _ in range(rng.choice([5, 9, 16]))] for _ in range(3)]
     live, counter = {}, 0
     for _ in range(300):
@@ -264,4 +265,64 @@ def test_random_orders_with_shared_prefixes(seed):
     for rid in list(live):
         m.release(rid)
     m.check_invariants()
+    if keep:
+        assert m.stats["revived_pages"] > 0 and m.stats["evicted_pages"] > 0
+        assert all(g.pool.num_used == m.num_idle_blocks for g in m.groups) and m.free_pages() == {0: 14}
+        kept = m.num_idle_blocks
+        assert kept == len(m.prefix.blocks) and m.drop_idle() == kept  # with no request left, all that is indexed is idle
+        m.check_invariants()
     assert all(g.pool.num_used == 0 for g in m.groups) and not m.prefix.blocks
+
+
+def test_pages_of_a_finished_prompt_wait_for_the_next_request_that_begins_alike():
+    m = sharing_manager(num_pages=8, keep_finished=True)
+    common = list(range(100, 110))  # two full pages of 4 and a half
+    run_prompt(m, "a", common + [1, 2, 3])  # 13 tokens: four pages, three of them full
+    pages_a = list(m.block_table("a", 0))
+    assert m.release("a") == len(m.groups)  # only the page that is not full goes back to the free list
+    assert m.num_idle_blocks == 3 and m.groups[0].pool.num_used == 3 and m.free_pages() == {0: 8}
+    m.check_invariants()
+    rc = m.admit("b", common + [7, 8])
+    assert rc.num_tokens == 8 and m.block_table("b", 0) == pages_a[:2]  # nothing is computed again
+    assert m.num_idle_blocks == 1 and m.stats["revived_pages"] == 2 * len(m.groups)
+    assert [m.groups[0].pool.refcount(p) for p in pages_a[:3]] == [2, 2, 1]
+    m.check_invariants()
+    m.extend("b", 12)
+    m.commit("b", 12)
+    m.release("b")
+    # b's own third page ([108, 109, 7, 8]) is kept beside a's ([108, 109, 1, 2])
+    assert m.num_idle_blocks == 4
+    m.check_invariants()
+
+
+def test_kept_pages_are_given_up_when_their_room_is_needed_ends_of_chains_first():
+    m = sharing_manager(num_pages=6, keep_finished=True)
+    old = list(range(12))
+    run_prompt(m, "old", old + [50])        # three full pages and one more
+    m.release("old")
+    new = list(range(20, 28))
+    run_prompt(m, "new", new + [51])        # two full pages and one more: the pool is full now (3 idle + 3)
+    m.release("new")
+    assert m.num_idle_blocks == 5 and m.groups[0].pool.num_free == 1 and m.free_pages() == {0: 6}
+    # a request that needs three pages takes the free one and the two LAST pages of the older chain
+    rc = m.admit("x", [90, 91, 92, 93, 94, 95, 96, 97, 98])
+    assert rc.num_tokens == 0 and m.can_extend("x", 9)
+    m.extend("x", 9)
+    m.commit("x", 9)
+    m.check_invariants()
+    assert m.stats["evicted_pages"] == 2 * len(m.groups) and m.num_idle_blocks == 3
+    assert m.admit("old again", old + [50]).num_tokens == 4   # the head of the older chain is still there
+    assert m.admit("new again", new + [51]).num_tokens == 8   # the newer chain is whole
+    assert m.num_idle_blocks == 0
+    # nothing idle is left to give up: the next request that needs room is refused, and nothing changes
+    m.admit("y", [1] * 9)
+    assert not m.can_extend("y", 9)
+    with pytest.raises(OutOfPages):
+        m.extend("y", 9)
+    m.check_invariants()
+    for rid in ("x", "old again", "new again", "y"):
+        m.release(rid)
+    assert m.free_pages() == {0: 6}
+    m.drop_idle()
+    assert all(g.pool.num_used == 0 for g in m.groups) and not m.prefix.blocks and not m.prefix.by_page
+    m.check_invariants()

@@ -26,6 +26,19 @@ def folders(tmp_path_factory):
     return {name: helpers.make_folder(root, TINY[name], seed=31 + i) for i, name in enumerate(("A", "B"))}
 
 
+def _all_pages_are_back(engine):
+    """No request holds a page: every page is on a free list, or is a page of a finished prompt that only the
+    prefix index keeps (it counts as free, and a request that needs its room gets it)."""
+    cache = engine.runner.cache
+    cache.check_invariants()
+    assert not cache.requests
+    assert all(cache.free_pages()[g.gid] == g.pool.num_pages for g in cache.groups)
+    assert all(g.pool.num_used == cache.num_idle_blocks for g in cache.groups)
+    cache.drop_idle()
+    assert all(g.pool.num_used == 0 for g in cache.groups)
+    cache.check_invariants()
+
+
 def _engine(folder, dtype, device=None, **kw):
     from ferrisinfer_b200 import SchedulerConfig
     from ferrisinfer_b200.engine.engine import Engine
@@ -56,7 +69,7 @@ def test_greedy_generation_follows_the_plain_implementation(name, dtype, device,
             p0 = plain.greedy(logits[len(prompt) - 1].float().numpy())[1]
             assert abs(out.generated_tokens[0].probability - p0) < 1e-5
     engine.runner.cache.check_invariants()
-    assert all(g.pool.num_used == 0 for g in engine.runner.cache.groups)
+    _all_pages_are_back(engine)
 
 
 def test_stop_token_and_length_limits(device, folders):
@@ -134,7 +147,7 @@ def test_preemption_when_pages_run_out_does_not_change_the_tokens(device, folder
     assert tight.scheduler.stats["preemptions"] >= 1 and sum(o.preemptions for o in outs) >= 1
     assert [o.generated_token_ids() for o in outs] == want
     tight.runner.cache.check_invariants()
-    assert all(g.pool.num_used == 0 for g in tight.runner.cache.groups)
+    _all_pages_are_back(tight)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -162,7 +175,7 @@ def test_requests_that_begin_alike_share_pages_and_generate_the_same(dtype, devi
             most_pages = max(most_pages, engine.runner.cache.groups[0].pool.num_used)
             engine.runner.cache.check_invariants()
         outs = [engine.output_of(i) for i in [first] + rest]
-        assert all(g.pool.num_used == 0 for g in engine.runner.cache.groups)
+        _all_pages_are_back(engine)
         return outs, most_pages, engine.runner.cache.stats
 
     shared, pages_shared, stats = run(True)
@@ -170,6 +183,42 @@ def test_requests_that_begin_alike_share_pages_and_generate_the_same(dtype, devi
     assert [o.generated_token_ids() for o in shared] == [o.generated_token_ids() for o in alone]
     assert all(o.reused_prompt_tokens == 48 for o in shared[1:]) and shared[0].reused_prompt_tokens == 0
     assert stats["shared_tokens"] == 7 * 48 and pages_shared <= pages_alone - 60
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_later_request_finds_the_pages_of_a_finished_one(dtype, device, folders):
+    """Requests one after the other with the same long beginning: the pages of the first one's prompt outlive it,
+    the later ones compute only what differs and generate what they generate in an engine that keeps nothing;
+    when other prompts need the room, the kept pages are given up and everything still comes out the same."""
+    from ferrisinfer_b200 import SamplingParams, SchedulerConfig
+
+    vocab = TINY["A"]["vocab_size"]
+    stem = helpers.random_ids(vocab, 41, 5)
+    prompts = [stem + helpers.random_ids(vocab, 2 + i, 300 + i) for i in range(3)]
+    others = [helpers.random_ids(vocab, 44, 400 + i) for i in range(3)]
+    params = SamplingParams.greedy(max_new_tokens=5)
+    sched = SchedulerConfig(max_batch_size=4, max_prefill_chunk_tokens=16, max_prefill_batch_tokens=32,
+                            max_sequence_length=128, max_generated_tokens=16, min_prefix_share_tokens=8)
+
+    def run(keep):
+        # 24 pages of 4: one request of ~50 tokens holds 13, so kept pages must make room for the others
+        engine = _engine(folders["A"], dtype, device, page_size=4, num_pages=24, scheduler=sched, keep_finished_prefixes=keep)
+        outs = []
+        for p in prompts + others + prompts[:1]:
+            rid = engine.submit(p, params)
+            while engine.has_unfinished():
+                engine.step()
+                engine.runner.cache.check_invariants()
+            outs.append(engine.output_of(rid))
+        stats = dict(engine.runner.cache.stats)
+        _all_pages_are_back(engine)
+        return outs, stats
+
+    kept, stats = run(True)
+    plain, plain_stats = run(False)
+    assert [o.generated_token_ids() for o in kept] == [o.generated_token_ids() for o in plain]
+    assert [o.reused_prompt_tokens for o in kept[:3]] == [0, 40, 40] and all(o.reused_prompt_tokens == 0 for o in plain)
+    assert stats["revived_pages"] >= 20 and stats["evicted_pages"] > 0 and plain_stats["revived_pages"] == 0
 
 
 def test_abort_gives_pages_back(device, folders):
@@ -185,7 +234,7 @@ def test_abort_gives_pages_back(device, folders):
         engine.step()
     assert engine.output_of(a).finish_reason is FinishReason.CANCELLED
     assert len(engine.output_of(b).generated_tokens) == 5
-    assert all(g.pool.num_used == 0 for g in engine.runner.cache.groups)
+    _all_pages_are_back(engine)
 
 
 def test_command_line(device, folders):
@@ -244,7 +293,7 @@ def test_running_a_step_ahead_changes_nothing_but_the_timing(dtype, device, fold
             if o.finish_reason is not FinishReason.CANCELLED:
                 assert seen[i] == o.generated_token_ids()
         engine.runner.cache.check_invariants()
-        assert all(g.pool.num_used == 0 for g in engine.runner.cache.groups)
+        _all_pages_are_back(engine)
         return [(o.generated_token_ids(), o.finish_reason) for o in outs], engine.steps_run_ahead
 
     free, _ = run(False, (None, None))
@@ -301,7 +350,7 @@ def test_requests_arriving_ending_and_preempted_at_random_with_a_step_in_flight(
             step += 1
             assert step < 2000
         outs = {i: engine.output_of(ids[i]) for i in range(n)}
-        assert all(g.pool.num_used == 0 for g in engine.runner.cache.groups)
+        _all_pages_are_back(engine)
         return outs, engine.scheduler.stats["preemptions"], engine.steps_run_ahead
 
     for run_ahead in (False, True):

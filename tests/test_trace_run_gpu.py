@@ -46,13 +46,18 @@ def run_trace(folder, dtype, steps, out_dir, max_tokens, vocab):
     return got
 
 
+LENGTHS = {"A": (70, 33, 101, 48, 64, 90), "B": (70, 33, 101, 48, 64, 90),
+           # head size 64: in bfloat16 the tensor-core kernels, and prompts long enough for the long-step ones
+           "D": (260, 33, 150, 140, 64)}
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_replay_in_every_way_of_cutting(name, dtype, device, tmp_path):
     folder = helpers.make_folder(tmp_path, TINY[name], seed=41, score_std=1.8)
     config, weights = helpers.read_folder(folder)
     vocab = config["vocab_size"]
-    lengths = (70, 33, 101, 48, 64, 90)
+    lengths = LENGTHS[name]
     requests = {f"q{i}": helpers.random_ids(vocab, n, 3 * i + n) for i, n in enumerate(lengths)}
     want = helpers.oracle_logits(config, weights, requests)
     tol = TOL[torch.float32 if dtype == "float32" else torch.bfloat16]

@@ -66,6 +66,7 @@ class RequestCache:
     registered_blocks: int = 0  # leading blocks of the prompt that are in the prefix index
     block_keys: list = field(default_factory=list)  # chain hash of each registered or borrowed block
     shared_tokens: int = 0  # tokens that came from other requests' pages at admission
+    revived_pages: int = 0  # of those pages, how many had outlived their last holder
 
 
 class PrefixIndex:
@@ -220,6 +221,7 @@ class CacheManager:
                     rc.block_keys.append(key)
                     if key in self._idle:  # pages that had outlived their last holder
                         del self._idle[key]
+                        rc.revived_pages += len(self.groups)
                         self.stats["revived_pages"] += len(self.groups)
                 rc.registered_blocks = len(found)
                 rc.num_tokens = rc.shared_tokens = len(found) * ps
@@ -366,6 +368,12 @@ class CacheManager:
         rc = self.requests.pop(request_id, None)
         if rc is None:
             raise CacheError(f"request {request_id!r} is released twice (or was never admitted)")
+        if rc.num_tokens == rc.shared_tokens and rc.shared_tokens:
+            # admitted and sent away again before it computed a token (its first portion did not fit): what it
+            # borrowed does not count as shared
+            self.stats["shared_tokens"] -= rc.shared_tokens
+            self.stats["shared_pages"] -= (rc.shared_tokens // self.page_size) * len(self.groups)
+            self.stats["revived_pages"] -= rc.revived_pages
         freed = 0
         for g in self.groups:
             for page in rc.tables[g.gid]:

@@ -11,10 +11,10 @@ from ferrisinfer_b200.sampling import SamplingParams
 FULL = PagedKV(2, 16, None)
 
 
-def make(num_pages=64, page_size=4, needs=(FULL,), **cfg):
+def make(num_pages=64, page_size=4, needs=(FULL,), cache_options=None, **cfg):
     config = SchedulerConfig(**{**dict(max_batch_size=4, max_prefill_chunk_tokens=8, max_prefill_batch_tokens=16,
                                        max_sequence_length=64, max_generated_tokens=32), **cfg})
-    cache = CacheManager(list(needs), page_size, num_pages, config.max_batch_size)
+    cache = CacheManager(list(needs), page_size, num_pages, config.max_batch_size, **(cache_options or {}))
     return Scheduler(config, cache), cache
 
 
@@ -174,6 +174,33 @@ def test_a_preempted_request_is_recomputed_as_one_prompt_and_keeps_its_tokens():
     # after the preemption b comes back with its prompt AND what it had generated, from position 0
     restarts = [s for s in log for (rid, start, count) in s if rid == "b" and start == 0]
     assert len(restarts) == 1 + b.preemptions
+
+
+def test_a_preempted_request_finds_its_own_pages_again_where_they_were_not_needed():
+    """The scene of the test above with kept prompt pages: the preempted request's full pages wait in the cache, the
+    request that needed room takes the last of them, and the rest is there when the preempted one comes back."""
+    sched, cache = make(num_pages=6, max_prefill_chunk_tokens=8, max_prefill_batch_tokens=32,
+                        cache_options=dict(prefix_sharing=True, keep_finished=True))
+    sched.submit("a", list(range(8)), greedy(12))
+    sched.submit("b", list(range(100, 116)), greedy(2))
+    log = []
+    while sched.has_unfinished():
+        plan, _ = run_step(sched, cache)
+        log.append(([(e.seq.request_id, e.start, e.count) for e in plan.entries], [s.request_id for s in plan.preempted]))
+    assert log[5] == ([("a", 12, 1)], ["b"])  # as without kept pages: b had 12 tokens in three full pages
+    # one of b's pages went to a; the other two still hold b's first 8 tokens, so no page is free for b's next
+    # portion while a runs (without kept pages b would compute those 8 tokens again here)
+    assert log[6] == ([("a", 13, 1)], [])
+    after = [entries for entries, _ in log[6:] if any(rid == "b" for rid, _, _ in entries)]
+    # a's last page took another of b's pages; b comes back at token 4, not 0, once a has ended
+    assert after[0][-1][:2] == ("b", 4)
+    b = sched.finished["b"]
+    assert b.generated == [1, 1] and b.preemptions >= 1 and b.reused_prompt_tokens == 4
+    assert sched.finished["a"].generated == [1] * 12
+    # b was admitted and sent away again in every step in which its next portion did not fit: that does not count
+    assert cache.stats["revived_pages"] == 1 and cache.stats["shared_tokens"] == 4 and cache.stats["evicted_pages"] >= 2
+    assert cache.free_pages() == {0: 6} and not cache.requests
+    cache.check_invariants()
 
 
 def test_cancel_gives_everything_back():

@@ -980,6 +980,43 @@ bool ferris_gemm_cluster_enabled() {
 // 38.4 us on pairs against 41.6 us, the products with one accumulator 20.5 us against 19.3 us (same number of
 // CTAs either way, and the pair's barriers cost more than the halved weight traffic saves).  Prefill with the
 // default against no pairs: 0.5B sizes 3.49-3.58 against 3.51-3.59 ms, 1.5B sizes 8.13-8.20 against 8.47-8.51 ms.
+// Which of the two kernels a step of T >= 128 tokens runs: the token-major one (tokens on the MMA's M side,
+// persistent CTAs, one CTA per tile of 128 x 128) or the weight-major one (K split over a cluster, so that a product
+// with few tiles still uses every SM).  Both move the same bytes from L2, 32 KB per tile and K slice; what differs is
+// over how many SMs.  Measured on B200: one SM takes in about 107 GB/s, all together about 6.3 TB/s, and the
+// cluster's sum costs the weight-major kernel about 3 us.  Down projection of the 0.5B sizes (K = 4864, N = 896),
+// token-major / weight-major: 256 tokens 27.2 / 15.2 us, 512 tokens 27.8 / 18.8 us, 768 tokens 28.7 / 24.5 us,
+// 1,024 tokens 29.0 / 33.1 us; the estimate below reproduces these within 10 %.
+// FERRIS_GEMM_LONG_MIN / ferris_set_gemm_long_min: a fixed number of tokens instead of the estimate.
+int g_long_min = -1;
+FERRIS_API int ferris_gemm_tcgen05_plan(int T, int N, int K, int accumulators, int* bt_out, int* splits_out,
+                                        long long* scratch_floats, int* counters);
+static bool token_major_pays(int mode, int T, int N, int K) {
+    if (g_long_min < 0) {
+        const char* v = getenv("FERRIS_GEMM_LONG_MIN");
+        g_long_min = v ? atoi(v) : 0;
+        if (g_long_min < 0) g_long_min = 0;
+    }
+    if (T < PT_BLOCK_M) return false;
+    if (g_long_min > 0) return T >= g_long_min;
+    const int sms = sm_count();
+    const int accs = mode == SWIGLU_BF16 ? 2 : 1;
+    const long long tiles = (long long)((T + PT_BLOCK_M - 1) / PT_BLOCK_M) * ((N + 127) / 128);
+    if (tiles >= sms / 2) return true;
+    int bt, splits, n_counters;
+    long long scratch_floats;
+    ferris_gemm_tcgen05_plan(T, N, K, accs, &bt, &splits, &scratch_floats, &n_counters);
+    if (splits < 2 || !ferris_gemm_cluster_enabled()) return true;
+    const double per_sm = 107e3, all_sms = 6.3e6, cluster_sum_us = 3.0;  // bytes per microsecond
+    const double kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+    const double bytes = (double)tiles * kblocks * (accs + 1) * 128 * BLOCK_K * 2;
+    const double wm_ctas = (double)((N + BLOCK_N - 1) / BLOCK_N) * ((T + bt - 1) / bt) * splits;
+    const double t_tm = bytes / (tiles * per_sm < all_sms ? tiles * per_sm : all_sms);
+    const double t_wm = bytes / (wm_ctas * per_sm < all_sms ? wm_ctas * per_sm : all_sms) + cluster_sum_us;
+    // the estimate is within 10 % of what was measured: the kernel with the cluster sum has to win by more
+    return t_tm <= 1.15 * t_wm;
+}
+
 int g_pair = -1;  // 0: no product on pairs, 1: every long-step product, 2: the SwiGLU product only
 bool ferris_gemm_pair_enabled(int mode) {
     if (g_pair < 0) {
@@ -1092,6 +1129,12 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
 // 1 if the K splits of the short-step kernel add up through a cluster's shared memory (then no product needs the
 // scratch and counters that ferris_gemm_tcgen05_plan speaks of), 0 if through global scratch.
 FERRIS_API int ferris_gemm_uses_clusters() { return ferris_gemm_cluster_enabled() ? 1 : 0; }
+
+// From how many tokens on a step runs the token-major kernel (at least 128; 0 selects the default).
+FERRIS_API int ferris_set_gemm_long_min(int tokens) {
+    g_long_min = tokens > 0 ? tokens : -1;
+    return FERRIS_OK;
+}
 
 // Long steps on CTA pairs (cta_group::2) instead of single CTAs: 0 none, 1 every product, 2 the gate / up product
 // only (the default); any other value selects the default.
@@ -1305,7 +1348,7 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
     cudaStream_t s = (cudaStream_t)stream;
     // long steps: the persistent token-major kernel (its 16-byte stores need aligned output rows)
     const int elt = (mode == STORE_BF16 || mode == SWIGLU_BF16) ? 2 : 4;
-    const bool long_step = T >= PT_BLOCK_M && !trace && !built && ((size_t)ldo * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0;
+    const bool long_step = !trace && !built && token_major_pays(mode, T, N, K) && ((size_t)ldo * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0;
     if (long_step && T > PT_BLOCK_M && ferris_gemm_pair_enabled(mode)) {
         // CTA pairs: tiles of 256 tokens x 256 weight rows (128 + 128 in SwiGLU mode), or x 128 where the
         // wider tile would leave pairs of SMs without work

@@ -259,6 +259,11 @@ def set_gemm_pairs(which=GEMM_PAIRS_SWIGLU) -> None:
     _lib().ferris_set_gemm_pair(_c_int(int(which)))
 
 
+def set_gemm_long_min(tokens: int = 0) -> None:
+    """From how many tokens on a product runs the token-major kernel (never below 128); 0: the library's default."""
+    _lib().ferris_set_gemm_long_min(_c_int(int(tokens)))
+
+
 class LazyRMSNorm:
     """The RMSNorm of the residual rows ``h`` that has not been computed yet.  A matrix product that can form
     it on its way (``gemm`` / ``gemm_swiglu`` for short bf16 steps) takes it as its input and no norm kernel

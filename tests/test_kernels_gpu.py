@@ -143,6 +143,43 @@ def test_gemm_tcgen05_store_and_accumulate(T, N, K, device):
     assert ops.kernel_status() == 0
 
 
+@pytest.mark.parametrize("T, N, K", [(300, 896, 4864), (700, 896, 4864), (200, 1536, 8960), (513, 1152, 896), (260, 130, 1000),
+                                     (1000, 384, 2048)])
+def test_gemm_of_a_few_hundred_tokens_on_either_kernel(T, N, K, device):
+    """Steps between 128 and about a thousand tokens run the token-major kernel or, where its few tiles would leave
+    most SMs idle, the weight-major one with several token tiles and a K split over a cluster: both, and the
+    library's own choice, against the plain product, in every mode."""
+    from ferrisinfer_b200.kernels import ops
+
+    x, w = rnd((T, K), BF16, device, 51), rnd((N, K), BF16, device, 52, scale=0.1)
+    bias = rnd((N,), F32, device, 53)
+    want = _gemm_reference(x, w)
+    I = N // 2
+    want_act = want[:, I:2 * I] * plain.silu(want[:, :I])
+    base = rnd((T, N), F32, device, 54)
+    try:
+        for long_min in (128, 1 << 30, 0):
+            ops.set_gemm_long_min(long_min)
+            out = torch.full((T, N), float("nan"), dtype=BF16, device=device)
+            ops.gemm_tcgen05(x, w, bias, out, 0)
+            _close(out, want + bias.cpu().double(), K, BF16)
+            out32 = torch.full((T, N), float("nan"), dtype=F32, device=device)
+            ops.gemm_tcgen05(x, w, None, out32, 1)
+            _close(out32, want, K, F32)
+            again = torch.empty_like(out32)
+            ops.gemm_tcgen05(x, w, None, again, 1)
+            assert torch.equal(again, out32)
+            acc = base.clone()
+            ops.gemm_tcgen05(x, w, bias, acc, 2)
+            _close(acc - base, want + bias.cpu().double(), K, F32)
+            act = torch.full((T, I), float("nan"), dtype=BF16, device=device)
+            ops.gemm_tcgen05(x, w, None, act, 3, up_row_offset=I)
+            _close(act, want_act, K, BF16)
+            assert ops.kernel_status() == 0
+    finally:
+        ops.set_gemm_long_min(0)
+
+
 @pytest.mark.parametrize("T, I, K", [(1, 4864, 896), (8, 300, 96), (64, 4864, 896), (130, 128, 64), (700, 224, 96)])
 def test_gemm_tcgen05_swiglu(T, I, K, device):
     from ferrisinfer_b200.kernels import ops

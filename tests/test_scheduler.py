@@ -243,6 +243,44 @@ def test_random_load_never_overdraws_the_pool(seed):
         assert seq.finish_reason is not None and len(seq.generated) <= seq.max_new_tokens
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_random_load_with_kept_prompt_pages(seed):
+    """Prompts that begin alike, a pool that forces preemptions, pages of finished and preempted prompts kept until
+    their room is needed: every request ends, nothing is lost, and what the scheduler promises the cache delivers
+    (run_step extends without checking)."""
+    import random
+
+    rng = random.Random(100 + seed)
+    sched, cache = make(num_pages=rng.choice([10, 14, 20]), page_size=rng.choice([2, 4]),
+                        max_prefill_chunk_tokens=rng.choice([3, 8]), max_prefill_batch_tokens=rng.choice([6, 16]),
+                        max_sequence_length=40, max_generated_tokens=12, min_prefix_share_tokens=rng.choice([0, 4]),
+                        cache_options=dict(prefix_sharing=True, keep_finished=True,
+                                           min_prefix_share_tokens=rng.choice([0, 4])))
+    stems = [[rng.randrange(9) for _ in range(rng.choice([6, 11, 17]))] for _ in range(3)]
+    submitted = 0
+    for step in range(400):
+        if submitted < 16 and rng.random() < 0.3:
+            prompt = list(rng.choice(stems)) + [rng.randrange(9) for _ in range(rng.randint(1, 6))]
+            try:
+                sched.submit(submitted, prompt, greedy(rng.randint(0, 12)))
+            except SchedulerError:
+                pass
+            submitted += 1
+        if sched.has_unfinished():
+            run_step(sched, cache, token=lambda seq: rng.randrange(5))
+        elif submitted >= 16:
+            break
+    assert not sched.has_unfinished() and not cache.requests
+    assert cache.free_pages() == {0: cache.groups[0].pool.num_pages} and cache.num_free_slots == 4
+    assert cache.groups[0].pool.num_used == cache.num_idle_blocks
+    assert cache.stats["revived_pages"] > 0
+    for seq in sched.finished.values():
+        assert seq.finish_reason is not None and len(seq.generated) <= seq.max_new_tokens
+    cache.drop_idle()
+    cache.check_invariants()
+    assert cache.groups[0].pool.num_used == 0
+
+
 def test_a_new_request_reuses_the_pages_of_a_live_request_with_the_same_beginning():
     config = SchedulerConfig(max_batch_size=4, max_prefill_chunk_tokens=8, max_prefill_batch_tokens=32,
                              max_sequence_length=64, max_generated_tokens=32, min_prefix_share_tokens=8)

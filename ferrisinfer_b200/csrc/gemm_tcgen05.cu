@@ -980,6 +980,8 @@ bool ferris_gemm_cluster_enabled() {
 // 38.4 us on pairs against 41.6 us, the products with one accumulator 20.5 us against 19.3 us (same number of
 // CTAs either way, and the pair's barriers cost more than the halved weight traffic saves).  Prefill with the
 // default against no pairs: 0.5B sizes 3.49-3.58 against 3.51-3.59 ms, 1.5B sizes 8.13-8.20 against 8.47-8.51 ms.
+// The gate / up product alone, pairs against single CTAs: 256 tokens 13.8 / 14.2 us, 512 tokens 18.5 / 19.8 us,
+// 1,024 tokens 25.1 / 27.0 us (0.5B sizes); 512 tokens 106 / 119 us, 2,048 tokens 377 / 434 us (7B sizes).
 // Which of the two kernels a step of T >= 128 tokens runs: the token-major one (tokens on the MMA's M side,
 // persistent CTAs, one CTA per tile of 128 x 128) or the weight-major one (K split over a cluster, so that a product
 // with few tiles still uses every SM).  Both move the same bytes from L2, 32 KB per tile and K slice; what differs is
@@ -1018,12 +1020,16 @@ static bool token_major_pays(int mode, int T, int N, int K) {
 }
 
 int g_pair = -1;  // 0: no product on pairs, 1: every long-step product, 2: the SwiGLU product only
-bool ferris_gemm_pair_enabled(int mode) {
+bool ferris_gemm_pair_enabled(int mode, int T) {
     if (g_pair < 0) {
         const char* v = getenv("FERRIS_GEMM_PAIR");
         g_pair = (v && v[0] >= '0' && v[0] <= '2') ? v[0] - '0' : 2;
     }
-    return g_pair == 1 || (g_pair == 2 && mode == SWIGLU_BF16);
+    if (g_pair == 1) return true;
+    // A pair's tile has 256 tokens: with an odd number of 128-token tiles the last pair is half empty, which costs
+    // more than pairs save while the tiles are few (384 tokens at the 0.5B sizes: 18.3 us on pairs, 14.1 us without).
+    const int m128 = (T + PT_BLOCK_M - 1) / PT_BLOCK_M;
+    return g_pair == 2 && mode == SWIGLU_BF16 && (m128 % 2 == 0 || m128 >= 9);
 }
 
 template <int MODE>
@@ -1349,7 +1355,7 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
     // long steps: the persistent token-major kernel (its 16-byte stores need aligned output rows)
     const int elt = (mode == STORE_BF16 || mode == SWIGLU_BF16) ? 2 : 4;
     const bool long_step = !trace && !built && token_major_pays(mode, T, N, K) && ((size_t)ldo * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0;
-    if (long_step && T > PT_BLOCK_M && ferris_gemm_pair_enabled(mode)) {
+    if (long_step && T > PT_BLOCK_M && ferris_gemm_pair_enabled(mode, T)) {
         // CTA pairs: tiles of 256 tokens x 256 weight rows (128 + 128 in SwiGLU mode), or x 128 where the
         // wider tile would leave pairs of SMs without work
         PTParams q;

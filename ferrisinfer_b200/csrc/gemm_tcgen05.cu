@@ -641,7 +641,7 @@ __global__ void __launch_bounds__(PT_THREADS)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a_bytes = PT_BLOCK_M * BLOCK_K * 2, b_bytes = p.bn * BLOCK_K * 2;
     const int stage_bytes = a_bytes + ACCS * b_bytes;
-    const int acc_cols = ACCS * p.bn;  // columns of one accumulator buffer
+    const int acc_cols = 256;  // columns of one accumulator buffer (ACCS * bn of them used)
     const int tiles = p.m_tiles * p.n_tiles;
     // fp32 outputs leave through shared memory and TMA: 4 KB (32 tokens x 32 floats, swizzled) per epilogue warp
     uint8_t* out_stage = smem + (size_t)PT_STAGES * stage_bytes + (size_t)(warp >= 2 ? warp - 2 : 0) * 4096;
@@ -1301,8 +1301,26 @@ static int run_tokens_m(const void* x, const void* w, const float* bias, void* o
     q.K = K;
     q.ldo = ldo;
     q.m_tiles = (T + PT_BLOCK_M - 1) / PT_BLOCK_M;
-    // 256 weight rows per tile where that still gives every SM a tile, else 128 (always 128 + 128 for SwiGLU)
-    q.bn = (accs == 2 || q.m_tiles * ((N + 255) / 256) < g_sms) ? 128 : 256;
+    // Weight rows per tile.  SwiGLU: 128 + 128.  The q/k/v mode: 256 where that still gives every SM a tile, else 128
+    // (whole heads).  Otherwise the width among 128 .. 256 that costs least: a CTA takes in (128 + bn) rows per K
+    // slice, and the CTAs go through ceil(tiles / SMs) rounds; 192 or 224 rows often fit in one round what 128 rows
+    // need two for (2,048 tokens x 1,536 outputs: 192 tiles of 128 in two rounds, 128 tiles of 192 in one).
+    if (accs == 2) {
+        q.bn = 128;
+    } else if (rope) {
+        q.bn = q.m_tiles * ((N + 255) / 256) < g_sms ? 128 : 256;
+    } else {
+        long long best = -1;
+        q.bn = 128;
+        for (int bn = 256; bn >= 128; bn -= 32) {
+            const long long tiles = (long long)q.m_tiles * ((N + bn - 1) / bn);
+            const long long cost = ((tiles + g_sms - 1) / g_sms) * (PT_BLOCK_M + bn);
+            if (best < 0 || cost < best) {
+                best = cost;
+                q.bn = bn;
+            }
+        }
+    }
     q.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
     q.n_tiles = (N + q.bn - 1) / q.bn;
     q.up_row_offset = up_row_offset;

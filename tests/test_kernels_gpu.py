@@ -103,7 +103,9 @@ def test_gemm_rows_do_not_depend_on_the_batch(device):
 # ------------------------------------------------------------------------- tensor-core gemm
 TC_SHAPES = [(1, 1152, 896), (8, 1152, 896), (64, 896, 4864), (5, 130, 72), (16, 128, 64), (17, 300, 1000),
              (300, 256, 128), (2048, 384, 256), (33, 1000, 80), (257, 129, 200),
-             (8, 3584, 18944), (8, 4608, 3584)]  # the last two: K splits whose clusters do not pack evenly into GPCs
+             (8, 3584, 18944), (8, 4608, 3584),  # K splits whose clusters do not pack evenly into GPCs
+             # long steps whose tiles are 224, 192 and 160 weight rows wide (one round of CTAs instead of two)
+             (4096, 896, 256), (2048, 1536, 192), (1024, 3584, 128), (2048, 1200, 72)]
 
 
 def _gemm_reference(x, w, bias=None):

@@ -1301,18 +1301,17 @@ static int run_tokens_m(const void* x, const void* w, const float* bias, void* o
     q.K = K;
     q.ldo = ldo;
     q.m_tiles = (T + PT_BLOCK_M - 1) / PT_BLOCK_M;
-    // Weight rows per tile.  SwiGLU: 128 + 128.  The q/k/v mode: 256 where that still gives every SM a tile, else 128
-    // (whole heads).  Otherwise the width among 128 .. 256 that costs least: a CTA takes in (128 + bn) rows per K
+    // Weight rows per tile.  SwiGLU: 128 + 128.  Otherwise the width among 128 .. 256 that costs least: a CTA takes in (128 + bn) rows per K
     // slice, and the CTAs go through ceil(tiles / SMs) rounds; 192 or 224 rows often fit in one round what 128 rows
     // need two for (2,048 tokens x 1,536 outputs: 192 tiles of 128 in two rounds, 128 tiles of 192 in one).
     if (accs == 2) {
         q.bn = 128;
-    } else if (rope) {
-        q.bn = q.m_tiles * ((N + 255) / 256) < g_sms ? 128 : 256;
     } else {
+        // the q/k/v mode takes whole heads (and pairs of 32-column chunks): steps of 64 or 128 rows
+        const int step = rope ? (rope->d == 64 ? 64 : 128) : 32;
         long long best = -1;
         q.bn = 128;
-        for (int bn = 256; bn >= 128; bn -= 32) {
+        for (int bn = 256; bn >= 128; bn -= step) {
             const long long tiles = (long long)q.m_tiles * ((N + bn - 1) / bn);
             const long long cost = ((tiles + g_sms - 1) / g_sms) * (PT_BLOCK_M + bn);
             if (best < 0 || cost < best) {

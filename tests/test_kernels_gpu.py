@@ -366,7 +366,9 @@ def test_rope_cache_write(nh, nkv, d, rotary, page, dtype, device):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("T,nh,nkv,d,K,page", [(128, 2, 1, 64, 64, 16), (300, 14, 2, 64, 896, 64), (257, 3, 1, 128, 136, 32),
-                                               (6400, 5, 2, 64, 72, 64), (1000, 1, 1, 128, 264, 16)])
+                                               (6400, 5, 2, 64, 72, 64), (1000, 1, 1, 128, 264, 16),
+                                               # tiles of 192 weight rows (three heads of 64) and of 256 (two heads of 128)
+                                               (2048, 20, 2, 64, 72, 64), (2048, 12, 2, 128, 136, 32)])
 def test_qkv_product_with_rotation_and_cache_write_in_its_epilogue(T, nh, nkv, d, K, page, device):
     """Queries rotated into the output rows, keys rotated and values straight into the paged cache, against the
     product in fp64 rotated by the plain implementation; tokens with slot -1 and all other slots stay untouched."""

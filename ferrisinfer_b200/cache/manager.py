@@ -21,6 +21,10 @@ Here ONE manager serves all requests:
 * Mixers with a ``FixedState`` need, and the engine itself (sampler state), get a tensor
   ``[slots, *shape]``; a request holds one slot id from admission to release, and the slot's rows
   are zeroed at admission.
+* Every pool has one page more than it hands out, and every state tensor one slot more
+  (``padding_page``, ``padding_slot``): rows that only fill a step up to a recorded batch size write
+  their key, value and state there, where no request ever reads.
+* A need of another kind than these two brings its own builder (``register_cache_need``).
 * With prefix sharing, full pages of prompts are found by later requests through a chain hash and
   shared, not copied.  With ``keep_finished`` the index holds a reference of its own, so the pages of
   a prompt outlive the request that computed them; they count as free, and the least recently used
@@ -121,11 +125,43 @@ class PrefixIndex:
                     self.by_page.pop((g2, p2), None)
 
 
+# need class -> builder(manager, run-order index, need) -> LayerCache.  A builder may use ``manager.page_group(need)``
+# (pages by block table) and ``manager.new_state(shape, dtype)`` (one row per request slot, zeroed at admission).
+_NEED_BUILDERS: dict = {}
+
+
+def register_cache_need(need_cls, builder) -> None:
+    """How the cache manager serves a kind of need that it does not know: ``builder(manager, index, need)``
+    returns the ``LayerCache`` that the mixer of run-order entry ``index`` gets."""
+    _NEED_BUILDERS[need_cls] = builder
+
+
+def _build_paged(manager, index, need):
+    g = manager.page_group(need)
+    g.members.append(index)
+    cache = LayerCache(need=need, group=g.gid)
+    if manager.device is not None:
+        # one page beyond the pool's: the padding page
+        shape = (g.pool.num_pages + 1, need.num_kv_heads, manager.page_size, need.head_dim)
+        cache.k = torch.zeros(shape, dtype=manager.dtype, device=manager.device)
+        cache.v = torch.zeros(shape, dtype=manager.dtype, device=manager.device)
+    return cache
+
+
+def _build_state(manager, index, need):
+    return LayerCache(need=need, state=manager.new_state(need.shape, need.dtype))
+
+
+register_cache_need(PagedKV, _build_paged)
+register_cache_need(FixedState, _build_state)
+
+
 class CacheManager:
     def __init__(self, needs: list, page_size: int, num_pages, max_requests: int,
                  dtype: torch.dtype = torch.float32, device=None, extra_states: Optional[dict] = None,
                  prefix_sharing: bool = False, min_prefix_share_tokens: int = 0, keep_finished: bool = False):
-        """``needs[i]``: the cache need of run-order entry i (PagedKV, FixedState or None).
+        """``needs[i]``: the cache need of run-order entry i (PagedKV, FixedState, a kind registered with
+        ``register_cache_need``, or None).
         ``num_pages``: pages per group (an int for all groups, or a dict gid -> int).
         ``device`` None: bookkeeping only (no tensors), as the CPU tests use it.
         ``keep_finished`` (with prefix sharing): shareable pages stay in the cache after their last
@@ -140,33 +176,18 @@ class CacheManager:
         self.groups: list = []
         self.layer_caches: list = [None] * len(needs)
         self.state_tensors: dict = {}
-        by_need: dict = {}
+        self._by_need: dict = {}
+        self._num_pages = num_pages
         for i, need in enumerate(needs):
-            if isinstance(need, PagedKV):
-                if need not in by_need:
-                    gid = len(self.groups)
-                    n = num_pages[gid] if isinstance(num_pages, dict) else num_pages
-                    self.groups.append(PageGroup(gid, need, [], self.page_size, PagePool(n)))
-                    by_need[need] = gid
-                g = self.groups[by_need[need]]
-                g.members.append(i)
-                cache = LayerCache(need=need, group=g.gid)
-                if device is not None:
-                    shape = (g.pool.num_pages, need.num_kv_heads, self.page_size, need.head_dim)
-                    cache.k = torch.zeros(shape, dtype=dtype, device=device)
-                    cache.v = torch.zeros(shape, dtype=dtype, device=device)
-                self.layer_caches[i] = cache
-            elif isinstance(need, FixedState):
-                cache = LayerCache(need=need)
-                if device is not None:
-                    cache.state = torch.zeros((self.max_requests, *need.shape), dtype=need.dtype, device=device)
-                self.layer_caches[i] = cache
-            elif need is not None:
+            if need is None:
+                continue
+            builder = next((b for cls, b in _NEED_BUILDERS.items() if isinstance(need, cls)), None)
+            if builder is None:
                 raise CacheError(f"run-order entry {i} has an unknown cache need {need!r}")
+            self.layer_caches[i] = builder(self, i, need)
         for name, need in (extra_states or {}).items():
             if device is not None:
-                self.state_tensors[name] = torch.zeros((self.max_requests, *need.shape), dtype=need.dtype,
-                                                       device=device)
+                self.state_tensors[name] = self.new_state(need.shape, need.dtype)
         self._free_slots = list(range(self.max_requests - 1, -1, -1))
         self.requests: dict = {}
         # Pages of prompts are shared only where a page means the same for every layer: all page groups keep
@@ -180,6 +201,43 @@ class CacheManager:
         # recently used first; a block's descendants in a chain always come before it
         self._idle: OrderedDict = OrderedDict()
         self.stats = {"shared_tokens": 0, "shared_pages": 0, "revived_pages": 0, "evicted_pages": 0}
+
+    # ------------------------------------------------------------------- set-up
+    def page_group(self, need: PagedKV) -> PageGroup:
+        """The page group of ``need`` (made at its first call): entries with the same need share page ids."""
+        gid = self._by_need.get(need)
+        if gid is None:
+            gid = len(self.groups)
+            n = self._num_pages[gid] if isinstance(self._num_pages, dict) else self._num_pages
+            self.groups.append(PageGroup(gid, need, [], self.page_size, PagePool(n)))
+            self._by_need[need] = gid
+        return self.groups[gid]
+
+    def new_state(self, shape, dtype) -> Optional[torch.Tensor]:
+        """A zeroed tensor with one row of ``shape`` per request slot and one more, the padding slot's
+        (None without a device)."""
+        if self.device is None:
+            return None
+        return torch.zeros((self.max_requests + 1, *shape), dtype=dtype, device=self.device)
+
+    @property
+    def padding_slot(self) -> int:
+        """A state slot that no request ever holds."""
+        return self.max_requests
+
+    def padding_page(self, gid: int) -> int:
+        """A page of group ``gid`` that no request ever holds."""
+        return self.groups[gid].pool.num_pages
+
+    def state_bytes(self) -> int:
+        """Bytes of the per-request state tensors (mixers' and the engine's)."""
+        total = 0
+        for cache in self.layer_caches:
+            if cache is not None and cache.state is not None:
+                total += cache.state.numel() * cache.state.element_size()
+        for t in self.state_tensors.values():
+            total += t.numel() * t.element_size()
+        return total
 
     # ------------------------------------------------------------------ requests
     def has(self, request_id) -> bool:

@@ -152,7 +152,13 @@ def _run(cmd, args, ns, out) -> int:
         load_model(path, ns.dtype, "cuda")
         torch.cuda.synchronize()
         t2 = time.perf_counter()
-        print(f"config: {(t1 - t0) * 1e3:.1f} ms\nweights + model: {(t2 - t1) * 1e3:.1f} ms\n"
+        from ..weights import SafetensorsFolder
+
+        st = SafetensorsFolder(path)
+        stored = sum(e.end - e.begin for e in st.entries.values())
+        st.close()
+        print(f"config: {(t1 - t0) * 1e3:.1f} ms\nweights + model: {(t2 - t1) * 1e3:.1f} ms "
+              f"({stored / 1e9:.2f} GB stored, {stored / 1e9 / max(t2 - t1, 1e-9):.2f} GB/s)\n"
               f"total: {(t2 - t0) * 1e3:.1f} ms", file=out)
         return 0
 

@@ -31,6 +31,7 @@ import os
 from dataclasses import dataclass, asdict
 from typing import Any, Optional
 
+from .json_file import read_config_json
 from ..errors import ConfigError, UnsupportedError
 
 _MISSING = object()
@@ -216,19 +217,3 @@ class Qwen2Config:
     @classmethod
     def from_json(cls, path: str) -> "Qwen2Config":
         return cls.from_dict(read_config_json(path))
-
-
-def read_config_json(path: str) -> dict:
-    """Parse ``path`` (a config.json, or a folder holding one) into a dict."""
-    if os.path.isdir(path):
-        path = os.path.join(path, "config.json")
-    try:
-        with open(path, "r", encoding="utf-8") as f:
-            d = json.load(f)
-    except FileNotFoundError:
-        raise ConfigError(f"no config.json at {path}") from None
-    except json.JSONDecodeError as e:
-        raise ConfigError(f"{path}: not valid JSON ({e})") from None
-    if not isinstance(d, dict):
-        raise ConfigError(f"{path}: top level must be a JSON object")
-    return d

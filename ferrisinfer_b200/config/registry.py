@@ -18,7 +18,7 @@ from dataclasses import dataclass
 from typing import Any, Callable
 
 from ..errors import ConfigError, UnsupportedError
-from .qwen2 import read_config_json
+from .json_file import read_config_json
 
 
 @dataclass(frozen=True)
@@ -73,5 +73,7 @@ def resolve_config(source) -> tuple[Architecture, Any]:
 
 
 def _ensure_builtin() -> None:
-    # the built-in architecture registers itself on import
-    from ..models import qwen2  # noqa: F401
+    # the architectures that come with the package register themselves on import
+    from .. import models
+
+    models.import_all()

@@ -284,7 +284,8 @@ __device__ __forceinline__ int cache_row_of(const int* table, int key, int page_
 // inv_freq == nullptr: nothing is fused (q is rotated and the cache written already).
 struct FusedRope {
     const float* inv_freq;    // [D / 2]; the whole head is rotated (rotary dims == D)
-    const int* slot_mapping;  // [rows of the step]: page * page_size + slot of the token, < 0 or null: no write
+    const int* slot_mapping;  // [rows of the step]: page * page_size + slot of the token; < 0: the token's k and v are
+                              // used but not stored; null: the cache holds them already (q alone is rotated)
     bf16* k_cache;
     bf16* v_cache;
 };
@@ -354,10 +355,19 @@ __global__ void __launch_bounds__(WARPS * 32)
     mbar_fence_init();
     __syncthreads();
     pdl_launch_dependents();
-    // With the rotation fused, nothing this kernel reads from the cache was written by the kernel before it
-    // (the token's own key and value come from its qkv row), and the step's metadata was uploaded long
-    // before: the first tiles are requested BEFORE the wait, which only the queries need.
-    const bool early = rope.inv_freq != nullptr;
+    // A kernel that rotates AND writes the cache reads nothing from the cache that this step wrote before it (the
+    // token's own key and value come from its qkv row, which it patches into the tile), and the step's metadata was
+    // uploaded before the step began: it requests its first tiles BEFORE the wait, which only the queries need.
+    // What such a tile holds was written by an EARLIER step.  A launch of this chain begins no sooner than every CTA
+    // of the launch before it has begun, and none of those CTAs ends before the launch before IT has ended; so for
+    // this kernel to run while a kernel of the previous step is unfinished, every CTA of the ~120 launches between
+    // them would have to be resident at once, which the SMs cannot hold (32 CTAs each at most).  Between a graph
+    // replay and the next step the stream orders everything.
+    // A kernel that only rotates q (a layer that reads another layer's cache: no slot mapping) reads position P as
+    // its owner wrote it a few launches ago in THIS step: it waits first and patches nothing.
+    const bool fused = rope.inv_freq != nullptr;
+    const bool patches = fused && rope.slot_mapping != nullptr;
+    const bool early = patches;
     if (!early) {
         pdl_wait();
         FERRIS_TL_BEGIN();
@@ -390,7 +400,7 @@ __global__ void __launch_bounds__(WARPS * 32)
         lim.hi[1] = g + 8 < G ? P : -1;
         lim.lo[0] = lim.lo[1] = lo;
     };
-    if (!early) load_queries();
+    if (!fused) load_queries();
     uint8_t* my_stages = smem + (size_t)warp * STAGES * STAGE_BYTES;
     auto first_tile_of = [&](int i) { return t_begin + (warp + i * WARPS) * NT; };
     // the block-table look-ups of the warp's tiles are independent loads, issued together
@@ -423,12 +433,12 @@ __global__ void __launch_bounds__(WARPS * 32)
     const bool tl_mark = threadIdx.x == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0;
     // the warp whose tiles include the token's own position (in the CTA of the last key range) will rotate k and copy v
     const int own_block = (last_tile >= t_begin && last_tile < t_end) ? (last_tile - t_begin) / NT : -1;
-    const bool owns_token = rope.inv_freq && own_block >= 0 && own_block % WARPS == warp;
+    const bool owns_token = patches && own_block >= 0 && own_block % WARPS == warp;
     float k_lo[D / 64], k_hi[D / 64];
     bf16 v_own[D / 32];
     // where the token's k and v go in the cache: step metadata, read before the wait as well
-    const int own_slot = (owns_token && rope.slot_mapping) ? rope.slot_mapping[tok] : -1;
-    if (early) {
+    const int own_slot = owns_token ? rope.slot_mapping[tok] : -1;
+    if (fused) {
         // the angles depend on the position alone: formed before the wait, off the step's critical path
         for (int i = threadIdx.x; i < D / 2; i += WARPS * 32) {
             float sn, cs;
@@ -436,8 +446,10 @@ __global__ void __launch_bounds__(WARPS * 32)
             cos_sin[i] = make_float2(cs, sn);
         }
         __syncthreads();
-        pdl_wait();
-        FERRIS_TL_BEGIN();
+        if (early) {
+            pdl_wait();
+            FERRIS_TL_BEGIN();
+        }
         FERRIS_TL_MARK(tl_mark, 9);
         if (owns_token) {
             // the token's own k and v (from the q/k/v product that has just finished) are requested with the queries
@@ -466,7 +478,7 @@ __global__ void __launch_bounds__(WARPS * 32)
         FERRIS_TL_MARK(tl_mark && i == 0, 1);
         const uint32_t base = smem_u32(my_stages + s * STAGE_BYTES);
         const int tile0 = first_tile_of(i);
-        if (rope.inv_freq && last_tile >= tile0 && last_tile < tile0 + NT && last_tile < t_end) {
+        if (patches && last_tile >= tile0 && last_tile < tile0 + NT && last_tile < t_end) {
             // this warp holds the tile of the token's own position: its key (rotated) and value come from the
             // step's qkv row, go to the cache for the steps to come, and into the tile just loaded
             uint8_t* tb = my_stages + s * STAGE_BYTES + (last_tile - tile0) * TILE_BYTES;

@@ -71,14 +71,7 @@ struct Params {
     const float* merge_ml;
     int merge_splits, merge_heads, merge_d;
     int* status;
-    unsigned long long* trace;  // optional: CTA (0,0,0) writes nanosecond timestamps of its phases here (8 slots)
 };
-
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return u * (g * (1.0f / (1.0f + expf(-g)))); }
 
@@ -110,7 +103,6 @@ __global__ void __launch_bounds__(THREADS)
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const bool traced = p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
     const int n0 = blockIdx.x * BLOCK_N, t0 = blockIdx.y * p.bt, split = blockIdx.z;
     const int a_bytes = BLOCK_N * BLOCK_K * 2, b_bytes = p.bt * BLOCK_K * 2;
     const int stage_bytes = ACCS * a_bytes + b_bytes;
@@ -152,7 +144,6 @@ __global__ void __launch_bounds__(THREADS)
     }
     pdl_wait();
     FERRIS_TL_BEGIN();
-    if (traced && threadIdx.x == 0) p.trace[0] = p.trace[1] = global_ns();
     // marks of the timeline build: the first epilogue thread of CTA (0, 0, 0)
     const bool tl_mark = threadIdx.x == 64 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
     FERRIS_TL_MARK(tl_mark, 9);  // this thread is past the wait
@@ -274,7 +265,6 @@ __global__ void __launch_bounds__(THREADS)
                 const int s = i % p.stages;
                 ok = mbar_wait(&full[s], (i / p.stages) & 1, p.status, 11);
                 if (!ok) break;
-                if (traced && i == 0) p.trace[2] = global_ns();
                 tcgen05_fence_after();
                 const uint32_t st = smem_u32(smem + (size_t)s * stage_bytes);
                 const uint64_t a_desc = umma_desc_k_major_sw128(st);
@@ -290,7 +280,6 @@ __global__ void __launch_bounds__(THREADS)
                 tcgen05_commit(&empty[s]);  // the stage is free once these MMAs have read it
             }
             tcgen05_commit(&accum_full);
-            if (traced) p.trace[3] = global_ns();
         }
     } else {
         // epilogue: eight warps; warp e reads TMEM lane quarter (warp % 4) (lane = weight row) and every
@@ -302,7 +291,6 @@ __global__ void __launch_bounds__(THREADS)
         const bool have = n_kb > 0 && mbar_wait(&accum_full, 0, p.status, 12);
         tcgen05_fence_after();
         FERRIS_TL_MARK(tl_mark, 1);  // accumulator ready
-        if (traced && threadIdx.x == 64) p.trace[4] = global_ns();
         const bool n_ok = n < p.N;
         const float bias_v = (p.bias && n_ok) ? p.bias[n] : 0.0f;
         if (p.splits == 1) {
@@ -461,7 +449,6 @@ __global__ void __launch_bounds__(THREADS)
         tcgen05_fence_after();
         tmem_dealloc(tmem, tmem_cols);
     }
-    if (traced && threadIdx.x == 32) p.trace[6] = global_ns();
     FERRIS_TL_END(10 + MODE + (p.norm_h ? 4 : 0) + (p.merge_o ? 8 : 0));
 }
 
@@ -1222,8 +1209,6 @@ FERRIS_API int ferris_gemm_tcgen05_builds_tokens(int T, int N, int K, int accumu
 // least up_row_offset + N); out: [T, N] rows ldo apart in the mode's type.
 // mode: 0 bf16 = acc + bias; 1 fp32 = acc + bias; 2 fp32 += acc + bias; 3 bf16 = silu(gate) * up.
 // scratch / counters: as ferris_gemm_tcgen05_plan says (counters must be zero; they are left zero).
-// trace: null, or 8 device u64: CTA (0,0,0) records nanosecond timestamps of its phases (start, set-up done,
-// first stage landed, last MMA issued, accumulator ready, epilogue done, TMEM freed).
 // A token operand that the kernel forms itself instead of loading x: an RMSNorm of fp32 rows, or the merge of the
 // partial results of split-KV attention.
 struct TokenSource {
@@ -1237,13 +1222,13 @@ struct TokenSource {
 
 static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N, int K,
                              int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch, int* counters,
-                             void* stream, unsigned long long* trace, const TokenSource& src);
+                             void* stream, const TokenSource& src);
 
 FERRIS_API int ferris_gemm_tcgen05(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N,
                                    int K, int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch,
-                                   int* counters, void* stream, unsigned long long* trace) {
+                                   int* counters, void* stream) {
     return gemm_tcgen05_impl(x, w, bias, out, mode, T, N, K, ldx, ldw, ldo, rows_w, up_row_offset, scratch, counters,
-                             stream, trace, TokenSource());
+                             stream, TokenSource());
 }
 
 // The same product with RMSNorm fused in front: x = bf16((h * rstd(h)) * norm_w) is formed inside the kernel from the
@@ -1260,7 +1245,7 @@ FERRIS_API int ferris_norm_gemm_tcgen05(const float* h, const float* norm_w, flo
     src.norm_w = norm_w;
     src.norm_eps = norm_eps;
     return gemm_tcgen05_impl(w, w, bias, out, mode, T, N, K, K, ldw, ldo, rows_w, up_row_offset, nullptr, nullptr, stream,
-                             nullptr, src);
+                             src);
 }
 
 // The same product with the merge of split-KV attention fused in front: the token operand x [T, heads * d] is formed
@@ -1282,8 +1267,7 @@ FERRIS_API int ferris_merge_gemm_tcgen05(const float* scratch_parts, int heads, 
     src.merge_heads = heads;
     src.merge_d = d;
     const int K = heads * d;
-    return gemm_tcgen05_impl(w, w, bias, out, mode, T, N, K, K, ldw, ldo, rows_w, 0, nullptr, nullptr, stream, nullptr,
-                             src);
+    return gemm_tcgen05_impl(w, w, bias, out, mode, T, N, K, K, ldw, ldo, rows_w, 0, nullptr, nullptr, stream, src);
 }
 
 // The persistent token-major kernel for a long step (T >= 128 tokens; output rows aligned for 16-byte stores).
@@ -1350,7 +1334,7 @@ static int run_tokens_m(const void* x, const void* w, const float* bias, void* o
 
 static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, void* out, int mode, int T, int N, int K,
                              int ldx, int ldw, int ldo, int rows_w, int up_row_offset, float* scratch, int* counters,
-                             void* stream, unsigned long long* trace, const TokenSource& src) {
+                             void* stream, const TokenSource& src) {
     const bool built = src.norm_h || src.merge_o;
     if (T <= 0 || N <= 0) return FERRIS_OK;
     if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ldx < K || ldw < K)
@@ -1371,7 +1355,7 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
     cudaStream_t s = (cudaStream_t)stream;
     // long steps: the persistent token-major kernel (its 16-byte stores need aligned output rows)
     const int elt = (mode == STORE_BF16 || mode == SWIGLU_BF16) ? 2 : 4;
-    const bool long_step = !trace && !built && token_major_pays(mode, T, N, K) && ((size_t)ldo * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0;
+    const bool long_step = !built && token_major_pays(mode, T, N, K) && ((size_t)ldo * elt) % 16 == 0 && ((uintptr_t)out & 15) == 0;
     if (long_step && T > PT_BLOCK_M && ferris_gemm_pair_enabled(mode, T)) {
         // CTA pairs: tiles of 256 tokens x 256 weight rows (128 + 128 in SwiGLU mode), or x 128 where the
         // wider tile would leave pairs of SMs without work
@@ -1447,7 +1431,6 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
     p.merge_heads = src.merge_heads;
     p.merge_d = src.merge_d;
     p.status = ferris_status_ptr();
-    p.trace = trace;
     const int stage_bytes = accs * BLOCK_N * BLOCK_K * 2 + bt * BLOCK_K * 2;
     const int part_bytes = cluster ? accs * bt * BLOCK_N * 4 : 0;
     const int per_split = (p.kblocks + splits - 1) / splits;

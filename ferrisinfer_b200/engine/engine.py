@@ -117,14 +117,23 @@ class Engine:
 
     # ------------------------------------------------------------------ set-up
     def _pages_that_fit(self, needs, page_size, fraction, sc) -> int:
-        from ..parts.base import PagedKV
+        """Pages per group that ``fraction`` of the free device memory holds, after what the per-request state of
+        fixed size (mixers' and the sampler's, one row per request slot and one more) takes from it."""
+        from ..parts.base import FixedState, PagedKV
 
         item = 2 if self.dtype == torch.bfloat16 else 4
         per_page = sum(2 * n.num_kv_heads * n.head_dim * page_size * item for n in needs if isinstance(n, PagedKV))
         if per_page == 0:
             return 1
+        states = [n for n in needs if isinstance(n, FixedState)] + [RNG_NEED]
+        state_bytes = 0
+        for n in states:
+            count = 1
+            for s in n.shape:
+                count *= int(s)
+            state_bytes += (sc.max_batch_size + 1) * count * torch.empty((), dtype=n.dtype).element_size()
         free, _total = torch.cuda.mem_get_info(self.device)
-        pages = int(free * fraction) // per_page
+        pages = max(0, int(free * fraction) - state_bytes) // per_page
         most = sc.max_batch_size * (-(-sc.max_sequence_length // page_size))
         return max(1, min(pages, most))
 

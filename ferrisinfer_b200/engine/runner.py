@@ -14,6 +14,7 @@ and forms logits only at the rows asked for.  Afterwards the requests' token cou
 from __future__ import annotations
 
 import gc
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Any, Optional, Sequence
 
@@ -40,7 +41,9 @@ class StepEntry:
 
 @dataclass
 class _HostStep:
-    """A step laid out on the host: the int32 pieces that go to the device, and what the host keeps."""
+    """A step laid out on the host: the int32 pieces that go to the device, and what the host keeps.
+    ``T``, ``S`` and ``n_want`` count the rows on the device, padding rows included; ``real`` is the number
+    of requests (and of wanted rows) that the caller brought."""
 
     pieces: list
     T: int
@@ -50,6 +53,7 @@ class _HostStep:
     max_blocks: int
     seqs: list
     n_want: int
+    real: int = 0
 
 
 @dataclass
@@ -66,14 +70,20 @@ class ModelRunner:
     """Owns the model, the cache manager and the workspace; ``step`` is the only way tokens run.
 
     Steps in which every request brings exactly one token and wants its logits (decoding) are replayed
-    from CUDA graphs, one per shape of step (counts of tokens, requests and wanted rows, width of the block
-    tables): the ~150 kernel launches of a step become one.  Their metadata lives in a static device buffer
-    that is rewritten before each replay.  Any other shape of step is recorded when it comes a second time
-    (portions of a fixed size recur); the rest launch their kernels one by one."""
+    from CUDA graphs: the ~150 kernel launches of a step become one.  Such a step is filled up with padding
+    rows to the next of a few batch sizes (``DECODE_BUCKETS``), so that a pool of 1..N decoding requests needs
+    a handful of graphs, one per (batch size, width of the block tables); a padding row is a token at position
+    0 of a request that does not exist, whose key, value and state go to the cache manager's padding page and
+    padding slot, and whose logits nobody reads.  All decode graphs write one shared logits buffer.  Any other
+    shape of step is recorded when it comes a second time (portions of a fixed size recur); the rest launch
+    their kernels one by one.  At most ``MAX_GRAPHS`` recorded steps are kept, the least recently replayed
+    goes first.  The metadata of a recorded step lives in a static device buffer that is rewritten before
+    each replay."""
 
     N_FIXED = 7  # token_ids, positions, token_seq, q_start, start_pos, state_slot, want
-    MAX_GRAPHS = 64  # recorded shapes of step
-    MAX_GRAPH_LOGITS_BYTES = 64 << 20  # a recorded step owns its logits buffer
+    MAX_GRAPHS = 48  # recorded shapes of step, decode steps included
+    MAX_GRAPH_LOGITS_BYTES = 64 << 20  # a recorded step that is no decode step owns its logits buffer
+    DECODE_BUCKETS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512)
 
     def __init__(self, model: DecoderModel, dtype: torch.dtype, device, page_size: int, num_pages: int,
                  max_requests: int, max_model_len: Optional[int] = None, extra_states: Optional[dict] = None,
@@ -95,14 +105,20 @@ class ModelRunner:
         self._staging = []  # ring of (pinned buffer, event of the last copy out of it)
         self._staging_next = 0
         self.cuda_graphs = bool(cuda_graphs) and self.device.type == "cuda" and getattr(model, "graph_safe", False)
-        self._graphs: dict = {}
+        self.max_requests = int(max_requests)
+        self._graphs: OrderedDict = OrderedDict()  # shape of step -> recorded step, least recently replayed first
         self._shapes_seen: dict = {}
+        self._decode_logits: Optional[torch.Tensor] = None  # [largest bucket, vocab], shared by the decode graphs
         self.graph_replays = 0
         self.graph_kernels = 0  # kernel launches made through graph replays
+        self.graphs_dropped = 0
 
     # ------------------------------------------------------------------ requests
-    def add_request(self, request_id) -> int:
-        return self.cache.admit(request_id).slot
+    def add_request(self, request_id, prompt: Optional[Sequence[int]] = None) -> int:
+        """Admit a request; returns its state slot.  With ``prompt`` (its known tokens) and prefix sharing on,
+        leading full pages that the cache already holds are borrowed: ``num_tokens(request_id)`` then says how
+        many tokens the request need not bring."""
+        return self.cache.admit(request_id, None if prompt is None else list(prompt)).slot
 
     def has_request(self, request_id) -> bool:
         return self.cache.has(request_id)
@@ -129,14 +145,15 @@ class ModelRunner:
         if device_tokens is not None and (any(len(e.tokens) != 1 for e in entries) or device_tokens.numel() != len(entries)
                                           or device_tokens.dtype != torch.int32):
             raise FerrisError("tokens on the device: one int32 for each entry of one token is needed")
-        host = self._layout(entries)
-        decode = host.max_q == 1 and host.n_want == host.S and all(list(e.want) == [0] for e in entries)
-        if self.cuda_graphs and out is None and self._graph_worthwhile(host, decode):
-            logits = self._step_graph(host, device_tokens)
+        decode = all(len(e.tokens) == 1 and len(e.want) == 1 and e.want[0] == 0 for e in entries)
+        graphs = self.cuda_graphs and out is None
+        host = self._layout(entries, pad_to=self._bucket(len(entries)) if (decode and graphs) else 0)
+        if graphs and self._graph_worthwhile(host, decode):
+            logits = self._step_graph(host, device_tokens, decode)
         else:
             dev = self._upload(host.pieces)
             if device_tokens is not None:
-                dev[:host.T].copy_(device_tokens)
+                dev[:host.real].copy_(device_tokens)
             ctx, logits_index = self._context(host, dev)
             logits = None
             if host.n_want:
@@ -148,11 +165,19 @@ class ModelRunner:
         self.steps_run += 1
         return logits
 
+    def _bucket(self, requests: int) -> int:
+        """The batch size a decode step of ``requests`` single tokens is filled up to."""
+        for b in self.DECODE_BUCKETS:
+            if b >= requests:
+                return b
+        return requests
+
     @staticmethod
     def _shape_key(host: _HostStep) -> tuple:
         """What fixes every launch of a step: the counts of tokens, requests, wanted rows and single tokens beside
         portions, the longest share and the width of the block tables.  Everything else (which tokens, positions,
-        pages, how the tokens divide among the requests) is data in the step's metadata buffer."""
+        pages, how the tokens divide among the requests, which rows are wanted) is data in the step's metadata
+        buffer."""
         return (host.T, host.S, host.max_q, host.max_blocks, host.n_want, int(host.pieces[-1].size))
 
     def _graph_worthwhile(self, host: _HostStep, decode: bool) -> bool:
@@ -167,28 +192,48 @@ class ModelRunner:
         if len(self._shapes_seen) > 4096:
             self._shapes_seen.clear()
         self._shapes_seen[key] = seen + 1
-        return seen >= 1 and host.n_want * self.vocab_size * 4 <= self.MAX_GRAPH_LOGITS_BYTES \
-            and len(self._graphs) < self.MAX_GRAPHS
+        return seen >= 1 and host.n_want * self.vocab_size * 4 <= self.MAX_GRAPH_LOGITS_BYTES
 
-    def _step_graph(self, host: _HostStep, device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def drop_graphs(self) -> None:
+        """Forget every recorded step (their buffers go with them)."""
+        if self._graphs:
+            torch.cuda.synchronize(self.device)
+            self.graphs_dropped += len(self._graphs)
+            self._graphs.clear()
+        self.workspace.unpin()
+
+    def _step_graph(self, host: _HostStep, device_tokens: Optional[torch.Tensor] = None,
+                    decode: bool = False) -> torch.Tensor:
         key = self._shape_key(host)
         entry = self._graphs.get(key)
         if entry is None:
+            while len(self._graphs) >= self.MAX_GRAPHS:
+                # the least recently replayed goes; nothing of it may still be running when its memory is freed
+                torch.cuda.synchronize(self.device)
+                self._graphs.popitem(last=False)
+                self.graphs_dropped += 1
             total = sum(p.size for p in host.pieces)
             meta = torch.zeros(total, dtype=torch.int32, device=self.device)
             self._upload(host.pieces, meta)
             if device_tokens is not None:
-                meta[:host.T].copy_(device_tokens)
+                meta[:host.real].copy_(device_tokens)
             ctx, logits_index = self._context(host, meta)
             # launch geometry that depends on the keys' length is fixed for the width of the block table
             ctx.max_kv_len = host.max_blocks * self.cache.page_size
             logits = None
-            if host.n_want:
+            if host.n_want and decode:
+                if self._decode_logits is None:
+                    rows = max(self._bucket(self.max_requests), host.n_want)
+                    self._decode_logits = torch.empty(rows, self.vocab_size, dtype=torch.float32, device=self.device)
+                if host.n_want <= self._decode_logits.shape[0]:
+                    logits = self._decode_logits[:host.n_want]
+            if host.n_want and logits is None:
                 logits = torch.empty(host.n_want, self.vocab_size, dtype=torch.float32, device=self.device)
             entry = _GraphEntry(meta, ctx, logits_index, logits)
             # the first step of this shape runs eagerly (it also sizes every workspace buffer) ...
             self.model.forward(ctx, self.cache.layer_caches, logits_index, logits)
-            # ... and is then recorded for the steps to come
+            # ... and is then recorded for the steps to come; from here on the workspace keeps what it replaces
+            self.workspace.pin()
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
@@ -206,15 +251,16 @@ class ModelRunner:
             entry.graph = graph
             self._graphs[key] = entry
             # the capture itself ran nothing, but the eager run before it did: the result is in ``logits``
-            return logits
+            return logits[:host.real] if decode else logits
+        self._graphs.move_to_end(key)
         self._upload(host.pieces, entry.meta)
         if device_tokens is not None:
-            entry.meta[:host.T].copy_(device_tokens)  # the token ids are the first piece of the metadata
+            entry.meta[:host.real].copy_(device_tokens)  # the token ids are the first piece of the metadata
         entry.ctx.seqs = host.seqs
         entry.graph.replay()
         self.graph_replays += 1
         self.graph_kernels += entry.kernels
-        return entry.logits
+        return entry.logits[:host.real] if decode else entry.logits
 
     # ------------------------------------------------------------------- upload
     def _upload(self, pieces, dest: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -248,7 +294,9 @@ class ModelRunner:
         return dest
 
     # ----------------------------------------------------------- step preparation
-    def _layout(self, entries) -> _HostStep:
+    def _layout(self, entries, pad_to: int = 0) -> _HostStep:
+        """Check the step, take its pages (all of the step or none; a refused step leaves no trace in the
+        cache) and lay its metadata out.  ``pad_to``: a step of single tokens is filled up to this many rows."""
         cache = self.cache
         seen = set()
         T = 0
@@ -261,12 +309,20 @@ class ModelRunner:
                 if not (0 <= w < n):
                     raise FerrisError(f"request {e.request_id!r}: wanted place {w} is not among its {n} tokens")
             T += n
+        S = len(entries)
+        if T == S:  # one token each
+            token_ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=S)
+        else:
+            token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        if token_ids.min() < 0 or token_ids.max() >= self.vocab_size:
+            raise FerrisError(f"a token id of the step lies outside [0, {self.vocab_size})")
+        token_ids = token_ids.astype(np.int32)
         admitted_here = []
-        for e in entries:
-            if not cache.has(e.request_id):
-                cache.admit(e.request_id)
-                admitted_here.append(e.request_id)
         try:
+            for e in entries:
+                if not cache.has(e.request_id):
+                    cache.admit(e.request_id)
+                    admitted_here.append(e.request_id)
             # all pages of the step or none
             short = {g.gid: 0 for g in cache.groups}
             for e in entries:
@@ -289,25 +345,27 @@ class ModelRunner:
         for e in entries:
             cache.extend(e.request_id, cache.get(e.request_id).num_tokens + len(e.tokens))
 
-        S = len(entries)
         ps = cache.page_size
         rcs = [cache.get(e.request_id) for e in entries]
         q_lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=S)
         start_pos = np.fromiter((rc.num_tokens for rc in rcs), dtype=np.int32, count=S)
         state_slot = np.fromiter((rc.slot for rc in rcs), dtype=np.int32, count=S)
+        pad = max(0, pad_to - S) if T == S else 0
+        if pad:
+            # padding rows: one token (id 0) at position 0 of a request that holds the padding page and slot
+            token_ids = np.concatenate([token_ids, np.zeros(pad, dtype=np.int32)])
+            q_lens = np.concatenate([q_lens, np.ones(pad, dtype=np.int32)])
+            start_pos = np.concatenate([start_pos, np.zeros(pad, dtype=np.int32)])
+            state_slot = np.concatenate([state_slot, np.full(pad, cache.padding_slot, dtype=np.int32)])
+        real, S, T = S, S + pad, T + pad
         q_start = np.zeros(S + 1, dtype=np.int32)
         np.cumsum(q_lens, out=q_start[1:])
-        if T == S:  # one token each
-            token_ids = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=S)
+        if T == S:
             token_seq = np.arange(S, dtype=np.int32)
             positions = start_pos.copy()
         else:
-            token_ids = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
             token_seq = np.repeat(np.arange(S, dtype=np.int32), q_lens)
             positions = (np.arange(T, dtype=np.int32) - q_start[token_seq] + start_pos[token_seq]).astype(np.int32)
-        if token_ids.min() < 0 or token_ids.max() >= self.vocab_size:
-            raise FerrisError(f"a token id of the step lies outside [0, {self.vocab_size})")
-        token_ids = token_ids.astype(np.int32)
         want_rows = []
         seqs = []
         for i, (e, rc) in enumerate(zip(entries, rcs)):
@@ -317,6 +375,7 @@ class ModelRunner:
             elif e.want:
                 want_rows += [row + w for w in e.want]
             seqs.append(SeqInfo(e.request_id, row, int(q_lens[i]), rc.num_tokens, rc.slot))
+        want_rows += list(range(real, S))  # the padding rows' logits are formed too: the step's shape is its bucket's
         max_q = int(q_lens.max())
         max_kv = int((start_pos + q_lens).max())
         # block tables are as wide as the next power of two of what the longest request needs, so that the
@@ -332,6 +391,8 @@ class ModelRunner:
             for i, e in enumerate(entries):
                 arr = cache.block_table_array(e.request_id, g.gid)
                 tables[i, :arr.size] = arr
+            if pad:
+                tables[real:, 0] = cache.padding_page(g.gid)
             pages = tables[token_seq, positions // ps]
             if (pages < 0).any():
                 raise CacheError(f"a token of the step has no page in group {g.gid}")
@@ -343,7 +404,7 @@ class ModelRunner:
             pieces += [slot_mapping, tables.reshape(-1)]
         singles = [s.q_start for s in seqs if s.q_len == 1] if max_q > 1 else []
         pieces.append(np.asarray(singles, dtype=np.int32))
-        return _HostStep(pieces, T, S, max_q, max_kv, max_blocks, seqs, int(want.size))
+        return _HostStep(pieces, T, S, max_q, max_kv, max_blocks, seqs, int(want.size), real)
 
     def _context(self, host: _HostStep, dev: torch.Tensor):
         views = []

@@ -31,7 +31,7 @@ _VP, _I, _F, _LL = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longl
 # Argument types of the launchers on the model's path: with these declared, plain Python ints and floats go straight
 # to C (a pointer would otherwise be cut to 32 bits, and wrapping every argument in a ctypes object costs microseconds).
 _SIGNATURES = {
-    "ferris_gemm_tcgen05": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _I, _VP, _VP, _VP, _VP],
+    "ferris_gemm_tcgen05": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _I, _VP, _VP, _VP],
     "ferris_norm_gemm_tcgen05": [_VP, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _VP],
     "ferris_merge_gemm_tcgen05": [_VP, _I, _I, _I, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _VP],
     "ferris_qkv_rope_gemm_tcgen05": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP],
@@ -212,8 +212,7 @@ def tensor_core_gemm_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
 _uses_clusters = None
 
 
-def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row_offset: int = 0,
-                 trace: Optional[torch.Tensor] = None):
+def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row_offset: int = 0):
     """out = x w^T on the tcgen05 tensor cores.  mode 0: bf16 store (+bias); 1: fp32 store (+bias);
     2: fp32 out += ; 3: bf16 silu(x w[:N]^T) * (x w[up_row_offset:up_row_offset+N]^T)."""
     global _uses_clusters
@@ -244,7 +243,7 @@ def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row
         lib.ferris_gemm_tcgen05(x.data_ptr(), w.data_ptr(), None if bias is None else bias.data_ptr(), out.data_ptr(),
                                 mode, T, N, K, ldx, ldw, ldo, rows_w, up_row_offset,
                                 None if scratch is None else scratch.data_ptr(), None if cnt is None else cnt.data_ptr(),
-                                _stream(), None if trace is None else trace.data_ptr()),
+                                _stream()),
         "tensor-core gemm",
     )
 

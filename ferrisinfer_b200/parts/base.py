@@ -155,11 +155,29 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    """What mixes the tokens of a request: attention over cached keys and values, a recurrence over a state
+    of fixed size, or anything else that declares its need with ``cache_need``.
+
+    A step hands the mixer all its tokens as one batch; which row belongs to which request is told twice, on
+    the host (``ctx.seqs``, a list of ``SeqInfo``) and on the device.  A mixer that wants its steps recorded
+    into CUDA graphs (``graph_safe``) works from the device arrays alone, because a replayed step runs no
+    Python: ``ctx.token_seq`` [T] (index of each row's request within the step), ``ctx.positions`` [T],
+    ``ctx.seq_q_start`` [S + 1] (first row of each request; rows of a request are consecutive and in order),
+    ``ctx.seq_start_pos`` [S] (tokens the request held before the step), ``ctx.seq_state_slot`` [S] (the row
+    of ``cache.state`` that is the request's, for a ``FixedState`` need) and, for a ``PagedKV`` need,
+    ``ctx.paged[cache.group]`` (block tables [S, max_blocks] and the cache slot of every row).  The shapes
+    T and S are those of the recorded step; the contents change from replay to replay.  A decode step may
+    carry padding rows after the real ones: single tokens at position 0 of requests that do not exist, whose
+    state slot and page are the cache manager's padding slot and padding page, so whatever a mixer writes
+    for them lands where nobody reads.  A mixer with state must carry the state across steps through its
+    slot and process a request's rows in order; it may not assume that a step holds the whole request."""
+
     # True if forward takes its input ``x`` either as a tensor or as the object that ``Norm.lazy`` returns
     # (which it hands to ``ops.gemm`` unchanged, or turns into a tensor with ``materialize()``).
     accepts_lazy_norm = False
-    # True if forward only launches kernels on the current stream from device-resident metadata (no host
-    # loops over requests, no allocation), so that a decode step can be recorded into a CUDA graph.
+    # True if forward only launches work on the current stream from device-resident metadata (no host
+    # loops over requests, no synchronisation, no read of ``ctx.seqs``), so that a step can be recorded into
+    # a CUDA graph.  One part that says False switches graphs off for the whole model.
     graph_safe = False
 
     def cache_need(self):

@@ -134,20 +134,31 @@ class SafetensorsFolder:
     def dtype(self, name: str) -> torch.dtype:
         return self.entries[name].dtype
 
-    def read(self, name: str) -> torch.Tensor:
-        """The tensor as stored (a CPU tensor that owns its memory)."""
-        e = self.entries[name]
-        mm = self._maps.get(e.file)
+    def _map_of(self, path: str) -> mmap.mmap:
+        mm = self._maps.get(path)
         if mm is None:
-            with open(e.file, "rb") as f:
+            with open(path, "rb") as f:
                 mm = mmap.mmap(f.fileno(), 0, access=mmap.ACCESS_READ)
-            self._maps[e.file] = mm
+            self._maps[path] = mm
+        return mm
+
+    def raw(self, name: str):
+        """The tensor's bytes as a read-only uint8 numpy array over the file's mapping: nothing is copied, pages
+        come in as they are touched."""
+        import numpy as np
+
+        e = self.entries[name]
+        return np.frombuffer(self._map_of(e.file), dtype=np.uint8, count=e.end - e.begin, offset=e.begin)
+
+    def read(self, name: str) -> torch.Tensor:
+        """The tensor as stored (a CPU tensor that owns its memory: one copy out of the mapping)."""
+        e = self.entries[name]
         count = 1
         for s in e.shape:
             count *= s
         if count == 0:
             return torch.empty(e.shape, dtype=e.dtype)
-        flat = torch.frombuffer(bytearray(mm[e.begin : e.end]), dtype=e.dtype)
+        flat = torch.from_numpy(self.raw(name).copy()).view(e.dtype)
         return flat.reshape(e.shape)
 
     def close(self) -> None:

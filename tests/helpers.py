@@ -215,13 +215,15 @@ def replay(runner, steps: list) -> dict:
     return out
 
 
-def oracle_logits(config: dict, weights: dict, requests: dict, dtype=torch.float64) -> dict:
-    """{(request id, position): logits row} from the plain implementation, whole sequences."""
+def oracle_logits(config: dict, weights: dict, requests: dict, dtype=torch.float64, device=None) -> dict:
+    """{(request id, position): logits row (CPU fp32)} from the plain implementation, whole sequences."""
     import plain_qwen2
 
+    if device is not None:
+        weights = {n: t.to(device) for n, t in weights.items()}
     out = {}
     for rid, ids in requests.items():
-        logits = plain_qwen2.forward(config, weights, ids, dtype).to(torch.float32)
+        logits = plain_qwen2.forward(config, weights, ids, dtype).to("cpu", torch.float32)
         for p in range(len(ids)):
             out[(rid, p)] = logits[p]
     return out

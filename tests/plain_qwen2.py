@@ -1,8 +1,8 @@
 """A plain, slow implementation of the Qwen2 decoder: whole sequences, no cache, one function per part.
 
 It is the oracle of the tests.  It shares no code with the package: it reads config.json as a
-dict and the tensors by their names in the model folder, and computes on the CPU with torch
-(float32, or float64 for a tighter oracle).
+dict and the tensors by their names in the model folder, and computes with torch's own operators
+(float32, or float64 for a tighter oracle), on the CPU unless it is told another device.
 
 It rests on the reference's formulas, each cited below by the file's path within
 Micro-ATP/FerrisInfer.  The reference is Rust and cannot be compiled on this image (no cargo or
@@ -49,7 +49,7 @@ def derived(config: dict) -> dict:
 # ------------------------------------------------------------------------------------- parts
 def embedding(ids, table):
     """h[t, :] = E[id_t, :]; no scaling (crates/ferrisinfer-kernel/src/cpu/attention.rs:3-99)."""
-    return table[torch.as_tensor(ids, dtype=torch.long)]
+    return table[torch.as_tensor(ids, dtype=torch.long, device=table.device)]
 
 
 def rms_norm(x, weight, eps):
@@ -86,8 +86,8 @@ def rope(x, positions, head_dim, rotary_dims, theta):
     if rotary_dims == 0:
         return x
     half = rotary_dims // 2
-    inv_freq = rotary_inverse_frequencies(head_dim, rotary_dims, theta)  # f32
-    pos = torch.as_tensor(positions, dtype=torch.float32)
+    inv_freq = rotary_inverse_frequencies(head_dim, rotary_dims, theta).to(x.device)  # f32
+    pos = torch.as_tensor(positions, dtype=torch.float32, device=x.device)
     angle = (pos[:, None] * inv_freq[None, :]).to(torch.float32)  # the product itself is f32
     angle = angle.to(x.dtype)
     cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
@@ -108,7 +108,7 @@ def attention(q, k, v, positions, window=None):
     nkv = k.shape[1]
     group = nh // nkv
     scale = 1.0 / math.sqrt(d)
-    pos = torch.as_tensor(positions, dtype=torch.long)
+    pos = torch.as_tensor(positions, dtype=torch.long, device=q.device)
     visible = pos[None, :] <= pos[:, None]
     if window is not None:
         visible &= pos[None, :] > (pos[:, None] - window)
@@ -151,12 +151,14 @@ def block(h, w, prefix, positions, dv, window):
                                    w[f"{prefix}.mlp.down_proj.weight"])
 
 
-def forward(config: dict, weights: dict, ids, dtype=torch.float32):
+def forward(config: dict, weights: dict, ids, dtype=torch.float32, device=None):
     """Logits [n, V] of every position of the token sequence ``ids``
     (crates/ferrisinfer-runtime/src/reference.rs:517-524 with :372-423 and :145-149).
-    ``weights`` holds the folder's tensors by name; they are widened to ``dtype`` first."""
+    ``weights`` holds the folder's tensors by name; they are widened to ``dtype`` first.
+    ``device``: where torch computes (the tensors' own by default); the large configurations of the GPU tests
+    run these same lines in float64 on the GPU, because the CPU takes minutes for them."""
     dv = derived(config)
-    w = {n: t.to(dtype) for n, t in weights.items()}
+    w = {n: t.to(device=device, dtype=dtype) for n, t in weights.items()}
     positions = list(range(len(ids)))
     h = embedding(ids, w["model.embed_tokens.weight"])
     for l in range(dv["layers"]):

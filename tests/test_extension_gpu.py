@@ -2,7 +2,10 @@
 to the package's files.
 
 The toy mixer keeps a state of its own per request (no keys, no pages): s <- decay * s + x_t for each token in
-order, out_t = s * gain.  The toy architecture puts it in layer 0, grouped-query attention in layer 1, names
+order, out_t = s * gain.  It reads which token belongs to which request, and which slot holds that request's state,
+from the step's DEVICE arrays alone (no loop over requests on the host), so it may be recorded into a CUDA graph:
+its decode steps are replayed from graphs like the built-in mixers', padding rows and all.  The toy architecture
+puts it in layer 0, grouped-query attention in layer 1, names
 layer 0 a second time in the run order (shared weights, a state of its own), and lets a last run of layer 1
 read the cache that the earlier run of layer 1 wrote.  It is never anyone's model: it only shows that layers
 are data.
@@ -51,6 +54,8 @@ def register_toy():
                                         register_part)
 
     class DecayMixer(Mixer):
+        graph_safe = True  # device-resident metadata only, no host loop, no synchronisation
+
         def __init__(self, hidden_size, decay):
             self.hidden_size, self.decay = hidden_size, decay
             self.gain = None
@@ -65,11 +70,22 @@ def register_toy():
             return FixedState((self.hidden_size,), torch.float32)
 
         def forward(self, x, h, ctx, cache, owns_cache):
-            for s in ctx.seqs:  # each request's tokens in order, its state carried in its slot
-                state = cache.state[s.state_slot]
-                for t in range(s.q_start, s.q_start + s.q_len):
-                    state.mul_(self.decay).add_(x[t].float())
-                    h[t] += state * self.gain
+            # s_t = decay^(j+1) s_before + sum_{i <= j} decay^(j-i) x_i for the j-th token of a request in this step:
+            # a masked [T, T] matrix of powers of the decay built from ctx.token_seq, times the step's rows
+            T = ctx.num_tokens
+            seq = ctx.token_seq.long()
+            rows = torch.arange(T, device=x.device)
+            offset = rows - ctx.seq_q_start.long()[seq]
+            lag = rows[:, None] - rows[None, :]
+            same = (seq[:, None] == seq[None, :]) & (lag >= 0)
+            powers = torch.where(same, torch.pow(self.decay, lag.clamp(min=0).float()), 0.0)
+            slots = ctx.seq_state_slot.long()
+            before = cache.state[slots[seq]]
+            carried = torch.pow(self.decay, (offset + 1).float())[:, None] * before
+            state = powers @ x.float() + carried
+            h += state * self.gain
+            last = ctx.seq_q_start.long()[1:] - 1  # each request's last row of the step holds its new state
+            cache.state.index_copy_(0, slots, state[last])
 
     register_part("mixer", "toy_decay", DecayMixer, replace=True)
 
@@ -137,39 +153,58 @@ def toy_plain_forward(cfg: ToyConfig, w: dict, ids):
     return plain.linear(plain.rms_norm(h, w["model.norm.weight"], cfg.eps), w["model.embed_tokens.weight"])
 
 
-def test_a_toy_mixer_with_state_is_registered_built_and_stepped(device, tmp_path):
+VARIANTS = {
+    # 32-bit, head size 16, pages of 4: the general attention kernel
+    "f32": (ToyConfig(), torch.float32, 4, dict(atol=2e-5, rtol=1e-4)),
+    # bfloat16, head size 64, pages of 16: the tensor-core attention kernels, also for the run that reads another
+    # run's cache (its decode kernel rotates q and must take the token's key and value from the cache)
+    "bf16": (ToyConfig(vocab_size=150, hidden_size=128, intermediate_size=96, num_heads=4, num_kv_heads=2, head_dim=64,
+                       decay=0.6, theta=10000.0), torch.bfloat16, 16, helpers.TOL[torch.bfloat16]),
+}
+
+
+@pytest.mark.parametrize("variant", list(VARIANTS))
+def test_a_toy_mixer_with_state_is_registered_built_and_stepped(variant, device, tmp_path):
     from ferrisinfer_b200.config import registered_architectures
     from ferrisinfer_b200.engine.runner import ModelRunner
+    from ferrisinfer_b200.kernels import ops
     from ferrisinfer_b200.parts import FixedState, PagedKV
     from ferrisinfer_b200.weights import load_model
 
+    cfg, dtype, page, tol = VARIANTS[variant]
     register_toy()
     assert "ToyDecayForCausalLM" in registered_architectures()
-    cfg = ToyConfig()
-    folder = helpers.make_folder(tmp_path, cfg.to_dict(), seed=5, store_dtype="float32")
+    folder = helpers.make_folder(tmp_path, cfg.to_dict(), seed=5, store_dtype="float32" if dtype is F32 else "bfloat16",
+                                 score_std=1.5)
     config, weights = helpers.read_folder(folder)
     assert config["architectures"] == ["ToyDecayForCausalLM"] and "model.layers.0.self_attn.gain" in weights
 
-    model, loaded = load_model(folder, "float32", device)
+    model, loaded = load_model(folder, dtype, device)
     assert loaded == cfg
+    assert model.graph_safe, "a mixer with state that works from device arrays does not switch graphs off"
     needs = model.cache_needs()
     assert isinstance(needs[0], FixedState) and isinstance(needs[1], PagedKV) and isinstance(needs[2], FixedState)
     assert needs[3] is None  # reads the cache of run 1
 
-    requests = {f"t{i}": helpers.random_ids(cfg.vocab_size, n, n) for i, n in enumerate((40, 9, 27, 33, 18))}
+    requests = {f"t{i}": helpers.random_ids(cfg.vocab_size, n, n) for i, n in enumerate((40, 9, 27, 33, 18, 70))}
     want = {}
     for rid, ids in requests.items():
         logits = toy_plain_forward(cfg, weights, ids).float()
         for p in range(len(ids)):
             want[(rid, p)] = logits[p]
-    for steps in (helpers.trace_whole(requests), helpers.trace_portions(requests),
+    replays = 0
+    for steps in (helpers.trace_whole(requests), helpers.trace_portions(requests), helpers.trace_tail_decoded(requests, 24),
                   helpers.trace_mixed(requests, seed=1, max_live=3)):
-        runner = ModelRunner(model, F32, device, page_size=4, num_pages=helpers.tokens_held(steps, 4) // 4,
+        runner = ModelRunner(model, dtype, device, page_size=page, num_pages=helpers.tokens_held(steps, page) // page,
                              max_requests=3)
         assert len(runner.cache.groups) == 1 and runner.cache.groups[0].members == [1]
-        assert runner.cache.layer_caches[0].state.shape == (3, cfg.hidden_size)
+        # one row per request slot and the padding slot's
+        assert runner.cache.layer_caches[0].state.shape == (3 + 1, cfg.hidden_size)
         assert runner.cache.layer_caches[2].state.data_ptr() != runner.cache.layer_caches[0].state.data_ptr()
         got = helpers.replay(runner, steps)
-        bad = helpers.first_mismatch(got, want, atol=2e-5, rtol=1e-4)
+        assert ops.kernel_status() == 0
+        bad = helpers.first_mismatch(got, want, **tol)
         assert bad is None, bad
         runner.cache.check_invariants()
+        replays += runner.graph_replays
+    assert replays > 50, "the single-token steps of the model with the toy mixer were replayed from graphs"

@@ -631,11 +631,17 @@ def test_attention_step_of_single_tokens_rotates_and_writes_on_its_way(nh, nkv, 
     assert torch.equal(k1, k2) and torch.equal(v1, v2), "the cache holds the same rotated keys and values"
     assert torch.equal(qkv1, qkv), "the fused path leaves the step's qkv rows alone"
     assert torch.allclose(got.float(), want.float(), atol=2e-2, rtol=2e-2), (got.float() - want.float()).abs().max()
-    # a layer that reads another layer's cache: q is rotated, nothing is written
+    # a layer that reads another layer's cache: q is rotated, nothing is written, and the token's key and value are
+    # the ones the cache holds, not the ones in this layer's own qkv rows (which are made different here)
     k3, v3 = k2.clone(), v2.clone()
+    other = qkv.clone()
+    other[:, nh * d:] = torch.randn(T, 2 * nkv * d, generator=g).to(BF16).to(device)
     again = torch.full_like(want, float("nan"))
-    ops.attention_step(qkv.clone(), again, k3, v3, meta, ctx, nh, nkv, d, inv_freq, d, window, scale, write_kv=False)
+    ops.attention_step(other, again, k3, v3, meta, ctx, nh, nkv, d, inv_freq, d, window, scale, write_kv=False)
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
     assert torch.equal(k3, k2) and torch.equal(v3, v2)
+    assert torch.allclose(again.float(), want.float(), atol=2e-2, rtol=2e-2), (again.float() - want.float()).abs().max()
 
 
 @pytest.mark.parametrize("nh, nkv, d, window", [(14, 2, 64, 0), (12, 2, 128, 0), (8, 8, 64, 100), (3, 1, 128, 0)])

@@ -142,3 +142,44 @@ def test_dtypes_on_the_device_follow_the_roles(tmp_path):
     model32, _ = load_model(folder, "float32", "cpu")
     assert model32.blocks[0].feed_forward.gate_up.dtype == torch.float32
     assert torch.equal(model32.blocks[0].feed_forward.gate_up[128:], stored["model.layers.0.mlp.up_proj.weight"].float())
+
+
+def test_tensors_nobody_asks_for_are_an_error_unless_told_otherwise(tmp_path):
+    """By default a tensor that no part asks for stands in the one error; with strict=False the folder loads and
+    the model says which tensors it left alone.  Missing tensors and wrong shapes stay errors either way."""
+    tensors = random_tensors(TINY_A, seed=4)
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    folder = tmp_path / "extra"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(TINY_A))
+    write_safetensors(str(folder / "model.safetensors"), tensors)
+    with pytest.raises(WeightLoadError):
+        load_model(str(folder), "float32", "cpu")
+    model, _ = load_model(str(folder), "float32", "cpu", strict=False)
+    assert model.unexpected_tensors == ["model.layers.0.self_attn.rotary_emb.inv_freq"] and model.bound
+    del tensors["model.norm.weight"]
+    write_safetensors(str(folder / "model.safetensors"), tensors)
+    with pytest.raises(WeightLoadError) as e:
+        load_model(str(folder), "float32", "cpu", strict=False)
+    assert e.value.missing == ["model.norm.weight"] and e.value.unexpected
+
+
+@pytest.mark.gpu
+def test_a_folder_goes_to_the_device_through_pinned_staging_buffers(tmp_path, monkeypatch):
+    """Tensors larger than a staging buffer are sent in pieces, shards are read through their own mappings, and what
+    arrives on the device is bit for bit what the safetensors package reads from the same files."""
+    from ferrisinfer_b200.weights import loader
+
+    monkeypatch.setattr(loader, "STAGING_BYTES", 4096)  # the embedding of 256 x 64 bf16 is 32 KB: eight pieces
+    folder = helpers.make_folder(tmp_path, TINY_A, seed=6)
+    _, stored = helpers.read_folder(folder)
+    for dtype in ("bfloat16", "float32"):
+        model, _ = load_model(folder, dtype, "cuda")
+        want = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+        assert model.embedding.weight.dtype == want and model.embedding.weight.is_cuda
+        assert torch.equal(model.embedding.weight.cpu(), stored["model.embed_tokens.weight"].to(want))
+        for l, block in enumerate(model.blocks):
+            p = f"model.layers.{l}"
+            assert torch.equal(block.feed_forward.down.cpu(), stored[f"{p}.mlp.down_proj.weight"].to(want))
+            assert torch.equal(block.mixer.qkv_bias.cpu()[:64], stored[f"{p}.self_attn.q_proj.bias"].float())
+            assert torch.equal(block.mixer_norm.weight.cpu(), stored[f"{p}.input_layernorm.weight"].float())

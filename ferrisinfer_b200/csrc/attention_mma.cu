@@ -330,10 +330,11 @@ __global__ void __launch_bounds__(WARPS * 32)
                             float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ block_tables,
                             int max_blocks, const int* __restrict__ token_seq, const int* __restrict__ positions,
                             const int* __restrict__ token_list, int nh, int nkv, int page_size, int window, float scale,
-                            int splits, const FusedRope rope, int* status) {
+                            int splits, const FusedRope rope, int* split_counters, int* status) {
     FERRIS_TL_ENTRY();
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full[WARPS][STAGES];
+    __shared__ int last_of_its_splits;
     __shared__ int tile_rows[WARPS][ROW_CACHE];  // cache rows of this warp's next tiles, looked up in one go
     __shared__ float2 cos_sin[D / 2];            // (cos, sin) of the token's rotation angles, when the rotation is fused
     uint8_t* smem = align1024(smem_raw);
@@ -559,6 +560,38 @@ __global__ void __launch_bounds__(WARPS * 32)
             if (c == 0) {
                 part_ml[slot * 2] = mm;
                 part_ml[slot * 2 + 1] = ll;
+            }
+        }
+    }
+    if (splits > 1 && split_counters) {
+        // The CTA that is last to finish among the key ranges of a (token, kv head) merges their partial results
+        // (the sums in the order of decode_merge_kernel, whichever CTA it is) and writes the output rows: no
+        // merge launch follows.  The counter goes back to zero for the next launch.
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int* counter = split_counters + (size_t)blockIdx.z * nkv + hk;
+            const int before = atomicAdd(counter, 1);
+            last_of_its_splits = before == splits - 1;
+            if (last_of_its_splits) *counter = 0;
+        }
+        __syncthreads();
+        if (last_of_its_splits) {
+            __threadfence();
+            for (int idx = threadIdx.x; idx < G * D; idx += WARPS * 32) {
+                const int r = idx / D, c = idx % D;
+                const int head = hk * G + r;
+                const size_t base = ((size_t)blockIdx.z * nh + head) * splits;
+                float mm = -INFINITY;
+                for (int s = 0; s < splits; ++s) mm = fmaxf(mm, __ldcg(&part_ml[(base + s) * 2]));
+                float ll = 0.0f, oo = 0.0f;
+                for (int s = 0; s < splits; ++s) {
+                    const float ms = __ldcg(&part_ml[(base + s) * 2]);
+                    const float f = ms == -INFINITY ? 0.0f : expf(ms - mm);
+                    ll += __ldcg(&part_ml[(base + s) * 2 + 1]) * f;
+                    oo += __ldcg(&part_o[(base + s) * D + c]) * f;
+                }
+                out[(size_t)tok * ldo + (size_t)head * D + c] = __float2bfloat16_rn(oo / ll);
             }
         }
     }
@@ -1257,12 +1290,15 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
                                  long long cache_pages, const int* block_tables, int max_blocks, const int* token_seq,
                                  const int* positions, const int* token_list, int tokens, int nh, int nkv, int d,
                                  int page_size, int window, float scale, int splits, float* scratch, void* stream,
-                                 const float* inv_freq = nullptr, const int* slot_mapping = nullptr, bool merge = true) {
+                                 const float* inv_freq = nullptr, const int* slot_mapping = nullptr, int merge = 1,
+                                 int* split_counters = nullptr) {
     if (tokens <= 0) return FERRIS_OK;
     int rc = check_common(nh, nkv, d, page_size, max_blocks);
     if (rc != FERRIS_OK) return rc;
     if (splits < 1 || splits > 65535) FERRIS_REFUSE("decode attention: %d splits", splits);
     if (splits > 1 && !scratch) FERRIS_REFUSE("decode attention: splitting the keys needs scratch memory");
+    if (merge == 2 && splits > 1 && !split_counters) FERRIS_REFUSE("decode attention: merging in the kernel needs counters");
+    int* counters = (merge == 2 && splits > 1) ? split_counters : nullptr;
     if (nkv > 65535 || tokens > 65535) FERRIS_REFUSE("decode attention: %d tokens x %d kv heads exceed one launch", tokens, nkv);
     const uint64_t rows = (uint64_t)cache_pages * nkv * page_size;
     CUtensorMap mk, mv;
@@ -1283,15 +1319,15 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
         const size_t smem = (size_t)WARPS * ST * 4 * 2 * TILE_KEYS * 64 * 2 + 1024;
         if ((rc = set_smem(decode_attention_kernel<64, ST>, smem)) != FERRIS_OK) return rc;
         ferris_launch(decode_attention_kernel<64, ST>, grid, dim3(WARPS * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
-            token_list, nh, nkv, page_size, window, scale, splits, rope, status);
-        if (splits > 1 && merge) ferris_launch(decode_merge_kernel<64>, dim3(tokens, nh), dim3(64), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
+            token_list, nh, nkv, page_size, window, scale, splits, rope, counters, status);
+        if (splits > 1 && merge == 1) ferris_launch(decode_merge_kernel<64>, dim3(tokens, nh), dim3(64), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
     } else {
         constexpr int ST = 3;  // per warp 3 stages of 2 tiles (16 KB)
         const size_t smem = (size_t)WARPS * ST * 2 * 2 * TILE_KEYS * 128 * 2 + 1024;
         if ((rc = set_smem(decode_attention_kernel<128, ST>, smem)) != FERRIS_OK) return rc;
         ferris_launch(decode_attention_kernel<128, ST>, grid, dim3(WARPS * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
-            token_list, nh, nkv, page_size, window, scale, splits, rope, status);
-        if (splits > 1 && merge) ferris_launch(decode_merge_kernel<128>, dim3(tokens, nh), dim3(128), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
+            token_list, nh, nkv, page_size, window, scale, splits, rope, counters, status);
+        if (splits > 1 && merge == 1) ferris_launch(decode_merge_kernel<128>, dim3(tokens, nh), dim3(128), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
     }
     FERRIS_LAUNCH_CHECK();
 }
@@ -1321,17 +1357,21 @@ FERRIS_API int ferris_decode_attention_listed(const void* q, int ldq, void* out,
 // Single-token steps whose q and k have NOT been rotated and whose k and v are NOT in the cache yet: the kernel
 // does the work of the rotary / cache-write kernel on its way (every dim of a head rotated: rotary dims == d).
 // qkv: the step's [tokens, (nh + 2 nkv) d] rows; slot_mapping null: rotate q only (a layer that reads another
-// layer's cache).  merge == 0 with splits > 1: the partial results of the key ranges stay in scratch, `out` is
-// not written, and the caller merges them (ferris_decode_merge, or the product that follows does it on its way).
+// layer's cache).  merge: 1 a merge kernel follows; 0 with splits > 1: the partial results of the key ranges stay
+// in scratch, `out` is not written, and the caller merges them (ferris_decode_merge, or the product that follows
+// does it on its way); 2: the CTA that finishes last among the key ranges of a (token, kv head) merges them, which
+// needs `counters`: tokens x nkv ints, zero before the first launch (every launch leaves them zero).
 FERRIS_API int ferris_decode_attention_rope(const void* qkv, int ldq, void* out, int ldo, void* k_cache, void* v_cache,
                                             long long cache_pages, const int* block_tables, int max_blocks,
                                             const int* token_seq, const int* positions, const float* inv_freq,
                                             const int* slot_mapping, int tokens, int nh, int nkv, int d, int page_size,
-                                            int window, float scale, int splits, float* scratch, int merge, void* stream) {
+                                            int window, float scale, int splits, float* scratch, int merge,
+                                            int* counters, void* stream) {
     if (!inv_freq) FERRIS_REFUSE("decode attention with rotation: no frequency table");
+    if (merge < 0 || merge > 2) FERRIS_REFUSE("decode attention with rotation: merge mode %d", merge);
     return decode_attention_impl(qkv, ldq, out, ldo, k_cache, v_cache, cache_pages, block_tables, max_blocks, token_seq,
                                  positions, nullptr, tokens, nh, nkv, d, page_size, window, scale, splits, scratch, stream,
-                                 inv_freq, slot_mapping, merge != 0);
+                                 inv_freq, slot_mapping, merge, counters);
 }
 
 // The merge alone, for partial results that ferris_decode_attention_rope left in scratch (merge == 0):

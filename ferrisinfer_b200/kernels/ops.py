@@ -40,7 +40,9 @@ _SIGNATURES = {
     "ferris_rope_cache_write": [_VP, _I, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP],
     "ferris_prefill_attention": [_VP, _I, _VP, _I, _VP, _VP, _LL, _VP, _I, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _F, _I, _VP],
     "ferris_decode_attention_rope": [_VP, _I, _VP, _I, _VP, _VP, _LL, _VP, _I, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I,
-                                     _F, _I, _VP, _I, _VP],
+                                     _F, _I, _VP, _I, _VP, _VP],
+    "ferris_gemm_skinny": [_VP, _I, _VP, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _VP],
+    "ferris_gemm_skinny_takes": [_I, _I, _I, _I],
     "ferris_embed_gather": [_VP, _I, _VP, _VP, _I, _I, _I, _VP, _VP],
 }
 _declared = False
@@ -371,15 +373,83 @@ def merge_gemm_tcgen05(x: "LazySplitMerge", w, bias, out, mode: int):
     )
 
 
+def set_gemm_skinny(on: bool = True) -> None:
+    """Steps of at most 16 tokens on the weight-stationary kernel of csrc/gemm_skinny.cu (True, the default, also
+    of the library unless FERRIS_GEMM_SKINNY=0), or on the tcgen05 kernel with its K split over a cluster (False)."""
+    _lib().ferris_set_gemm_skinny(_c_int(1 if on else 0))
+    _skinny_shapes.clear()
+
+
+_skinny_shapes: dict = {}
+
+
+def gemm_skinny_enabled() -> bool:
+    return bool(_lib().ferris_gemm_skinny_enabled())
+
+
+def _skinny_takes(x, w, out, accs: int) -> bool:
+    """Whether the skinny kernel takes this product: bf16, at most 16 tokens, K a multiple of 8, aligned rows, and a
+    number of outputs that its plan covers (``x``: a tensor or a LazyRMSNorm that has not been computed)."""
+    T, K = x.shape
+    if T > 16 or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or w.dim() != 2 or w.shape[1] != K or K % 8:
+        return False
+    if w.stride(1) != 1 or w.stride(0) % 8 or w.data_ptr() % 16:
+        return False
+    if isinstance(x, LazyRMSNorm):
+        if x._done or not (x.h.is_cuda and x.h.dtype == torch.float32 and x.h.is_contiguous() and x.h.data_ptr() % 16 == 0
+                           and x.weight.data_ptr() % 16 == 0):
+            return False
+    elif not (x.dim() == 2 and x.is_cuda and x.stride(1) == 1 and (x.stride(0) % 2 == 0 or T == 1) and x.data_ptr() % 4 == 0):
+        return False
+    N = out.shape[1]
+    key = (T > 8, N, K, accs)
+    takes = _skinny_shapes.get(key)
+    if takes is None:
+        takes = bool(_lib().ferris_gemm_skinny_takes(T, N, K, accs))
+        _skinny_shapes[key] = takes
+    return takes
+
+
+def gemm_skinny(x, w, bias, out, mode: int, up_row_offset: int = 0):
+    """out (+)= x w^T (+ bias) for at most 16 tokens; ``x`` a bf16 tensor or a LazyRMSNorm (formed in the kernel).
+    Modes as gemm_tcgen05."""
+    T, K = x.shape
+    rows_w, K2, ldw = _rows(w, "gemm weight")
+    T2, N, ldo = _rows(out, "gemm output")
+    want_dtype = torch.bfloat16 if mode in (0, 3) else torch.float32
+    if K != K2 or T != T2 or out.dtype != want_dtype:
+        raise KernelError(f"skinny gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} {out.dtype}, mode {mode}")
+    if bias is not None:
+        _need(bias, "gemm bias", torch.float32)
+        if bias.numel() != N:
+            raise KernelError("gemm: bias length differs from the output width")
+    lazy = isinstance(x, LazyRMSNorm)
+    ldx = K if lazy else (x.stride(0) if T > 1 else max(x.stride(0), K))
+    _check(
+        _lib().ferris_gemm_skinny(None if lazy else x.data_ptr(), ldx, x.h.data_ptr() if lazy else None,
+                                  x.weight.data_ptr() if lazy else None, x.eps if lazy else 0.0, w.data_ptr(),
+                                  None if bias is None else bias.data_ptr(), out.data_ptr(), mode, T, N, K, ldw, ldo,
+                                  rows_w, up_row_offset, _stream()),
+        "skinny gemm",
+    )
+
+
+def _mode_of(out, accumulate: bool) -> int:
+    return 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1)
+
+
 def gemm(x, w, bias, out, accumulate: bool = False):
-    """The matrix product of the model, out (+)= x w^T + bias: the tcgen05 kernel for bf16 operands it takes,
-    the CUDA-core kernel for everything else (all of the 32-bit path).  ``x`` may be a LazyRMSNorm or a
-    LazySplitMerge."""
+    """The matrix product of the model, out (+)= x w^T + bias: for bf16 operands the skinny kernel (at most 16
+    tokens) or the tcgen05 kernels, the CUDA-core kernel for everything else (all of the 32-bit path).  ``x`` may
+    be a LazyRMSNorm or a LazySplitMerge."""
     if isinstance(x, LazySplitMerge):
         if w.shape[0] == out.shape[1] and _merge_gemm_takes(x, w):
             merge_gemm_tcgen05(x, w, bias, out, 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1))
             return
         x = x.materialize()
+    if w.shape[0] == out.shape[1] and x.shape[0] <= 16 and gemm_skinny_enabled() and _skinny_takes(x, w, out, 1):
+        gemm_skinny(x, w, bias, out, _mode_of(out, accumulate))
+        return
     if isinstance(x, LazyRMSNorm):
         if w.shape[0] == out.shape[1] and _norm_gemm_takes(x, w, 1):
             norm_gemm_tcgen05(x, w, bias, out, 2 if accumulate else (0 if out.dtype == torch.bfloat16 else 1))
@@ -400,6 +470,9 @@ def gemm_swiglu(x, gate_up_weight, out, workspace=None):
     T, I = out.shape
     if gate_up_weight.shape[0] != 2 * I:
         raise KernelError(f"gemm_swiglu: weight {tuple(gate_up_weight.shape)} for {I} outputs")
+    if T <= 16 and out.dtype == torch.bfloat16 and gemm_skinny_enabled() and _skinny_takes(x, gate_up_weight, out, 2):
+        gemm_skinny(x, gate_up_weight, None, out, 3, up_row_offset=I)
+        return
     if isinstance(x, LazyRMSNorm):
         if out.dtype == torch.bfloat16 and _norm_gemm_takes(x, gate_up_weight, 2):
             norm_gemm_tcgen05(x, gate_up_weight, None, out, 3, up_row_offset=I)
@@ -657,7 +730,11 @@ def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_head
         splits = decode_splits(T, num_kv_heads, kv_span)
         need = T * num_heads * splits * (head_dim + 2) if splits > 1 else 0
         scratch = ctx.workspace.get("attn_split_scratch", (need,), torch.float32) if need else None
-        leave = bool(lazy_merge and need)
+        # Who merges the key ranges: with the skinny products the attention kernel itself (its last CTA per token
+        # and kv head), otherwise the output product on its way (lazy_merge) or a merge kernel
+        in_kernel = bool(need) and gemm_skinny_enabled() and T * num_kv_heads <= _SPLIT_COUNTERS
+        leave = bool(lazy_merge and need) and not in_kernel
+        counters = _split_counters(qkv.device) if in_kernel else None
         _, _, ldq = _rows(qkv, "attention queries")
         _, _, ldo = _rows(out, "attention output")
         _check(
@@ -666,14 +743,30 @@ def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_head
                 ctypes.c_longlong(k_cache.shape[0]), _ptr(meta.block_tables), _c_int(meta.block_tables.shape[1]),
                 _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(inv_freq), _ptr(meta.slot_mapping if write_kv else None),
                 _c_int(T), _c_int(num_heads), _c_int(num_kv_heads), _c_int(head_dim), _c_int(page_size),
-                _c_int(window or 0), _c_float(scale), _c_int(splits), _ptr(scratch), _c_int(0 if leave else 1), _stream()),
-            "decode attention with rotation", 2 if (splits > 1 and not leave) else 1,
+                _c_int(window or 0), _c_float(scale), _c_int(splits), _ptr(scratch),
+                _c_int(2 if in_kernel else (0 if leave else 1)), _ptr(counters), _stream()),
+            "decode attention with rotation", 2 if (splits > 1 and not leave and not in_kernel) else 1,
         )
         return LazySplitMerge(scratch, out, num_heads, head_dim, splits) if leave else out
     rope_cache_write(qkv, ctx.positions, inv_freq, meta.slot_mapping, k_cache, v_cache, num_heads, num_kv_heads,
                      head_dim, rotary_dim, page_size, write_kv=write_kv)
     paged_attention(qkv, out, k_cache, v_cache, meta.block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale)
     return out
+
+
+_SPLIT_COUNTERS = 1 << 16
+_split_counter_buffers: dict = {}
+
+
+def _split_counters(device) -> torch.Tensor:
+    """Counters of finished key ranges per (token, kv head) for the in-kernel merge: zero before the first launch,
+    left zero by every launch, one buffer per device for the life of the process (recorded steps point at it)."""
+    key = str(device)
+    buf = _split_counter_buffers.get(key)
+    if buf is None:
+        buf = torch.zeros(_SPLIT_COUNTERS, dtype=torch.int32, device=device)
+        _split_counter_buffers[key] = buf
+    return buf
 
 
 def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale):

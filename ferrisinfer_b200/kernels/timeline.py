@@ -20,7 +20,7 @@ from ..errors import KernelError
 from . import ops
 
 WORDS = 16  # per slot: kernel id, CTAs, entry, start, end, CTAs done, ten marks
-UNITS = ("elementwise", "gemm_tcgen05", "attention_mma", "sampling")
+UNITS = ("elementwise", "gemm_tcgen05", "gemm_skinny", "attention_mma", "sampling")
 KERNELS = {
     1: "embedding", 2: "rmsnorm", 3: "rotary + cache write", 4: "decode attention", 5: "greedy sampling",
     6: "rmsnorm (warp per row)", 7: "prefill attention (mma.sync)", 8: "prefill attention (tcgen05)",
@@ -29,6 +29,9 @@ KERNELS = {
     30: "pair gemm -> bf16", 31: "pair gemm -> fp32", 32: "pair gemm += fp32", 33: "pair gemm swiglu",
     10: "gemm -> bf16", 11: "gemm -> fp32", 12: "gemm += fp32", 13: "gemm swiglu",
     14: "norm + gemm -> bf16", 15: "norm + gemm -> fp32", 16: "norm + gemm += fp32", 17: "norm + gemm swiglu",
+    40: "skinny gemm -> bf16", 41: "skinny gemm -> fp32", 42: "skinny gemm += fp32", 43: "skinny gemm swiglu",
+    44: "skinny norm + gemm -> bf16", 45: "skinny norm + gemm -> fp32", 46: "skinny norm + gemm += fp32",
+    47: "skinny norm + gemm swiglu",
     18: "merge + gemm -> bf16", 19: "merge + gemm -> fp32", 20: "merge + gemm += fp32",
 }
 

@@ -231,12 +231,25 @@ def test_gemm_on_cta_pairs(T, N, K, mode, device):
     _close(paired, ref, K, dtype)
 
 
+@pytest.fixture
+def skinny_off():
+    """The products of short steps on the tcgen05 kernel with its K split over a cluster, as before the skinny kernel."""
+    from ferrisinfer_b200.kernels import ops
+
+    ops.set_gemm_skinny(False)
+    yield
+    ops.set_gemm_skinny(True)
+
+
+@pytest.mark.parametrize("skinny", [True, False], ids=["skinny", "tcgen05"])
 @pytest.mark.parametrize("T", [1, 8, 16])
 @pytest.mark.parametrize("N, K", [(1152, 896), (130, 72), (896, 512), (300, 1000)])
-def test_gemm_with_rmsnorm_formed_on_its_way(T, N, K, device):
+def test_gemm_with_rmsnorm_formed_on_its_way(T, N, K, skinny, device, request):
     """ops.gemm given the not-yet-computed norm of the residual rows: one kernel, same numbers as norm then product."""
     from ferrisinfer_b200.kernels import ops
 
+    if not skinny:
+        request.getfixturevalue("skinny_off")
     h = rnd((T, K), F32, device, 31, scale=2.0)
     nw = 1 + rnd((K,), F32, device, 32, scale=0.1)
     w = rnd((N, K), BF16, device, 33, scale=0.1)
@@ -681,9 +694,9 @@ def test_attention_single_tokens_beside_portions_at_long_context(impl, device):
 
 
 @pytest.mark.parametrize("nh, nkv, d, T", [(14, 2, 64, 8), (12, 2, 128, 3), (7, 1, 64, 16), (14, 2, 64, 1)])
-def test_output_product_merges_the_key_ranges_on_its_way(nh, nkv, d, T, device):
+def test_output_product_merges_the_key_ranges_on_its_way(nh, nkv, d, T, device, skinny_off):
     """A decode step that leaves the partial results of its key ranges to the product that follows, against the
-    same step with the merge kernel."""
+    same step with the merge kernel (the path of the tcgen05 short-step products)."""
     from ferrisinfer_b200.kernels import ops
     from ferrisinfer_b200.parts.base import PagedMeta
 
@@ -834,6 +847,108 @@ def test_sampling_distribution(device):
     freq = torch.bincount(tok.cpu().long(), minlength=5).double() / n
     want = torch.softmax(row[0].double(), 0)
     assert (freq - want).abs().max() < 0.02, (freq, want)
+
+
+# ------------------------------------------------------------------------------- skinny gemm
+SKINNY_SHAPES = [(1152, 896), (896, 4864), (130, 72), (300, 1000), (9728, 896),
+                 (4608, 3584), (896, 18944),  # slabs that do not fit into shared memory: the stages are a ring
+                 (9472, 64), (7, 8), (17920, 1536)]  # 64 rows per CTA; one K block of 8; more CTAs than SMs
+
+
+@pytest.mark.parametrize("T", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N, K", SKINNY_SHAPES)
+def test_gemm_skinny(T, N, K, device):
+    """The weight-stationary product of short steps alone: every mode against the product in float64, twice the
+    same bits, and a row's result whatever else is in the step."""
+    from ferrisinfer_b200.kernels import ops
+
+    wide = rnd((T, K + 16), BF16, device, 51)
+    x = wide[:, 8:8 + K]  # rows of a wider buffer
+    w = rnd((N, K), BF16, device, 52, scale=0.1)
+    bias = rnd((N,), F32, device, 53)
+    want = _gemm_reference(x, w)
+    out = torch.full((T, N), float("nan"), dtype=BF16, device=device)
+    assert ops._skinny_takes(x, w, out, 1)
+    ops.gemm_skinny(x, w, bias, out, 0)
+    _close(out, want + bias.cpu().double(), K, BF16)
+    out32 = torch.full((T, N), float("nan"), dtype=F32, device=device)
+    ops.gemm_skinny(x, w, None, out32, 1)
+    _close(out32, want, K, F32)
+    again = torch.empty_like(out32)
+    ops.gemm_skinny(x, w, None, again, 1)
+    assert torch.equal(again, out32)
+    one = torch.empty(1, N, dtype=F32, device=device)
+    ops.gemm_skinny(x[T - 1:T], w, None, one, 1)
+    assert torch.equal(one[0], out32[T - 1]), "a row's sum does not depend on the rows beside it"
+    acc = rnd((T, N), F32, device, 54)
+    before = acc.clone()
+    ops.gemm_skinny(x, w, bias, acc, 2)
+    _close(acc - before, want + bias.cpu().double(), K, F32)
+    if N % 2 == 0:
+        I = N // 2
+        act = torch.full((T, I), float("nan"), dtype=BF16, device=device)
+        if ops._skinny_takes(x, w, act, 2):
+            ops.gemm_skinny(x, w, None, act, 3, up_row_offset=I)
+            want_act = want[:, I:] * plain.silu(want[:, :I])
+            assert (act.cpu().double() - want_act).abs().max().item() <= 3e-2 * (want_act.abs().max().item() + 1e-3)
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+
+
+def test_gemm_skinny_leaves_tall_products_and_long_steps_to_the_other_kernels(device):
+    from ferrisinfer_b200.errors import KernelError
+    from ferrisinfer_b200.kernels import ops
+
+    w = rnd((151936, 64), BF16, device, 55)
+    x = rnd((4, 64), BF16, device, 56)
+    assert not ops._skinny_takes(x, w, torch.empty(4, 151936, device=device), 1)  # the output head
+    w2 = rnd((256, 64), BF16, device, 57)
+    assert not ops._skinny_takes(rnd((17, 64), BF16, device, 58), w2, torch.empty(17, 256, device=device), 1)
+    assert not ops._skinny_takes(rnd((4, 60), BF16, device, 59), rnd((256, 60), BF16, device, 60),
+                                 torch.empty(4, 256, device=device), 1)
+    with pytest.raises(KernelError):
+        ops.gemm_skinny(rnd((17, 64), BF16, device, 58), w2, None, torch.empty(17, 256, dtype=BF16, device=device), 0)
+
+
+@pytest.mark.parametrize("nh, nkv, d, T, window", [(14, 2, 64, 8, 0), (12, 2, 128, 3, 0), (7, 1, 64, 16, 0), (14, 2, 64, 1, 0),
+                                                   (4, 4, 64, 5, 1000)])
+def test_decode_attention_merges_its_key_ranges_in_its_last_cta(nh, nkv, d, T, window, device, request):
+    """With the skinny products the decode kernel merges the partial results of its key ranges itself: the CTA that
+    finishes last among the ranges of a (token, kv head) adds them in the merge kernel's order.  The result is the
+    merge kernel's bit for bit, launch after launch (the counters return to zero)."""
+    from ferrisinfer_b200.kernels import ops
+    from ferrisinfer_b200.parts.base import PagedMeta
+
+    page = 16
+    lengths = [4096, 2500, 4000, 3333, 4090, 2049, 3000, 3500, 2100, 2200, 2300, 2400, 2600, 2700, 2800, 2900][:T]
+    seqs = [(kv, 1) for kv in lengths]
+    case = AttentionCase(device, BF16, nh, nkv, d, page, seqs, seed=T + d, window=window)
+    qkv, k, v, tables, ctx, _ = case.device_inputs()
+    g = torch.Generator().manual_seed(6)
+    qkv[:, nh * d:] = torch.randn(T, 2 * nkv * d, generator=g).to(BF16).to(device)
+    slots = torch.tensor([tables[i, (kv - 1) // page].item() * page + (kv - 1) % page for i, (kv, _) in enumerate(seqs)],
+                         dtype=torch.int32, device=device)
+    inv_freq = torch.tensor(plain.rotary_inverse_frequencies(d, d, 1e6).numpy(), device=device)
+    meta = PagedMeta(block_tables=tables, slot_mapping=slots, page_size=page)
+    scale = 1.0 / math.sqrt(d)
+    got = []
+    for _ in range(3):
+        out = torch.full((T, nh * d), float("nan"), dtype=BF16, device=device)
+        k1, v1 = k.clone(), v.clone()
+        launches = ops.launch_count()
+        assert ops.attention_step(qkv.clone(), out, k1, v1, meta, ctx, nh, nkv, d, inv_freq, d, window, scale,
+                                  lazy_merge=True) is out
+        assert ops.launch_count() - launches == 1
+        got.append(out)
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    assert int(ops._split_counters(device).abs().sum().item()) == 0
+    request.getfixturevalue("skinny_off")
+    want = torch.full((T, nh * d), float("nan"), dtype=BF16, device=device)
+    k2, v2 = k.clone(), v.clone()
+    ops.attention_step(qkv.clone(), want, k2, v2, meta, ctx, nh, nkv, d, inv_freq, d, window, scale)
+    assert all(torch.equal(o, want) for o in got)
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
 
 
 # ------------------------------------------------------------------------- switches of the library

@@ -124,3 +124,78 @@ def test_sampler_walk_matches_the_reference_order():
     assert tok in (1, 3, 2)
     assert plain.sample(row, 0.0, 0, 1.0, rng)[0] == 1  # temperature 0 is greedy
     assert plain.sample(row, 1.0, 1, 1.0, rng)[0] == 1  # top_k 1 is greedy
+
+
+# ------------------------------------------------------------------------------------------------------------
+# The reference's unit vectors above use head size 2, theta 1, one kv head and a zero feed-forward, so they do not
+# tell rotate-half pairs from interleaved ones, fix no frequency schedule, no gate / up role and no head-to-kv-head
+# mapping.  The reference cannot be run here, and model code of installed packages is not a source for this
+# project, so those four readings rest on the cited lines.  What the tests below add is a second evaluation of each
+# of them, element by element with ``math`` alone from the cited formula, at sizes where a slip in the vectorised
+# code (a wrong slice, a transposed pair, a head mapped to the wrong kv head) shows.
+# ------------------------------------------------------------------------------------------------------------
+def test_rotary_pairs_and_frequencies_element_by_element():
+    """crates/ferrisinfer-kernel/src/cpu/attention.rs:1254-1291: step = theta^(-2/d); inv_freq_i a running product;
+    pairs (i, i + R/2); dims >= R untouched."""
+    import math
+
+    import numpy as np
+
+    d, R, theta, pos = 8, 4, 100.0, 3
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(1, 2, d, generator=g, dtype=torch.float64)
+    got = plain.rope(x, [pos], d, R, theta)[0]
+    step = np.float32(theta) ** (np.float32(-2.0) / np.float32(d))
+    inv = [np.float32(1.0)]
+    for _ in range(R // 2 - 1):
+        inv.append(np.float32(inv[-1] * step))
+    for head in range(2):
+        want = x[0, head].tolist()
+        for i in range(R // 2):
+            angle = float(np.float32(np.float32(pos) * inv[i]))
+            lo, hi = x[0, head, i].item(), x[0, head, i + R // 2].item()
+            want[i] = lo * math.cos(angle) - hi * math.sin(angle)
+            want[i + R // 2] = hi * math.cos(angle) + lo * math.sin(angle)
+        assert max(abs(a - b) for a, b in zip(got[head].tolist(), want)) < 1e-12
+    assert torch.equal(got[:, R:], x[0, :, R:])
+
+
+def test_heads_read_their_kv_head_element_by_element():
+    """crates/ferrisinfer-kernel/src/cpu/attention.rs:744-757: head hq reads kv head hq / (nh / nkv), keys 0..=P."""
+    import math
+
+    n, nh, nkv, d = 5, 6, 2, 4
+    g = torch.Generator().manual_seed(2)
+    q = torch.randn(n, nh, d, generator=g, dtype=torch.float64)
+    k = torch.randn(n, nkv, d, generator=g, dtype=torch.float64)
+    v = torch.randn(n, nkv, d, generator=g, dtype=torch.float64)
+    got = plain.attention(q, k, v, list(range(n)))
+    for p in range(n):
+        for hq in range(nh):
+            hk = hq // (nh // nkv)
+            s = [sum(q[p, hq, c].item() * k[j, hk, c].item() for c in range(d)) / math.sqrt(d) for j in range(p + 1)]
+            m = max(s)
+            w = [math.exp(a - m) for a in s]
+            for c in range(d):
+                want = sum(w[j] * v[j, hk, c].item() for j in range(p + 1)) / sum(w)
+                assert abs(got[p, hq, c].item() - want) < 1e-12
+
+
+def test_gate_and_up_roles_element_by_element():
+    """crates/ferrisinfer-runtime/src/reference.rs:346-368 with crates/ferrisinfer-io/src/hf.rs:437-457: the SiLU is
+    taken of the gate_proj product (w3), which multiplies the up_proj product (w1)."""
+    import math
+
+    H, I = 3, 4
+    g = torch.Generator().manual_seed(3)
+    y = torch.randn(1, H, generator=g, dtype=torch.float64)
+    wg, wu = (torch.randn(I, H, generator=g, dtype=torch.float64) for _ in range(2))
+    wd = torch.randn(H, I, generator=g, dtype=torch.float64)
+    got = plain.swiglu_feed_forward(y, wg, wu, wd)[0]
+    act = []
+    for i in range(I):
+        gate = sum(y[0, c].item() * wg[i, c].item() for c in range(H))
+        up = sum(y[0, c].item() * wu[i, c].item() for c in range(H))
+        act.append(up * (gate * (1.0 / (1.0 + math.exp(-gate)))))
+    for o in range(H):
+        assert abs(got[o].item() - sum(act[i] * wd[o, i].item() for i in range(I))) < 1e-12

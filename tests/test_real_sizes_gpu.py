@@ -2,8 +2,8 @@
 
 Two layers each, a vocabulary of a few thousand (so that the float64 oracle stays cheap), pages of 16, query and
 key projections scaled so that the attention scores spread over about a unit.  What only these widths bring together
-runs here and is compared: the RMSNorm formed inside the short-step product with its K split over a cluster of 7,
-key ranges of a decode step merged inside the output product, graphs of decode steps filled up to a bucket, the
+runs here and is compared: the weight-stationary products of single tokens with the RMSNorm formed on their way,
+key ranges of a decode step merged by the attention kernel's last CTA, graphs of decode steps filled up to a bucket, the
 q/k/v product of long portions with rotation and cache write in its epilogue over 14 + 2 + 2 heads, the gate/up
 product on CTA pairs, both head sizes of the tensor-core attention kernels.  Every way of cutting: whole, the last
 32 tokens one by one, portions of changing size down to two tokens, and up to four live requests mixed with so few
@@ -135,13 +135,13 @@ def test_each_request_alone_and_whole(name, dtype, device, models, monkeypatch):
 def test_last_32_tokens_one_by_one(name, dtype, device, models, monkeypatch):
     _, requests, _, _ = models(name)
     steps = helpers.trace_tail_decoded(requests, tail=32)
-    runner, calls = _check(name, dtype, device, models, steps, requests, monkeypatch,
-                           ("norm_gemm_tcgen05", "merge_gemm_tcgen05"))
+    runner, calls = _check(name, dtype, device, models, steps, requests, monkeypatch, ("gemm_skinny",))
     if dtype is torch.bfloat16:
         assert runner.graph_replays >= 100, "single tokens are replayed from graphs"
         assert len(runner._graphs) <= 6, "one graph per width of block table, not per request"
-        if name != "7B":  # at the widest size a CTA cannot hold all its K slices: the norm is a kernel of its own
-            assert calls.count["norm_gemm_tcgen05"] > 0 and calls.count["merge_gemm_tcgen05"] > 0
+        assert calls.count["gemm_skinny"] >= 8, "the products of single tokens run the weight-stationary kernel"
+    else:
+        assert calls.count["gemm_skinny"] == 0
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["f32", "bf16"])

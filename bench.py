@@ -3,13 +3,17 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
-Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8 and context 4,096, K decode steps
-timed on the device with CUDA events (step function + sampling kernel; token ids preset on the host).
-``e2e``: the same through ``Engine.step()``: host token ids in (pinned metadata, one copy per step) and
-sampled tokens out (one read per step).  ``prefill``: one 2,048-token prompt.  ``roofline``: bytes a
-decode step must read (every weight once, the cache of the live requests) over its time, against the
-measured copy bandwidth.  ``points``: decode at batch 1 and 64.  Peaks come from MEASURED_PEAKS.json
-when present, else the fallback figures of this pool.
+Prints ONE JSON line.  ``value``: decoded tokens a second at batch 8 and context 4,096: regions of exactly K
+decode steps each, timed on the device with CUDA events (step function + sampling kernel; token ids preset on
+the host), the cache refilled between regions so that every region ends at the same context; the median region
+is reported, the fastest and slowest beside it.  ``e2e``: the same through ``Engine.step()``: host token ids in
+(pinned metadata, one copy per step) and sampled tokens out (one read per step).  ``prefill``: one 2,048-token
+prompt.  ``roofline``: bytes a decode step must read (every weight once, the cache of the live requests) over
+its time, against the measured copy bandwidth.  ``points``: decode at batch 1 and 64 with their fractions of that
+roofline, and the workloads of the two larger published sizes (a mixed batch of 32 requests at the 1.5B sizes;
+decode, prefill and eight requests that share a prefix at the 7B sizes).  ``kernels``: what the step's dominant
+kernels reach alone, each timed over the weights or caches of all layers in turn (more than L2 holds).  Peaks come
+from MEASURED_PEAKS.json when present, else the fallback figures of this pool.
 
 The weights (1 GB) and the cache are far larger than the 126 MB L2, so every step reads them from
 HBM; no explicit L2 flush is needed between timed steps.
@@ -37,6 +41,10 @@ QWEN25_05B = {
     "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "hidden_act": "silu", "tie_word_embeddings": True,
     "use_sliding_window": False, "sliding_window": None, "max_window_layers": 24,
 }
+QWEN25_15B = dict(QWEN25_05B, hidden_size=1536, intermediate_size=8960, num_hidden_layers=28, num_attention_heads=12,
+                  num_key_value_heads=2, max_window_layers=28)
+QWEN25_7B = dict(QWEN25_05B, vocab_size=152064, hidden_size=3584, intermediate_size=18944, num_hidden_layers=28,
+                 num_attention_heads=28, num_key_value_heads=4, tie_word_embeddings=False, max_window_layers=28)
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -123,7 +131,7 @@ def model_numbers(cfg: dict) -> dict:
 
 def decode_bytes(cfg, batch, context) -> float:
     n = model_numbers(cfg)
-    weights = (n["L"] * (n["layer_matrix"] * 2 + n["layer_vectors"] * 4) + n["head"] * 2 + n["H"] * 4)
+    weights = (n["L"] * (n["layer_matrix"] * 2 + n["layer_vectors"] * 4) + n["head"] * 2 + n["H"] * 4)  # tied or not: the head is read once
     return float(weights + batch * context * n["kv_bytes_per_token"])
 
 
@@ -167,39 +175,42 @@ def fill_cache(engine, batch, context):
     return ids
 
 
-def time_decode(engine, batch, context, steps, warmup):
-    """K decode steps (step function + greedy sampling kernel) timed with CUDA events."""
+def time_decode(engine, batch, context, steps, warmup, regions=1):
+    """Regions of exactly ``steps`` decode steps (step function + greedy sampling kernel), each timed with CUDA
+    events after ``warmup`` untimed steps; the cache is refilled before every region, so that each one ends at
+    ``context``.  Returns (ms per step of each region, kernel launches of one region)."""
     import torch
 
     from ferrisinfer_b200.engine.runner import StepEntry
     from ferrisinfer_b200.kernels import ops
 
-    start_ctx = context - steps - warmup - 1
-    ids = fill_cache(engine, batch, start_ctx)
     vocab = engine.model.vocab_size
     gen = torch.Generator().manual_seed(1)
     tokens = torch.randint(0, vocab, (steps + warmup, batch), generator=gen).tolist()
     out_tok = torch.empty(batch, dtype=torch.int32, device=engine.device)
+    times, launches = [], 0
+    for _ in range(max(1, regions)):
+        ids = fill_cache(engine, batch, context - steps - warmup - 1)
 
-    def one(i):
-        logits = engine.runner.step([StepEntry(rid, [tokens[i][b]], [0]) for b, rid in enumerate(ids)])
-        ops.sample(logits, out_tok)
+        def one(i):
+            logits = engine.runner.step([StepEntry(rid, [tokens[i][b]], [0]) for b, rid in enumerate(ids)])
+            ops.sample(logits, out_tok)
 
-    for i in range(warmup):
-        one(i)
-    torch.cuda.synchronize()
-    launches0 = ops.launch_count() + engine.runner.graph_kernels
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(warmup, warmup + steps):
-        one(i)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / steps
-    launches = ops.launch_count() + engine.runner.graph_kernels - launches0
-    for rid in ids:
-        engine.runner.free_request(rid)
-    return ms, launches
+        for i in range(warmup):
+            one(i)
+        torch.cuda.synchronize()
+        launches0 = ops.launch_count() + engine.runner.graph_kernels
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(warmup, warmup + steps):
+            one(i)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) / steps)
+        launches = ops.launch_count() + engine.runner.graph_kernels - launches0
+        for rid in ids:
+            engine.runner.free_request(rid)
+    return times, launches
 
 
 def time_prefill(engine, tokens, warmup=2, iters=3):
@@ -257,6 +268,210 @@ def time_e2e(engine, batch, context, steps, warmup):
     for rid in ids:
         sched.cancel(rid)
     return ms, n, engine.runner.last_h2d_bytes, 8 * batch  # an int32 token and an fp32 probability per request
+
+
+def time_mixed(cfg, requests=32, chunk=512, new_tokens=32, seed=3):
+    """The mixed workload of the 1.5B sizes: ``requests`` prompts of 128 to 2,048 tokens, in portions of ``chunk``
+    beside the decoded tokens of the requests that are further on, through Engine.generate.  Returns tokens
+    (prompt + generated) a second and the wall time in ms."""
+    import random
+
+    import torch
+
+    from ferrisinfer_b200 import SamplingParams, SchedulerConfig
+    from ferrisinfer_b200.engine.engine import Engine
+
+    rng = random.Random(seed)
+    prompts = [[rng.randrange(cfg["vocab_size"]) for _ in range(rng.randint(128, 2048))] for _ in range(requests)]
+    total = sum(len(p) for p in prompts) + requests * new_tokens
+    sched = SchedulerConfig(max_batch_size=requests, max_prefill_chunk_tokens=chunk, max_prefill_batch_tokens=2 * chunk,
+                            max_sequence_length=2048 + new_tokens + 8, max_generated_tokens=new_tokens)
+    pages = sum(-(-(len(p) + new_tokens + 8) // 16) for p in prompts) + 8
+    engine = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=16, init_device="cuda", num_pages=pages, scheduler=sched)
+    params = SamplingParams.greedy(max_new_tokens=new_tokens)
+    engine.generate(prompts[:4], params)  # warm-up: kernels loaded, buffers sized
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = engine.generate(prompts, params)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    assert all(len(o.generated_tokens) == new_tokens for o in outs)
+    del engine
+    torch.cuda.empty_cache()
+    return total / wall, wall * 1e3
+
+
+def time_shared_prefix(cfg, requests=8, prefix=1024, tail=64, new_tokens=16):
+    """Eight requests whose prompts share their first 1,024 tokens, through Engine.generate with prefix sharing:
+    tokens (prompt + generated) a second, and how many prompt tokens were taken from shared pages."""
+    import random
+
+    import torch
+
+    from ferrisinfer_b200 import SamplingParams, SchedulerConfig
+    from ferrisinfer_b200.engine.engine import Engine
+
+    rng = random.Random(11)
+    stem = [rng.randrange(cfg["vocab_size"]) for _ in range(prefix)]
+    prompts = [stem + [rng.randrange(cfg["vocab_size"]) for _ in range(tail + i)] for i in range(requests)]
+    sched = SchedulerConfig(max_batch_size=requests, max_prefill_chunk_tokens=1024, max_prefill_batch_tokens=2048,
+                            max_sequence_length=prefix + tail + requests + new_tokens + 8, max_generated_tokens=new_tokens)
+    engine = Engine(config=cfg, seed=0, dtype="bfloat16", page_size=16, init_device="cuda",
+                    num_pages=requests * 80 + 8, scheduler=sched, prefix_sharing=True)
+    params = SamplingParams.greedy(max_new_tokens=new_tokens)
+    engine.generate([p[:200] for p in prompts[:2]], params)
+    engine.runner.cache.drop_idle()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    first = engine.submit(prompts[0], params)
+    while not engine.scheduler.running or engine.scheduler.running[0].num_computed < len(prompts[0]):
+        engine.step()
+    rest = [engine.submit(p, params) for p in prompts[1:]]
+    while engine.has_unfinished():
+        engine.step()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    outs = [engine.output_of(i) for i in [first] + rest]
+    reused = sum(o.reused_prompt_tokens for o in outs)
+    total = sum(len(p) for p in prompts) + requests * new_tokens
+    del engine
+    torch.cuda.empty_cache()
+    return total / wall, reused
+
+
+def larger_sizes(steps, warmup) -> dict:
+    """The workloads of the 1.5B and 7B sizes: random weights drawn on the device, same harness as the headline."""
+    import torch
+
+    out = {}
+    tok_s, _ms = time_mixed(dict(QWEN25_15B))
+    out["q15b_mixed32_tok_s"] = round(tok_s, 1)
+    cfg = dict(QWEN25_7B)
+    steps = max(8, steps // 4)
+    for b in (1, 8, 64):
+        engine = build_engine(cfg, b, CONTEXT, extra_tokens=PREFILL_TOKENS if b == 8 else 0)
+        times, _ = time_decode(engine, b, CONTEXT, steps, warmup)
+        ms = statistics.median(times)
+        out[f"q7b_decode_b{b}"] = round(b / ms * 1e3, 1)
+        out[f"q7b_decode_b{b}_frac"] = round(decode_bytes(cfg, b, CONTEXT) / (ms * 1e-3) / 1e9 / load_peaks()[0]["hbm_gbs"], 4)
+        if b == 8:
+            pms = time_prefill(engine, PREFILL_TOKENS)
+            out["q7b_prefill_2048_tok_s"] = round(PREFILL_TOKENS / pms * 1e3, 1)
+            out["q7b_prefill_frac"] = round(prefill_flops(cfg, PREFILL_TOKENS) / (pms * 1e-3) / (load_peaks()[0]["bf16_tflops"] * 1e12), 4)
+        del engine
+        torch.cuda.empty_cache()
+    tok_s, reused = time_shared_prefix(cfg)
+    out["q7b_shared_prefix8_tok_s"] = round(tok_s, 1)
+    out["q7b_shared_prefix8_reused_tokens"] = reused
+    return out
+
+
+def kernel_numbers(engine, cfg, peaks) -> dict:
+    """What the dominant kernels of the step reach alone.  Each is recorded once per layer into a CUDA graph, over
+    that layer's own weights or cache (all layers together are far more than L2 holds), and the graph is timed."""
+    import math
+
+    import torch
+
+    from ferrisinfer_b200.kernels import ops
+    from ferrisinfer_b200.parts.base import PagedMeta, StepContext
+
+    dev = engine.device
+    n = model_numbers(cfg)
+    H, I, L, d, nh, nkv = n["H"], cfg["intermediate_size"], n["L"], n["d"], n["nh"], cfg["num_key_value_heads"]
+    blocks = engine.model.blocks
+    out = {}
+
+    def timed(body, reps=3):
+        body()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            body()
+        g.replay()
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            best = e0.elapsed_time(e1) if best is None else min(best, e0.elapsed_time(e1))
+        return best * 1e-3 / L  # seconds per launch
+
+    # decode, 8 tokens: gate/up and down (weight bytes a second)
+    T = 8
+    x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+    act = torch.empty(T, I, dtype=torch.bfloat16, device=dev)
+    h = torch.zeros(T, H, dtype=torch.float32, device=dev)
+    sec = timed(lambda: [ops.gemm_swiglu(x, b.feed_forward.gate_up, act) for b in blocks])
+    out["decode_gate_up_gbs"] = round(2 * I * H * 2 / sec / 1e9, 1)
+    sec = timed(lambda: [ops.gemm(act, b.feed_forward.down, None, h, accumulate=True) for b in blocks])
+    out["decode_down_gbs"] = round(I * H * 2 / sec / 1e9, 1)
+    # the output head, 8 rows
+    logits = torch.empty(T, n["V"], dtype=torch.float32, device=dev)
+    w_head = engine.model.output.weight
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ops.gemm(x, w_head, None, logits)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(4):
+        ops.gemm(x, w_head, None, logits)
+    e1.record()
+    torch.cuda.synchronize()
+    out["lm_head_gbs"] = round(n["V"] * H * 2 / (e0.elapsed_time(e1) * 1e-3 / 4) / 1e9, 1)
+    # decode attention, 64 requests at context 4,096, over every layer's cache
+    B = 64
+    caches = [c for c in engine.runner.cache.layer_caches if c is not None and c.k is not None]
+    pages_per = CONTEXT // 16
+    have = caches[0].k.shape[0]
+    if have >= B * pages_per:
+        tables = torch.arange(B * pages_per, dtype=torch.int32, device=dev).view(B, pages_per)
+        ws = engine.runner.workspace
+        ctx = StepContext(num_tokens=B, num_seqs=B, token_ids=torch.zeros(B, dtype=torch.int32, device=dev),
+                          positions=torch.full((B,), CONTEXT - 1, dtype=torch.int32, device=dev),
+                          token_seq=torch.arange(B, dtype=torch.int32, device=dev),
+                          seq_q_start=torch.arange(B + 1, dtype=torch.int32, device=dev),
+                          seq_start_pos=torch.full((B,), CONTEXT - 1, dtype=torch.int32, device=dev),
+                          seq_state_slot=torch.zeros(B, dtype=torch.int32, device=dev), seqs=[], paged={}, max_q_len=1,
+                          max_kv_len=CONTEXT, act_dtype=torch.bfloat16, workspace=ws, device=dev)
+        slots = (tables[:, -1] * 16 + 15).contiguous()
+        meta = PagedMeta(block_tables=tables, slot_mapping=slots, page_size=16)
+        qkv = torch.randn(B, (nh + 2 * nkv) * d, device=dev).to(torch.bfloat16)
+        o = torch.empty(B, nh * d, dtype=torch.bfloat16, device=dev)
+        inv_freq, rot = blocks[0].mixer.position.rotary_table(dev)
+        sec = timed(lambda: [ops.attention_step(qkv, o, c.k, c.v, meta, ctx, nh, nkv, d, inv_freq, rot, 0, 1.0 / math.sqrt(d))
+                             for c in caches])
+        out["decode_attention_b64_gbs"] = round(B * CONTEXT * 2 * nkv * d * 2 / sec / 1e9, 1)
+    # prefill, 2,048 tokens: the gate/up product and the attention
+    Tp = PREFILL_TOKENS
+    xp = torch.randn(Tp, H, device=dev).to(torch.bfloat16)
+    actp = torch.empty(Tp, I, dtype=torch.bfloat16, device=dev)
+    sec = timed(lambda: [ops.gemm_swiglu(xp, b.feed_forward.gate_up, actp) for b in blocks])
+    out["prefill_gate_up_tflops"] = round(2.0 * Tp * 2 * I * H / sec / 1e12, 1)
+    if have >= Tp // 16:
+        tables = torch.arange(Tp // 16, dtype=torch.int32, device=dev).view(1, -1)
+        qkvp = torch.randn(Tp, (nh + 2 * nkv) * d, device=dev).to(torch.bfloat16)
+        op = torch.empty(Tp, nh * d, dtype=torch.bfloat16, device=dev)
+        q_start = torch.tensor([0, Tp], dtype=torch.int32, device=dev)
+        start_pos = torch.zeros(1, dtype=torch.int32, device=dev)
+        sec = timed(lambda: [ops.prefill_attention(qkvp, op, c.k, c.v, tables, q_start, start_pos, 1, Tp, nh, nkv, d, 0,
+                                                   1.0 / math.sqrt(d)) for c in caches])
+        out["prefill_attention_tflops"] = round(2.0 * Tp * Tp * d * nh / sec / 1e12, 1)  # causal: half of 4 T^2 d nh
+    # the temperature sampler, 8 rows of the whole vocabulary
+    from ferrisinfer_b200 import SamplingParams
+
+    params = [SamplingParams(temperature=0.7, top_k=20, top_p=0.9, seed=42 + i) for i in range(T)]
+    engine.sampler.sample(logits, params, list(range(T)))
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(4):
+        engine.sampler.sample(logits, params, list(range(T)))
+    e1.record()
+    torch.cuda.synchronize()
+    out["sampler_top_k_top_p_b8_us"] = round(e0.elapsed_time(e1) * 1e3 / 4, 1)
+    return out
 
 
 def reference_arm(args) -> int:
@@ -333,7 +548,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
-    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-points", action="store_true", help="no decode at batch 1 and 64")
+    ap.add_argument("--skip-extra", action="store_true", help="no workloads of the 1.5B and 7B sizes, no per-kernel numbers")
+    ap.add_argument("--regions", type=int, default=5, help="timed regions of --steps decode steps each (the median is reported)")
     ap.add_argument("--timeline", nargs="?", const="decode", choices=["decode", "prefill"], default=None,
                     help="instead of the measurement: the timeline of one decode step (or of one prefill of 2,048 "
                          "tokens) from hooks inside the kernels (a build of the kernel library of its own; prints a "
@@ -360,17 +577,30 @@ def main() -> int:
 
     engine = build_engine(cfg, args.batch, CONTEXT, extra_tokens=PREFILL_TOKENS)
     clocks.start()
-    ms, launches = time_decode(engine, args.batch, CONTEXT, args.steps, args.warmup)
+    region_ms, launches = time_decode(engine, args.batch, CONTEXT, args.steps, args.warmup, regions=args.regions)
+    ms = statistics.median(region_ms)
     prefill_ms = time_prefill(engine, PREFILL_TOKENS)
     e2e_ms, e2e_tokens, h2d, d2h = time_e2e(engine, args.batch, CONTEXT, args.steps, args.warmup)
-    points = {}
+    points, kernels = {}, {}
+    if not args.skip_extra:
+        del engine
+        torch.cuda.empty_cache()
+        # the per-kernel numbers want the cache of 64 requests at the bench's context
+        engine = build_engine(cfg, 64, CONTEXT)
+        kernels = kernel_numbers(engine, cfg, peaks)
     if not args.skip_points:
         for b in (1, 64):
             del engine
             torch.cuda.empty_cache()
             engine = build_engine(cfg, b, CONTEXT)
-            pms, _ = time_decode(engine, b, CONTEXT, max(8, args.steps // 2), args.warmup)
+            times, _ = time_decode(engine, b, CONTEXT, max(8, args.steps // 2), args.warmup, regions=min(3, args.regions))
+            pms = statistics.median(times)
             points[f"decode_b{b}"] = round(b / pms * 1e3, 1)
+            points[f"decode_b{b}_frac"] = round(decode_bytes(cfg, b, CONTEXT) / (pms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4)
+    del engine
+    torch.cuda.empty_cache()
+    if not args.skip_extra:
+        points.update(larger_sizes(args.steps, args.warmup))
     clock_record = clocks.stop()
 
     value = args.batch / ms * 1e3
@@ -381,7 +611,8 @@ def main() -> int:
     line = {
         "metric": "decode tok/s at batch 8, context 4096 (Qwen2.5-0.5B sizes, random weights)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": round(ms, 4), "ms_per_step_min": round(min(region_ms), 4), "ms_per_step_max": round(max(region_ms), 4),
+        "regions": len(region_ms), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded uniform token ids, random-init weights)", "impl": "ours",
         "config": {
             "model": "Qwen2.5-0.5B sizes", "layers": cfg["num_hidden_layers"], "layers_of_model": full_layers,
@@ -401,6 +632,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4)},
         "points": points,
+        "kernels": kernels,
         "clocks": clock_record,
     }
     print(json.dumps(line))

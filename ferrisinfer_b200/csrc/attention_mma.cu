@@ -330,11 +330,10 @@ __global__ void __launch_bounds__(WARPS * 32)
                             float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ block_tables,
                             int max_blocks, const int* __restrict__ token_seq, const int* __restrict__ positions,
                             const int* __restrict__ token_list, int nh, int nkv, int page_size, int window, float scale,
-                            int splits, const FusedRope rope, int* split_counters, int* status) {
+                            int splits, const FusedRope rope, int cluster_merge, int* status) {
     FERRIS_TL_ENTRY();
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full[WARPS][STAGES];
-    __shared__ int last_of_its_splits;
     __shared__ int tile_rows[WARPS][ROW_CACHE];  // cache rows of this warp's next tiles, looked up in one go
     __shared__ float2 cos_sin[D / 2];            // (cos, sin) of the token's rotation angles, when the rotation is fused
     uint8_t* smem = align1024(smem_raw);
@@ -553,6 +552,14 @@ __global__ void __launch_bounds__(WARPS * 32)
         const int head = hk * G + r;
         if (splits == 1) {
             out[(size_t)tok * ldo + (size_t)head * D + c] = __float2bfloat16_rn(oo / ll);
+        } else if (cluster_merge) {
+            // this key range's (maximum, sum, output row) stays in shared memory for the cluster to merge
+            float* fin = merge + WARPS * 16 * (D + 2);
+            fin[r * (D + 2) + 2 + c] = oo;
+            if (c == 0) {
+                fin[r * (D + 2)] = mm;
+                fin[r * (D + 2) + 1] = ll;
+            }
         } else {
             // partial results are indexed by the row's place in this launch (blockIdx.z), not in the step
             const size_t slot = ((size_t)blockIdx.z * nh + head) * splits + split;
@@ -563,37 +570,41 @@ __global__ void __launch_bounds__(WARPS * 32)
             }
         }
     }
-    if (splits > 1 && split_counters) {
-        // The CTA that is last to finish among the key ranges of a (token, kv head) merges their partial results
-        // (the sums in the order of decode_merge_kernel, whichever CTA it is) and writes the output rows: no
-        // merge launch follows.  The counter goes back to zero for the next launch.
-        __threadfence();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int* counter = split_counters + (size_t)blockIdx.z * nkv + hk;
-            const int before = atomicAdd(counter, 1);
-            last_of_its_splits = before == splits - 1;
-            if (last_of_its_splits) *counter = 0;
-        }
-        __syncthreads();
-        if (last_of_its_splits) {
-            __threadfence();
-            for (int idx = threadIdx.x; idx < G * D; idx += WARPS * 32) {
-                const int r = idx / D, c = idx % D;
-                const int head = hk * G + r;
-                const size_t base = ((size_t)blockIdx.z * nh + head) * splits;
-                float mm = -INFINITY;
-                for (int s = 0; s < splits; ++s) mm = fmaxf(mm, __ldcg(&part_ml[(base + s) * 2]));
-                float ll = 0.0f, oo = 0.0f;
-                for (int s = 0; s < splits; ++s) {
-                    const float ms = __ldcg(&part_ml[(base + s) * 2]);
-                    const float f = ms == -INFINITY ? 0.0f : expf(ms - mm);
-                    ll += __ldcg(&part_ml[(base + s) * 2 + 1]) * f;
-                    oo += __ldcg(&part_o[(base + s) * D + c]) * f;
-                }
-                out[(size_t)tok * ldo + (size_t)head * D + c] = __float2bfloat16_rn(oo / ll);
+    if (splits > 1 && cluster_merge) {
+        // The key ranges of a (token, kv head) are the CTAs of one thread-block cluster: each takes a share of the
+        // G x D outputs and adds the ranges' partial results, read from their shared memory, in the order of the
+        // ranges (the sums of decode_merge_kernel): no scratch in global memory, no merge launch.
+        FERRIS_TL_MARK(tl_mark, 5);
+        cluster_sync();
+        FERRIS_TL_MARK(tl_mark, 6);
+        const uint32_t fin = smem_u32(merge + WARPS * 16 * (D + 2));
+        const int share = (G * D + splits - 1) / splits;
+        const int begin = (int)cluster_ctarank() * share, end = min(begin + share, G * D);
+        for (int idx = begin + threadIdx.x; idx < end; idx += WARPS * 32) {
+            const int r = idx / D, c = idx % D;
+            const uint32_t row = fin + (uint32_t)(r * (D + 2)) * 4u;
+            float ms[8], ls[8], os[8];
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                const bool have = sp < splits;
+                ms[sp] = have ? ld_peer_shared_f32(row, sp) : -INFINITY;
+                ls[sp] = have ? ld_peer_shared_f32(row + 4u, sp) : 0.0f;
+                os[sp] = have ? ld_peer_shared_f32(row + (uint32_t)(2 + c) * 4u, sp) : 0.0f;
             }
+            float mm = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) mm = fmaxf(mm, ms[sp]);
+            float ll = 0.0f, oo = 0.0f;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                if (sp >= splits) continue;
+                const float f = ms[sp] == -INFINITY ? 0.0f : expf(ms[sp] - mm);
+                ll += ls[sp] * f;
+                oo += os[sp] * f;
+            }
+            out[(size_t)tok * ldo + (size_t)(hk * G + r) * D + c] = __float2bfloat16_rn(oo / ll);
         }
+        cluster_sync();  // nobody leaves while a peer may still read its shared memory
     }
 #ifdef FERRIS_TIMELINE
     __syncthreads();
@@ -1290,15 +1301,12 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
                                  long long cache_pages, const int* block_tables, int max_blocks, const int* token_seq,
                                  const int* positions, const int* token_list, int tokens, int nh, int nkv, int d,
                                  int page_size, int window, float scale, int splits, float* scratch, void* stream,
-                                 const float* inv_freq = nullptr, const int* slot_mapping = nullptr, int merge = 1,
-                                 int* split_counters = nullptr) {
+                                 const float* inv_freq = nullptr, const int* slot_mapping = nullptr, int merge = 1) {
     if (tokens <= 0) return FERRIS_OK;
     int rc = check_common(nh, nkv, d, page_size, max_blocks);
     if (rc != FERRIS_OK) return rc;
     if (splits < 1 || splits > 65535) FERRIS_REFUSE("decode attention: %d splits", splits);
-    if (splits > 1 && !scratch) FERRIS_REFUSE("decode attention: splitting the keys needs scratch memory");
-    if (merge == 2 && splits > 1 && !split_counters) FERRIS_REFUSE("decode attention: merging in the kernel needs counters");
-    int* counters = (merge == 2 && splits > 1) ? split_counters : nullptr;
+    if (splits > 1 && !scratch && merge != 3) FERRIS_REFUSE("decode attention: splitting the keys needs scratch memory");
     if (nkv > 65535 || tokens > 65535) FERRIS_REFUSE("decode attention: %d tokens x %d kv heads exceed one launch", tokens, nkv);
     const uint64_t rows = (uint64_t)cache_pages * nkv * page_size;
     CUtensorMap mk, mv;
@@ -1314,20 +1322,51 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
     rope.slot_mapping = slot_mapping;
     rope.k_cache = (bf16*)const_cast<void*>(k_cache);
     rope.v_cache = (bf16*)const_cast<void*>(v_cache);
+    const int cluster = (merge == 3 && splits > 1) ? 1 : 0;
+    if (cluster && splits > 8) FERRIS_REFUSE("decode attention: a cluster merges at most 8 key ranges, not %d", splits);
+    auto launch = [&](auto kernel, size_t smem) -> cudaError_t {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(WARPS * 32);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[2];
+        int n = 0;
+        if (cluster) {
+            attr[n].id = cudaLaunchAttributeClusterDimension;
+            attr[n].val.clusterDim.x = (unsigned)splits;
+            attr[n].val.clusterDim.y = 1;
+            attr[n].val.clusterDim.z = 1;
+            ++n;
+        }
+        if (ferris_pdl_enabled()) {
+            attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[n].val.programmaticStreamSerializationAllowed = 1;
+            ++n;
+        }
+        cfg.attrs = attr;
+        cfg.numAttrs = n;
+        return cudaLaunchKernelEx(&cfg, kernel, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables,
+                                  max_blocks, token_seq, positions, token_list, nh, nkv, page_size, window, scale, splits,
+                                  rope, cluster, status);
+    };
+    cudaError_t e = cudaSuccess;
     if (d == 64) {
         constexpr int ST = 3;  // per warp 3 stages of 4 tiles (16 KB)
         const size_t smem = (size_t)WARPS * ST * 4 * 2 * TILE_KEYS * 64 * 2 + 1024;
         if ((rc = set_smem(decode_attention_kernel<64, ST>, smem)) != FERRIS_OK) return rc;
-        ferris_launch(decode_attention_kernel<64, ST>, grid, dim3(WARPS * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
-            token_list, nh, nkv, page_size, window, scale, splits, rope, counters, status);
-        if (splits > 1 && merge == 1) ferris_launch(decode_merge_kernel<64>, dim3(tokens, nh), dim3(64), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
+        e = launch(decode_attention_kernel<64, ST>, smem);
+        if (e == cudaSuccess && splits > 1 && merge == 1) ferris_launch(decode_merge_kernel<64>, dim3(tokens, nh), dim3(64), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
     } else {
         constexpr int ST = 3;  // per warp 3 stages of 2 tiles (16 KB)
         const size_t smem = (size_t)WARPS * ST * 2 * 2 * TILE_KEYS * 128 * 2 + 1024;
         if ((rc = set_smem(decode_attention_kernel<128, ST>, smem)) != FERRIS_OK) return rc;
-        ferris_launch(decode_attention_kernel<128, ST>, grid, dim3(WARPS * 32), smem, s, mk, mv, (const bf16*)q, ldq, (bf16*)out, ldo, part_o, part_ml, block_tables, max_blocks, token_seq, positions,
-            token_list, nh, nkv, page_size, window, scale, splits, rope, counters, status);
-        if (splits > 1 && merge == 1) ferris_launch(decode_merge_kernel<128>, dim3(tokens, nh), dim3(128), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
+        e = launch(decode_attention_kernel<128, ST>, smem);
+        if (e == cudaSuccess && splits > 1 && merge == 1) ferris_launch(decode_merge_kernel<128>, dim3(tokens, nh), dim3(128), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
+    }
+    if (e != cudaSuccess) {
+        ferris_set_error("decode attention: %s", cudaGetErrorString(e));
+        return (int)e;
     }
     FERRIS_LAUNCH_CHECK();
 }
@@ -1359,19 +1398,70 @@ FERRIS_API int ferris_decode_attention_listed(const void* q, int ldq, void* out,
 // qkv: the step's [tokens, (nh + 2 nkv) d] rows; slot_mapping null: rotate q only (a layer that reads another
 // layer's cache).  merge: 1 a merge kernel follows; 0 with splits > 1: the partial results of the key ranges stay
 // in scratch, `out` is not written, and the caller merges them (ferris_decode_merge, or the product that follows
-// does it on its way); 2: the CTA that finishes last among the key ranges of a (token, kv head) merges them, which
-// needs `counters`: tokens x nkv ints, zero before the first launch (every launch leaves them zero).
+// does it on its way); 3: the key ranges of a (token, kv head) form a thread-block cluster (at most 8 ranges) that
+// merges them through its distributed shared memory, without scratch (ferris_decode_cluster_splits says how many
+// ranges).  A merge by the CTA that finishes last among the ranges (a fence, a counter in global memory) was measured
+// too: it cost the decode step of 8 tokens 8.6 us a layer, twice what the merge kernel costs.
 FERRIS_API int ferris_decode_attention_rope(const void* qkv, int ldq, void* out, int ldo, void* k_cache, void* v_cache,
                                             long long cache_pages, const int* block_tables, int max_blocks,
                                             const int* token_seq, const int* positions, const float* inv_freq,
                                             const int* slot_mapping, int tokens, int nh, int nkv, int d, int page_size,
                                             int window, float scale, int splits, float* scratch, int merge,
-                                            int* counters, void* stream) {
+                                            void* stream) {
     if (!inv_freq) FERRIS_REFUSE("decode attention with rotation: no frequency table");
-    if (merge < 0 || merge > 2) FERRIS_REFUSE("decode attention with rotation: merge mode %d", merge);
+    if (merge != 0 && merge != 1 && merge != 3) FERRIS_REFUSE("decode attention with rotation: merge mode %d", merge);
     return decode_attention_impl(qkv, ldq, out, ldo, k_cache, v_cache, cache_pages, block_tables, max_blocks, token_seq,
                                  positions, nullptr, tokens, nh, nkv, d, page_size, window, scale, splits, scratch, stream,
-                                 inv_freq, slot_mapping, merge, counters);
+                                 inv_freq, slot_mapping, merge);
+}
+
+// Into how many key ranges a step of `tokens` single tokens is cut when a cluster merges them (merge mode 3): at
+// most 8 (a portable cluster), no more than fill the SMs once, at least eight 16-key tiles each, and only as many as
+// the GPU holds clusters of that size at once (the CTAs of a cluster share a GPC; a cluster that has to wait for
+// one costs a second round).  0: this head size has no such kernel.
+FERRIS_API int ferris_decode_cluster_splits(int tokens, int nkv, int d, int max_kv_len) {
+    if (tokens <= 0 || nkv <= 0 || (d != 64 && d != 128)) return 0;
+    static int fits[2][9] = {};  // clusters of size s that are resident at once, by head size; 0 = not asked yet
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+        sms = 148;
+    const int groups = tokens * nkv;
+    int want = sms / groups;
+    if (want > 8) want = 8;
+    const int most = (max_kv_len / TILE_KEYS) / 8;
+    if (want > most) want = most;
+    if (want < 1) want = 1;
+    for (int sp = want; sp > 1; --sp) {
+        int& have = fits[d == 64 ? 0 : 1][sp];
+        if (have == 0) {
+            have = -1;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(sp, 1, 1);
+            cfg.blockDim = dim3(WARPS * 32);
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = (unsigned)sp;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            int clusters = 0;
+            cudaError_t e;
+            if (d == 64) {
+                cfg.dynamicSmemBytes = (size_t)WARPS * 3 * 4 * 2 * TILE_KEYS * 64 * 2 + 1024;
+                set_smem(decode_attention_kernel<64, 3>, cfg.dynamicSmemBytes);
+                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<64, 3>, &cfg);
+            } else {
+                cfg.dynamicSmemBytes = (size_t)WARPS * 3 * 2 * 2 * TILE_KEYS * 128 * 2 + 1024;
+                set_smem(decode_attention_kernel<128, 3>, cfg.dynamicSmemBytes);
+                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<128, 3>, &cfg);
+            }
+            if (e == cudaSuccess && clusters > 0) have = clusters;
+            else cudaGetLastError();
+        }
+        if (have >= groups) return sp;
+    }
+    return 1;
 }
 
 // The merge alone, for partial results that ferris_decode_attention_rope left in scratch (merge == 0):

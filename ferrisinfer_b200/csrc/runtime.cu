@@ -153,6 +153,36 @@ int ferris_encode_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t row
     return FERRIS_OK;
 }
 
+// A bf16 matrix [rows, cols] (cols a multiple of 64) seen as [rows][64-column blocks][64]: one box is `box_rows` rows of
+// `box_kblocks` consecutive blocks, and lands in shared memory as box_rows x box_kblocks lines of 128 bytes (line
+// row * box_kblocks + block), swizzled by the line's number.  One copy thus brings what box_kblocks copies of the
+// 2-D map bring; with an odd box_kblocks the eight rows of one block fall into eight different swizzle phases.
+int ferris_make_tensor_map_kblocks(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                                   uint32_t box_rows, uint32_t box_kblocks) {
+    const MapKey key = {base, rows, cols, row_stride, box_rows, box_kblocks, 2u};
+    MapSlot& slot = slot_of(key);
+    if (slot.used && same(slot.key, key)) {
+        *map = slot.map;
+        return FERRIS_OK;
+    }
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) FERRIS_REFUSE("tensor map: the driver offers no cuTensorMapEncodeTiled");
+    if (((uintptr_t)base & 15) || ((row_stride * 2) & 15) || (cols & 63) || box_rows == 0 || box_rows > 256 ||
+        box_kblocks == 0 || box_kblocks > 256)
+        FERRIS_REFUSE("tensor map: base %p, row stride %llu, %llu columns, box %u rows x %u blocks do not meet the rules", base,
+                      (unsigned long long)row_stride, (unsigned long long)cols, box_rows, box_kblocks);
+    cuuint64_t dims[3] = {64, cols / 64, rows};
+    cuuint64_t strides[2] = {128, row_stride * 2};
+    cuuint32_t box[3] = {64, box_kblocks, box_rows};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) FERRIS_REFUSE("tensor map: cuTensorMapEncodeTiled (3-D) failed with %d", (int)r);
+    slot = {key, *map, true};
+    return FERRIS_OK;
+}
+
 int ferris_make_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                                   uint64_t row_stride, uint32_t box_rows) {
     const MapKey key = {base, rows, cols, row_stride, box_rows, 32u, 1u};

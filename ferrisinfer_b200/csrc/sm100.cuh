@@ -107,6 +107,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+// The same with three coordinates (x innermost).
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
 // TMA tile shared -> global: a plain store, or an element-wise add into global memory (done by the memory
 // system, so the old values are never read by the SM).  Completion is tracked per thread in bulk groups.
 // Coordinates must not be negative; rows and columns beyond the tensor's extent are dropped.
@@ -143,6 +151,10 @@ __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                  : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
 }
 
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
@@ -340,6 +352,8 @@ __device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar, uint16_t cta_
 // A 2-D bf16 tensor [rows, cols] with `row_stride` elements between rows, read in boxes of
 // box_rows x box_cols with 128-byte swizzle (box_cols * 2 bytes must be 128).
 // Returns 0 or a negative error (text in ferris_last_error()).
+int ferris_make_tensor_map_kblocks(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
+                                   uint32_t box_rows, uint32_t box_kblocks);
 int ferris_make_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
                               uint32_t box_rows, uint32_t box_cols);
 

@@ -40,7 +40,7 @@ _SIGNATURES = {
     "ferris_rope_cache_write": [_VP, _I, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP],
     "ferris_prefill_attention": [_VP, _I, _VP, _I, _VP, _VP, _LL, _VP, _I, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _F, _I, _VP],
     "ferris_decode_attention_rope": [_VP, _I, _VP, _I, _VP, _VP, _LL, _VP, _I, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I,
-                                     _F, _I, _VP, _I, _VP, _VP],
+                                     _F, _I, _VP, _I, _VP],
     "ferris_gemm_skinny": [_VP, _I, _VP, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _VP],
     "ferris_gemm_skinny_takes": [_I, _I, _I, _I],
     "ferris_embed_gather": [_VP, _I, _VP, _VP, _I, _I, _I, _VP, _VP],
@@ -399,7 +399,7 @@ def _skinny_takes(x, w, out, accs: int) -> bool:
         if x._done or not (x.h.is_cuda and x.h.dtype == torch.float32 and x.h.is_contiguous() and x.h.data_ptr() % 16 == 0
                            and x.weight.data_ptr() % 16 == 0):
             return False
-    elif not (x.dim() == 2 and x.is_cuda and x.stride(1) == 1 and (x.stride(0) % 2 == 0 or T == 1) and x.data_ptr() % 4 == 0):
+    elif not (x.dim() == 2 and x.is_cuda and x.stride(1) == 1 and (x.stride(0) % 8 == 0 or T == 1) and x.data_ptr() % 16 == 0):
         return False
     N = out.shape[1]
     key = (T > 8, N, K, accs)
@@ -727,14 +727,19 @@ def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_head
                 or inv_freq.numel() != head_dim // 2 or meta.slot_mapping.numel() != T):
             raise KernelError(f"attention step: qkv {tuple(qkv.shape)}, cache {tuple(k_cache.shape)}, out {tuple(out.shape)}")
         kv_span = min(ctx.max_kv_len, window) if window else ctx.max_kv_len
-        splits = decode_splits(T, num_kv_heads, kv_span)
-        need = T * num_heads * splits * (head_dim + 2) if splits > 1 else 0
+        # Who merges the key ranges: with the skinny products the attention kernel itself (the ranges of a token and
+        # kv head are a thread-block cluster that adds them through its shared memory); otherwise the output product
+        # on its way (lazy_merge) or a merge kernel
+        in_cluster = gemm_skinny_enabled()
+        if in_cluster:
+            splits = int(_lib().ferris_decode_cluster_splits(T, num_kv_heads, head_dim, kv_span))
+            in_cluster = splits >= 1
+        if not in_cluster:
+            splits = decode_splits(T, num_kv_heads, kv_span)
+        need = T * num_heads * splits * (head_dim + 2) if (splits > 1 and not in_cluster) else 0
         scratch = ctx.workspace.get("attn_split_scratch", (need,), torch.float32) if need else None
-        # Who merges the key ranges: with the skinny products the attention kernel itself (its last CTA per token
-        # and kv head), otherwise the output product on its way (lazy_merge) or a merge kernel
-        in_kernel = bool(need) and gemm_skinny_enabled() and T * num_kv_heads <= _SPLIT_COUNTERS
-        leave = bool(lazy_merge and need) and not in_kernel
-        counters = _split_counters(qkv.device) if in_kernel else None
+        leave = bool(lazy_merge and need)
+        mode = 3 if in_cluster else (0 if leave else 1)
         _, _, ldq = _rows(qkv, "attention queries")
         _, _, ldo = _rows(out, "attention output")
         _check(
@@ -743,30 +748,14 @@ def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_head
                 ctypes.c_longlong(k_cache.shape[0]), _ptr(meta.block_tables), _c_int(meta.block_tables.shape[1]),
                 _ptr(ctx.token_seq), _ptr(ctx.positions), _ptr(inv_freq), _ptr(meta.slot_mapping if write_kv else None),
                 _c_int(T), _c_int(num_heads), _c_int(num_kv_heads), _c_int(head_dim), _c_int(page_size),
-                _c_int(window or 0), _c_float(scale), _c_int(splits), _ptr(scratch),
-                _c_int(2 if in_kernel else (0 if leave else 1)), _ptr(counters), _stream()),
-            "decode attention with rotation", 2 if (splits > 1 and not leave and not in_kernel) else 1,
+                _c_int(window or 0), _c_float(scale), _c_int(splits), _ptr(scratch), _c_int(mode), _stream()),
+            "decode attention with rotation", 2 if (splits > 1 and mode == 1) else 1,
         )
         return LazySplitMerge(scratch, out, num_heads, head_dim, splits) if leave else out
     rope_cache_write(qkv, ctx.positions, inv_freq, meta.slot_mapping, k_cache, v_cache, num_heads, num_kv_heads,
                      head_dim, rotary_dim, page_size, write_kv=write_kv)
     paged_attention(qkv, out, k_cache, v_cache, meta.block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale)
     return out
-
-
-_SPLIT_COUNTERS = 1 << 16
-_split_counter_buffers: dict = {}
-
-
-def _split_counters(device) -> torch.Tensor:
-    """Counters of finished key ranges per (token, kv head) for the in-kernel merge: zero before the first launch,
-    left zero by every launch, one buffer per device for the life of the process (recorded steps point at it)."""
-    key = str(device)
-    buf = _split_counter_buffers.get(key)
-    if buf is None:
-        buf = torch.zeros(_SPLIT_COUNTERS, dtype=torch.int32, device=device)
-        _split_counter_buffers[key] = buf
-    return buf
 
 
 def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale):

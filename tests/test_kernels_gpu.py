@@ -851,7 +851,7 @@ def test_sampling_distribution(device):
 
 # ------------------------------------------------------------------------------- skinny gemm
 SKINNY_SHAPES = [(1152, 896), (896, 4864), (130, 72), (300, 1000), (9728, 896),
-                 (4608, 3584), (896, 18944),  # slabs that do not fit into shared memory: the stages are a ring
+                 (4608, 3584), (896, 6016),  # slabs that do not fit into shared memory: the stages are a ring
                  (9472, 64), (7, 8), (17920, 1536)]  # 64 rows per CTA; one K block of 8; more CTAs than SMs
 
 
@@ -868,7 +868,11 @@ def test_gemm_skinny(T, N, K, device):
     bias = rnd((N,), F32, device, 53)
     want = _gemm_reference(x, w)
     out = torch.full((T, N), float("nan"), dtype=BF16, device=device)
-    assert ops._skinny_takes(x, w, out, 1)
+    if not ops._skinny_takes(x, w, out, 1):
+        # the step's rows stand whole in shared memory beside the weight stages: long rows of more than 8 tokens, or more
+        # than 8 tokens beside slabs of 64 rows, do not fit
+        assert T > 8 and (K > 3000 or N > 9000)
+        pytest.skip("left to the tcgen05 kernel")
     ops.gemm_skinny(x, w, bias, out, 0)
     _close(out, want + bias.cpu().double(), K, BF16)
     out32 = torch.full((T, N), float("nan"), dtype=F32, device=device)
@@ -879,7 +883,11 @@ def test_gemm_skinny(T, N, K, device):
     assert torch.equal(again, out32)
     one = torch.empty(1, N, dtype=F32, device=device)
     ops.gemm_skinny(x[T - 1:T], w, None, one, 1)
-    assert torch.equal(one[0], out32[T - 1]), "a row's sum does not depend on the rows beside it"
+    if T <= 8:
+        assert torch.equal(one[0], out32[T - 1]), "a row's sum does not depend on the rows beside it"
+    else:
+        # more than 8 tokens may be cut into other groups of K blocks: the same sum in another order
+        assert torch.allclose(one[0], out32[T - 1], rtol=1e-5, atol=1e-5 * math.sqrt(K) * want.abs().max().item())
     acc = rnd((T, N), F32, device, 54)
     before = acc.clone()
     ops.gemm_skinny(x, w, bias, acc, 2)
@@ -912,10 +920,11 @@ def test_gemm_skinny_leaves_tall_products_and_long_steps_to_the_other_kernels(de
 
 @pytest.mark.parametrize("nh, nkv, d, T, window", [(14, 2, 64, 8, 0), (12, 2, 128, 3, 0), (7, 1, 64, 16, 0), (14, 2, 64, 1, 0),
                                                    (4, 4, 64, 5, 1000)])
-def test_decode_attention_merges_its_key_ranges_in_its_last_cta(nh, nkv, d, T, window, device, request):
-    """With the skinny products the decode kernel merges the partial results of its key ranges itself: the CTA that
-    finishes last among the ranges of a (token, kv head) adds them in the merge kernel's order.  The result is the
-    merge kernel's bit for bit, launch after launch (the counters return to zero)."""
+def test_decode_attention_merges_its_key_ranges_in_a_cluster(nh, nkv, d, T, window, device, request):
+    """With the skinny products the decode kernel merges the partial results of its key ranges itself: the ranges of
+    a (token, kv head) are the CTAs of a thread-block cluster, which adds them through its shared memory in the
+    order of the ranges.  One launch, no scratch; the same bits launch after launch; and the merge kernel's result
+    within rounding (the two paths cut the keys into ranges of different lengths)."""
     from ferrisinfer_b200.kernels import ops
     from ferrisinfer_b200.parts.base import PagedMeta
 
@@ -931,6 +940,7 @@ def test_decode_attention_merges_its_key_ranges_in_its_last_cta(nh, nkv, d, T, w
     inv_freq = torch.tensor(plain.rotary_inverse_frequencies(d, d, 1e6).numpy(), device=device)
     meta = PagedMeta(block_tables=tables, slot_mapping=slots, page_size=page)
     scale = 1.0 / math.sqrt(d)
+    assert ops._lib().ferris_decode_cluster_splits(T, nkv, d, min(window, 4096) if window else 4096) > 1
     got = []
     for _ in range(3):
         out = torch.full((T, nh * d), float("nan"), dtype=BF16, device=device)
@@ -942,12 +952,12 @@ def test_decode_attention_merges_its_key_ranges_in_its_last_cta(nh, nkv, d, T, w
         got.append(out)
     torch.cuda.synchronize()
     assert ops.kernel_status() == 0
-    assert int(ops._split_counters(device).abs().sum().item()) == 0
+    assert torch.equal(got[0], got[1]) and torch.equal(got[0], got[2])
     request.getfixturevalue("skinny_off")
     want = torch.full((T, nh * d), float("nan"), dtype=BF16, device=device)
     k2, v2 = k.clone(), v.clone()
     ops.attention_step(qkv.clone(), want, k2, v2, meta, ctx, nh, nkv, d, inv_freq, d, window, scale)
-    assert all(torch.equal(o, want) for o in got)
+    assert torch.allclose(got[0].float(), want.float(), atol=2e-2, rtol=2e-2), (got[0].float() - want.float()).abs().max()
     assert torch.equal(k1, k2) and torch.equal(v1, v2)
 
 

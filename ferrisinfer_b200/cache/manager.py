@@ -141,10 +141,11 @@ def _build_paged(manager, index, need):
     g.members.append(index)
     cache = LayerCache(need=need, group=g.gid)
     if manager.device is not None:
-        # one page beyond the pool's: the padding page
-        shape = (g.pool.num_pages + 1, need.num_kv_heads, manager.page_size, need.head_dim)
-        cache.k = torch.zeros(shape, dtype=manager.dtype, device=manager.device)
-        cache.v = torch.zeros(shape, dtype=manager.dtype, device=manager.device)
+        # one page beyond the pool's: the padding page.  Keys and values are the two planes of one tensor, so that
+        # a kernel can fetch a tile of keys and the tile of values of the same tokens with one copy.
+        shape = (2, g.pool.num_pages + 1, need.num_kv_heads, manager.page_size, need.head_dim)
+        planes = torch.zeros(shape, dtype=manager.dtype, device=manager.device)
+        cache.k, cache.v = planes[0], planes[1]
     return cache
 
 

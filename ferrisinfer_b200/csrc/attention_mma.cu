@@ -65,7 +65,9 @@ __device__ __forceinline__ void load_q(WarpState<D>& st, const bf16* row0, const
 
 // One tile of 16 keys starting at absolute key `key0`; K and V tiles lie in shared memory as D/64
 // swizzled boxes of 16 rows x 128 bytes each (box c = columns 64c .. 64c+63).
-template <int D>
+// CS: bytes between the 64-column boxes of one tile (2048 when the boxes of K lie together and those of V after them;
+// 4096 when each box of K is followed by the box of V of the same columns).
+template <int D, int CS = 2048>
 __device__ __forceinline__ void attend_tile(WarpState<D>& st, uint32_t k_smem, uint32_t v_smem, int key0,
                                             const RowLimits& lim, float scale) {
     const int lane = threadIdx.x & 31;
@@ -85,7 +87,7 @@ __device__ __forceinline__ void attend_tile(WarpState<D>& st, uint32_t k_smem, u
             for (int ks = 0; ks < D / 16; ks += 2) {
                 const int cc = 2 * ks + mi;  // 16-byte chunk of the row: k columns 8cc .. 8cc+7
                 uint32_t r[4];
-                ldmatrix_x4(r, k_smem + (cc >> 3) * 2048 + swizzle128(8 * j + r8, cc & 7));
+                ldmatrix_x4(r, k_smem + (cc >> 3) * CS + swizzle128(8 * j + r8, cc & 7));
                 mma_bf16_16816(s[j], st.q[ks], r[0], r[1]);
                 mma_bf16_16816(s[j], st.q[ks + 1], r[2], r[3]);
             }
@@ -142,7 +144,7 @@ __device__ __forceinline__ void attend_tile(WarpState<D>& st, uint32_t k_smem, u
         for (int n = 0; n < D / 8; n += 2) {
             const int cc = n + (mi >> 1);
             uint32_t r[4];
-            ldmatrix_x4_trans(r, v_smem + (cc >> 3) * 2048 + swizzle128(row, cc & 7));
+            ldmatrix_x4_trans(r, v_smem + (cc >> 3) * CS + swizzle128(row, cc & 7));
             mma_bf16_16816(st.o[n], p, r[0], r[1]);
             mma_bf16_16816(st.o[n + 1], p, r[2], r[3]);
         }
@@ -152,7 +154,7 @@ __device__ __forceinline__ void attend_tile(WarpState<D>& st, uint32_t k_smem, u
 // NT consecutive 16-key tiles (16 NT keys from `key0`) at once: one running-maximum update and one
 // rescale of the output per block, and NT independent score tiles in flight.  The tiles lie
 // `tile_bytes` apart in shared memory, each laid out as attend_tile expects.
-template <int D, int NT>
+template <int D, int NT, int CS = 2048, int VOFF = (D / 64) * 2048>
 __device__ __forceinline__ void attend_block(WarpState<D>& st, uint32_t base, uint32_t tile_bytes, int key0,
                                              const RowLimits& lim, float scale) {
     const int lane = threadIdx.x & 31;
@@ -172,7 +174,7 @@ __device__ __forceinline__ void attend_block(WarpState<D>& st, uint32_t base, ui
             for (int ks = 0; ks < D / 16; ks += 2) {
                 const int cc = 2 * ks + mi;
                 uint32_t r[4];
-                ldmatrix_x4(r, k_smem + (cc >> 3) * 2048 + swizzle128(8 * j + r8, cc & 7));
+                ldmatrix_x4(r, k_smem + (cc >> 3) * CS + swizzle128(8 * j + r8, cc & 7));
                 mma_bf16_16816(s[2 * k + j], st.q[ks], r[0], r[1]);
                 mma_bf16_16816(s[2 * k + j], st.q[ks + 1], r[2], r[3]);
             }
@@ -234,13 +236,13 @@ __device__ __forceinline__ void attend_block(WarpState<D>& st, uint32_t base, ui
             p[2] = pack_bf16(e10, e11);
             p[3] = pack_bf16(e12, e13);
         }
-        const uint32_t v_smem = base + k * tile_bytes + (D / 64) * 2048;
+        const uint32_t v_smem = base + k * tile_bytes + VOFF;
         const int row = (mi & 1) * 8 + r8;
 #pragma unroll
         for (int n = 0; n < D / 8; n += 2) {
             const int cc = n + (mi >> 1);
             uint32_t r[4];
-            ldmatrix_x4_trans(r, v_smem + (cc >> 3) * 2048 + swizzle128(row, cc & 7));
+            ldmatrix_x4_trans(r, v_smem + (cc >> 3) * CS + swizzle128(row, cc & 7));
             mma_bf16_16816(st.o[n], p, r[0], r[1]);
             mma_bf16_16816(st.o[n + 1], p, r[2], r[3]);
         }
@@ -323,7 +325,11 @@ __device__ __forceinline__ void rotate_q(WarpState<D>& st, const float2* cos_sin
 // split's key range in turn, each with a pipeline of its own; their results are merged through
 // shared memory and written either as the final output or as one partial (m, l, O) per split.
 // =============================================================================================
-template <int D, int STAGES>
+// PAIR: the key and the value cache are two planes of one tensor, and `map_k` is a 3-D map over both: one copy brings
+// the 64-column box of K and the box of V of the same 16 keys and columns (4 KB instead of two copies of 2 KB; a
+// copy costs the TMA unit ~30 ns whatever it brings, and a CTA of a long context issues hundreds).  A tile then lies
+// in shared memory as (K box, V box) per 64 columns instead of all K boxes followed by all V boxes.
+template <int D, int STAGES, bool PAIR>
 __global__ void __launch_bounds__(WARPS * 32)
     decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
@@ -341,6 +347,8 @@ __global__ void __launch_bounds__(WARPS * 32)
     constexpr int TILE_BYTES = 2 * TILE_KEYS * D * 2;
     constexpr int STAGE_BYTES = NT * TILE_BYTES;
     constexpr int BLOCK_CACHE = ROW_CACHE / NT;  // blocks whose rows the cache holds
+    constexpr int CS = PAIR ? 4096 : 2048;             // bytes between the 64-column boxes of a tile
+    constexpr int VOFF = PAIR ? 2048 : (D / 64) * 2048;  // where a tile's V boxes begin
 
     const int split = blockIdx.x, hk = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -421,8 +429,12 @@ __global__ void __launch_bounds__(WARPS * 32)
             const int row = tile_rows[warp][(i % BLOCK_CACHE) * NT + k];
 #pragma unroll
             for (int c = 0; c < D / 64; ++c) {
-                tma_load_2d(stage + k * TILE_BYTES + c * 2048, &map_k, 64 * c, row, bar);
-                tma_load_2d(stage + k * TILE_BYTES + (D / 64) * 2048 + c * 2048, &map_v, 64 * c, row, bar);
+                if (PAIR) {
+                    tma_load_3d(stage + k * TILE_BYTES + c * CS, &map_k, 64 * c, row, 0, bar);
+                } else {
+                    tma_load_2d(stage + k * TILE_BYTES + c * 2048, &map_k, 64 * c, row, bar);
+                    tma_load_2d(stage + k * TILE_BYTES + (D / 64) * 2048 + c * 2048, &map_v, 64 * c, row, bar);
+                }
             }
         }
     };
@@ -486,7 +498,7 @@ __global__ void __launch_bounds__(WARPS * 32)
             const int slot = own_slot;
             const size_t crow = slot >= 0 ? ((size_t)(slot / page_size) * nkv + hk) * page_size + slot % page_size : 0;
             auto put = [&](uint8_t* tile, bf16* cache, int c, bf16 v) {
-                *reinterpret_cast<bf16*>(tile + (c >> 6) * 2048 + swizzle128(r, (c & 63) >> 3) + (c & 7) * 2) = v;
+                *reinterpret_cast<bf16*>(tile + (c >> 6) * CS + swizzle128(r, (c & 63) >> 3) + (c & 7) * 2) = v;
                 if (slot >= 0) cache[crow * D + c] = v;
             };
 #pragma unroll
@@ -497,16 +509,16 @@ __global__ void __launch_bounds__(WARPS * 32)
                 put(tb, rope.k_cache, i2 + D / 2, __float2bfloat16_rn(k_hi[j] * a.x + k_lo[j] * a.y));
             }
 #pragma unroll
-            for (int j = 0; j < D / 32; ++j) put(tb + (D / 64) * 2048, rope.v_cache, lane + 32 * j, v_own[j]);
+            for (int j = 0; j < D / 32; ++j) put(tb + VOFF, rope.v_cache, lane + 32 * j, v_own[j]);
             fence_proxy_async();
             __syncwarp();
         }
         if (tile0 + NT <= t_end) {
-            attend_block<D, NT>(st, base, TILE_BYTES, tile0 * TILE_KEYS, lim, scale);
+            attend_block<D, NT, CS, VOFF>(st, base, TILE_BYTES, tile0 * TILE_KEYS, lim, scale);
         } else {
             for (int k = 0; tile0 + k < t_end; ++k)
-                attend_tile<D>(st, base + k * TILE_BYTES, base + k * TILE_BYTES + (D / 64) * 2048,
-                               (tile0 + k) * TILE_KEYS, lim, scale);
+                attend_tile<D, CS>(st, base + k * TILE_BYTES, base + k * TILE_BYTES + VOFF, (tile0 + k) * TILE_KEYS, lim,
+                                   scale);
         }
         __syncwarp();
         if (lane == 0 && i + STAGES < my_count) issue(i + STAGES);
@@ -1264,6 +1276,26 @@ int cache_map(const void* base, uint64_t rows, int d, CUtensorMap* out) {
     return FERRIS_OK;
 }
 
+// One map over the key cache and the value cache when they are two planes of one tensor (the value plane begins where
+// the key plane ends): dims (d, rows, 2), box (64, 16, 2).  Returns false when they are not, or the map cannot be made.
+MapCacheEntry g_pair_maps[MAP_CACHE];
+int g_pair_map_count = 0;
+bool cache_pair_map(const void* k_base, const void* v_base, uint64_t rows, int d, CUtensorMap* out) {
+    const uint64_t plane = rows * (uint64_t)d * 2;
+    if ((const uint8_t*)v_base != (const uint8_t*)k_base + plane) return false;
+    for (int i = 0; i < g_pair_map_count; ++i)
+        if (g_pair_maps[i].base == k_base && g_pair_maps[i].rows == rows && g_pair_maps[i].d == d) {
+            *out = g_pair_maps[i].map;
+            return true;
+        }
+    CUtensorMap m;
+    if (ferris_make_tensor_map_planes(&m, k_base, rows, (uint64_t)d, plane, TILE_KEYS) != FERRIS_OK) return false;
+    const int slot = g_pair_map_count < MAP_CACHE ? g_pair_map_count++ : 0;
+    g_pair_maps[slot] = {k_base, rows, d, m};
+    *out = m;
+    return true;
+}
+
 int check_common(int nh, int nkv, int d, int page_size, int max_blocks) {
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) FERRIS_REFUSE("attention: %d heads over %d kv heads", nh, nkv);
     if (nh / nkv > 16) FERRIS_REFUSE("tensor-core attention takes groups of at most 16 heads, not %d", nh / nkv);
@@ -1351,19 +1383,26 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
                                   rope, cluster, status);
     };
     cudaError_t e = cudaSuccess;
+    CUtensorMap mkv;
+    const bool pair = cache_pair_map(k_cache, v_cache, rows, d, &mkv);
+    if (pair) mk = mkv;
+    constexpr int ST = 3;  // per warp 3 stages of 16 KB: 4 tiles of head size 64, 2 of head size 128
+    const size_t smem = (size_t)WARPS * ST * 16384 + 1024;
+#define FERRIS_DECODE_LAUNCH(DD, PP)                                                             \
+    do {                                                                                         \
+        if ((rc = set_smem(decode_attention_kernel<DD, ST, PP>, smem)) != FERRIS_OK) return rc;  \
+        e = launch(decode_attention_kernel<DD, ST, PP>, smem);                                   \
+    } while (0)
     if (d == 64) {
-        constexpr int ST = 3;  // per warp 3 stages of 4 tiles (16 KB)
-        const size_t smem = (size_t)WARPS * ST * 4 * 2 * TILE_KEYS * 64 * 2 + 1024;
-        if ((rc = set_smem(decode_attention_kernel<64, ST>, smem)) != FERRIS_OK) return rc;
-        e = launch(decode_attention_kernel<64, ST>, smem);
+        if (pair) FERRIS_DECODE_LAUNCH(64, true);
+        else FERRIS_DECODE_LAUNCH(64, false);
         if (e == cudaSuccess && splits > 1 && merge == 1) ferris_launch(decode_merge_kernel<64>, dim3(tokens, nh), dim3(64), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
     } else {
-        constexpr int ST = 3;  // per warp 3 stages of 2 tiles (16 KB)
-        const size_t smem = (size_t)WARPS * ST * 2 * 2 * TILE_KEYS * 128 * 2 + 1024;
-        if ((rc = set_smem(decode_attention_kernel<128, ST>, smem)) != FERRIS_OK) return rc;
-        e = launch(decode_attention_kernel<128, ST>, smem);
+        if (pair) FERRIS_DECODE_LAUNCH(128, true);
+        else FERRIS_DECODE_LAUNCH(128, false);
         if (e == cudaSuccess && splits > 1 && merge == 1) ferris_launch(decode_merge_kernel<128>, dim3(tokens, nh), dim3(128), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
     }
+#undef FERRIS_DECODE_LAUNCH
     if (e != cudaSuccess) {
         ferris_set_error("decode attention: %s", cudaGetErrorString(e));
         return (int)e;
@@ -1449,12 +1488,12 @@ FERRIS_API int ferris_decode_cluster_splits(int tokens, int nkv, int d, int max_
             cudaError_t e;
             if (d == 64) {
                 cfg.dynamicSmemBytes = (size_t)WARPS * 3 * 4 * 2 * TILE_KEYS * 64 * 2 + 1024;
-                set_smem(decode_attention_kernel<64, 3>, cfg.dynamicSmemBytes);
-                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<64, 3>, &cfg);
+                set_smem(decode_attention_kernel<64, 3, true>, cfg.dynamicSmemBytes);
+                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<64, 3, true>, &cfg);
             } else {
                 cfg.dynamicSmemBytes = (size_t)WARPS * 3 * 2 * 2 * TILE_KEYS * 128 * 2 + 1024;
-                set_smem(decode_attention_kernel<128, 3>, cfg.dynamicSmemBytes);
-                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<128, 3>, &cfg);
+                set_smem(decode_attention_kernel<128, 3, true>, cfg.dynamicSmemBytes);
+                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<128, 3, true>, &cfg);
             }
             if (e == cudaSuccess && clusters > 0) have = clusters;
             else cudaGetLastError();

@@ -65,15 +65,14 @@ struct SkParams {
 
 __device__ __forceinline__ float sk_silu_mul(float g, float u) { return u * (g * (1.0f / (1.0f + expf(-g)))); }
 
-__device__ __forceinline__ void sk_write(const SkParams& p, int t, int n, float a, float b) {
-    const float bias_v = p.bias ? p.bias[n] : 0.0f;
+// a: the product (the gate's in SwiGLU mode), b: the up product, bias_v: bias[n] or 0, old: what out[t, n] held.
+__device__ __forceinline__ void sk_write(const SkParams& p, int t, int n, float a, float b, float bias_v, float old) {
     if (p.mode == SK_STORE_BF16) {
         reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(a + bias_v);
     } else if (p.mode == SK_STORE_F32) {
         reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = a + bias_v;
     } else if (p.mode == SK_ACCUM_F32) {
-        float* o = reinterpret_cast<float*>(p.out) + (size_t)t * p.ldo + n;
-        *o = *o + (a + bias_v);
+        reinterpret_cast<float*>(p.out)[(size_t)t * p.ldo + n] = old + (a + bias_v);
     } else {
         reinterpret_cast<bf16*>(p.out)[(size_t)t * p.ldo + n] = __float2bfloat16_rn(sk_silu_mul(a, b));
     }
@@ -150,17 +149,54 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
         return;
     }
 
+    // What does not depend on the launch before is read BEFORE the wait, so that no trip to HBM stands on the step's
+    // critical path after it: the bias of this thread's outputs and the norm's weight (each layer has its own: they
+    // are never in L2 when the step comes to them).  The old values of the outputs (the residual that an accumulating
+    // product adds to) are requested right after the wait and used at the very end.
+    constexpr int OUTS = SK_MAX_MT * NT / 2;  // outputs of one thread: element tid + 256 i of the accumulator tiles
+    const int per_acc = p.mt * NT * 4;
+    int out_t[OUTS], out_n[OUTS];
+    float bias_r[OUTS], old_r[OUTS];
+#pragma unroll
+    for (int i = 0; i < OUTS; ++i) {
+        const int q = threadIdx.x + SK_WARPS * 32 * i;
+        const int ln = q & 31, e = q >> 5;
+        const int j = e & 3, nt = (e >> 2) % NT, m = (e >> 2) / NT;
+        const int row = m * 16 + (ln >> 2) + ((j & 2) ? 8 : 0);
+        const int t = nt * 8 + (ln & 3) * 2 + (j & 1);
+        const int n = n0 + row;
+        const bool valid = q < per_acc * 32 && row < p.rows && n < p.N && t < p.T;
+        out_t[i] = valid ? t : -1;
+        out_n[i] = n;
+        bias_r[i] = (valid && p.bias) ? p.bias[n] : 0.0f;
+        old_r[i] = 0.0f;
+    }
+    const int n4 = p.K / 4, tile4 = p.kblocks * 16;
+    const float4* w4 = reinterpret_cast<const float4*>(p.norm_w);
+    const float4 zero4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float4 wv[8];
+    if (p.norm_h && tile4 <= 256) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) wv[j] = j * 32 + lane < n4 ? w4[j * 32 + lane] : zero4;
+    } else if (p.norm_h) {
+        for (int i = threadIdx.x; i * 32 < p.K; i += SK_WARPS * 32)  // one 128-byte line of the weight per thread
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.norm_w + i * 32));
+    }
+
     pdl_wait();
     FERRIS_TL_BEGIN();
     const bool tl_mark = threadIdx.x == 0 && blockIdx.x == 0;
     FERRIS_TL_MARK(tl_mark, 9);
+    if (p.mode == SK_ACCUM_F32) {
+#pragma unroll
+        for (int i = 0; i < OUTS; ++i)
+            if (out_t[i] >= 0) old_r[i] = reinterpret_cast<const float*>(p.out)[(size_t)out_t[i] * p.ldo + out_n[i]];
+    }
     if (p.norm_h) {
         // One warp per row: ms = sum(x^2) / K;  r = 1 / sqrt(ms + eps);  y = (x r) w, rounded to bf16 and written where
         // TMA would have put it (rows of 128 bytes, 16-byte chunks swizzled); rows beyond T and columns beyond K are
         // zero.  A lane takes every 32nd group of four columns, eight groups at a time with all their loads in flight
         // together; a row of up to 1,024 columns is read once and stays in registers between the two passes.
-        const int n4 = p.K / 4, tile4 = p.kblocks * 16;
-        const float4* w4 = reinterpret_cast<const float4*>(p.norm_w);
         for (int t = warp; t < p.x_rows; t += SK_WARPS) {
             const float4* row = reinterpret_cast<const float4*>(p.norm_h + (size_t)(t < p.T ? t : 0) * p.K);
             const bool live = t < p.T;
@@ -175,16 +211,11 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
                 *reinterpret_cast<uint2*>(x_smem + (size_t)grp * x_box_bytes +
                                           swizzle128(t * p.nb + (kb - grp * p.nb), (idx >> 1) & 7) + (idx & 1) * 8) = v;
             };
-            const float4 zero4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             float ss = 0.0f;
             if (tile4 <= 256) {
-                float4 hv[8], wv[8];
+                float4 hv[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int idx = j * 32 + lane;
-                    hv[j] = (live && idx < n4) ? row[idx] : zero4;
-                    wv[j] = idx < n4 ? w4[idx] : zero4;
-                }
+                for (int j = 0; j < 8; ++j) hv[j] = (live && j * 32 + lane < n4) ? row[j * 32 + lane] : zero4;
 #pragma unroll
                 for (int j = 0; j < 8; ++j) ss += (hv[j].x * hv[j].x + hv[j].y * hv[j].y) + (hv[j].z * hv[j].z + hv[j].w * hv[j].w);
                 ss = warp_sum(ss);
@@ -203,16 +234,16 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
                 ss = warp_sum(ss);
                 const float r = 1.0f / sqrtf(ss / (float)p.K + p.norm_eps);
                 for (int base = 0; base < tile4; base += 256) {
-                    float4 hv[8], wv[8];
+                    float4 hv[8], wl[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
                         const int idx = base + j * 32 + lane;
                         hv[j] = (live && idx < n4) ? row[idx] : zero4;
-                        wv[j] = idx < n4 ? w4[idx] : zero4;
+                        wl[j] = idx < n4 ? w4[idx] : zero4;
                     }
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        if (base + j * 32 + lane < tile4) put(base + j * 32 + lane, hv[j], wv[j], r);
+                        if (base + j * 32 + lane < tile4) put(base + j * 32 + lane, hv[j], wl[j], r);
                 }
             }
         }
@@ -303,7 +334,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
     // The eight warps' partial tiles, added in warp order: [warp][accumulator, tile, token tile, element][lane].
     asm volatile("bar.sync 1, 256;" ::: "memory");  // nobody reads the stages any more
     float* red = reinterpret_cast<float*>(smem);
-    const int per_acc = p.mt * NT * 4, per_warp = ACCS * per_acc;
+    const int per_warp = ACCS * per_acc;
 #pragma unroll
     for (int a = 0; a < ACCS; ++a)
 #pragma unroll
@@ -317,20 +348,18 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
         }
     asm volatile("bar.sync 1, 256;" ::: "memory");
     FERRIS_TL_MARK(tl_mark, 3);
-    for (int q = threadIdx.x; q < per_acc * 32; q += SK_WARPS * 32) {
+#pragma unroll
+    for (int i = 0; i < OUTS; ++i) {
+        if (out_t[i] < 0) continue;
+        const int q = threadIdx.x + SK_WARPS * 32 * i;
         const int ln = q & 31, e = q >> 5;
-        const int j = e & 3, nt = (e >> 2) % NT, m = (e >> 2) / NT;
-        const int row = m * 16 + (ln >> 2) + ((j & 2) ? 8 : 0);
-        const int t = nt * 8 + (ln & 3) * 2 + (j & 1);
-        const int n = n0 + row;
-        if (row >= p.rows || n >= p.N || t >= p.T) continue;
         float va = 0.0f, vb = 0.0f;
 #pragma unroll
         for (int w = 0; w < SK_WARPS; ++w) {
             va += red[(size_t)(w * per_warp + e) * 32 + ln];
             if (ACCS == 2) vb += red[(size_t)(w * per_warp + per_acc + e) * 32 + ln];
         }
-        sk_write(p, t, n, va, vb);
+        sk_write(p, out_t[i], out_n[i], va, vb, bias_r[i], old_r[i]);
     }
     FERRIS_TL_MARK(tl_mark, 4);
     FERRIS_TL_END(40 + p.mode + (p.norm_h ? 4 : 0));

@@ -183,6 +183,28 @@ int ferris_make_tensor_map_kblocks(CUtensorMap* map, const void* base, uint64_t 
     return FERRIS_OK;
 }
 
+// Two bf16 matrices [rows, cols] that lie `plane_bytes` apart, as one 3-D tensor (cols, rows, 2): a box is 64 columns x
+// `box_rows` rows of both, and lands in shared memory as the first matrix's box followed by the second's, each
+// swizzled like a 2-D box.
+int ferris_make_tensor_map_planes(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t plane_bytes,
+                                  uint32_t box_rows) {
+    EncodeTiledFn fn = encode_tiled();
+    if (!fn) FERRIS_REFUSE("tensor map: the driver offers no cuTensorMapEncodeTiled");
+    if (((uintptr_t)base & 15) || ((cols * 2) & 15) || (plane_bytes & 15) || plane_bytes < rows * cols * 2 || box_rows == 0 ||
+        box_rows > 256 || (box_rows & 7))
+        FERRIS_REFUSE("tensor map: base %p, %llu columns, planes %llu bytes apart, box of %u rows do not meet the rules", base,
+                      (unsigned long long)cols, (unsigned long long)plane_bytes, box_rows);
+    cuuint64_t dims[3] = {cols, rows, 2};
+    cuuint64_t strides[2] = {cols * 2, plane_bytes};
+    cuuint32_t box[3] = {64, box_rows, 2};
+    cuuint32_t elem[3] = {1, 1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) FERRIS_REFUSE("tensor map: cuTensorMapEncodeTiled (planes) failed with %d", (int)r);
+    return FERRIS_OK;
+}
+
 int ferris_make_tensor_map_2d_f32(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
                                   uint64_t row_stride, uint32_t box_rows) {
     const MapKey key = {base, rows, cols, row_stride, box_rows, 32u, 1u};

@@ -352,6 +352,8 @@ __device__ __forceinline__ void tcgen05_commit_pair(uint64_t* bar, uint16_t cta_
 // A 2-D bf16 tensor [rows, cols] with `row_stride` elements between rows, read in boxes of
 // box_rows x box_cols with 128-byte swizzle (box_cols * 2 bytes must be 128).
 // Returns 0 or a negative error (text in ferris_last_error()).
+int ferris_make_tensor_map_planes(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t plane_bytes,
+                                  uint32_t box_rows);
 int ferris_make_tensor_map_kblocks(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,
                                    uint32_t box_rows, uint32_t box_kblocks);
 int ferris_make_tensor_map_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t row_stride,

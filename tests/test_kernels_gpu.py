@@ -950,9 +950,15 @@ def test_decode_attention_merges_its_key_ranges_in_a_cluster(nh, nkv, d, T, wind
                                   lazy_merge=True) is out
         assert ops.launch_count() - launches == 1
         got.append(out)
+    # keys and values as the two planes of one tensor (as the cache manager allocates them): a tile of keys and the
+    # tile of values of the same tokens come with one copy; the result is the same to the bit
+    planes = torch.stack([k, v]).contiguous()
+    paired = torch.full((T, nh * d), float("nan"), dtype=BF16, device=device)
+    ops.attention_step(qkv.clone(), paired, planes[0], planes[1], meta, ctx, nh, nkv, d, inv_freq, d, window, scale)
     torch.cuda.synchronize()
     assert ops.kernel_status() == 0
-    assert torch.equal(got[0], got[1]) and torch.equal(got[0], got[2])
+    assert torch.equal(got[0], got[1]) and torch.equal(got[0], got[2]) and torch.equal(paired, got[0])
+    assert torch.equal(planes[0], k1) and torch.equal(planes[1], v1)
     request.getfixturevalue("skinny_off")
     want = torch.full((T, nh * d), float("nan"), dtype=BF16, device=device)
     k2, v2 = k.clone(), v.clone()

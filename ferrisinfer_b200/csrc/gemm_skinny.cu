@@ -436,6 +436,9 @@ bool sk_plan(int T, int N, int K, int accs, SkPlan* out) {
             // it).  Warp g % 8 takes group g, which is constant per stage when the stages are a multiple of eight.
             stages = stages / SK_WARPS * SK_WARPS;
             if (stages <= 0) continue;
+            // More than 8 tokens beside long rows leave the weights a small ring, and the tcgen05 kernel is then the
+            // faster one (down projection of the 0.5B sizes at 16 tokens: 9.4 us here, 7.1 us there).
+            if (x_rows > 8 && stages * 2 < groups) continue;
         }
         // blocks on the busiest warp, the copies it waits for, and what a ring adds
         const double cost = (double)((groups + SK_WARPS - 1) / SK_WARPS) * nb + 0.4 * groups + 1.0 * (groups - stages);

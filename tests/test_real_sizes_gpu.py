@@ -3,7 +3,7 @@
 Two layers each, a vocabulary of a few thousand (so that the float64 oracle stays cheap), pages of 16, query and
 key projections scaled so that the attention scores spread over about a unit.  What only these widths bring together
 runs here and is compared: the weight-stationary products of single tokens with the RMSNorm formed on their way,
-key ranges of a decode step merged by the attention kernel's last CTA, graphs of decode steps filled up to a bucket, the
+key ranges of a decode step merged through a thread-block cluster, graphs of decode steps filled up to a bucket, the
 q/k/v product of long portions with rotation and cache write in its epilogue over 14 + 2 + 2 heads, the gate/up
 product on CTA pairs, both head sizes of the tensor-core attention kernels.  Every way of cutting: whole, the last
 32 tokens one by one, portions of changing size down to two tokens, and up to four live requests mixed with so few

@@ -321,16 +321,17 @@ __device__ __forceinline__ void rotate_q(WarpState<D>& st, const float2* cos_sin
 }
 
 // =============================================================================================
-// Decode: one CTA per (split, kv head, token).  Its four warps take the 16-key tiles of the
+// Decode: one CTA per (split, kv head, token).  Its NW warps take the 16-key tiles of the
 // split's key range in turn, each with a pipeline of its own; their results are merged through
-// shared memory and written either as the final output or as one partial (m, l, O) per split.
+// shared memory and written as the final output, as one partial (m, l, O) per split, or sent to
+// the CTAs of the cluster that the splits of a (token, kv head) form.
 // =============================================================================================
 // PAIR: the key and the value cache are two planes of one tensor, and `map_k` is a 3-D map over both: one copy brings
 // the 64-column box of K and the box of V of the same 16 keys and columns (4 KB instead of two copies of 2 KB; a
 // copy costs the TMA unit ~30 ns whatever it brings, and a CTA of a long context issues hundreds).  A tile then lies
 // in shared memory as (K box, V box) per 64 columns instead of all K boxes followed by all V boxes.
-template <int D, int STAGES, bool PAIR>
-__global__ void __launch_bounds__(WARPS * 32)
+template <int D, int STAGES, bool PAIR, int NW>
+__global__ void __launch_bounds__(NW * 32)
     decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
                             float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ block_tables,
@@ -339,8 +340,8 @@ __global__ void __launch_bounds__(WARPS * 32)
                             int splits, const FusedRope rope, int cluster_merge, int* status) {
     FERRIS_TL_ENTRY();
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full[WARPS][STAGES];
-    __shared__ int tile_rows[WARPS][ROW_CACHE];  // cache rows of this warp's next tiles, looked up in one go
+    __shared__ uint64_t full[NW][STAGES];
+    __shared__ int tile_rows[NW][ROW_CACHE];  // cache rows of this warp's next tiles, looked up in one go
     __shared__ float2 cos_sin[D / 2];            // (cos, sin) of the token's rotation angles, when the rotation is fused
     uint8_t* smem = align1024(smem_raw);
     constexpr int NT = D == 64 ? 4 : 2;  // 16-key tiles per pipeline stage and per softmax update
@@ -363,6 +364,7 @@ __global__ void __launch_bounds__(WARPS * 32)
     mbar_fence_init();
     __syncthreads();
     pdl_launch_dependents();
+    if (splits > 1 && cluster_merge) cluster_arrive_relaxed();  // first phase of the cluster's barrier: "this CTA runs"
     // A kernel that rotates AND writes the cache reads nothing from the cache that this step wrote before it (the
     // token's own key and value come from its qkv row, which it patches into the tile), and the step's metadata was
     // uploaded before the step began: it requests its first tiles BEFORE the wait, which only the queries need.
@@ -394,7 +396,7 @@ __global__ void __launch_bounds__(WARPS * 32)
     const int t_begin = first_tile + split * per_split;
     const int t_end = min(t_begin + per_split, last_tile + 1);
     const int n_blocks = t_end > t_begin ? (t_end - t_begin + NT - 1) / NT : 0;
-    const int my_count = n_blocks > warp ? (n_blocks - warp + WARPS - 1) / WARPS : 0;
+    const int my_count = n_blocks > warp ? (n_blocks - warp + NW - 1) / NW : 0;
 
     WarpState<D> st;
     init_state(st);
@@ -410,7 +412,7 @@ __global__ void __launch_bounds__(WARPS * 32)
     };
     if (!fused) load_queries();
     uint8_t* my_stages = smem + (size_t)warp * STAGES * STAGE_BYTES;
-    auto first_tile_of = [&](int i) { return t_begin + (warp + i * WARPS) * NT; };
+    auto first_tile_of = [&](int i) { return t_begin + (warp + i * NW) * NT; };
     // the block-table look-ups of the warp's tiles are independent loads, issued together
     auto fill_rows = [&](int first_block) {
         for (int e = lane; e < ROW_CACHE; e += 32) {
@@ -445,14 +447,14 @@ __global__ void __launch_bounds__(WARPS * 32)
     const bool tl_mark = threadIdx.x == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0;
     // the warp whose tiles include the token's own position (in the CTA of the last key range) will rotate k and copy v
     const int own_block = (last_tile >= t_begin && last_tile < t_end) ? (last_tile - t_begin) / NT : -1;
-    const bool owns_token = patches && own_block >= 0 && own_block % WARPS == warp;
+    const bool owns_token = patches && own_block >= 0 && own_block % NW == warp;
     float k_lo[D / 64], k_hi[D / 64];
     bf16 v_own[D / 32];
     // where the token's k and v go in the cache: step metadata, read before the wait as well
     const int own_slot = owns_token ? rope.slot_mapping[tok] : -1;
     if (fused) {
         // the angles depend on the position alone: formed before the wait, off the step's critical path
-        for (int i = threadIdx.x; i < D / 2; i += WARPS * 32) {
+        for (int i = threadIdx.x; i < D / 2; i += NW * 32) {
             float sn, cs;
             sincosf((float)P * rope.inv_freq[i], &sn, &cs);
             cos_sin[i] = make_float2(cs, sn);
@@ -526,10 +528,10 @@ __global__ void __launch_bounds__(WARPS * 32)
     finish_rows(st);
     FERRIS_TL_MARK(tl_mark, 2);
 
-    // merge the four warps through shared memory (the stages are no longer read)
+    // merge the warps through shared memory (the stages are no longer read)
     __syncthreads();
     FERRIS_TL_MARK(tl_mark, 3);
-    float* merge = reinterpret_cast<float*>(smem);  // [WARPS][16][D + 2]
+    float* merge = reinterpret_cast<float*>(smem);  // [NW][16][D + 2]
     {
         const int g = lane >> 2, t = lane & 3;
         float* mine = merge + (size_t)warp * 16 * (D + 2);
@@ -548,60 +550,81 @@ __global__ void __launch_bounds__(WARPS * 32)
         }
     }
     __syncthreads();
-    for (int idx = threadIdx.x; idx < G * D; idx += WARPS * 32) {
-        const int r = idx / D, c = idx % D;
+    // per row: the maximum over the warps, each warp's factor e^{m_w - M}, and the sum; one thread per row
+    __shared__ float warp_factor[NW][16], row_m[16], row_l[16];
+    if ((int)threadIdx.x < G) {
+        const int r = threadIdx.x;
         float mm = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) mm = fmaxf(mm, merge[(size_t)(w * 16 + r) * (D + 2)]);
-        float ll = 0.0f, oo = 0.0f;
+        for (int w = 0; w < NW; ++w) mm = fmaxf(mm, merge[(size_t)(w * 16 + r) * (D + 2)]);
+        float ll = 0.0f;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) {
+        for (int w = 0; w < NW; ++w) {
             const float* rw = merge + (size_t)(w * 16 + r) * (D + 2);
             const float f = rw[0] == -INFINITY ? 0.0f : expf(rw[0] - mm);
+            warp_factor[w][r] = f;
             ll += rw[1] * f;
-            oo += rw[2 + c] * f;
         }
+        row_m[r] = mm;
+        row_l[r] = ll;
+    }
+    __syncthreads();
+    // With a cluster, element idx of the G x D outputs belongs to the CTA idx / share of the cluster: every key range
+    // sends its (maximum, sum) of every row and its unnormalised output elements to the owners' shared memory
+    // (a region of its own behind the stages: a peer may still be in its key loop), one barrier follows, and the
+    // owner adds the ranges in their order (the sums of decode_merge_kernel): no scratch in global memory, no
+    // merge launch, and after the barrier a CTA reads its own shared memory only.
+    const bool pushes = splits > 1 && cluster_merge;
+    const int share = (G * D + splits - 1) / splits;
+    const uint32_t recv_ml = smem_u32(smem + (size_t)NW * STAGES * STAGE_BYTES);  // [splits][G][2]
+    const uint32_t recv_o = recv_ml + (uint32_t)(splits * G * 2) * 4u;             // [splits][share]
+    if (pushes) {
+        cluster_wait();  // first phase: every CTA of the cluster runs
+        for (int i = threadIdx.x; i < G * splits; i += NW * 32) {
+            const int r = i % G, owner = i / G;
+            const uint32_t at = recv_ml + (uint32_t)((split * G + r) * 2) * 4u;
+            st_peer_shared_f32(at, (uint32_t)owner, row_m[r]);
+            st_peer_shared_f32(at + 4u, (uint32_t)owner, row_l[r]);
+        }
+    }
+    for (int idx = threadIdx.x; idx < G * D; idx += NW * 32) {
+        const int r = idx / D, c = idx % D;
+        float oo = 0.0f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) oo += merge[(size_t)(w * 16 + r) * (D + 2) + 2 + c] * warp_factor[w][r];
         const int head = hk * G + r;
         if (splits == 1) {
-            out[(size_t)tok * ldo + (size_t)head * D + c] = __float2bfloat16_rn(oo / ll);
+            out[(size_t)tok * ldo + (size_t)head * D + c] = __float2bfloat16_rn(oo / row_l[r]);
         } else if (cluster_merge) {
-            // this key range's (maximum, sum, output row) stays in shared memory for the cluster to merge
-            float* fin = merge + WARPS * 16 * (D + 2);
-            fin[r * (D + 2) + 2 + c] = oo;
-            if (c == 0) {
-                fin[r * (D + 2)] = mm;
-                fin[r * (D + 2) + 1] = ll;
-            }
+            const int owner = idx / share;
+            st_peer_shared_f32(recv_o + (uint32_t)(split * share + idx - owner * share) * 4u, (uint32_t)owner, oo);
         } else {
             // partial results are indexed by the row's place in this launch (blockIdx.z), not in the step
             const size_t slot = ((size_t)blockIdx.z * nh + head) * splits + split;
             part_o[slot * D + c] = oo;
             if (c == 0) {
-                part_ml[slot * 2] = mm;
-                part_ml[slot * 2 + 1] = ll;
+                part_ml[slot * 2] = row_m[r];
+                part_ml[slot * 2 + 1] = row_l[r];
             }
         }
     }
-    if (splits > 1 && cluster_merge) {
-        // The key ranges of a (token, kv head) are the CTAs of one thread-block cluster: each takes a share of the
-        // G x D outputs and adds the ranges' partial results, read from their shared memory, in the order of the
-        // ranges (the sums of decode_merge_kernel): no scratch in global memory, no merge launch.
+    if (pushes) {
         FERRIS_TL_MARK(tl_mark, 5);
-        cluster_sync();
+        cluster_arrive_release();
+        cluster_wait();
         FERRIS_TL_MARK(tl_mark, 6);
-        const uint32_t fin = smem_u32(merge + WARPS * 16 * (D + 2));
-        const int share = (G * D + splits - 1) / splits;
-        const int begin = (int)cluster_ctarank() * share, end = min(begin + share, G * D);
-        for (int idx = begin + threadIdx.x; idx < end; idx += WARPS * 32) {
-            const int r = idx / D, c = idx % D;
-            const uint32_t row = fin + (uint32_t)(r * (D + 2)) * 4u;
+        const float* my_ml = reinterpret_cast<const float*>(smem + (size_t)NW * STAGES * STAGE_BYTES);
+        const float* my_o = my_ml + splits * G * 2;
+        const int begin = split * share, end = min(begin + share, G * D);
+        for (int idx = begin + threadIdx.x; idx < end; idx += NW * 32) {
+            const int r = idx / D;
             float ms[8], ls[8], os[8];
 #pragma unroll
             for (int sp = 0; sp < 8; ++sp) {
                 const bool have = sp < splits;
-                ms[sp] = have ? ld_peer_shared_f32(row, sp) : -INFINITY;
-                ls[sp] = have ? ld_peer_shared_f32(row + 4u, sp) : 0.0f;
-                os[sp] = have ? ld_peer_shared_f32(row + (uint32_t)(2 + c) * 4u, sp) : 0.0f;
+                ms[sp] = have ? my_ml[(sp * G + r) * 2] : -INFINITY;
+                ls[sp] = have ? my_ml[(sp * G + r) * 2 + 1] : 0.0f;
+                os[sp] = have ? my_o[sp * share + idx - begin] : 0.0f;
             }
             float mm = -INFINITY;
 #pragma unroll
@@ -614,9 +637,8 @@ __global__ void __launch_bounds__(WARPS * 32)
                 ll += ls[sp] * f;
                 oo += os[sp] * f;
             }
-            out[(size_t)tok * ldo + (size_t)(hk * G + r) * D + c] = __float2bfloat16_rn(oo / ll);
+            out[(size_t)tok * ldo + (size_t)(hk * G) * D + idx] = __float2bfloat16_rn(oo / ll);
         }
-        cluster_sync();  // nobody leaves while a peer may still read its shared memory
     }
 #ifdef FERRIS_TIMELINE
     __syncthreads();
@@ -1329,6 +1351,17 @@ FERRIS_API long long ferris_decode_attention_scratch_floats(int tokens, int nh, 
     return (long long)tokens * nh * splits * (d + 2);
 }
 
+// The decode kernel's shape, warps * 10 + stages of 16 KB per warp, by the blocks of keys (64 keys of head size 64, 32
+// of head size 128) that a CTA may get.  A warp works a block off in about a microsecond, one block after the other, so
+// a CTA with many blocks wants many warps (12 warps with one stage each hold as many bytes in flight as 4 warps with
+// three); a CTA with few blocks wants few, because every warp adds to the merge at the end.  Measured per decode
+// step at the 0.5B sizes (4 x 3 / 8 x 1 / 12 x 1 warps x stages): batch 8 of 512 keys 0.683 / 0.691 / 0.709 ms; batch 1
+// of 4,096 keys (9 blocks) 0.783 / 0.748 / 0.778; batch 8 (11 blocks) 0.798 / 0.792 / 0.784; batch 32 (33 blocks)
+// 1.498 / 1.477 / 1.461; batch 64 (65 blocks) 1.887 / 1.866 / 1.849; batch 8 of 16,384 keys 1.096 / 1.098 / 1.055.
+// `blocks` comes from the width of the block tables, which is up to twice what the requests hold.  With at most 64
+// CTAs (batches of 1 to 4 at 8 key ranges) eight warps were the fastest at every length measured.
+static int decode_shape(int blocks, int ctas) { return blocks <= 4 ? 43 : ((blocks < 10 || ctas <= 64) ? 81 : 121); }
+
 static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, const void* k_cache, const void* v_cache,
                                  long long cache_pages, const int* block_tables, int max_blocks, const int* token_seq,
                                  const int* positions, const int* token_list, int tokens, int nh, int nkv, int d,
@@ -1356,10 +1389,25 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
     rope.v_cache = (bf16*)const_cast<void*>(v_cache);
     const int cluster = (merge == 3 && splits > 1) ? 1 : 0;
     if (cluster && splits > 8) FERRIS_REFUSE("decode attention: a cluster merges at most 8 key ranges, not %d", splits);
-    auto launch = [&](auto kernel, size_t smem) -> cudaError_t {
+    cudaError_t e = cudaSuccess;
+    CUtensorMap mkv;
+    const bool pair = cache_pair_map(k_cache, v_cache, rows, d, &mkv);
+    if (pair) mk = mkv;
+    // warps x stages of 16 KB each (4 tiles of head size 64, 2 of head size 128)
+    long long keys = (long long)max_blocks * page_size;
+    if (window > 0 && window + TILE_KEYS < keys) keys = window + TILE_KEYS;
+    const int tiles_per_range = (int)(((keys + TILE_KEYS - 1) / TILE_KEYS + splits - 1) / splits);
+    const int tiles_per_block = d == 64 ? 4 : 2;
+    const int shape = decode_shape((tiles_per_range + tiles_per_block - 1) / tiles_per_block, splits * nkv * tokens);
+    const int nw = shape / 10, st = shape % 10;
+    // behind the stages: what the key ranges of a cluster send each other, [splits][G][2] + [splits][share] fp32
+    const int G = nh / nkv;
+    const size_t recv_bytes = cluster ? (size_t)splits * (2 * G + (G * d + splits - 1) / splits) * 4 : 0;
+    const size_t smem = (size_t)nw * st * 16384 + 1024 + recv_bytes;
+    auto launch = [&](auto kernel) -> cudaError_t {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
-        cfg.blockDim = dim3(WARPS * 32);
+        cfg.blockDim = dim3(nw * 32);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = s;
         cudaLaunchAttribute attr[2];
@@ -1382,16 +1430,16 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
                                   max_blocks, token_seq, positions, token_list, nh, nkv, page_size, window, scale, splits,
                                   rope, cluster, status);
     };
-    cudaError_t e = cudaSuccess;
-    CUtensorMap mkv;
-    const bool pair = cache_pair_map(k_cache, v_cache, rows, d, &mkv);
-    if (pair) mk = mkv;
-    constexpr int ST = 3;  // per warp 3 stages of 16 KB: 4 tiles of head size 64, 2 of head size 128
-    const size_t smem = (size_t)WARPS * ST * 16384 + 1024;
-#define FERRIS_DECODE_LAUNCH(DD, PP)                                                             \
-    do {                                                                                         \
-        if ((rc = set_smem(decode_attention_kernel<DD, ST, PP>, smem)) != FERRIS_OK) return rc;  \
-        e = launch(decode_attention_kernel<DD, ST, PP>, smem);                                   \
+#define FERRIS_DECODE_LAUNCH_AS(DD, PP, NWW, STT)                                                        \
+    do {                                                                                                 \
+        if ((rc = set_smem(decode_attention_kernel<DD, STT, PP, NWW>, smem)) != FERRIS_OK) return rc;   \
+        e = launch(decode_attention_kernel<DD, STT, PP, NWW>);                                           \
+    } while (0)
+#define FERRIS_DECODE_LAUNCH(DD, PP)                              \
+    do {                                                          \
+        if (shape == 121) FERRIS_DECODE_LAUNCH_AS(DD, PP, 12, 1); \
+        else if (shape == 81) FERRIS_DECODE_LAUNCH_AS(DD, PP, 8, 1); \
+        else FERRIS_DECODE_LAUNCH_AS(DD, PP, 4, 3);               \
     } while (0)
     if (d == 64) {
         if (pair) FERRIS_DECODE_LAUNCH(64, true);
@@ -1402,6 +1450,7 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
         else FERRIS_DECODE_LAUNCH(128, false);
         if (e == cudaSuccess && splits > 1 && merge == 1) ferris_launch(decode_merge_kernel<128>, dim3(tokens, nh), dim3(128), 0, s, part_o, part_ml, (bf16*)out, ldo, token_list, nh, splits);
     }
+#undef FERRIS_DECODE_LAUNCH_AS
 #undef FERRIS_DECODE_LAUNCH
     if (e != cudaSuccess) {
         ferris_set_error("decode attention: %s", cudaGetErrorString(e));
@@ -1476,7 +1525,9 @@ FERRIS_API int ferris_decode_cluster_splits(int tokens, int nkv, int d, int max_
             have = -1;
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(sp, 1, 1);
-            cfg.blockDim = dim3(WARPS * 32);
+            // every shape of the kernel takes more than half an SM's shared memory: one CTA per SM; asked for the
+            // shape with the most threads and bytes
+            cfg.blockDim = dim3(12 * 32);
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeClusterDimension;
             attr[0].val.clusterDim.x = (unsigned)sp;
@@ -1485,15 +1536,14 @@ FERRIS_API int ferris_decode_cluster_splits(int tokens, int nkv, int d, int max_
             cfg.attrs = attr;
             cfg.numAttrs = 1;
             int clusters = 0;
-            cudaError_t e;
+            cudaError_t e = cudaSuccess;
+            cfg.dynamicSmemBytes = (size_t)12 * 16384 + 1024 + (size_t)(8 * 2 * 16 + 16 * d + 8) * 4;
             if (d == 64) {
-                cfg.dynamicSmemBytes = (size_t)WARPS * 3 * 4 * 2 * TILE_KEYS * 64 * 2 + 1024;
-                set_smem(decode_attention_kernel<64, 3, true>, cfg.dynamicSmemBytes);
-                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<64, 3, true>, &cfg);
+                set_smem(decode_attention_kernel<64, 1, true, 12>, cfg.dynamicSmemBytes);
+                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<64, 1, true, 12>, &cfg);
             } else {
-                cfg.dynamicSmemBytes = (size_t)WARPS * 3 * 2 * 2 * TILE_KEYS * 128 * 2 + 1024;
-                set_smem(decode_attention_kernel<128, 3, true>, cfg.dynamicSmemBytes);
-                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<128, 3, true>, &cfg);
+                set_smem(decode_attention_kernel<128, 1, true, 12>, cfg.dynamicSmemBytes);
+                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<128, 1, true, 12>, &cfg);
             }
             if (e == cudaSuccess && clusters > 0) have = clusters;
             else cudaGetLastError();

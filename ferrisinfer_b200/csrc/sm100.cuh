@@ -94,6 +94,21 @@ __device__ __forceinline__ float ld_peer_shared_f32(uint32_t addr, uint32_t rank
     return v;
 }
 
+// The barrier in two halves, for every thread on its own (no warp has to be converged): a thread arrives once and
+// waits once per phase, in that order.
+__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
+__device__ __forceinline__ void cluster_arrive_release() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
+
+// Stores an fp32 at shared address `addr` (this CTA's numbering) in the shared memory of CTA `rank` of the cluster.
+// The target CTA must be running (a cluster barrier that it has arrived on says so), and sees the value after the
+// next cluster barrier with release / acquire.
+__device__ __forceinline__ void st_peer_shared_f32(uint32_t addr, uint32_t rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------

@@ -176,7 +176,7 @@ def fill_cache(engine, batch, context):
 
 
 def time_decode(engine, batch, context, steps, warmup, regions=1):
-    """Regions of exactly ``steps`` decode steps (step function + greedy sampling kernel), each timed with CUDA
+    """Regions of exactly ``steps`` decode steps (step function with greedy sampling in its output head), each timed with CUDA
     events after ``warmup`` untimed steps; the cache is refilled before every region, so that each one ends at
     ``context``.  Returns (ms per step of each region, kernel launches of one region)."""
     import torch
@@ -187,14 +187,13 @@ def time_decode(engine, batch, context, steps, warmup, regions=1):
     vocab = engine.model.vocab_size
     gen = torch.Generator().manual_seed(1)
     tokens = torch.randint(0, vocab, (steps + warmup, batch), generator=gen).tolist()
-    out_tok = torch.empty(batch, dtype=torch.int32, device=engine.device)
     times, launches = [], 0
     for _ in range(max(1, regions)):
         ids = fill_cache(engine, batch, context - steps - warmup - 1)
 
         def one(i):
-            logits = engine.runner.step([StepEntry(rid, [tokens[i][b]], [0]) for b, rid in enumerate(ids)])
-            ops.sample(logits, out_tok)
+            # as Engine.step runs a step of greedy requests: the output head picks the tokens, no logits are stored
+            engine.runner.step([StepEntry(rid, [tokens[i][b]], [0]) for b, rid in enumerate(ids)], greedy=True)
 
         for i in range(warmup):
             one(i)
@@ -520,8 +519,7 @@ def timeline(args) -> int:
     out_tok = torch.empty(args.batch, dtype=torch.int32, device=engine.device)
 
     def one(i):
-        logits = engine.runner.step([StepEntry(rid, [(7 * i + b) % 1000], [0]) for b, rid in enumerate(ids)])
-        ops.sample(logits, out_tok)
+        engine.runner.step([StepEntry(rid, [(7 * i + b) % 1000], [0]) for b, rid in enumerate(ids)], greedy=True)
 
     for i in range(4):
         one(i)

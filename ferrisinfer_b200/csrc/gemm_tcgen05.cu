@@ -33,7 +33,18 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 320;  // TMA warp, MMA warp, eight epilogue warps
 constexpr int MAX_STAGES = 8;
 
-enum Mode { STORE_BF16 = 0, STORE_F32 = 1, ACCUM_F32 = 2, SWIGLU_BF16 = 3, QKV_ROPE_BF16 = 4 };
+enum Mode { STORE_BF16 = 0, STORE_F32 = 1, ACCUM_F32 = 2, SWIGLU_BF16 = 3, QKV_ROPE_BF16 = 4, ARGMAX_F32 = 5 };
+
+// Mode ARGMAX_F32 (the output head of a step whose rows all take the greatest logit): no logits are stored.  Every
+// tile of 128 outputs leaves, per token, the sort key of its best (value, index) pair, its maximum and its sum of
+// exp(value - maximum) (16 bytes: key high word, key low word, maximum, sum), and a small kernel merges the tiles'
+// entries: the lowest index among equal maxima, probability 1 / sum exp(l - max), as the sampling kernel's greedy
+// rows (crates/ferrisinfer-kernel/src/cpu/matmul.rs:190-274 is the reference's fused product + argmax).
+// The key orders (value, index) pairs: greater value first, then lower index; a NaN sorts last.
+__device__ __forceinline__ uint32_t argmax_key_hi(float v) {
+    const uint32_t u = __float_as_uint(v);
+    return v != v ? 0u : ((u & 0x80000000u) ? ~u : (u | 0x80000000u));
+}
 
 // Where the q/k/v product of a long step leaves its output (mode QKV_ROPE_BF16 of the token-major kernel): the
 // columns are heads of d values, nh query heads, then nkv key heads, then nkv value heads.  Query and key heads are
@@ -70,6 +81,7 @@ struct Params {
     const float* merge_o;
     const float* merge_ml;
     int merge_splits, merge_heads, merge_d;
+    float* out_prob;    // mode ARGMAX_F32: out is int32 [T] (the tokens), this fp32 [T], scratch the tiles' entries
     int* status;
 };
 
@@ -293,7 +305,58 @@ __global__ void __launch_bounds__(THREADS)
         FERRIS_TL_MARK(tl_mark, 1);  // accumulator ready
         const bool n_ok = n < p.N;
         const float bias_v = (p.bias && n_ok) ? p.bias[n] : 0.0f;
-        if (p.splits == 1) {
+        if constexpr (MODE == ARGMAX_F32) {
+            // per token: best key, maximum and sum over this warp's 32 outputs, then over the tile's four lane quarters
+            __shared__ float4 quarter_best[4][128];
+            // Both warps of a lane quarter read every chunk of 16 tokens and take every second token of it.  Three
+            // warp reductions a token, all on integers (redux.sync): the key's high word (the value), its low word
+            // among the lanes that hold that value (the index), and the sum of exp(value - maximum) in fixed point
+            // (24 fractional bits: 32 terms of at most 1 fit a word; the sum is good to 2^-24 of its largest term).
+            for (int c0 = 0; c0 < p.bt && t0 + c0 < p.T; c0 += 16) {
+                uint32_t ra[16];
+                if (have) {
+                    tmem_load_32x16(lane_addr + c0, ra);
+                    tmem_load_wait();
+                }
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    if ((c & 1) != half || t0 + c0 + c >= p.T) continue;  // the same for the whole warp
+                    const float x = (have && n_ok) ? __uint_as_float(ra[c]) : -INFINITY;
+                    const uint32_t hi = n_ok ? argmax_key_hi(x) : 0u;
+                    const uint32_t best_hi = __reduce_max_sync(0xffffffffu, hi);
+                    const uint32_t best_lo = __reduce_max_sync(0xffffffffu, (n_ok && hi == best_hi) ? 0xFFFFFFFFu - (uint32_t)n : 0u);
+                    // the maximum itself, back from its key (0: no lane holds a number)
+                    const float m = best_hi == 0u ? -INFINITY
+                                                  : __uint_as_float((best_hi & 0x80000000u) ? (best_hi & 0x7FFFFFFFu) : ~best_hi);
+                    const float e = (x == x && m != -INFINITY) ? expf(x - m) : 0.0f;  // exp(-inf - m) = 0
+                    const uint32_t fixed = __reduce_add_sync(0xffffffffu, (uint32_t)(e * 16777216.0f + 0.5f));
+                    if (lane == 0)
+                        quarter_best[quarter][c0 + c] =
+                            make_float4(__uint_as_float(best_hi), __uint_as_float(best_lo), m, (float)fixed * (1.0f / 16777216.0f));
+                }
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const int tl = threadIdx.x - 64;
+            if (tl < p.bt && t0 + tl < p.T) {
+                uint32_t bh = 0u, bl = 0u;
+                float m = -INFINITY;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 v = quarter_best[q][tl];
+                    const uint32_t h = __float_as_uint(v.x), l = __float_as_uint(v.y);
+                    if (h > bh || (h == bh && l > bl)) bh = h, bl = l;
+                    m = fmaxf(m, v.z);
+                }
+                float sum = 0.0f;
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const float4 v = quarter_best[q][tl];
+                    sum += v.z == -INFINITY ? 0.0f : v.w * expf(v.z - m);
+                }
+                reinterpret_cast<float4*>(p.scratch)[(size_t)blockIdx.x * p.T + t0 + tl] =
+                    make_float4(__uint_as_float(bh), __uint_as_float(bl), m, sum);
+            }
+        } else if (p.splits == 1) {
             if (have) {
                 for (int c0 = half * 16; c0 < p.bt; c0 += 32) {
                     uint32_t ra[16], rb[16];
@@ -449,7 +512,65 @@ __global__ void __launch_bounds__(THREADS)
         tcgen05_fence_after();
         tmem_dealloc(tmem, tmem_cols);
     }
-    FERRIS_TL_END(10 + MODE + (p.norm_h ? 4 : 0) + (p.merge_o ? 8 : 0));
+    FERRIS_TL_END(MODE == ARGMAX_F32 ? 21 : 10 + MODE + (p.norm_h ? 4 : 0) + (p.merge_o ? 8 : 0));
+}
+
+// The tiles' entries of mode ARGMAX_F32, [tiles][T] of (key high, key low, maximum, sum), merged per token: one CTA a
+// token, its threads over the tiles.
+constexpr int AM_THREADS = 256;
+__global__ void __launch_bounds__(AM_THREADS)
+    argmax_merge_kernel(const float4* __restrict__ part, int tiles, int T, int* __restrict__ out_token,
+                        float* __restrict__ out_prob) {
+    __shared__ uint32_t s_hi[AM_THREADS / 32], s_lo[AM_THREADS / 32];
+    __shared__ float s_m[AM_THREADS / 32], s_sum[AM_THREADS / 32];
+    FERRIS_TL_ENTRY();
+    pdl_wait();
+    pdl_launch_dependents();
+    FERRIS_TL_BEGIN();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t bh = 0u, bl = 0u;
+    float m = -INFINITY, sum = 0.0f;
+    for (int i0 = threadIdx.x; i0 < tiles; i0 += 4 * AM_THREADS) {
+        float4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {  // four loads in flight
+            const int i = i0 + j * AM_THREADS;
+            v[j] = i < tiles ? part[(size_t)i * T + t] : make_float4(0.0f, 0.0f, -INFINITY, 0.0f);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t h = __float_as_uint(v[j].x), l = __float_as_uint(v[j].y);
+            if (h > bh || (h == bh && l > bl)) bh = h, bl = l;
+            if (v[j].z > m) {
+                sum *= expf(m - v[j].z);  // exp(-inf) = 0 the first time
+                m = v[j].z;
+            }
+            sum += v[j].z == -INFINITY ? 0.0f : v[j].w * expf(v[j].z - m);
+        }
+    }
+    // warp, then CTA: the greatest key, the maximum, the sums brought to that maximum
+    const uint32_t wh = __reduce_max_sync(0xffffffffu, bh);
+    const uint32_t wl = __reduce_max_sync(0xffffffffu, bh == wh ? bl : 0u);
+    const float wm = warp_max(m);
+    const float ws = warp_sum(m == -INFINITY ? 0.0f : sum * expf(m - wm));
+    if (lane == 0) s_hi[warp] = wh, s_lo[warp] = wl, s_m[warp] = wm, s_sum[warp] = ws;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t h = 0u, l = 0u;
+        float mm = -INFINITY;
+        for (int w = 0; w < AM_THREADS / 32; ++w) {
+            if (s_hi[w] > h || (s_hi[w] == h && s_lo[w] > l)) h = s_hi[w], l = s_lo[w];
+            mm = fmaxf(mm, s_m[w]);
+        }
+        float denom = 0.0f;
+        for (int w = 0; w < AM_THREADS / 32; ++w) denom += s_m[w] == -INFINITY ? 0.0f : s_sum[w] * expf(s_m[w] - mm);
+        out_token[t] = (int)(0xFFFFFFFFu - l);
+        if (out_prob) out_prob[t] = 1.0f / denom;
+    }
+#ifdef FERRIS_TIMELINE
+    __syncthreads();
+#endif
+    FERRIS_TL_END(27);
 }
 
 // =============================================================================================
@@ -1456,6 +1577,60 @@ static int gemm_tcgen05_impl(const void* x, const void* w, const float* bias, vo
         case ACCUM_F32: return launch<ACCUM_F32>(mw, mx, p, grid, smem, cz, s);
         default: return launch<SWIGLU_BF16>(mw, mx, p, grid, smem, cz, s);
     }
+}
+
+// Floats of scratch that ferris_gemm_argmax_tcgen05 needs: one entry of 4 per tile of 128 outputs and token.
+FERRIS_API long long ferris_gemm_argmax_scratch_floats(int T, int N) {
+    return (long long)((N + BLOCK_N - 1) / BLOCK_N) * T * 4;
+}
+
+// The output head of rows that all take their greatest logit: out_token[t] = the lowest index among the greatest of
+// sum_k x[t, k] w[n, k], n < N; out_prob[t] = 1 / sum_n exp(l[n] - max) (may be null).  No logits are stored.
+// At most 128 rows; scratch: ferris_gemm_argmax_scratch_floats floats, 16-byte aligned.
+FERRIS_API int ferris_gemm_argmax_tcgen05(const void* x, const void* w, int* out_token, float* out_prob, int T, int N, int K,
+                                          int ldx, int ldw, int rows_w, float* scratch, void* stream) {
+    if (T <= 0) return FERRIS_OK;
+    if (N <= 0 || T > 128) FERRIS_REFUSE("product + argmax: %d rows (at most 128) over %d outputs", T, N);
+    if (K <= 0 || (K & 7) || (ldx & 7) || (ldw & 7) || ldx < K || ldw < K)
+        FERRIS_REFUSE("product + argmax: K=%d and row strides %d, %d must be multiples of 8 elements", K, ldx, ldw);
+    if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)scratch & 15) || !scratch || !out_token)
+        FERRIS_REFUSE("product + argmax: operands must be there and 16-byte aligned");
+    if (N > rows_w) FERRIS_REFUSE("product + argmax: %d outputs from %d weight rows", N, rows_w);
+    sm_count();
+    cudaStream_t s = (cudaStream_t)stream;
+    const int bt = (T + 15) / 16 * 16;
+    CUtensorMap mw, mx;
+    int rc = weight_map(w, (uint64_t)rows_w, (uint64_t)K, (uint64_t)ldw, &mw);
+    if (rc != FERRIS_OK) return rc;
+    rc = ferris_make_tensor_map_2d(&mx, x, (uint64_t)T, (uint64_t)K, (uint64_t)ldx, (uint32_t)bt, BLOCK_K);
+    if (rc != FERRIS_OK) return rc;
+    Params p = {};
+    p.out = out_token;
+    p.out_prob = out_prob;
+    p.scratch = scratch;
+    p.T = T;
+    p.N = N;
+    p.K = K;
+    p.ldo = N;
+    p.bt = bt;
+    p.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+    p.splits = 1;
+    p.status = ferris_status_ptr();
+    const int stage_bytes = BLOCK_N * BLOCK_K * 2 + bt * BLOCK_K * 2;
+    int stages = (227 * 1024 - 2048 - 8192) / stage_bytes;  // 8 KB of the kernel's own for the lane quarters' entries
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages > p.kblocks) stages = p.kblocks;
+    const int tiles = (N + BLOCK_N - 1) / BLOCK_N;
+    if (tiles >= 4 * g_sms) {  // as the product that stores the logits: two CTAs share an SM
+        const int fit = (227 * 1024 / 2 - 3072 - 8192) / stage_bytes;
+        if (fit >= 4 && stages > fit) stages = fit;
+    }
+    p.stages = stages;
+    const size_t smem = (size_t)stages * stage_bytes + 1024;
+    rc = launch<ARGMAX_F32>(mw, mx, p, dim3(tiles, 1, 1), smem, 1u, s);
+    if (rc != FERRIS_OK) return rc;
+    ferris_launch(argmax_merge_kernel, dim3(T), dim3(AM_THREADS), 0, s, (const float4*)scratch, tiles, T, out_token, out_prob);
+    FERRIS_LAUNCH_CHECK();
 }
 
 // The q/k/v product of a long step with its rotation and cache write in the epilogue: out[:, :nh d] gets the rotated

@@ -204,11 +204,16 @@ class Engine:
             entries.append(StepEntry(seq.request_id, tokens, [e.count - 1] if wants else []))
             if wants:
                 sampling.append(seq)
-        logits = self.runner.step(entries, device_tokens=device_tokens)
+        # rows that all take their most likely token are sampled by the step itself (its output head stores no logits)
+        greedy = bool(sampling) and all(s.params.is_greedy for s in sampling)
+        logits = self.runner.step(entries, device_tokens=device_tokens, greedy=greedy)
         flight = _InFlight(plan, sampling)
         if sampling:
             n = len(sampling)
-            flight.tokens, probs = self.sampler.sample(logits, [s.params for s in sampling], [s.slot for s in sampling])
+            if greedy:
+                flight.tokens, probs = logits
+            else:
+                flight.tokens, probs = self.sampler.sample(logits, [s.params for s in sampling], [s.slot for s in sampling])
             buf = self._results[self._results_next]
             self._results_next = (self._results_next + 1) % len(self._results)
             if buf[0] is None or buf[0].numel() < n:

@@ -62,6 +62,7 @@ class _GraphEntry:
     ctx: StepContext
     logits_index: torch.Tensor
     logits: torch.Tensor
+    greedy: Any = None  # (tokens, probabilities) of a step that samples greedily on its way
     graph: Any = None
     kernels: int = 0  # kernel launches that one replay stands for
 
@@ -131,14 +132,17 @@ class ModelRunner:
 
     # ---------------------------------------------------------------------- step
     def step(self, entries: Sequence[StepEntry], out: Optional[torch.Tensor] = None,
-             device_tokens: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+             device_tokens: Optional[torch.Tensor] = None, greedy: bool = False):
         """Run the tokens of ``entries`` as one batch from the cache that earlier steps left.
         Returns fp32 logits [wanted, vocab] in the order of the entries and of their ``want``
         (None if nothing is wanted).  Requests that are not admitted yet are admitted.
         The returned tensor is the runner's own buffer: it is overwritten by the next step.
         ``device_tokens`` (int32 on the device, one per entry): every entry brings one token whose id the
         host does not know yet (it was sampled by a step that is still running); the ids in ``entries`` are
-        placeholders and the step reads the real ones from this tensor."""
+        placeholders and the step reads the real ones from this tensor.
+        ``greedy``: instead of the logits the step returns (tokens int32 [wanted], probabilities fp32 [wanted]) on
+        the device, each wanted row's most likely token (the lowest index among equals) and its probability; the
+        output head then stores no logits where its kernel can avoid it.  The two tensors are the runner's own too."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return None
@@ -148,18 +152,24 @@ class ModelRunner:
         decode = all(len(e.tokens) == 1 and len(e.want) == 1 and e.want[0] == 0 for e in entries)
         graphs = self.cuda_graphs and out is None
         host = self._layout(entries, pad_to=self._bucket(len(entries)) if (decode and graphs) else 0)
-        if graphs and self._graph_worthwhile(host, decode):
-            logits = self._step_graph(host, device_tokens, decode)
+        greedy = bool(greedy) and host.n_want > 0 and out is None
+        if graphs and self._graph_worthwhile(host, decode, greedy):
+            logits = self._step_graph(host, device_tokens, decode, greedy)
         else:
             dev = self._upload(host.pieces)
             if device_tokens is not None:
                 dev[:host.real].copy_(device_tokens)
             ctx, logits_index = self._context(host, dev)
             logits = None
-            if host.n_want:
-                logits = out if out is not None else self.workspace.get("logits", (host.n_want, self.vocab_size),
-                                                                        torch.float32)
-            self.model.forward(ctx, self.cache.layer_caches, logits_index, logits)
+            if greedy:
+                logits = (torch.empty(host.n_want, dtype=torch.int32, device=self.device),
+                          torch.empty(host.n_want, dtype=torch.float32, device=self.device))
+                self.model.forward(ctx, self.cache.layer_caches, logits_index, None, greedy_out=logits)
+            else:
+                if host.n_want:
+                    logits = out if out is not None else self.workspace.get("logits", (host.n_want, self.vocab_size),
+                                                                            torch.float32)
+                self.model.forward(ctx, self.cache.layer_caches, logits_index, logits)
         for e, s in zip(entries, host.seqs):
             self.cache.commit(e.request_id, s.start_pos + s.q_len)
         self.steps_run += 1
@@ -173,26 +183,26 @@ class ModelRunner:
         return requests
 
     @staticmethod
-    def _shape_key(host: _HostStep) -> tuple:
+    def _shape_key(host: _HostStep, greedy: bool = False) -> tuple:
         """What fixes every launch of a step: the counts of tokens, requests, wanted rows and single tokens beside
         portions, the longest share and the width of the block tables.  Everything else (which tokens, positions,
         pages, how the tokens divide among the requests, which rows are wanted) is data in the step's metadata
         buffer."""
-        return (host.T, host.S, host.max_q, host.max_blocks, host.n_want, int(host.pieces[-1].size))
+        return (host.T, host.S, host.max_q, host.max_blocks, host.n_want, int(host.pieces[-1].size), bool(greedy))
 
-    def _graph_worthwhile(self, host: _HostStep, decode: bool) -> bool:
+    def _graph_worthwhile(self, host: _HostStep, decode: bool, greedy: bool = False) -> bool:
         """Decode steps are recorded at first sight; any other shape of step when it comes a second time (portions of
         a fixed size recur, most mixed steps do not), unless its logits would make the graph's own buffer large."""
         if decode:
             return True
-        key = self._shape_key(host)
+        key = self._shape_key(host, greedy)
         if key in self._graphs:
             return True
         seen = self._shapes_seen.get(key, 0)
         if len(self._shapes_seen) > 4096:
             self._shapes_seen.clear()
         self._shapes_seen[key] = seen + 1
-        return seen >= 1 and host.n_want * self.vocab_size * 4 <= self.MAX_GRAPH_LOGITS_BYTES
+        return seen >= 1 and (greedy or host.n_want * self.vocab_size * 4 <= self.MAX_GRAPH_LOGITS_BYTES)
 
     def drop_graphs(self) -> None:
         """Forget every recorded step (their buffers go with them)."""
@@ -203,8 +213,8 @@ class ModelRunner:
         self.workspace.unpin()
 
     def _step_graph(self, host: _HostStep, device_tokens: Optional[torch.Tensor] = None,
-                    decode: bool = False) -> torch.Tensor:
-        key = self._shape_key(host)
+                    decode: bool = False, greedy: bool = False):
+        key = self._shape_key(host, greedy)
         entry = self._graphs.get(key)
         if entry is None:
             while len(self._graphs) >= self.MAX_GRAPHS:
@@ -221,17 +231,21 @@ class ModelRunner:
             # launch geometry that depends on the keys' length is fixed for the width of the block table
             ctx.max_kv_len = host.max_blocks * self.cache.page_size
             logits = None
-            if host.n_want and decode:
+            picked = None
+            if greedy:
+                picked = (torch.empty(host.n_want, dtype=torch.int32, device=self.device),
+                          torch.empty(host.n_want, dtype=torch.float32, device=self.device))
+            elif host.n_want and decode:
                 if self._decode_logits is None:
                     rows = max(self._bucket(self.max_requests), host.n_want)
                     self._decode_logits = torch.empty(rows, self.vocab_size, dtype=torch.float32, device=self.device)
                 if host.n_want <= self._decode_logits.shape[0]:
                     logits = self._decode_logits[:host.n_want]
-            if host.n_want and logits is None:
+            if host.n_want and logits is None and not greedy:
                 logits = torch.empty(host.n_want, self.vocab_size, dtype=torch.float32, device=self.device)
-            entry = _GraphEntry(meta, ctx, logits_index, logits)
+            entry = _GraphEntry(meta, ctx, logits_index, logits, picked)
             # the first step of this shape runs eagerly (it also sizes every workspace buffer) ...
-            self.model.forward(ctx, self.cache.layer_caches, logits_index, logits)
+            self.model.forward(ctx, self.cache.layer_caches, logits_index, logits, greedy_out=picked)
             # ... and is then recorded for the steps to come; from here on the workspace keeps what it replaces
             self.workspace.pin()
             torch.cuda.synchronize(self.device)
@@ -243,7 +257,7 @@ class ModelRunner:
             gc.disable()
             try:
                 with torch.cuda.graph(graph):
-                    self.model.forward(ctx, self.cache.layer_caches, logits_index, logits)
+                    self.model.forward(ctx, self.cache.layer_caches, logits_index, logits, greedy_out=picked)
             finally:
                 if collecting:
                     gc.enable()
@@ -251,7 +265,7 @@ class ModelRunner:
             entry.graph = graph
             self._graphs[key] = entry
             # the capture itself ran nothing, but the eager run before it did: the result is in ``logits``
-            return logits[:host.real] if decode else logits
+            return self._result(entry, host, decode)
         self._graphs.move_to_end(key)
         self._upload(host.pieces, entry.meta)
         if device_tokens is not None:
@@ -260,6 +274,13 @@ class ModelRunner:
         entry.graph.replay()
         self.graph_replays += 1
         self.graph_kernels += entry.kernels
+        return self._result(entry, host, decode)
+
+    @staticmethod
+    def _result(entry: _GraphEntry, host: _HostStep, decode: bool):
+        """What a recorded step hands back: its logits, or its tokens and probabilities; without the padding rows."""
+        if entry.greedy is not None:
+            return (entry.greedy[0][:host.real], entry.greedy[1][:host.real]) if decode else entry.greedy
         return entry.logits[:host.real] if decode else entry.logits
 
     # ------------------------------------------------------------------- upload

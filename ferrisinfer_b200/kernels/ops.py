@@ -41,6 +41,7 @@ _SIGNATURES = {
     "ferris_prefill_attention": [_VP, _I, _VP, _I, _VP, _VP, _LL, _VP, _I, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _F, _I, _VP],
     "ferris_decode_attention_rope": [_VP, _I, _VP, _I, _VP, _VP, _LL, _VP, _I, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I,
                                      _F, _I, _VP, _I, _VP],
+    "ferris_gemm_argmax_tcgen05": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _VP, _VP],
     "ferris_gemm_skinny": [_VP, _I, _VP, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _VP],
     "ferris_gemm_skinny_takes": [_I, _I, _I, _I],
     "ferris_embed_gather": [_VP, _I, _VP, _VP, _I, _I, _I, _VP, _VP],
@@ -248,6 +249,53 @@ def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row
                                 _stream()),
         "tensor-core gemm",
     )
+
+
+def gemm_argmax(x, w, out_token, out_prob, scratch):
+    """out_token[t] = the lowest index among the greatest of (x w^T)[t, :], out_prob[t] = its softmax probability
+    (may be None): the output head of rows that all take their greatest logit, on the tcgen05 tensor cores, without
+    storing the logits.  At most 128 rows; ``scratch``: fp32, ``gemm_argmax_scratch_floats`` long."""
+    T, K, ldx = _rows(x, "gemm input")
+    N, K2, ldw = _rows(w, "gemm weight")
+    if K != K2 or T > 128 or not tensor_core_gemm_takes(x, w):
+        raise KernelError(f"product + argmax: x {tuple(x.shape)}, w {tuple(w.shape)} are not taken")
+    _need(out_token, "tokens", torch.int32)
+    if out_prob is not None:
+        _need(out_prob, "probabilities", torch.float32)
+    _need(scratch, "scratch", torch.float32)
+    if out_token.numel() != T or (out_prob is not None and out_prob.numel() != T) \
+            or scratch.numel() < gemm_argmax_scratch_floats(T, N):
+        raise KernelError("product + argmax: one token (and probability) per row and enough scratch are needed")
+    _check(
+        _lib().ferris_gemm_argmax_tcgen05(x.data_ptr(), w.data_ptr(), out_token.data_ptr(),
+                                          None if out_prob is None else out_prob.data_ptr(), T, N, K, ldx, ldw, N,
+                                          scratch.data_ptr(), _stream()),
+        "product + argmax",
+    )
+
+
+def gemm_argmax_scratch_floats(rows: int, outputs: int) -> int:
+    return 4 * rows * ((outputs + 127) // 128)
+
+
+GREEDY_HEAD_MAX_ROWS = 16
+
+
+def greedy_head(y, w, out_token, out_prob, workspace):
+    """The output head and greedy sampling of the rows ``y`` [n, H] in one: out_token int32 [n], out_prob fp32 [n].
+    bf16 rows, at most 16: the product that stores no logits; anything else: logits into the workspace, then the
+    sampling kernel's greedy rows.  The same tokens and probabilities either way (up to the rounding of the sums).
+    (The product's epilogue reduces over the 128 outputs of a tile, which lie across the lanes of its warps, with
+    three warp reductions a token; measured inside the decode step of the 0.5B sizes, that costs the product 5 us
+    at 8 rows and 32 us at 64, against 19 and 30 us for the sampling kernel and the stored logits.)"""
+    n, V = y.shape[0], w.shape[0]
+    if n <= GREEDY_HEAD_MAX_ROWS and tensor_core_gemm_takes(y, w):
+        scratch = workspace.get("argmax_tiles", (gemm_argmax_scratch_floats(n, V),), torch.float32)
+        gemm_argmax(y, w, out_token, out_prob, scratch)
+        return
+    logits = workspace.get("logits", (n, V), torch.float32)
+    gemm(y, w, None, logits)
+    sample(logits, out_token, out_prob)
 
 
 GEMM_PAIRS_NONE, GEMM_PAIRS_ALL, GEMM_PAIRS_SWIGLU = 0, 1, 2

@@ -32,6 +32,7 @@ KERNELS = {
     40: "skinny gemm -> bf16", 41: "skinny gemm -> fp32", 42: "skinny gemm += fp32", 43: "skinny gemm swiglu",
     44: "skinny norm + gemm -> bf16", 45: "skinny norm + gemm -> fp32", 46: "skinny norm + gemm += fp32",
     47: "skinny norm + gemm swiglu",
+    21: "gemm + argmax", 27: "argmax merge",
     18: "merge + gemm -> bf16", 19: "merge + gemm -> fp32", 20: "merge + gemm += fp32",
 }
 

@@ -50,6 +50,12 @@ class OutputHead(Part):
         """logits fp32 [n, V] = y [n, H] W^T."""
         ops.gemm(y, self.weight, None, logits)
 
+    def forward_greedy(self, y, tokens, probs, workspace):
+        """tokens int32 [n] = the index of each row's greatest logit (the lowest among equals), probs fp32 [n] its
+        softmax probability; the logits themselves are stored nowhere where a kernel can avoid it (the reference's
+        fused product + argmax: crates/ferrisinfer-kernel/src/cpu/matmul.rs:190-274)."""
+        ops.greedy_head(y, self.weight, tokens, probs, workspace)
+
 
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("output", "linear_head", OutputHead)

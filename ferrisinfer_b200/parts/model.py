@@ -82,10 +82,11 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ forward
     def forward(self, ctx: StepContext, caches: list, logits_index: Optional[torch.Tensor],
-                logits_out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+                logits_out: Optional[torch.Tensor], greedy_out=None) -> Optional[torch.Tensor]:
         """Run the step's tokens through every run-order entry.  ``caches[i]`` is the
         LayerCache of entry i (None if it has no need).  Logits (fp32 [n, V]) are formed for the
-        rows that ``logits_index`` names, into ``logits_out``."""
+        rows that ``logits_index`` names, into ``logits_out``; or, with ``greedy_out`` = (tokens int32 [n],
+        probabilities fp32 [n]), each such row's best token and its probability instead of its logits."""
         T = ctx.num_tokens
         ctx.shared.clear()  # what parts share belongs to one pass; a context may be run again (to record a graph)
         h = ctx.workspace.get("residual", (T, self.hidden_size), torch.float32)
@@ -98,6 +99,9 @@ class DecoderModel:
         n = logits_index.numel()
         y = ctx.workspace.get("final_normed", (n, self.hidden_size), ctx.act_dtype)
         self.final_norm.forward(h, y, row_index=logits_index)
+        if greedy_out is not None:
+            self.output.forward_greedy(y, greedy_out[0], greedy_out[1], ctx.workspace)
+            return None
         self.output.forward(y, logits_out)
         return logits_out
 

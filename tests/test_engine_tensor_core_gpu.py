@@ -87,15 +87,29 @@ def _pages_back(engine):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", ["D", "0.5B"])
-def test_greedy_generation_follows_the_plain_implementation(name, dtype, device, folders, oracle):
+def test_greedy_generation_follows_the_plain_implementation(name, dtype, device, folders, oracle, monkeypatch):
     from ferrisinfer_b200 import SamplingParams
     from ferrisinfer_b200.kernels import ops
 
     vocab = CONFIGS[name]["vocab_size"]
     prompts = [helpers.random_ids(vocab, n, 3 * n) for n in (5, 140, 333, 61, 17)]
     engine = _engine(folders[name], dtype, device)
+    calls = {"gemm_argmax": 0, "sample": 0}
+    for fn in calls:
+        real = getattr(ops, fn)
+
+        def counted(*a, _fn=fn, _real=real, **k):
+            calls[_fn] += 1
+            return _real(*a, **k)
+
+        monkeypatch.setattr(ops, fn, counted)
     outs = engine.generate(prompts, SamplingParams.greedy(max_new_tokens=12))
     assert ops.kernel_status() == 0
+    # greedy rows are picked by the output head itself: in bfloat16 without logits, in 32-bit through the sampling kernel
+    if dtype == "bfloat16":
+        assert calls["gemm_argmax"] > 0 and calls["sample"] == 0
+    else:
+        assert calls["gemm_argmax"] == 0 and calls["sample"] > 0
     for prompt, out in zip(prompts, outs):
         assert len(out.generated_token_ids()) == 12
         _follows_plain(oracle, name, dtype, prompt, out.generated_token_ids())

@@ -757,6 +757,69 @@ def test_argmax_takes_the_lowest_index_among_equal_maxima(device):
         assert abs(prob[i].item() - want[i][1]) < 1e-6 * max(1.0, 1 / want[i][1]) + 1e-6
 
 
+@pytest.mark.parametrize("T, N, K", [(1, 2501, 64), (8, 151936, 896), (64, 3001, 1536), (100, 777, 128), (128, 4096, 264),
+                                     (5, 100, 72)])
+def test_output_head_picks_the_greatest_logit_without_storing_the_logits(T, N, K, device):
+    """The product + argmax kernel against the plain greedy sampler over logits in float64, and against the stored
+    logits followed by the sampling kernel (the same token).  Rows are made so
+    that the best logit lies at the vocabulary's first and last index, in the last, partly filled tile, and twice
+    (the lower index wins)."""
+    from ferrisinfer_b200.engine.workspace import Workspace
+    from ferrisinfer_b200.kernels import ops
+
+    x = rnd((T, K), BF16, device, 61)
+    w = rnd((N, K), BF16, device, 62, scale=0.05)
+    # a weight row that is a multiple of a token's own row gives that token a logit that stands out
+    plant = {0: [N - 1], 1 % T: [0]} if T > 1 else {0: [N - 1]}
+    if T > 2:
+        plant[2] = [N // 2 + 1, 7]  # twice the same logit: index 7 wins
+    if T > 3:
+        plant[3] = [N - 3, N - 2]
+    for t, rows in plant.items():
+        for r in rows:
+            w[r] = (x[t].float() * 0.5).to(BF16)
+    tok = torch.full((T,), -1, dtype=torch.int32, device=device)
+    prob = torch.full((T,), float("nan"), dtype=F32, device=device)
+    scratch = torch.empty(ops.gemm_argmax_scratch_floats(T, N), dtype=F32, device=device)
+    launches = ops.launch_count()
+    ops.gemm_argmax(x, w, tok, prob, scratch)
+    assert ops.launch_count() - launches == 1  # one call: the product and the merge of its tiles
+    logits = torch.empty(T, N, dtype=F32, device=device)
+    ops.gemm(x, w, None, logits)
+    tok2 = torch.empty(T, dtype=torch.int32, device=device)
+    prob2 = torch.empty(T, dtype=F32, device=device)
+    ops.sample(logits, tok2, prob2)
+    torch.cuda.synchronize()
+    assert ops.kernel_status() == 0
+    assert torch.equal(tok, tok2)
+    # the stored logits of few tiles are summed over a K split, the fused product's are not: they differ by a rounding
+    # of the logit (~1e-6 absolute), and so do the probabilities
+    assert torch.allclose(prob, prob2, rtol=5e-5, atol=1e-7)
+    for t, rows in plant.items():
+        if t in (0, 1 % T) or T > 2:
+            assert tok[t].item() == min(rows), (t, tok[t].item(), rows)
+    exact = x.double() @ w.double().T
+    best = exact.max(dim=1).values
+    chosen = exact.gather(1, tok.long().unsqueeze(1)).squeeze(1)
+    assert ((best - chosen) <= 1e-3 * best.abs().clamp(min=1.0)).all()
+    want_prob = torch.softmax(exact, dim=1).gather(1, tok.long().unsqueeze(1)).squeeze(1)
+    assert torch.allclose(prob.double(), want_prob, rtol=2e-3, atol=1e-6)
+    # through the part's entry: the same for bf16 rows; 32-bit rows go through stored logits and the sampling kernel
+    ws = Workspace(device)
+    for rows in (x, x.float()):
+        weight = w if rows.dtype == BF16 else w.float()
+        tok3 = torch.full((T,), -1, dtype=torch.int32, device=device)
+        prob3 = torch.empty(T, dtype=F32, device=device)
+        ops.greedy_head(rows, weight, tok3, prob3, ws)
+        if rows.dtype == BF16:
+            assert torch.equal(tok3, tok) and torch.allclose(prob3, prob, rtol=5e-5, atol=1e-7)
+            if T <= ops.GREEDY_HEAD_MAX_ROWS:
+                assert torch.equal(prob3, prob), "few rows go through the product that stores no logits"
+        else:
+            got = exact.gather(1, tok3.long().unsqueeze(1)).squeeze(1)
+            assert ((best - got) <= 1e-5 * best.abs().clamp(min=1.0)).all()
+
+
 def exact_interval(row, T, k, p, token):
     """In float64: the mass before ``token`` and through it in the reference's order (descending logit, ascending
     index), after the top-k and top-p cuts, both as fractions of the retained mass; None if the token was cut."""

@@ -17,6 +17,10 @@
 //     K blocks in turn with mma.sync m16n8k16 (both operands by ldmatrix from shared memory; no load from
 //     global memory stands in the loop), and their eight partial tiles are added in warp order through shared
 //     memory.
+//   * Where the slab does not fit beside the step's rows (long rows: the down projection of the larger sizes), the
+//     rows are not held whole: each stage of the ring carries the box of the step's rows for its K blocks behind
+//     its box of weights (requested after the wait, counted on the same barrier), so that all of shared memory is
+//     weights in flight and nothing has to arrive before the first multiplication.
 // The tensor pipe is idle either way at these sizes; tcgen05.mma costs ~100 cycles an instruction whatever its
 // width, which caps an SM at ~80 GB/s of weights with 16 tokens, and one thread issues them all.  Eight warps of
 // mma.sync take in weights at the rate shared memory delivers them.  Steps of more than 16 tokens run the tcgen05
@@ -58,6 +62,7 @@ struct SkParams {
     int groups;    // ceil(kblocks / nb)
     int stages;    // groups of weights that shared memory holds at once
     int boxes_3d;  // the copies use the 3-D maps (K a multiple of 64); else nb == 1 and the 2-D maps
+    int x_in_stages;  // the step's rows travel with the weights, a box per stage, instead of standing whole beside them
     int up_row_offset;
     int mode;
     int* status;
@@ -93,8 +98,8 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
     // A group of nb K blocks is one TMA box: box_rows x nb lines of 128 bytes, line (row * nb + block), swizzled by the
     // line's number (with nb == 1 that is the plain 2-D box of one block).
     const int box_bytes = p.box_rows * p.nb * 128;
-    const int stage_bytes = ACCS * box_bytes;
     const int x_box_bytes = p.x_rows * p.nb * 128;
+    const int stage_bytes = ACCS * box_bytes + (p.x_in_stages ? x_box_bytes : 0);
     uint8_t* x_smem = smem + (size_t)p.stages * stage_bytes;
     const bool ring = p.groups > p.stages;  // the slab does not fit: stages are used again
 
@@ -113,7 +118,16 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
 
     if (warp == SK_WARPS) {
         // The weights depend on no earlier launch: everything the stages hold is requested before any wait.
-        auto request = [&](int g) {
+        // the box of the step's rows for group g, into its stage (counted on the stage's barrier)
+        auto request_rows = [&](int g) {
+            const int s = g % p.stages;
+            uint8_t* at = smem + (size_t)s * stage_bytes + ACCS * box_bytes;
+            if (p.boxes_3d)
+                tma_load_3d(at, &map_x, 0, g * p.nb, 0, &full[s]);
+            else
+                tma_load_2d(at, &map_x, g * SK_BLOCK_K, 0, &full[s]);
+        };
+        auto request = [&](int g, bool with_rows) {
             const int s = g % p.stages;
             uint8_t* st = smem + (size_t)s * stage_bytes;
             mbar_expect_tx(&full[s], stage_bytes);
@@ -124,11 +138,17 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
                 tma_load_2d(st, &map_w, g * SK_BLOCK_K, n0, &full[s]);
                 if (ACCS == 2) tma_load_2d(st + box_bytes, &map_w, g * SK_BLOCK_K, p.up_row_offset + n0, &full[s]);
             }
+            if (with_rows) request_rows(g);
         };
         const int first = min(p.groups, p.stages);
         if (lane == 0)
-            for (int g = 0; g < first; ++g) request(g);
-        if (!p.norm_h) {
+            for (int g = 0; g < first; ++g) request(g, false);
+        if (p.x_in_stages) {
+            // the rows of the first stages follow their weights after the wait; later stages get both at once
+            pdl_wait();
+            if (lane == 0)
+                for (int g = 0; g < first; ++g) request_rows(g);
+        } else if (!p.norm_h) {
             // the step's rows were written by the launch before: requested after the wait, one box per group, the
             // lanes taking the boxes in turn
             pdl_wait();
@@ -144,7 +164,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
         if (lane == 0)
             for (int g = first; g < p.groups; ++g) {
                 if (!mbar_wait(&empty[g % p.stages], ((g / p.stages) - 1) & 1, p.status, 40)) break;
-                request(g);
+                request(g, p.x_in_stages != 0);
             }
         return;
     }
@@ -248,7 +268,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
             }
         }
         asm volatile("bar.sync 1, 256;" ::: "memory");
-    } else {
+    } else if (!p.x_in_stages) {
         mbar_wait(&full_x, 0, p.status, 42);
     }
     FERRIS_TL_MARK(tl_mark, 0);
@@ -279,7 +299,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
         waited += FERRIS_TL_CLOCK() - c0;
         FERRIS_TL_MARK(tl_mark && i == 0, 1);
         const uint32_t st = smem_u32(smem + (size_t)s * stage_bytes);
-        const uint32_t xg = x_base + g * x_box_bytes;
+        const uint32_t xg = p.x_in_stages ? st + ACCS * box_bytes : x_base + g * x_box_bytes;
         const int blocks = min(p.nb, p.kblocks - g * p.nb);
         for (int kbi = 0; kbi < blocks; ++kbi) {
             // B fragments of the four K steps: tokens are the rows of the box; matrices (tokens 0-7 | 8-15) x
@@ -382,6 +402,7 @@ int sk_sm_count() {
 struct SkPlan {
     int rows, box_rows, x_rows, mt, ctas, kblocks, nb, groups, stages;
     size_t smem;
+    int x_in_stages;
 };
 
 // Shared memory of one CTA: the step's rows whole, the weight stages beside them; a slab that does not fit streams
@@ -391,18 +412,23 @@ struct SkPlan {
 // ends is worth more than an early start of the next launch's copies: a ring's later groups are requested only as
 // the earlier ones are consumed, one more trip to memory on the step's critical path, while a launch that has to wait
 // for the SM still has the ~2 us between the end of the launch before and its own wait for its copies.
-// FERRIS_SKINNY_SMEM_KB in the environment overrides (16 to 200).
+// Beyond 190 KB nothing changes at those sizes; the rings of the larger sizes gain from every KB, because more of it
+// lets a copy bring more K blocks of a row, and longer runs of a weight row come faster out of HBM: down projection
+// of the 7B sizes (rows of 37 KB) 35.4 us with copies of 3 blocks (190 KB), 26.3 us with 5 (200 KB and more); of the
+// 1.5B sizes 9.8 us at 190 KB, 9.3 us at 220 KB.  So the default is 220 KB.
+// FERRIS_SKINNY_SMEM_KB in the environment overrides (16 to 220).
 int g_sk_budget = 0;
 int sk_smem_budget() {
     if (g_sk_budget <= 0) {
         const char* v = getenv("FERRIS_SKINNY_SMEM_KB");
-        g_sk_budget = (v ? atoi(v) : 190) * 1024;
-        if (g_sk_budget < 16 * 1024 || g_sk_budget > 200 * 1024) g_sk_budget = 190 * 1024;
+        g_sk_budget = (v ? atoi(v) : 220) * 1024;
+        if (g_sk_budget < 16 * 1024 || g_sk_budget > 220 * 1024) g_sk_budget = 220 * 1024;
     }
     return g_sk_budget;
 }
 
-bool sk_plan(int T, int N, int K, int accs, SkPlan* out) {
+// rows_by_tma: the step's rows exist as bf16 (not formed by the kernel as a norm), so they may travel with the weights.
+bool sk_plan(int T, int N, int K, int accs, bool rows_by_tma, SkPlan* out) {
     if (T < 1 || T > SK_MAX_TOKENS || N < 1 || K < 8 || (K & 7)) return false;
     const int sms = sk_sm_count();
     int rows = (N + sms - 1) / sms;
@@ -417,18 +443,21 @@ bool sk_plan(int T, int N, int K, int accs, SkPlan* out) {
     // be about as many as the warps, or many more.  Odd sizes only: the eight rows of a block then lie in eight
     // different swizzle phases of the box, and ldmatrix reads them without bank conflicts.  Without whole blocks
     // (K no multiple of 64) the 2-D map brings one block per copy.
-    int best_nb = 1, best_stages = 0;
+    int best_nb = 1, best_stages = 0, best_in_stages = 0;
     double best_cost = 1e30;
+    for (int variant = 0; variant < (rows_by_tma ? 2 : 1); ++variant)
     for (int nb = 1; nb <= 15; nb += 2) {
         if (nb > 1 && (K & 63)) break;
         if (nb > kblocks) break;
         const int groups = (kblocks + nb - 1) / nb;
-        const int stage_bytes = accs * box_rows * nb * 128;
-        const int x_bytes = groups * x_rows * nb * 128;
+        // variant 1: the rows travel with the weights (only where the slab is a ring anyway)
+        const int stage_bytes = (accs * box_rows + (variant ? x_rows : 0)) * nb * 128;
+        const int x_bytes = variant ? 0 : groups * x_rows * nb * 128;
         if (x_bytes >= sk_smem_budget()) continue;
         int stages = (sk_smem_budget() - x_bytes) / stage_bytes;
         if (stages > SK_MAX_STAGES) stages = SK_MAX_STAGES;
         if (stages >= groups) {
+            if (variant) continue;  // everything fits: the rows stand whole, as one request
             stages = groups;
         } else {
             // A ring: the groups of a stage must all go to one warp, which then sees the stage's fills in order
@@ -438,11 +467,13 @@ bool sk_plan(int T, int N, int K, int accs, SkPlan* out) {
             if (stages <= 0) continue;
             // More than 8 tokens beside long rows leave the weights a small ring, and the tcgen05 kernel is then the
             // faster one (down projection of the 0.5B sizes at 16 tokens: 9.4 us here, 7.1 us there).
-            if (x_rows > 8 && stages * 2 < groups) continue;
+            if (!variant && x_rows > 8 && stages * 2 < groups) continue;
         }
-        // blocks on the busiest warp, the copies it waits for, and what a ring adds
-        const double cost = (double)((groups + SK_WARPS - 1) / SK_WARPS) * nb + 0.4 * groups + 1.0 * (groups - stages);
-        if (cost < best_cost) best_cost = cost, best_nb = nb, best_stages = stages;
+        // blocks on the busiest warp, the copies it waits for, and what a ring adds: the groups that are not in
+        // shared memory when the wait ends, each a trip to memory behind the one before it in its stage
+        const double cost = (double)((groups + SK_WARPS - 1) / SK_WARPS) * nb + 0.4 * groups +
+                            1.0 * (groups - stages) * (variant ? 0.5 : 1.0);
+        if (cost < best_cost) best_cost = cost, best_nb = nb, best_stages = stages, best_in_stages = variant;
     }
     if (best_stages == 0) return false;  // rows too long to stand beside their weights: the tcgen05 kernel's
     const int nb = best_nb, groups = (kblocks + nb - 1) / nb, stages = best_stages;
@@ -450,9 +481,10 @@ bool sk_plan(int T, int N, int K, int accs, SkPlan* out) {
     const int mt = (rows + 15) / 16;
     const size_t red_bytes = (size_t)SK_WARPS * accs * mt * nt * 4 * 32 * sizeof(float);
     // the warps' partial tiles reuse the stages (and, if they need more, the rows behind them, which nobody reads then)
-    size_t smem = (size_t)stages * accs * box_rows * nb * 128 + (size_t)groups * x_rows * nb * 128;
+    size_t smem = best_in_stages ? (size_t)stages * (accs * box_rows + x_rows) * nb * 128
+                                 : (size_t)stages * accs * box_rows * nb * 128 + (size_t)groups * x_rows * nb * 128;
     if (smem < red_bytes) smem = red_bytes;
-    *out = {rows, box_rows, x_rows, mt, ctas, kblocks, nb, groups, stages, smem + 1024};
+    *out = {rows, box_rows, x_rows, mt, ctas, kblocks, nb, groups, stages, smem + 1024, best_in_stages};
     return true;
 }
 
@@ -485,10 +517,11 @@ FERRIS_API int ferris_set_gemm_skinny(int on) {
     return FERRIS_OK;
 }
 
-// 1 if ferris_gemm_skinny takes a product of these sizes (accumulators: 2 for SwiGLU, else 1).
-FERRIS_API int ferris_gemm_skinny_takes(int T, int N, int K, int accumulators) {
+// 1 if ferris_gemm_skinny takes a product of these sizes (accumulators: 2 for SwiGLU, else 1; rows_by_tma: the step's
+// rows exist as bf16, 0 if the kernel is to form them as a norm).
+FERRIS_API int ferris_gemm_skinny_takes(int T, int N, int K, int accumulators, int rows_by_tma) {
     SkPlan plan;
-    return (ferris_gemm_skinny_enabled() && sk_plan(T, N, K, accumulators == 2 ? 2 : 1, &plan)) ? 1 : 0;
+    return (ferris_gemm_skinny_enabled() && sk_plan(T, N, K, accumulators == 2 ? 2 : 1, rows_by_tma != 0, &plan)) ? 1 : 0;
 }
 
 // x: bf16 [T, K] rows ldx apart (16-byte aligned rows), or null with norm_h / norm_w / norm_eps: the rows are the RMSNorm of the fp32 rows
@@ -501,7 +534,7 @@ FERRIS_API int ferris_gemm_skinny(const void* x, int ldx, const float* norm_h, c
     if (mode < 0 || mode > 3) FERRIS_REFUSE("skinny gemm: unknown mode %d", mode);
     const int accs = mode == SK_SWIGLU_BF16 ? 2 : 1;
     SkPlan plan;
-    if (!sk_plan(T, N, K, accs, &plan))
+    if (!sk_plan(T, N, K, accs, norm_h == nullptr, &plan))
         FERRIS_REFUSE("skinny gemm: %d tokens x %d outputs x K=%d is not a shape it takes (at most %d tokens, K a "
                       "multiple of 8, at most %d rows)", T, N, K, SK_MAX_TOKENS, 2 * SK_MAX_ROWS * sk_sm_count());
     if ((ldw & 7) || ldw < K || ((uintptr_t)w & 15)) FERRIS_REFUSE("skinny gemm: weight rows must be 16-byte aligned");
@@ -549,6 +582,7 @@ FERRIS_API int ferris_gemm_skinny(const void* x, int ldx, const float* norm_h, c
     p.groups = plan.groups;
     p.stages = plan.stages;
     p.boxes_3d = boxes_3d ? 1 : 0;
+    p.x_in_stages = plan.x_in_stages;
     p.up_row_offset = up_row_offset;
     p.mode = mode;
     p.status = ferris_status_ptr();

@@ -43,7 +43,7 @@ _SIGNATURES = {
                                      _F, _I, _VP, _I, _VP],
     "ferris_gemm_argmax_tcgen05": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _VP, _VP],
     "ferris_gemm_skinny": [_VP, _I, _VP, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _VP],
-    "ferris_gemm_skinny_takes": [_I, _I, _I, _I],
+    "ferris_gemm_skinny_takes": [_I, _I, _I, _I, _I],
     "ferris_embed_gather": [_VP, _I, _VP, _VP, _I, _I, _I, _VP, _VP],
 }
 _declared = False
@@ -450,10 +450,11 @@ def _skinny_takes(x, w, out, accs: int) -> bool:
     elif not (x.dim() == 2 and x.is_cuda and x.stride(1) == 1 and (x.stride(0) % 8 == 0 or T == 1) and x.data_ptr() % 16 == 0):
         return False
     N = out.shape[1]
-    key = (T > 8, N, K, accs)
+    formed = isinstance(x, LazyRMSNorm)  # rows that the kernel forms stand whole in shared memory; others may stream
+    key = (T > 8, N, K, accs, formed)
     takes = _skinny_shapes.get(key)
     if takes is None:
-        takes = bool(_lib().ferris_gemm_skinny_takes(T, N, K, accs))
+        takes = bool(_lib().ferris_gemm_skinny_takes(T, N, K, accs, 0 if formed else 1))
         _skinny_shapes[key] = takes
     return takes
 

@@ -896,6 +896,52 @@ def test_sampling_matches_the_plain_sampler(V, device):
         assert differ <= 1, differ
 
 
+@pytest.mark.parametrize("V", [3, 7, 33, 1000])
+def test_sampling_at_the_edges(V, device):
+    """Vocabularies smaller than the row's eight CTAs have parts, rows with -inf entries (a masked vocabulary), one
+    finite logit only, logits spread over hundreds of units (everything but the top falls below the histogram's range)
+    and rows of one value: the chosen token's span of the retained mass holds the draw, in float64."""
+    from ferrisinfer_b200.kernels import ops
+
+    g = torch.Generator().manual_seed(V)
+    base = torch.randn(6, V, generator=g) * 2.0
+    base[1, ::2] = float("-inf")                      # every second token masked
+    base[2] = float("-inf")
+    base[2, V // 2] = 0.3                             # one token left
+    base[3] = torch.linspace(-300.0, 40.0, V)         # a spread far beyond the histogram's range at T = 0.5
+    base[4] = 1.25                                    # all equal
+    base[5, : max(1, V // 3)] = float("-inf")
+    options = [(0.8, 0, 1.0), (1.0, 0, 0.9), (0.7, 5, 1.0), (0.5, 0, 0.95), (1.0, 2, 1.0), (1.3, 0, 0.5)]
+    rows = base.shape[0]
+    temperature = torch.tensor([o[0] for o in options])
+    top_k = torch.tensor([o[1] for o in options], dtype=torch.int32)
+    top_p = torch.tensor([o[2] for o in options])
+    slots = torch.arange(rows, dtype=torch.int32)
+    states = torch.randint(1, 2**62, (rows,), generator=g)
+    dev_states = states.clone().to(device)
+    tok = torch.empty(rows, dtype=torch.int32, device=device)
+    prob = torch.empty(rows, dtype=F32, device=device)
+    for draw in range(4):
+        ops.sample(base.to(device), tok, prob, temperature.to(device), top_k.to(device), top_p.to(device),
+                   slots.to(device), dev_states)
+        torch.cuda.synchronize()
+        assert ops.kernel_status() == 0
+        for r in range(rows):
+            T, k, p = options[r]
+            row = base[r].numpy()
+            rng = plain.XorShift64Star(int(states[r].item()))
+            u = rng.next_f32()
+            states[r] = rng.state - (1 << 64) if rng.state >= 1 << 63 else rng.state
+            assert dev_states[r].item() == states[r].item()
+            chosen = tok[r].item()
+            assert 0 <= chosen < V and row[chosen] > float("-inf"), (r, chosen)
+            span = exact_interval(row, T, k, p, chosen)
+            assert span is not None, (r, chosen)
+            lo, hi = span
+            assert lo - 1e-5 <= u <= hi + 1e-5, (r, u, lo, hi)
+            assert abs(prob[r].item() - (hi - lo)) < 1e-3 * (hi - lo) + 1e-6
+
+
 def test_sampling_distribution(device):
     """Ten thousand draws at temperature 1 from a row of five tokens follow softmax."""
     from ferrisinfer_b200.kernels import ops

@@ -4,7 +4,9 @@
 // a running maximum, sum and weighted value sum each, merged at the end.
 //
 //   query head hq uses kv head hq / (nh / nkv); s_j = (q . k_j) * scale; the query at absolute
-//   position P attends keys lo..P, lo = 0 or P - window + 1; softmax over them; out = sum w_j v_j
+//   position P attends keys lo..P, lo = 0 or P - window + 1; softmax over them; out = sum w_j v_j.
+//   With `slopes` (one per query head; a position encoding that acts on the scores, not on q and k):
+//   s_j += slopes[hq] * (j - P), a penalty linear in the distance.
 // (crates/ferrisinfer-kernel/src/cpu/attention.rs:729-781, 1125-1155: streaming softmax with a
 // running maximum, which this kernel keeps per warp).  The step's own keys are already in the
 // cache when this runs, so prompts, portions of prompts and single decoded tokens are one case.
@@ -24,7 +26,8 @@ __global__ void __launch_bounds__(ATT_THREADS)
                                 const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                                 const int* __restrict__ block_tables, int max_blocks,
                                 const int* __restrict__ token_seq, const int* __restrict__ positions, int nh,
-                                int nkv, int d, int page_size, int window, float scale) {
+                                int nkv, int d, int page_size, int window, float scale,
+                                const float* __restrict__ slopes) {
     extern __shared__ float smem[];  // per warp: m, z, acc[d]
     pdl_wait();
     pdl_launch_dependents();
@@ -35,6 +38,7 @@ __global__ void __launch_bounds__(ATT_THREADS)
     const int P = positions[t];
     const int lo = (window > 0 && P - window + 1 > 0) ? P - window + 1 : 0;
     const int* table = block_tables + (size_t)seq * max_blocks;
+    const float slope = slopes ? slopes[hq] : 0.0f;
 
     float qv[MAX_PER_LANE], acc[MAX_PER_LANE];
     const T* qrow = q + (size_t)t * ldq + (size_t)hq * d;
@@ -55,7 +59,7 @@ __global__ void __launch_bounds__(ATT_THREADS)
             const int i = lane + 32 * r;
             if (i < d) dot = fmaf(qv[r], to_float(k_cache[base + i]), dot);
         }
-        const float s = warp_sum(dot) * scale;
+        const float s = slopes ? fmaf(slope, (float)(j - P), warp_sum(dot) * scale) : warp_sum(dot) * scale;
         float wgt;
         if (s > m) {
             const float rescale = expf(m - s);  // exp(-inf) = 0 on the first key
@@ -111,7 +115,8 @@ __global__ void __launch_bounds__(ATT_THREADS)
 FERRIS_API int ferris_paged_attention_simt(const void* q, int ldq, void* out, int ldo, const void* k_cache,
                                            const void* v_cache, int dtype, const int* block_tables, int max_blocks,
                                            const int* token_seq, const int* positions, int tokens, int nh, int nkv,
-                                           int d, int page_size, int window, float scale, void* stream) {
+                                           int d, int page_size, int window, float scale, const float* slopes,
+                                           void* stream) {
     if (tokens <= 0) return FERRIS_OK;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0) FERRIS_REFUSE("attention: %d heads over %d kv heads", nh, nkv);
     if (d <= 0 || d > 32 * MAX_PER_LANE) FERRIS_REFUSE("attention: head size %d not in 1..%d", d, 32 * MAX_PER_LANE);
@@ -122,10 +127,10 @@ FERRIS_API int ferris_paged_attention_simt(const void* q, int ldq, void* out, in
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == FERRIS_F32)
         ferris_launch(paged_attention_simt_kernel<float>, grid, dim3(ATT_THREADS), smem, s, (const float*)q, ldq, (float*)out, ldo, (const float*)k_cache, (const float*)v_cache, block_tables,
-            max_blocks, token_seq, positions, nh, nkv, d, page_size, window, scale);
+            max_blocks, token_seq, positions, nh, nkv, d, page_size, window, scale, slopes);
     else if (dtype == FERRIS_BF16)
         ferris_launch(paged_attention_simt_kernel<bf16>, grid, dim3(ATT_THREADS), smem, s, (const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks,
-            token_seq, positions, nh, nkv, d, page_size, window, scale);
+            token_seq, positions, nh, nkv, d, page_size, window, scale, slopes);
     else
         FERRIS_REFUSE("attention: unknown dtype %d", dtype);
     FERRIS_LAUNCH_CHECK();

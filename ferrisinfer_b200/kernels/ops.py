@@ -640,8 +640,11 @@ def rope_cache_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optio
 
 def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                          block_tables: torch.Tensor, token_seq: torch.Tensor, positions: torch.Tensor,
-                         num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float):
-    """General attention over the paged cache; q is read from the first nh*d columns of ``qkv``."""
+                         num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
+                         score_slopes: Optional[torch.Tensor] = None):
+    """General attention over the paged cache; q is read from the first nh*d columns of ``qkv``.
+    ``score_slopes`` (fp32 [num_heads]): the score of a query at position P and the key at position j gets
+    slopes[head] * (j - P) added."""
     T, _, ldq = _rows(qkv, "attention queries")
     T2, width, ldo = _rows(out, "attention output")
     _need(k_cache, "key cache", qkv.dtype)
@@ -653,12 +656,16 @@ def paged_attention_simt(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Te
         raise KernelError(f"attention: q {tuple(qkv.shape)}, out {tuple(out.shape)}")
     if k_cache.dim() != 4 or k_cache.shape[1] != num_kv_heads or k_cache.shape[3] != head_dim or block_tables.dim() != 2:
         raise KernelError(f"attention: cache {tuple(k_cache.shape)}, tables {tuple(block_tables.shape)}")
+    if score_slopes is not None:
+        _need(score_slopes, "score slopes", torch.float32)
+        if score_slopes.numel() != num_heads:
+            raise KernelError("attention: one score slope per query head is needed")
     _check(
         _lib().ferris_paged_attention_simt(_ptr(qkv), _c_int(ldq), _ptr(out), _c_int(ldo), _ptr(k_cache), _ptr(v_cache),
                                            _dt(qkv, "attention"), _ptr(block_tables), _c_int(block_tables.shape[1]),
                                            _ptr(token_seq), _ptr(positions), _c_int(T), _c_int(num_heads),
                                            _c_int(num_kv_heads), _c_int(head_dim), _c_int(k_cache.shape[2]),
-                                           _c_int(window or 0), _c_float(scale), _stream()),
+                                           _c_int(window or 0), _c_float(scale), _ptr(score_slopes), _stream()),
         "paged attention",
     )
 
@@ -750,20 +757,24 @@ def set_prefill_tcgen05(on=True) -> None:
 
 
 def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_heads, head_dim, inv_freq, rotary_dim,
-                   window, scale, write_kv: bool = True, lazy_merge: bool = False, rotated: bool = False):
+                   window, scale, write_kv: bool = True, lazy_merge: bool = False, rotated: bool = False,
+                   score_slopes: Optional[torch.Tensor] = None):
     """Everything between the q/k/v product and the output product of an attention layer: rotate q and k by
     position, put k and v into the paged cache (``meta``: the step's block tables and slots for the cache's
     page group), attend.  A step of single tokens with whole-head rotation on the tensor-core path is ONE
     kernel (the split-KV kernel rotates and writes on its way); everything else is the rotary / cache-write
     kernel followed by ``paged_attention``.  Returns ``out``; with ``lazy_merge`` it may return a
     LazySplitMerge instead (``out`` not yet written), which ``gemm`` takes as its input.  ``rotated``: the
-    q/k/v product has rotated and stored already (``qkv_rope_gemm``), only attention is left."""
+    q/k/v product has rotated and stored already (``qkv_rope_gemm``), only attention is left.
+    ``score_slopes`` (fp32 [num_heads], of a position encoding that acts on the scores): slopes[head] * (j - P) is
+    added to the score of the key at position j for the query at position P; the general kernel then attends."""
     T = qkv.shape[0]
     page_size = k_cache.shape[2]
     if rotated:
-        paged_attention(qkv, out, k_cache, v_cache, meta.block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale)
+        paged_attention(qkv, out, k_cache, v_cache, meta.block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale,
+                        score_slopes=score_slopes)
         return out
-    if (ctx.max_q_len == 1 and rotary_dim == head_dim and inv_freq is not None
+    if (ctx.max_q_len == 1 and rotary_dim == head_dim and inv_freq is not None and score_slopes is None
             and tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim, page_size)):
         _need(k_cache, "key cache", qkv.dtype)
         _need(v_cache, "value cache", qkv.dtype)
@@ -803,15 +814,17 @@ def attention_step(qkv, out, k_cache, v_cache, meta, ctx, num_heads, num_kv_head
         return LazySplitMerge(scratch, out, num_heads, head_dim, splits) if leave else out
     rope_cache_write(qkv, ctx.positions, inv_freq, meta.slot_mapping, k_cache, v_cache, num_heads, num_kv_heads,
                      head_dim, rotary_dim, page_size, write_kv=write_kv)
-    paged_attention(qkv, out, k_cache, v_cache, meta.block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale)
+    paged_attention(qkv, out, k_cache, v_cache, meta.block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale,
+                    score_slopes=score_slopes)
     return out
 
 
-def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale):
+def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, num_kv_heads, head_dim, window, scale,
+                    score_slopes: Optional[torch.Tensor] = None):
     """Attention of the step's tokens over the paged cache (their own keys are in it already).
     ``ctx`` is the step context.  bf16 with head size 64 / 128 runs on the tensor cores: the split-KV
-    kernel when every request brings one token, the prefill kernel otherwise; every other geometry, and
-    the 32-bit path, runs the general kernel."""
+    kernel when every request brings one token, the prefill kernel otherwise; every other geometry, the
+    32-bit path, and scores with slopes added (``score_slopes``) run the general kernel."""
     _need(k_cache, "key cache", qkv.dtype)
     _need(v_cache, "value cache", qkv.dtype)
     _need(block_tables, "block tables", torch.int32)
@@ -820,9 +833,9 @@ def paged_attention(qkv, out, k_cache, v_cache, block_tables, ctx, num_heads, nu
         raise KernelError(f"attention: cache {tuple(k_cache.shape)}, tables {tuple(block_tables.shape)}")
     if out.dtype != qkv.dtype or out.shape[1] != num_heads * head_dim or out.shape[0] != qkv.shape[0]:
         raise KernelError(f"attention: q {tuple(qkv.shape)}, out {tuple(out.shape)}")
-    if not tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim, k_cache.shape[2]):
+    if score_slopes is not None or not tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim, k_cache.shape[2]):
         paged_attention_simt(qkv, out, k_cache, v_cache, block_tables, ctx.token_seq, ctx.positions, num_heads,
-                             num_kv_heads, head_dim, window, scale)
+                             num_kv_heads, head_dim, window, scale, score_slopes=score_slopes)
         return
     T = qkv.shape[0]
     singles = getattr(ctx, "single_rows", None)

@@ -88,6 +88,7 @@ class GroupedQueryAttention(Mixer):
         qkv = ctx.workspace.get("attn_qkv", (T, self.q_size + 2 * self.kv_size), x.dtype)
         table = self.position.rotary_table(qkv.device)
         inv_freq, rotary = table if table is not None else (None, 0)
+        slopes = self.position.score_slopes(nh, qkv.device)
         # a long step of prompt portions: rotation and cache write ride in the product's epilogue
         fused = False
         if (inv_freq is not None and ctx.max_q_len > 1 and T >= ops.QKV_ROPE_MIN_TOKENS
@@ -104,7 +105,7 @@ class GroupedQueryAttention(Mixer):
         out = ctx.workspace.get("attn_out", (T, self.q_size), x.dtype)
         attended = ops.attention_step(qkv, out, cache.k, cache.v, meta, ctx, nh, nkv, d, inv_freq, rotary,
                                       self.window or 0, self.scale, write_kv=owns_cache, lazy_merge=True,
-                                      rotated=fused)
+                                      rotated=fused, score_slopes=slopes)
         ops.gemm(attended, self.o_weight, None, h, accumulate=True)
 
 

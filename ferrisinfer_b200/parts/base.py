@@ -136,7 +136,8 @@ class Norm(Part):
 
 class PositionEncoding(Part):
     """How positions enter a mixer.  ``rotary_table`` lets the attention mixer fuse the
-    rotation with its cache write; a kind without one is applied through ``apply``."""
+    rotation with its cache write; a kind without one is applied through ``apply``; a kind that acts on
+    the attention scores instead of (or beside) q and k says so with ``score_slopes``."""
 
     # as for Mixer: True if ``apply`` may be recorded into a CUDA graph (kinds with a rotary table never run it)
     graph_safe = False
@@ -152,6 +153,12 @@ class PositionEncoding(Part):
               head_dim: int) -> None:
         """Encode positions into the q and k heads of ``qkv`` in place."""
         raise NotImplementedError
+
+    def score_slopes(self, num_heads: int, device=None) -> Optional[torch.Tensor]:
+        """fp32 [num_heads] on ``device`` if the encoding adds ``slopes[head] * (j - P)`` to the score of the key at
+        position j for the query at position P (a penalty linear in the distance; j <= P); None (the default) if it
+        adds nothing to the scores.  Such scores are attended by the general kernel in every precision."""
+        return None
 
 
 class Mixer(Part):

@@ -489,7 +489,6 @@ def timeline(args) -> int:
     import torch
 
     from ferrisinfer_b200.engine.runner import StepEntry
-    from ferrisinfer_b200.kernels import ops
     from ferrisinfer_b200.kernels.timeline import StepTimeline, summarize
 
     cfg = dict(QWEN25_05B)
@@ -516,8 +515,6 @@ def timeline(args) -> int:
     engine = build_engine(cfg, args.batch, CONTEXT)
     tl = StepTimeline(engine.device)
     ids = fill_cache(engine, args.batch, CONTEXT - 16)
-    out_tok = torch.empty(args.batch, dtype=torch.int32, device=engine.device)
-
     def one(i):
         engine.runner.step([StepEntry(rid, [(7 * i + b) % 1000], [0]) for b, rid in enumerate(ids)], greedy=True)
 

@@ -25,6 +25,7 @@ namespace {
 constexpr int TILE_KEYS = 16;
 constexpr int WARPS = 4;
 constexpr int ROW_CACHE = 64;  // block-table look-ups a warp keeps ahead
+constexpr int MAX_CLUSTER = 16;  // key ranges that one thread-block cluster merges (more than 8: not portable, but B200's)
 
 // Position limits of one thread's two rows (g and g + 8 of the warp's 16-row slab).
 struct RowLimits {
@@ -618,9 +619,9 @@ __global__ void __launch_bounds__(NW * 32)
         const int begin = split * share, end = min(begin + share, G * D);
         for (int idx = begin + threadIdx.x; idx < end; idx += NW * 32) {
             const int r = idx / D;
-            float ms[8], ls[8], os[8];
+            float ms[MAX_CLUSTER], ls[MAX_CLUSTER], os[MAX_CLUSTER];
 #pragma unroll
-            for (int sp = 0; sp < 8; ++sp) {
+            for (int sp = 0; sp < MAX_CLUSTER; ++sp) {
                 const bool have = sp < splits;
                 ms[sp] = have ? my_ml[(sp * G + r) * 2] : -INFINITY;
                 ls[sp] = have ? my_ml[(sp * G + r) * 2 + 1] : 0.0f;
@@ -628,10 +629,10 @@ __global__ void __launch_bounds__(NW * 32)
             }
             float mm = -INFINITY;
 #pragma unroll
-            for (int sp = 0; sp < 8; ++sp) mm = fmaxf(mm, ms[sp]);
+            for (int sp = 0; sp < MAX_CLUSTER; ++sp) mm = fmaxf(mm, ms[sp]);
             float ll = 0.0f, oo = 0.0f;
 #pragma unroll
-            for (int sp = 0; sp < 8; ++sp) {
+            for (int sp = 0; sp < MAX_CLUSTER; ++sp) {
                 if (sp >= splits) continue;
                 const float f = ms[sp] == -INFINITY ? 0.0f : expf(ms[sp] - mm);
                 ll += ls[sp] * f;
@@ -1388,7 +1389,8 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
     rope.k_cache = (bf16*)const_cast<void*>(k_cache);
     rope.v_cache = (bf16*)const_cast<void*>(v_cache);
     const int cluster = (merge == 3 && splits > 1) ? 1 : 0;
-    if (cluster && splits > 8) FERRIS_REFUSE("decode attention: a cluster merges at most 8 key ranges, not %d", splits);
+    if (cluster && splits > MAX_CLUSTER)
+        FERRIS_REFUSE("decode attention: a cluster merges at most %d key ranges, not %d", MAX_CLUSTER, splits);
     cudaError_t e = cudaSuccess;
     CUtensorMap mkv;
     const bool pair = cache_pair_map(k_cache, v_cache, rows, d, &mkv);
@@ -1418,6 +1420,10 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
             attr[n].val.clusterDim.y = 1;
             attr[n].val.clusterDim.z = 1;
             ++n;
+            if (splits > 8) {
+                const cudaError_t allowed = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+                if (allowed != cudaSuccess) return allowed;
+            }
         }
         if (ferris_pdl_enabled()) {
             attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -1504,18 +1510,20 @@ FERRIS_API int ferris_decode_attention_rope(const void* qkv, int ldq, void* out,
 }
 
 // Into how many key ranges a step of `tokens` single tokens is cut when a cluster merges them (merge mode 3): at
-// most 8 (a portable cluster), no more than fill the SMs once, at least eight 16-key tiles each, and only as many as
-// the GPU holds clusters of that size at once (the CTAs of a cluster share a GPC; a cluster that has to wait for
-// one costs a second round).  0: this head size has no such kernel.
+// most 8 (a portable cluster), or up to 16 where the block tables span 16,384 keys or more (one or two requests
+// with long contexts: 16 CTAs instead of 8 stream each kv head's keys); no more than fill the SMs once, at least
+// eight 16-key tiles each, and only as many as the GPU holds clusters of that size at once (the CTAs of a cluster
+// share a GPC; a cluster that has to wait for one costs a second round).  0: this head size has no such kernel.
 FERRIS_API int ferris_decode_cluster_splits(int tokens, int nkv, int d, int max_kv_len) {
     if (tokens <= 0 || nkv <= 0 || (d != 64 && d != 128)) return 0;
-    static int fits[2][9] = {};  // clusters of size s that are resident at once, by head size; 0 = not asked yet
+    static int fits[2][MAX_CLUSTER + 1] = {};  // clusters of size s that are resident at once, by head size; 0 = not asked yet
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
         sms = 148;
     const int groups = tokens * nkv;
     int want = sms / groups;
-    if (want > 8) want = 8;
+    const int cap = max_kv_len >= 16384 ? MAX_CLUSTER : 8;
+    if (want > cap) want = cap;
     const int most = (max_kv_len / TILE_KEYS) / 8;
     if (want > most) want = most;
     if (want < 1) want = 1;
@@ -1537,7 +1545,11 @@ FERRIS_API int ferris_decode_cluster_splits(int tokens, int nkv, int d, int max_
             cfg.numAttrs = 1;
             int clusters = 0;
             cudaError_t e = cudaSuccess;
-            cfg.dynamicSmemBytes = (size_t)12 * 16384 + 1024 + (size_t)(8 * 2 * 16 + 16 * d + 8) * 4;
+            cfg.dynamicSmemBytes = (size_t)12 * 16384 + 1024 + (size_t)(MAX_CLUSTER * 2 * 16 + 16 * d + MAX_CLUSTER) * 4;
+            if (sp > 8) {
+                if (d == 64) cudaFuncSetAttribute(decode_attention_kernel<64, 1, true, 12>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+                else cudaFuncSetAttribute(decode_attention_kernel<128, 1, true, 12>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            }
             if (d == 64) {
                 set_smem(decode_attention_kernel<64, 1, true, 12>, cfg.dynamicSmemBytes);
                 e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<64, 1, true, 12>, &cfg);

@@ -1028,7 +1028,8 @@ def test_gemm_skinny_leaves_tall_products_and_long_steps_to_the_other_kernels(de
 
 
 @pytest.mark.parametrize("nh, nkv, d, T, window", [(14, 2, 64, 8, 0), (12, 2, 128, 3, 0), (7, 1, 64, 16, 0), (14, 2, 64, 1, 0),
-                                                   (4, 4, 64, 5, 1000)])
+                                                   (4, 4, 64, 5, 1000),
+                                                   (14, 2, 64, -2, 0), (12, 2, 128, -1, 0)])  # T < 0: -T long requests
 def test_decode_attention_merges_its_key_ranges_in_a_cluster(nh, nkv, d, T, window, device, request):
     """With the skinny products the decode kernel merges the partial results of its key ranges itself: the ranges of
     a (token, kv head) are the CTAs of a thread-block cluster, which adds them through its shared memory in the
@@ -1038,7 +1039,14 @@ def test_decode_attention_merges_its_key_ranges_in_a_cluster(nh, nkv, d, T, wind
     from ferrisinfer_b200.parts.base import PagedMeta
 
     page = 16
-    lengths = [4096, 2500, 4000, 3333, 4090, 2049, 3000, 3500, 2100, 2200, 2300, 2400, 2600, 2700, 2800, 2900][:T]
+    span = 4096
+    if T < 0:
+        # one or two requests of some 20,000 keys: block tables of 16,384 keys and more are cut into up to 16 ranges,
+        # a cluster larger than the portable 8
+        T, span = -T, 20000
+        lengths = [20000, 17001][:T]
+    else:
+        lengths = [4096, 2500, 4000, 3333, 4090, 2049, 3000, 3500, 2100, 2200, 2300, 2400, 2600, 2700, 2800, 2900][:T]
     seqs = [(kv, 1) for kv in lengths]
     case = AttentionCase(device, BF16, nh, nkv, d, page, seqs, seed=T + d, window=window)
     qkv, k, v, tables, ctx, _ = case.device_inputs()
@@ -1049,7 +1057,8 @@ def test_decode_attention_merges_its_key_ranges_in_a_cluster(nh, nkv, d, T, wind
     inv_freq = torch.tensor(plain.rotary_inverse_frequencies(d, d, 1e6).numpy(), device=device)
     meta = PagedMeta(block_tables=tables, slot_mapping=slots, page_size=page)
     scale = 1.0 / math.sqrt(d)
-    assert ops._lib().ferris_decode_cluster_splits(T, nkv, d, min(window, 4096) if window else 4096) > 1
+    ranges = ops._lib().ferris_decode_cluster_splits(T, nkv, d, min(window, span) if window else ctx.max_kv_len)
+    assert ranges > (8 if span > 16384 else 1)
     got = []
     for _ in range(3):
         out = torch.full((T, nh * d), float("nan"), dtype=BF16, device=device)

@@ -15,6 +15,8 @@
 // the kernel runs on to its end with a wrong result instead of hanging.
 #include <limits.h>
 #include <stdlib.h>
+
+#include <type_traits>
 #include <math.h>
 
 #include "common.cuh"
@@ -260,6 +262,142 @@ __device__ __forceinline__ void finish_rows(WarpState<D>& st) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same for a group of at most 8 query heads (the decode kernel's case at every published size), TRANSPOSED:
+// the 16 keys of a tile are the rows of the MMA and the query heads its 8 columns,
+//   S^T [16 keys x 8 heads] = K [16 x D] Q^T,        O^T [D x 8 heads] += V^T [D x 16 keys] P^T,
+// which halves the MMAs and the exponentials (no rows 8 to 15 that belong to no head).  A thread holds columns
+// 2 t and 2 t + 1 (t = lane % 4) of every row it has a share in: the running maximum and sum are per COLUMN, reduced
+// over the lanes that differ in lane / 4; P^T becomes the B operand of the second product through movmatrix.
+// ---------------------------------------------------------------------------------------------
+template <int D>
+struct WarpStateT {
+    uint32_t q[D / 16][2];  // B fragments of Q^T: head lane / 4, columns 16 ks + 2 t (+ 8)
+    float o[D / 16][4];     // O^T: rows 16 i + lane / 4 (+ 8), columns 2 t, 2 t + 1
+    float m[2], l[2];       // running maximum and (per-thread partial) sum of heads 2 t and 2 t + 1
+};
+
+template <int D>
+__device__ __forceinline__ void init_state(WarpStateT<D>& st) {
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) st.o[i][e] = 0.0f;
+    st.m[0] = st.m[1] = -INFINITY;
+    st.l[0] = st.l[1] = 0.0f;
+}
+
+// The query fragments of head lane / 4; ``row`` null: no such head (zeros).
+template <int D>
+__device__ __forceinline__ void load_q(WarpStateT<D>& st, const bf16* row) {
+    const int t = threadIdx.x & 3;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+        st.q[ks][0] = row ? *reinterpret_cast<const uint32_t*>(row + ks * 16 + 2 * t) : 0u;
+        st.q[ks][1] = row ? *reinterpret_cast<const uint32_t*>(row + ks * 16 + 2 * t + 8) : 0u;
+    }
+}
+
+// NT consecutive 16-key tiles of which the first ``valid`` exist (the same for the whole warp), keys from ``key0``;
+// the token sees keys lo..hi.  Layout of the tiles as for attend_block.
+template <int D, int NT, int CS, int VOFF>
+__device__ __forceinline__ void attend_block_t(WarpStateT<D>& st, uint32_t base, uint32_t tile_bytes, int key0, int valid,
+                                               int lo, int hi, float scale) {
+    const int lane = threadIdx.x & 31;
+    const int g = lane >> 2;
+    const int mi = lane >> 3, r8 = lane & 7;
+    float s[NT][4];
+#pragma unroll
+    for (int k = 0; k < NT; ++k)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[k][e] = 0.0f;
+    // S^T = K Q^T: A fragments of K by ldmatrix (keys 0-7 | 8-15 of the tile x columns 0-7 | 8-15 of the K step)
+#pragma unroll
+    for (int k = 0; k < NT; ++k) {
+        if (k >= valid) continue;
+        const uint32_t k_smem = base + k * tile_bytes;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            const int cc = 2 * ks + (mi >> 1);
+            uint32_t a[4];
+            ldmatrix_x4(a, k_smem + (cc >> 3) * CS + swizzle128((mi & 1) * 8 + r8, cc & 7));
+            mma_bf16_16816(s[k], a, st.q[ks][0], st.q[ks][1]);
+        }
+    }
+    // scale, mask (per key = per row), maximum per column
+    float mx[2] = {-INFINITY, -INFINITY};
+    const bool interior = valid == NT && key0 + 16 * NT - 1 <= hi && key0 >= lo;
+    if (interior) {
+#pragma unroll
+        for (int k = 0; k < NT; ++k)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                s[k][e] *= scale;
+                mx[e & 1] = fmaxf(mx[e & 1], s[k][e]);
+            }
+    } else {
+#pragma unroll
+        for (int k = 0; k < NT; ++k)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = key0 + 16 * k + g + ((e & 2) ? 8 : 0);
+                const bool ok = k < valid && key <= hi && key >= lo;
+                s[k][e] = ok ? s[k][e] * scale : -INFINITY;
+                mx[e & 1] = fmaxf(mx[e & 1], s[k][e]);
+            }
+    }
+    float corr[2], sub[2];
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 4));
+        mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 8));
+        mx[c] = fmaxf(mx[c], __shfl_xor_sync(0xffffffffu, mx[c], 16));
+        const float m_new = fmaxf(st.m[c], mx[c]);
+        sub[c] = m_new == -INFINITY ? 0.0f : m_new;
+        corr[c] = st.m[c] == -INFINITY ? 0.0f : expf(st.m[c] - sub[c]);
+        st.m[c] = m_new;
+        st.l[c] *= corr[c];
+    }
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+        st.o[i][0] *= corr[0];
+        st.o[i][1] *= corr[1];
+        st.o[i][2] *= corr[0];
+        st.o[i][3] *= corr[1];
+    }
+#pragma unroll
+    for (int k = 0; k < NT; ++k) {
+        if (k >= valid) continue;
+        const float e0 = expf(s[k][0] - sub[0]), e1 = expf(s[k][1] - sub[1]);
+        const float e2 = expf(s[k][2] - sub[0]), e3 = expf(s[k][3] - sub[1]);
+        st.l[0] += e0 + e2;
+        st.l[1] += e1 + e3;
+        // P^T as the B operand: keys 2 t, 2 t + 1 (+ 8) of head lane / 4
+        const uint32_t b0 = movmatrix_trans(pack_bf16(e0, e1));
+        const uint32_t b1 = movmatrix_trans(pack_bf16(e2, e3));
+        const uint32_t v_smem = base + k * tile_bytes + VOFF;
+        // A fragments of V^T by transposing ldmatrix: columns 16 i .. of the head x the tile's 16 keys
+#pragma unroll
+        for (int i = 0; i < D / 16; ++i) {
+            const int cc = 2 * i + (mi & 1);
+            uint32_t a[4];
+            ldmatrix_x4_trans(a, v_smem + (cc >> 3) * CS + swizzle128((mi >> 1) * 8 + r8, cc & 7));
+            mma_bf16_16816(st.o[i], a, b0, b1);
+        }
+    }
+}
+
+// The per-thread partial sums of a column, over the eight threads that share it.
+template <int D>
+__device__ __forceinline__ void finish_rows(WarpStateT<D>& st) {
+#pragma unroll
+    for (int c = 0; c < 2; ++c) {
+        st.l[c] += __shfl_xor_sync(0xffffffffu, st.l[c], 4);
+        st.l[c] += __shfl_xor_sync(0xffffffffu, st.l[c], 8);
+        st.l[c] += __shfl_xor_sync(0xffffffffu, st.l[c], 16);
+    }
+}
+
 // The first 1024-byte boundary of the shared address space at or after p (swizzled TMA tiles need it).
 __device__ __forceinline__ uint8_t* align1024(uint8_t* p) { return p + ((1024u - (smem_u32(p) & 1023u)) & 1023u); }
 
@@ -321,6 +459,24 @@ __device__ __forceinline__ void rotate_q(WarpState<D>& st, const float2* cos_sin
     }
 }
 
+// The same for the transposed fragments (head lane / 4 only).
+template <int D>
+__device__ __forceinline__ void rotate_q(WarpStateT<D>& st, const float2* cos_sin) {
+    constexpr int HS = D / 32;
+    const int t = threadIdx.x & 3;
+#pragma unroll
+    for (int ks = 0; ks < HS; ++ks) {
+#pragma unroll
+        for (int e2 = 0; e2 < 2; ++e2) {
+            const int c = 16 * ks + 2 * t + 8 * e2;
+            const float2 a0 = cos_sin[c], a1 = cos_sin[c + 1];
+            const float2 lo = unpack_bf16(st.q[ks][e2]), hi = unpack_bf16(st.q[ks + HS][e2]);
+            st.q[ks][e2] = pack_bf16(lo.x * a0.x - hi.x * a0.y, lo.y * a1.x - hi.y * a1.y);
+            st.q[ks + HS][e2] = pack_bf16(hi.x * a0.x + lo.x * a0.y, hi.y * a1.x + lo.y * a1.y);
+        }
+    }
+}
+
 // =============================================================================================
 // Decode: one CTA per (split, kv head, token).  Its NW warps take the 16-key tiles of the
 // split's key range in turn, each with a pipeline of its own; their results are merged through
@@ -331,10 +487,11 @@ __device__ __forceinline__ void rotate_q(WarpState<D>& st, const float2* cos_sin
 // the 64-column box of K and the box of V of the same 16 keys and columns (4 KB instead of two copies of 2 KB; a
 // copy costs the TMA unit ~30 ns whatever it brings, and a CTA of a long context issues hundreds).  A tile then lies
 // in shared memory as (K box, V box) per 64 columns instead of all K boxes followed by all V boxes.
-template <int D, int STAGES, bool PAIR, int NW>
+// TR: the group has at most 8 query heads and the warps work on the transposed products (attend_block_t).
+template <int D, int STAGES, bool PAIR, int NW, bool TR>
 __global__ void __launch_bounds__(NW * 32)
     decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                            const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
+                            const bf16* q, int ldq, bf16* __restrict__ out, int ldo,
                             float* __restrict__ part_o, float* __restrict__ part_ml, const int* __restrict__ block_tables,
                             int max_blocks, const int* __restrict__ token_seq, const int* __restrict__ positions,
                             const int* __restrict__ token_list, int nh, int nkv, int page_size, int window, float scale,
@@ -399,13 +556,17 @@ __global__ void __launch_bounds__(NW * 32)
     const int n_blocks = t_end > t_begin ? (t_end - t_begin + NT - 1) / NT : 0;
     const int my_count = n_blocks > warp ? (n_blocks - warp + NW - 1) / NW : 0;
 
-    WarpState<D> st;
+    typename std::conditional<TR, WarpStateT<D>, WarpState<D>>::type st;
     init_state(st);
     RowLimits lim;
     auto load_queries = [&]() {
         const int g = lane >> 2;
         const bf16* qrow = q + (size_t)tok * ldq + (size_t)hk * G * D;
-        load_q(st, g < G ? qrow + (size_t)g * D : nullptr, g + 8 < G ? qrow + (size_t)(g + 8) * D : nullptr);
+        if constexpr (TR) {
+            load_q(st, g < G ? qrow + (size_t)g * D : nullptr);
+        } else {
+            load_q(st, g < G ? qrow + (size_t)g * D : nullptr, g + 8 < G ? qrow + (size_t)(g + 8) * D : nullptr);
+        }
         if (rope.inv_freq) rotate_q<D>(st, cos_sin);
         lim.hi[0] = g < G ? P : -1;
         lim.hi[1] = g + 8 < G ? P : -1;
@@ -516,7 +677,9 @@ __global__ void __launch_bounds__(NW * 32)
             fence_proxy_async();
             __syncwarp();
         }
-        if (tile0 + NT <= t_end) {
+        if constexpr (TR) {
+            attend_block_t<D, NT, CS, VOFF>(st, base, TILE_BYTES, tile0 * TILE_KEYS, min(NT, t_end - tile0), lo, P, scale);
+        } else if (tile0 + NT <= t_end) {
             attend_block<D, NT, CS, VOFF>(st, base, TILE_BYTES, tile0 * TILE_KEYS, lim, scale);
         } else {
             for (int k = 0; tile0 + k < t_end; ++k)
@@ -533,7 +696,24 @@ __global__ void __launch_bounds__(NW * 32)
     __syncthreads();
     FERRIS_TL_MARK(tl_mark, 3);
     float* merge = reinterpret_cast<float*>(smem);  // [NW][16][D + 2]
-    {
+    if constexpr (TR) {
+        // a thread holds heads 2 t and 2 t + 1: of each, the output columns 16 i + lane / 4 (+ 8)
+        const int g = lane >> 2, t = lane & 3;
+        float* mine = merge + (size_t)warp * 16 * (D + 2);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            float* r = mine + (2 * t + c) * (D + 2);
+            if (g == 0) {
+                r[0] = st.m[c];
+                r[1] = st.l[c];
+            }
+#pragma unroll
+            for (int i = 0; i < D / 16; ++i) {
+                r[2 + 16 * i + g] = st.o[i][c];
+                r[2 + 16 * i + g + 8] = st.o[i][2 + c];
+            }
+        }
+    } else {
         const int g = lane >> 2, t = lane & 3;
         float* mine = merge + (size_t)warp * 16 * (D + 2);
 #pragma unroll
@@ -650,7 +830,7 @@ __global__ void __launch_bounds__(NW * 32)
 
 // Merge of the splits: out = sum_s O_s e^{m_s - M} / sum_s l_s e^{m_s - M}.  One block per (token, head).
 template <int D>
-__global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+__global__ void decode_merge_kernel(const float* part_o, const float* part_ml,
                                     bf16* __restrict__ out, int ldo, const int* __restrict__ token_list, int nh,
                                     int splits) {
     pdl_wait();
@@ -683,7 +863,7 @@ constexpr int PF_STAGE_TILES = 4;  // 64 keys per stage
 template <int D, int STAGES>
 __global__ void __launch_bounds__((WARPS + 1) * 32)
     prefill_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                             const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
+                             const bf16* q, int ldq, bf16* __restrict__ out, int ldo,
                              const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ seq_q_start,
                              const int* __restrict__ seq_start_pos, int nh, int nkv, int page_size, int window,
                              float scale, int skip_single, int* status) {
@@ -888,7 +1068,7 @@ constexpr int t5_threads(int groups) { return (T5_GROUP_WARPS * groups + 2) * 32
 template <int D, int GROUPS, int STAGES>
 __global__ void __launch_bounds__(t5_threads(GROUPS), 1)
     prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-                                 const bf16* __restrict__ q, int ldq, bf16* __restrict__ out, int ldo,
+                                 const bf16* q, int ldq, bf16* __restrict__ out, int ldo,
                                  const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ seq_q_start,
                                  const int* __restrict__ seq_start_pos, int nh, int nkv, int page_size, int window,
                                  float scale, int skip_single, int* status) {
@@ -1352,16 +1532,23 @@ FERRIS_API long long ferris_decode_attention_scratch_floats(int tokens, int nh, 
     return (long long)tokens * nh * splits * (d + 2);
 }
 
-// The decode kernel's shape, warps * 10 + stages of 16 KB per warp, by the blocks of keys (64 keys of head size 64, 32
-// of head size 128) that a CTA may get.  A warp works a block off in about a microsecond, one block after the other, so
-// a CTA with many blocks wants many warps (12 warps with one stage each hold as many bytes in flight as 4 warps with
-// three); a CTA with few blocks wants few, because every warp adds to the merge at the end.  Measured per decode
-// step at the 0.5B sizes (4 x 3 / 8 x 1 / 12 x 1 warps x stages): batch 8 of 512 keys 0.683 / 0.691 / 0.709 ms; batch 1
-// of 4,096 keys (9 blocks) 0.783 / 0.748 / 0.778; batch 8 (11 blocks) 0.798 / 0.792 / 0.784; batch 32 (33 blocks)
-// 1.498 / 1.477 / 1.461; batch 64 (65 blocks) 1.887 / 1.866 / 1.849; batch 8 of 16,384 keys 1.096 / 1.098 / 1.055.
-// `blocks` comes from the width of the block tables, which is up to twice what the requests hold.  With at most 64
-// CTAs (batches of 1 to 4 at 8 key ranges) eight warps were the fastest at every length measured.
-static int decode_shape(int blocks, int ctas) { return blocks <= 4 ? 43 : ((blocks < 10 || ctas <= 64) ? 81 : 121); }
+// The decode kernel's shape, warps * 10 + stages of 16 KB per warp.  A warp works a block of keys (64 of head size 64,
+// 32 of head size 128) off in a dependent chain, one block after the other, so a CTA with many blocks wants many warps
+// (8 or 12 warps with one stage each hold as many bytes in flight as 4 warps with three); every warp adds to the merge
+// at the end.
+// Groups of at most 8 heads (the transposed products, half the work a block): eight warps with one stage each were the
+// fastest or within half a percent of it wherever measured (ms a decode step at the 0.5B sizes, 4 x 3 / 8 x 1 / 12 x 1
+// warps x stages): batch 1 of 4,096 keys . / 0.702 / 0.738; batch 4 0.727 / 0.692 / 0.710; batch 8 0.771 / 0.744 /
+// 0.741; batch 16 0.963 / 0.924 / 0.961; batch 32 1.491 / 1.437 / 1.433; batch 64 1.847 / 1.750 / 1.781; batch 8 of
+// 512 keys 0.657 / 0.653 / 0.675; batch 8 of 16,384 keys 1.050 / 0.989 / 0.986.
+// Larger groups (16 rows a warp): by the blocks a CTA may get (from the width of the block tables, which is up to
+// twice what the requests hold); measured with the 16-row products at a group of 7: batch 8 of 512 keys 0.683 /
+// 0.691 / 0.709; batch 1 of 4,096 keys 0.783 / 0.748 / 0.778; batch 8 0.798 / 0.792 / 0.784; batch 32 1.498 / 1.477
+// / 1.461; batch 64 1.887 / 1.866 / 1.849; batch 8 of 16,384 keys 1.096 / 1.098 / 1.055.
+static int decode_shape(int group, int blocks, int ctas) {
+    if (group <= 8) return 81;
+    return blocks <= 4 ? 43 : ((blocks < 10 || ctas <= 64) ? 81 : 121);
+}
 
 static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, const void* k_cache, const void* v_cache,
                                  long long cache_pages, const int* block_tables, int max_blocks, const int* token_seq,
@@ -1400,7 +1587,7 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
     if (window > 0 && window + TILE_KEYS < keys) keys = window + TILE_KEYS;
     const int tiles_per_range = (int)(((keys + TILE_KEYS - 1) / TILE_KEYS + splits - 1) / splits);
     const int tiles_per_block = d == 64 ? 4 : 2;
-    const int shape = decode_shape((tiles_per_range + tiles_per_block - 1) / tiles_per_block, splits * nkv * tokens);
+    const int shape = decode_shape(nh / nkv, (tiles_per_range + tiles_per_block - 1) / tiles_per_block, splits * nkv * tokens);
     const int nw = shape / 10, st = shape % 10;
     // behind the stages: what the key ranges of a cluster send each other, [splits][G][2] + [splits][share] fp32
     const int G = nh / nkv;
@@ -1436,10 +1623,15 @@ static int decode_attention_impl(const void* q, int ldq, void* out, int ldo, con
                                   max_blocks, token_seq, positions, token_list, nh, nkv, page_size, window, scale, splits,
                                   rope, cluster, status);
     };
-#define FERRIS_DECODE_LAUNCH_AS(DD, PP, NWW, STT)                                                        \
-    do {                                                                                                 \
-        if ((rc = set_smem(decode_attention_kernel<DD, STT, PP, NWW>, smem)) != FERRIS_OK) return rc;   \
-        e = launch(decode_attention_kernel<DD, STT, PP, NWW>);                                           \
+#define FERRIS_DECODE_LAUNCH_AS(DD, PP, NWW, STT)                                                                \
+    do {                                                                                                         \
+        if (G <= 8) {                                                                                            \
+            if ((rc = set_smem(decode_attention_kernel<DD, STT, PP, NWW, true>, smem)) != FERRIS_OK) return rc;  \
+            e = launch(decode_attention_kernel<DD, STT, PP, NWW, true>);                                         \
+        } else {                                                                                                 \
+            if ((rc = set_smem(decode_attention_kernel<DD, STT, PP, NWW, false>, smem)) != FERRIS_OK) return rc; \
+            e = launch(decode_attention_kernel<DD, STT, PP, NWW, false>);                                        \
+        }                                                                                                        \
     } while (0)
 #define FERRIS_DECODE_LAUNCH(DD, PP)                              \
     do {                                                          \
@@ -1547,15 +1739,15 @@ FERRIS_API int ferris_decode_cluster_splits(int tokens, int nkv, int d, int max_
             cudaError_t e = cudaSuccess;
             cfg.dynamicSmemBytes = (size_t)12 * 16384 + 1024 + (size_t)(MAX_CLUSTER * 2 * 16 + 16 * d + MAX_CLUSTER) * 4;
             if (sp > 8) {
-                if (d == 64) cudaFuncSetAttribute(decode_attention_kernel<64, 1, true, 12>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
-                else cudaFuncSetAttribute(decode_attention_kernel<128, 1, true, 12>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+                if (d == 64) cudaFuncSetAttribute(decode_attention_kernel<64, 1, true, 12, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+                else cudaFuncSetAttribute(decode_attention_kernel<128, 1, true, 12, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
             }
             if (d == 64) {
-                set_smem(decode_attention_kernel<64, 1, true, 12>, cfg.dynamicSmemBytes);
-                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<64, 1, true, 12>, &cfg);
+                set_smem(decode_attention_kernel<64, 1, true, 12, true>, cfg.dynamicSmemBytes);
+                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<64, 1, true, 12, true>, &cfg);
             } else {
-                set_smem(decode_attention_kernel<128, 1, true, 12>, cfg.dynamicSmemBytes);
-                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<128, 1, true, 12>, &cfg);
+                set_smem(decode_attention_kernel<128, 1, true, 12, true>, cfg.dynamicSmemBytes);
+                e = cudaOccupancyMaxActiveClusters(&clusters, decode_attention_kernel<128, 1, true, 12, true>, &cfg);
             }
             if (e == cudaSuccess && clusters > 0) have = clusters;
             else cudaGetLastError();

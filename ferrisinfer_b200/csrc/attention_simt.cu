@@ -22,8 +22,7 @@ constexpr int MAX_PER_LANE = 8;  // head size up to 256
 
 template <typename T>
 __global__ void __launch_bounds__(ATT_THREADS)
-    paged_attention_simt_kernel(const T* __restrict__ q, int ldq, T* __restrict__ out, int ldo,
-                                const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+    paged_attention_simt_kernel(const T* q, int ldq, T* __restrict__ out, int ldo, const T* k_cache, const T* v_cache,
                                 const int* __restrict__ block_tables, int max_blocks,
                                 const int* __restrict__ token_seq, const int* __restrict__ positions, int nh,
                                 int nkv, int d, int page_size, int window, float scale,

@@ -50,6 +50,11 @@ typedef __nv_bfloat16 bf16;
 // CTA of this grid has called it (or exited), so CTAs that are not resident yet are never starved.
 // Launched without the attribute (FERRIS_PDL=0), both are no-ops.
 // ---------------------------------------------------------------------------------------------
+// What a kernel reads after the wait from the launch before it must not come through a `const T* __restrict__`
+// parameter: the compiler takes such memory for unchanging during the kernel, may load it through the non-coherent
+// path and may move the load above the wait (the "memory" clobber does not hold back a load it believes invariant),
+// and then reads what the buffer held a launch or a step ago.  Only weights, tables and the step's metadata are
+// declared that way; activations, caches, logits and partial results are plain pointers.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -8,7 +8,7 @@
 // An id outside [0, vocab) writes zeros and sets *status to 1 + the offending token index.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int* ids,
                                     float* __restrict__ out, int hidden, int vocab, int* status) {
     FERRIS_TL_ENTRY();
     pdl_wait();
@@ -50,7 +50,7 @@ FERRIS_API int ferris_embed_gather(const void* table, int dtype, const int* ids,
 // rows whose logits are wanted).
 // ---------------------------------------------------------------------------------------------
 template <typename TOut>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w,
+__global__ void rmsnorm_kernel(const float* x, const float* __restrict__ w,
                                const int* __restrict__ row_index, TOut* __restrict__ out, int hidden,
                                float eps) {
     __shared__ float scratch[33];
@@ -87,7 +87,7 @@ __device__ __forceinline__ void store4(bf16* o, float a, float b, float c, float
 // The same norm, one WARP per row: the row (up to 4096 floats, a multiple of 4) is read once with 16-byte loads
 // and stays in registers between the sum of squares and the scaling.  For long steps.
 template <typename TOut, int VEC>  // VEC float4 per lane: hidden <= 128 * VEC
-__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* __restrict__ x, const float* __restrict__ w,
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(const float* x, const float* __restrict__ w,
                                                            const int* __restrict__ row_index, TOut* __restrict__ out,
                                                            int rows, int hidden, float eps) {
     FERRIS_TL_ENTRY();
@@ -167,7 +167,7 @@ FERRIS_API int ferris_rmsnorm(const float* x, const float* w, const int* row_ind
 // gate_up holds gate in columns [0, I) and up in [I, 2I) of each row.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int tokens, int inter) {
+__global__ void swiglu_kernel(const T* gate_up, T* __restrict__ out, int tokens, int inter) {
     pdl_wait();
     pdl_launch_dependents();
     const size_t n = (size_t)tokens * inter;

@@ -15,7 +15,7 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
 // MODE 0: out = acc (+bias), stored as TOut.  MODE 1: out(float) += acc (+bias).
 template <typename TIn, typename TOut, int MODE>
-__global__ void __launch_bounds__(256) gemm_simt_kernel(const TIn* __restrict__ x, const TIn* __restrict__ w,
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const TIn* x, const TIn* __restrict__ w,
                                                         const float* __restrict__ bias, TOut* __restrict__ out,
                                                         int M, int N, int K, int ldx, int ldw, int ldo) {
     __shared__ float xs[BK][BM + 1];

@@ -519,7 +519,7 @@ __global__ void __launch_bounds__(THREADS)
 // token, its threads over the tiles.
 constexpr int AM_THREADS = 256;
 __global__ void __launch_bounds__(AM_THREADS)
-    argmax_merge_kernel(const float4* __restrict__ part, int tiles, int T, int* __restrict__ out_token,
+    argmax_merge_kernel(const float4* part, int tiles, int T, int* __restrict__ out_token,
                         float* __restrict__ out_prob) {
     __shared__ uint32_t s_hi[AM_THREADS / 32], s_lo[AM_THREADS / 32];
     __shared__ float s_m[AM_THREADS / 32], s_sum[AM_THREADS / 32];

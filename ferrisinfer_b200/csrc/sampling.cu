@@ -457,7 +457,7 @@ __device__ __forceinline__ float block_max_f32(float v, float* scratch) {
 }
 
 __global__ void __launch_bounds__(THREADS)
-    sample_kernel(const float* __restrict__ logits, int ldl, int V, const float* __restrict__ temperature,
+    sample_kernel(const float* logits, int ldl, int V, const float* __restrict__ temperature,
                   const int* __restrict__ top_k, const float* __restrict__ top_p, const int* __restrict__ slots,
                   u64* __restrict__ rng_states, int* __restrict__ out_token, float* __restrict__ out_prob) {
     extern __shared__ __align__(16) unsigned char raw[];
@@ -598,7 +598,7 @@ struct OnlineMax {
 };
 
 __global__ void __launch_bounds__(GREEDY_THREADS)
-    greedy_kernel(const float* __restrict__ logits, int ldl, int V, int* __restrict__ out_token,
+    greedy_kernel(const float* logits, int ldl, int V, int* __restrict__ out_token,
                   float* __restrict__ out_prob) {
     __shared__ u64 red[32];
     __shared__ float fred[33];

@@ -553,7 +553,8 @@ ATT_TOL = {F32: dict(atol=2e-5, rtol=1e-4), BF16: dict(atol=2e-2, rtol=2e-2)}
 @pytest.mark.parametrize("impl", ["simt", "dispatch"])
 @pytest.mark.parametrize("dtype", [F32, BF16])
 @pytest.mark.parametrize("nh, nkv, d, page", [(4, 2, 16, 4), (3, 1, 32, 8), (5, 5, 48, 16), (14, 2, 64, 16),
-                                              (12, 2, 128, 16), (7, 1, 64, 16), (2, 1, 256, 32), (6, 2, 80, 16)])
+                                              (12, 2, 128, 16), (7, 1, 64, 16), (2, 1, 256, 32), (6, 2, 80, 16),
+                                              (12, 1, 64, 16), (16, 1, 128, 16)])  # groups of more than 8 heads
 def test_attention_mixed_batch(nh, nkv, d, page, dtype, impl, device):
     """Whole prompts, portions and single decoded tokens in one batch, lengths at and around page edges."""
     seqs = [(1, 1), (page, page), (page + 1, 1), (3 * page, 1), (3 * page - 1, 2), (77, 77), (130, 17), (200, 1), (5, 3)]
@@ -613,7 +614,8 @@ def test_attention_long_context_decode_batch(impl, device):
     assert torch.allclose(got, want, **ATT_TOL[BF16]), (got - want).abs().max()
 
 
-@pytest.mark.parametrize("nh, nkv, d, window", [(14, 2, 64, 0), (12, 2, 128, 0), (4, 4, 64, 40), (7, 1, 64, 0)])
+@pytest.mark.parametrize("nh, nkv, d, window", [(14, 2, 64, 0), (12, 2, 128, 0), (4, 4, 64, 40), (7, 1, 64, 0),
+                                                (24, 2, 64, 0), (16, 1, 128, 0)])  # groups of 12 and 16: 16-row products
 def test_attention_step_of_single_tokens_rotates_and_writes_on_its_way(nh, nkv, d, window, device):
     """The one-kernel path of a decode step against the two-kernel path: same output, same cache."""
     from ferrisinfer_b200.kernels import ops
@@ -1028,7 +1030,7 @@ def test_gemm_skinny_leaves_tall_products_and_long_steps_to_the_other_kernels(de
 
 
 @pytest.mark.parametrize("nh, nkv, d, T, window", [(14, 2, 64, 8, 0), (12, 2, 128, 3, 0), (7, 1, 64, 16, 0), (14, 2, 64, 1, 0),
-                                                   (4, 4, 64, 5, 1000),
+                                                   (4, 4, 64, 5, 1000), (24, 2, 64, 6, 0), (16, 1, 128, 9, 0),
                                                    (14, 2, 64, -2, 0), (12, 2, 128, -1, 0)])  # T < 0: -T long requests
 def test_decode_attention_merges_its_key_ranges_in_a_cluster(nh, nkv, d, T, window, device, request):
     """With the skinny products the decode kernel merges the partial results of its key ranges itself: the ranges of

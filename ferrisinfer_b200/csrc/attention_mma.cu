@@ -1540,7 +1540,10 @@ FERRIS_API long long ferris_decode_attention_scratch_floats(int tokens, int nh, 
 // fastest or within half a percent of it wherever measured (ms a decode step at the 0.5B sizes, 4 x 3 / 8 x 1 / 12 x 1
 // warps x stages): batch 1 of 4,096 keys . / 0.702 / 0.738; batch 4 0.727 / 0.692 / 0.710; batch 8 0.771 / 0.744 /
 // 0.741; batch 16 0.963 / 0.924 / 0.961; batch 32 1.491 / 1.437 / 1.433; batch 64 1.847 / 1.750 / 1.781; batch 8 of
-// 512 keys 0.657 / 0.653 / 0.675; batch 8 of 16,384 keys 1.050 / 0.989 / 0.986.
+// 512 keys 0.657 / 0.653 / 0.675; batch 8 of 16,384 keys 1.050 / 0.989 / 0.986.  Stages of 96 keys instead of 64 (eight
+// warps then hold 192 KB, and the tiles of a key range divide more evenly among them) were slower at every batch but
+// one (batch 1 / 4 / 8 / 16 / 64: 0.747 / 0.721 / 0.741 / 0.965 / 1.794 against 0.703 / 0.692 / 0.744 / 0.924 / 1.750):
+// a CTA of 129 KB shares its SM with the launches before and after it, one of 197 KB does not.
 // Larger groups (16 rows a warp): by the blocks a CTA may get (from the width of the block tables, which is up to
 // twice what the requests hold); measured with the 16-row products at a group of 7: batch 8 of 512 keys 0.683 /
 // 0.691 / 0.709; batch 1 of 4,096 keys 0.783 / 0.748 / 0.778; batch 8 0.798 / 0.792 / 0.784; batch 32 1.498 / 1.477

@@ -606,7 +606,7 @@ __global__ void __launch_bounds__(NW * 32)
     if (lane == 0)
         for (int i = 0; i < STAGES && i < my_count; ++i) issue(i);
     // marks of the timeline build: thread 0 of the CTA of the last key range of token 0, kv head 0
-    const bool tl_mark = threadIdx.x == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0;
+    [[maybe_unused]] const bool tl_mark = threadIdx.x == 0 && blockIdx.x == gridDim.x - 1 && blockIdx.y == 0 && blockIdx.z == 0;
     // the warp whose tiles include the token's own position (in the CTA of the last key range) will rotate k and copy v
     const int own_block = (last_tile >= t_begin && last_tile < t_end) ? (last_tile - t_begin) / NT : -1;
     const bool owns_token = patches && own_block >= 0 && own_block % NW == warp;
@@ -1254,7 +1254,7 @@ __global__ void __launch_bounds__(t5_threads(GROUPS), 1)
         for (int j = 0; j < D / 2; ++j) o[j] = 0.0f;
         const int n_own = n_kb > g ? (n_kb - g + GROUPS - 1) / GROUPS : 0;  // this group's key blocks: g, g + GROUPS, ...
         // timeline build: where the first thread of the heaviest CTA spends its cycles
-        const bool tl_probe = threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+        [[maybe_unused]] const bool tl_probe = threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
         long long t_wait_s = 0, t_max = 0, t_fold = 0, t_exp = 0, c0 = FERRIS_TL_CLOCK(), c1;
         for (int j = 0; j < n_own; ++j) {
             const int i = j * GROUPS + g;

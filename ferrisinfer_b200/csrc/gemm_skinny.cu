@@ -205,7 +205,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
 
     pdl_wait();
     FERRIS_TL_BEGIN();
-    const bool tl_mark = threadIdx.x == 0 && blockIdx.x == 0;
+    [[maybe_unused]] const bool tl_mark = threadIdx.x == 0 && blockIdx.x == 0;
     FERRIS_TL_MARK(tl_mark, 9);
     if (p.mode == SK_ACCUM_F32) {
 #pragma unroll
@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(SK_THREADS, 1)
     // stage and phase of this warp's next group, kept without a division in the loop
     int s = warp % p.stages, phase = (warp / p.stages) & 1;
     const int s_step = SK_WARPS % p.stages, phase_step = (SK_WARPS / p.stages) & 1;
-    long long waited = 0, began = FERRIS_TL_CLOCK();  // timeline build: cycles this warp waits for weights
+    [[maybe_unused]] long long waited = 0, began = FERRIS_TL_CLOCK();  // timeline build: cycles this warp waits for weights
     for (int i = 0; i < mine; ++i) {
         const int g = warp + SK_WARPS * i;
         const long long c0 = FERRIS_TL_CLOCK();

@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(THREADS)
     pdl_wait();
     FERRIS_TL_BEGIN();
     // marks of the timeline build: the first epilogue thread of CTA (0, 0, 0)
-    const bool tl_mark = threadIdx.x == 64 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    [[maybe_unused]] const bool tl_mark = threadIdx.x == 64 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
     FERRIS_TL_MARK(tl_mark, 9);  // this thread is past the wait
 
     if (p.norm_h && warp >= 2) {
@@ -946,7 +946,7 @@ __global__ void __launch_bounds__(PT_THREADS)
             int it = 0, local = 0;
             bool ok = true;
             long long wait_load = 0, wait_drain = 0, c0 = FERRIS_TL_CLOCK();  // timeline build: where the MMA thread waits
-            const long long began = c0;
+            [[maybe_unused]] const long long began = c0;
             for (int tile = pair; tile < tiles && ok; tile += pairs, ++local) {
                 const int buf = local & 1;
                 c0 = FERRIS_TL_CLOCK();

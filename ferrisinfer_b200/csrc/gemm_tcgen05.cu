@@ -1621,9 +1621,13 @@ FERRIS_API int ferris_gemm_argmax_tcgen05(const void* x, const void* w, int* out
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages > p.kblocks) stages = p.kblocks;
     const int tiles = (N + BLOCK_N - 1) / BLOCK_N;
-    if (tiles >= 4 * g_sms) {  // as the product that stores the logits: two CTAs share an SM
-        const int fit = (227 * 1024 / 2 - 3072 - 8192) / stage_bytes;
-        if (fit >= 4 && stages > fit) stages = fit;
+    if (tiles >= 4 * g_sms) {
+        // Many tiles and no K split: shallow rings, so that CTAs share an SM and one streams weights while another's
+        // set-up or epilogue runs.  Three to an SM here (three stages of 18 KB at 16 rows; the step of 8 rows at the
+        // 0.5B sizes: 0.732-0.734 ms against 0.739 with two and 0.735 with four), where the product that stores the
+        // logits is best with two (1.742 / 1.745 / 1.752 ms at 64 rows with two / three / four).
+        const int fit = (227 * 1024 / 3 - 3072 - 8192) / stage_bytes;
+        if (fit >= 2 && stages > fit) stages = fit;
     }
     p.stages = stages;
     const size_t smem = (size_t)stages * stage_bytes + 1024;

@@ -278,16 +278,18 @@ def gemm_argmax_scratch_floats(rows: int, outputs: int) -> int:
     return 4 * rows * ((outputs + 127) // 128)
 
 
-GREEDY_HEAD_MAX_ROWS = 16
+GREEDY_HEAD_MAX_ROWS = 96
 
 
 def greedy_head(y, w, out_token, out_prob, workspace):
     """The output head and greedy sampling of the rows ``y`` [n, H] in one: out_token int32 [n], out_prob fp32 [n].
-    bf16 rows, at most 16: the product that stores no logits; anything else: logits into the workspace, then the
+    bf16 rows, at most 96: the product that stores no logits; anything else: logits into the workspace, then the
     sampling kernel's greedy rows.  The same tokens and probabilities either way (up to the rounding of the sums).
     (The product's epilogue reduces over the 128 outputs of a tile, which lie across the lanes of its warps, with
-    three warp reductions a token; measured inside the decode step of the 0.5B sizes, that costs the product 5 us
-    at 8 rows and 32 us at 64, against 19 and 30 us for the sampling kernel and the stored logits.)"""
+    three warp reductions a token.  With three of its CTAs to an SM that hides behind the weights' way in: measured
+    inside the decode step of the 0.5B sizes against stored logits and the sampling kernel, ms a step at 17 / 24 / 48 /
+    64 / 96 / 128 rows: 1.212 / 1.260 / 1.633 / 1.733 / 2.382 / 2.492 against 1.227 / 1.276 / 1.638 / 1.743 / 2.420 /
+    2.487.)"""
     n, V = y.shape[0], w.shape[0]
     if n <= GREEDY_HEAD_MAX_ROWS and tensor_core_gemm_takes(y, w):
         scratch = workspace.get("argmax_tiles", (gemm_argmax_scratch_floats(n, V),), torch.float32)

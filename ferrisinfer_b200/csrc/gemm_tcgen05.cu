@@ -102,7 +102,10 @@ __device__ __forceinline__ void write_out(const Params& p, int t, int n, float a
     }
 }
 
-template <int MODE>
+// WIDE: the K split's cluster may have up to 16 CTAs (beyond the portable size) instead of 8.  A kernel of its own:
+// the narrow kernel's sum of eight peers is sensitive to every change (the other eight reads merely predicated, or
+// in a loop that it jumps over, cost a decode step of 24 to 64 rows 13 to 37 us).
+template <int MODE, bool WIDE = false>
 __global__ void __launch_bounds__(THREADS)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                         const Params p) {
@@ -487,15 +490,16 @@ __global__ void __launch_bounds__(THREADS)
                 const int t = t0 + tl;
                 if (t >= p.T || n >= p.N) continue;
                 const uint32_t addr = part + (uint32_t)((tl * BLOCK_N + quarter * 32 + lane) * 4);
-                float va[8], vb[8];
+                constexpr int PEERS = WIDE ? 16 : 8;
+                float va[PEERS], vb[PEERS];
 #pragma unroll
-                for (int s = 0; s < 8; ++s) {
+                for (int s = 0; s < PEERS; ++s) {
                     va[s] = s < p.splits ? ld_peer_shared_f32(addr, s) : 0.0f;
                     if (ACCS == 2) vb[s] = s < p.splits ? ld_peer_shared_f32(addr + (uint32_t)(p.bt * BLOCK_N * 4), s) : 0.0f;
                 }
                 float a = 0.0f, b = 0.0f;
 #pragma unroll
-                for (int s = 0; s < 8; ++s) {
+                for (int s = 0; s < PEERS; ++s) {
                     a += va[s];
                     if (ACCS == 2) b += vb[s];
                 }
@@ -1172,13 +1176,22 @@ int launch_pair(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap&
 
 // How many clusters of `size` CTAs of the short-step kernel (one CTA per SM) the GPU holds at once: the CTAs of a
 // cluster share a GPC, so the answer is less than SMs / size where the size does not divide a GPC's SMs.
+int g_max_split = -1;
+static int max_split() {
+    if (g_max_split < 0) {
+        const char* v = getenv("FERRIS_GEMM_MAX_SPLIT");
+        const int n = v ? atoi(v) : 16;
+        g_max_split = (n >= 1 && n <= 16) ? n : 16;
+    }
+    return g_max_split;
+}
 int g_active_clusters[17] = {};
 int active_clusters(int size) {
     if (size < 1 || size > 16) return 0;
     if (size == 1) return g_sms;
     if (g_active_clusters[size] != 0) return g_active_clusters[size] > 0 ? g_active_clusters[size] : g_sms / size;
     g_active_clusters[size] = -1;  // unknown: assume perfect packing
-    auto kernel = gemm_tcgen05_kernel<ACCUM_F32>;
+    auto kernel = gemm_tcgen05_kernel<ACCUM_F32, true>;
     const int smem = 200 * 1024;
     if (ferris_allow_dynamic_smem((const void*)kernel, smem) != FERRIS_OK) {  // only ever raises the allowance
         cudaGetLastError();
@@ -1227,7 +1240,25 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 g
     int rc = ferris_allow_dynamic_smem((const void*)gemm_tcgen05_kernel<MODE>, smem);
     if (rc != FERRIS_OK) return rc;
     cudaError_t e = cudaSuccess;
-    if (cluster_z > 1)
+    if (cluster_z > 8) {
+        // beyond the portable size: the kernel that sums sixteen peers (one accumulator only), allowed once
+        if constexpr (MODE == STORE_BF16 || MODE == STORE_F32 || MODE == ACCUM_F32) {
+            rc = ferris_allow_dynamic_smem((const void*)gemm_tcgen05_kernel<MODE, true>, smem);
+            if (rc != FERRIS_OK) return rc;
+            static bool allowed = false;
+            if (!allowed) {
+                if (cudaFuncSetAttribute(gemm_tcgen05_kernel<MODE, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) !=
+                    cudaSuccess) {
+                    cudaGetLastError();
+                    FERRIS_REFUSE("gemm: clusters of %u CTAs are not allowed here", cluster_z);
+                }
+                allowed = true;
+            }
+            e = ferris_launch_cluster(gemm_tcgen05_kernel<MODE, true>, grid, dim3(THREADS), smem, s, cluster_z, mw, mx, p);
+        } else {
+            FERRIS_REFUSE("gemm: a K split of %u in mode %d", cluster_z, MODE);
+        }
+    } else if (cluster_z > 1)
         e = ferris_launch_cluster(gemm_tcgen05_kernel<MODE>, grid, dim3(THREADS), smem, s, cluster_z, mw, mx, p);
     else
         e = ferris_launch(gemm_tcgen05_kernel<MODE>, grid, dim3(THREADS), smem, s, mw, mx, p);
@@ -1266,7 +1297,9 @@ FERRIS_API int ferris_gemm_tcgen05_plan(int T, int N, int K, int accumulators, i
     // while the SMs would lack CTAs even with the deepest K split.
     const int n_tiles = (N + BLOCK_N - 1) / BLOCK_N;
     const int kblocks = (K + BLOCK_K - 1) / BLOCK_K;
-    const int most = kblocks >= 4 ? (kblocks / 2 < 8 ? kblocks / 2 : 8) : 1;  // a cluster has at most 8 CTAs
+    // a cluster has at most 16 CTAs (8 is the portable size; active_clusters tells whether more are to be had)
+    const int widest = (ferris_gemm_cluster_enabled() && accumulators != 2) ? max_split() : 8;
+    const int most = kblocks >= 4 ? (kblocks / 2 < widest ? kblocks / 2 : widest) : 1;
     int bt;
     if (T <= 128) {
         // One token tile: a tcgen05.mma costs about the same ~100 cycles for any width up to 128 (measured), so a

@@ -1189,17 +1189,19 @@ int g_active_clusters[17] = {};
 int active_clusters(int size) {
     if (size < 1 || size > 16) return 0;
     if (size == 1) return g_sms;
-    if (g_active_clusters[size] != 0) return g_active_clusters[size] > 0 ? g_active_clusters[size] : g_sms / size;
-    g_active_clusters[size] = -1;  // unknown: assume perfect packing
+    // no answer: perfect packing is assumed up to the portable size, and no cluster at all beyond it
+    const int unknown = size > 8 ? 0 : g_sms / size;
+    if (g_active_clusters[size] != 0) return g_active_clusters[size] > 0 ? g_active_clusters[size] : unknown;
+    g_active_clusters[size] = -1;
     auto kernel = gemm_tcgen05_kernel<ACCUM_F32, true>;
     const int smem = 200 * 1024;
     if (ferris_allow_dynamic_smem((const void*)kernel, smem) != FERRIS_OK) {  // only ever raises the allowance
         cudaGetLastError();
-        return g_sms / size;
+        return unknown;
     }
     if (size > 8 && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
         cudaGetLastError();
-        return g_sms / size;
+        return unknown;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1, 1, size);
@@ -1215,7 +1217,7 @@ int active_clusters(int size) {
     int clusters = 0;
     if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg) != cudaSuccess || clusters <= 0) {
         cudaGetLastError();
-        return g_sms / size;
+        return unknown;
     }
     g_active_clusters[size] = clusters;
     return clusters;

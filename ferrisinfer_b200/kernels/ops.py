@@ -251,6 +251,14 @@ def gemm_tcgen05(x, w, bias, out, mode: int, n_out: Optional[int] = None, up_row
     )
 
 
+def gemm_plan(tokens: int, outputs: int, k: int, accumulators: int = 1) -> tuple[int, int]:
+    """How the short-step tcgen05 kernel would cut a product: (token tile, K splits)."""
+    bt, splits, floats, counters = _c_int(), _c_int(), ctypes.c_longlong(), _c_int()
+    _lib().ferris_gemm_tcgen05_plan(_c_int(tokens), _c_int(outputs), _c_int(k), _c_int(accumulators), ctypes.byref(bt),
+                                    ctypes.byref(splits), ctypes.byref(floats), ctypes.byref(counters))
+    return bt.value, splits.value
+
+
 def gemm_argmax(x, w, out_token, out_prob, scratch):
     """out_token[t] = the lowest index among the greatest of (x w^T)[t, :], out_prob[t] = its softmax probability
     (may be None): the output head of rows that all take their greatest logit, on the tcgen05 tensor cores, without

@@ -104,8 +104,28 @@ def test_gemm_rows_do_not_depend_on_the_batch(device):
 TC_SHAPES = [(1, 1152, 896), (8, 1152, 896), (64, 896, 4864), (5, 130, 72), (16, 128, 64), (17, 300, 1000),
              (300, 256, 128), (2048, 384, 256), (33, 1000, 80), (257, 129, 200),
              (8, 3584, 18944), (8, 4608, 3584),  # K splits whose clusters do not pack evenly into GPCs
+             (32, 1536, 8960), (100, 1536, 1536),  # few tiles and a long K: clusters of more than 8 CTAs
              # long steps whose tiles are 224, 192 and 160 weight rows wide (one round of CTAs instead of two)
              (4096, 896, 256), (2048, 1536, 192), (1024, 3584, 128), (2048, 1200, 72)]
+
+
+def test_few_tiles_with_a_long_k_are_split_beyond_the_portable_cluster_size(device):
+    """The down projection of a step of 17 to 127 tokens: 7 tiles of 128 rows would leave most SMs idle with 8 K
+    splits; where the GPU holds enough clusters of 16 CTAs at once the plan uses them (TC_SHAPES runs such shapes
+    through every epilogue, twice for equality)."""
+    from ferrisinfer_b200.kernels import ops
+
+    ops.require_device()
+    for T, N, K in [(64, 896, 4864), (32, 1536, 8960), (100, 1536, 1536)]:
+        bt, splits = ops.gemm_plan(T, N, K)
+        tiles = (N + 127) // 128
+        assert bt == (T + 15) // 16 * 16 and 1 <= splits <= 16
+        assert tiles * splits <= ops.sm_count()
+        assert splits <= (K + 63) // 64 // 2, "at least two K slices a CTA"
+    if ops.sm_count() >= 128:
+        assert ops.gemm_plan(64, 896, 4864)[1] > 8
+    # two accumulators (gate and up) keep to the portable size
+    assert ops.gemm_plan(64, 256, 4864, 2)[1] <= 8
 
 
 def _gemm_reference(x, w, bias=None):

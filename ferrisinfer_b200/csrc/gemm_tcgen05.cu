@@ -480,7 +480,60 @@ __global__ void __launch_bounds__(THREADS)
         FERRIS_TL_MARK(tl_mark, 2);  // partial in shared memory
         cluster_sync();
         FERRIS_TL_MARK(tl_mark, 3);  // all partials of the cluster in place
-        if (warp >= 2) {
+        const bool by_four = (p.ldo & 3) == 0 && (p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+        if (warp >= 2 && by_four) {
+            // A warp takes a token (the tokens rank, rank + splits, ... of the tile, the eight warps in turn), a lane
+            // four weight rows of it: a quarter of the requests to the peers' shared memory, 16-byte reads and writes of
+            // the output rows.
+            const int e = warp - 2, rank = (int)cluster_ctarank();
+            const int n4 = n0 + lane * 4;
+            const uint32_t part = smem_u32(smem + (size_t)p.stages * stage_bytes);
+            float bias4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (p.bias && n4 < p.N) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) bias4[c] = p.bias[n4 + c];
+            }
+            for (int tl = rank + e * p.splits; tl < p.bt; tl += 8 * p.splits) {
+                const int t = t0 + tl;
+                if (t >= p.T) break;
+                if (n4 >= p.N) continue;
+                float4 old = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (MODE == ACCUM_F32) old = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.out) + (size_t)t * p.ldo + n4);
+                const uint32_t addr = part + (uint32_t)((tl * BLOCK_N + lane * 4) * 4);
+                float a[4] = {0.0f, 0.0f, 0.0f, 0.0f}, b[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int s0 = 0; s0 < (WIDE ? 16 : 8); s0 += 8) {
+                    float4 v[8];
+#pragma unroll
+                    for (int sp = 0; sp < 8; ++sp)
+                        v[sp] = s0 + sp < p.splits ? ld_peer_shared_f32x4(addr, s0 + sp) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                    for (int sp = 0; sp < 8; ++sp) a[0] += v[sp].x, a[1] += v[sp].y, a[2] += v[sp].z, a[3] += v[sp].w;
+                    if (ACCS == 2) {
+#pragma unroll
+                        for (int sp = 0; sp < 8; ++sp)
+                            v[sp] = s0 + sp < p.splits ? ld_peer_shared_f32x4(addr + (uint32_t)(p.bt * BLOCK_N * 4), s0 + sp)
+                                                       : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                        for (int sp = 0; sp < 8; ++sp) b[0] += v[sp].x, b[1] += v[sp].y, b[2] += v[sp].z, b[3] += v[sp].w;
+                    }
+                }
+                if (MODE == ACCUM_F32) {
+                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)t * p.ldo + n4) =
+                        make_float4(old.x + (a[0] + bias4[0]), old.y + (a[1] + bias4[1]), old.z + (a[2] + bias4[2]),
+                                    old.w + (a[3] + bias4[3]));
+                } else if (MODE == STORE_F32) {
+                    *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)t * p.ldo + n4) =
+                        make_float4(a[0] + bias4[0], a[1] + bias4[1], a[2] + bias4[2], a[3] + bias4[3]);
+                } else {
+                    float y[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) y[c] = MODE == SWIGLU_BF16 ? silu_mul(a[c], b[c]) : a[c] + bias4[c];
+                    *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p.out) + (size_t)t * p.ldo + n4) =
+                        make_uint2(pack_bf16(y[0], y[1]), pack_bf16(y[2], y[3]));
+                }
+            }
+        } else if (warp >= 2) {
             const int quarter = warp & 3, half = (warp - 2) >> 2;
             const int n = n0 + quarter * 32 + lane;
             const float bias_v = (p.bias && n < p.N) ? p.bias[n] : 0.0f;

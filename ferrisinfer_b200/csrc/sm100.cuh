@@ -94,6 +94,18 @@ __device__ __forceinline__ float ld_peer_shared_f32(uint32_t addr, uint32_t rank
     return v;
 }
 
+// Four consecutive fp32 at shared address `addr` (16-byte aligned) in the shared memory of CTA `rank`.
+__device__ __forceinline__ float4 ld_peer_shared_f32x4(uint32_t addr, uint32_t rank) {
+    uint32_t remote;
+    float4 v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(remote)
+                 : "memory");
+    return v;
+}
+
 // The barrier in two halves, for every thread on its own (no warp has to be converged): a thread arrives once and
 // waits once per phase, in that order.
 __device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed;" ::: "memory"); }
